@@ -1,0 +1,5 @@
+from .engine import CheckpointEngine
+from .hf import HFCheckpointEngine
+from .sharded import DSCheckpointEngine
+
+__all__ = ["CheckpointEngine", "HFCheckpointEngine", "DSCheckpointEngine"]

@@ -1,0 +1,71 @@
+"""Hugging Face export checkpoints (recipe name ``huggingface``).
+
+Writes ``output_dir/global_step_<N>/{config.json, model.safetensors | model-0000i-of-0000N.safetensors +
+model.safetensors.index.json, tokenizer files}``.  Parity: arctic_training/checkpoint/hf_engine.py:28-161.
+Under ZeRO-3 the parameters are gathered one unit (decoder layer) at a time — every rank takes part in the
+gathers, rank 0 streams tensors into shards of bounded size — so the full model is never resident on one
+GPU.  With PEFT only trainable tensors are written.  Loading is not supported (resume uses the sharded
+engine), as in the reference.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+
+import torch
+
+from ..logging import logger
+from ..models.hf_io import ShardedSafetensorsWriter
+from ..models.hf_io import native_to_hf
+from ..models.hf_io import save_config
+from .engine import CheckpointEngine
+
+
+class HFCheckpointEngine(CheckpointEngine):
+    name = "huggingface"
+    max_shard_bytes = 4 << 30
+
+    @property
+    def latest_checkpoint_exists(self) -> bool:
+        return False
+
+    def _export_filter(self, model_module: torch.nn.Module):
+        if getattr(self.trainer.config.model, "peft_config", None):
+            trainable = {n for n, p in model_module.named_parameters() if p.requires_grad}
+            return lambda name: name in trainable
+        return lambda name: True
+
+    def save(self, model) -> None:
+        out_dir = self.checkpoint_dir
+        module = model.module if hasattr(model, "module") else model
+        cfg = getattr(module, "config", None)
+        is_main = self.global_rank == 0
+        keep = self._export_filter(module)
+        writer = ShardedSafetensorsWriter(out_dir, self.max_shard_bytes) if is_main else None
+        arch = cfg if isinstance(cfg, dict) else None
+        if hasattr(model, "iter_full_named_parameters"):
+            named = model.iter_full_named_parameters()
+        else:
+            named = ((n, p.data) for n, p in module.named_parameters())
+        for name, tensor in named:
+            if not keep(name) or writer is None:
+                continue
+            items = native_to_hf(name, tensor, arch) if arch is not None else [(name, tensor)]
+            for hf_name, t in items:
+                writer.add(hf_name, t)
+        if is_main:
+            writer.finish()
+            if arch is not None:
+                save_config(arch, out_dir, dtype=next(module.parameters()).dtype)
+            elif cfg is not None and hasattr(cfg, "save_pretrained"):
+                cfg.save_pretrained(out_dir)
+            tok = getattr(self.trainer, "tokenizer", None)
+            if tok is not None and hasattr(tok, "save_pretrained"):
+                tok.save_pretrained(out_dir)
+            logger.info(f"saved Hugging Face checkpoint to {out_dir}")
+        from ..comm import dist as cdist
+
+        cdist.barrier()
+
+    def load(self, model: Any) -> None:
+        raise NotImplementedError("the Hugging Face engine exports only; resume with the sharded engine")

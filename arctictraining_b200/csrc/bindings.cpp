@@ -1,0 +1,44 @@
+// Operator registration: every kernel of the library is reachable as torch.ops.atb200.<name>.
+#include <ATen/ATen.h>
+#include <torch/library.h>
+
+#include <tuple>
+
+namespace atb {
+std::tuple<at::Tensor, at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Tensor& w, double eps);
+std::tuple<at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::Tensor& x, const at::Tensor& w,
+                                               const at::Tensor& rstd);
+void rope_inplace(at::Tensor x, const at::Tensor& cosb, const at::Tensor& sinb, bool inverse);
+at::Tensor swiglu_fwd(const at::Tensor& gu);
+at::Tensor swiglu_bwd(const at::Tensor& dout, const at::Tensor& gu);
+void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,
+                const c10::optional<at::Tensor>& out_lp, double lr, double beta1, double beta2, double eps, double wd,
+                int64_t step, const c10::optional<at::Tensor>& grad_scale);
+at::Tensor sumsq(const at::Tensor& x);
+void accum_bf16(const at::Tensor& src, at::Tensor acc, double scale, bool overwrite);
+std::tuple<at::Tensor, at::Tensor> ce_fwd_bwd(at::Tensor logits, const at::Tensor& labels,
+                                              const c10::optional<at::Tensor>& grad_scale,
+                                              const c10::optional<at::Tensor>& row_scale, bool write_grad);
+at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
+                     const c10::optional<at::Tensor>& out, int64_t max_ctas);
+int64_t read_and_clear_error_flag(const at::Tensor& like);
+}  // namespace atb
+
+TORCH_LIBRARY(atb200, m) {
+    m.def("rmsnorm_fwd(Tensor x, Tensor w, float eps) -> (Tensor, Tensor)", &atb::rmsnorm_fwd);
+    m.def("rmsnorm_bwd(Tensor dy, Tensor x, Tensor w, Tensor rstd) -> (Tensor, Tensor)", &atb::rmsnorm_bwd);
+    m.def("rope_inplace(Tensor(a!) x, Tensor cos, Tensor sin, bool inverse) -> ()", &atb::rope_inplace);
+    m.def("swiglu_fwd(Tensor gu) -> Tensor", &atb::swiglu_fwd);
+    m.def("swiglu_bwd(Tensor dout, Tensor gu) -> Tensor", &atb::swiglu_bwd);
+    m.def(
+        "adamw_step(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor? out_lp, float lr, float beta1, "
+        "float beta2, float eps, float wd, int step, Tensor? grad_scale) -> ()",
+        &atb::adamw_step);
+    m.def("sumsq(Tensor x) -> Tensor", &atb::sumsq);
+    m.def("accum_bf16(Tensor src, Tensor(a!) acc, float scale, bool overwrite) -> ()", &atb::accum_bf16);
+    m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor labels, Tensor? grad_scale, Tensor? row_scale, bool write_grad) -> (Tensor, Tensor)",
+          &atb::ce_fwd_bwd);
+    m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas) -> Tensor",
+          &atb::gemm_bf16);
+    m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);
+}

@@ -1,0 +1,420 @@
+// bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with fp32 accumulators in TMEM,
+// persistent warp-specialised CTAs (one per SM) and a double-buffered accumulator so that the epilogue
+// of tile i overlaps the main loop of tile i+1.
+//
+//   C[M, N] = op(A) * op(B)^T      A: [M, K] (K contiguous) or [K, M] (M contiguous, "MN-major")
+//                                  B: [N, K] (K contiguous) or [K, N] (N contiguous, "MN-major")
+//
+// so one kernel serves the forward (x W^T), the data gradient (dY W) and the weight gradient (dY^T X)
+// of a linear layer.  Epilogues: plain store, accumulate into C, SwiGLU on block-interleaved gate/up
+// columns (64 gate columns followed by their 64 up columns).
+//
+// Roles inside a CTA of 192 threads: warp 0 = TMA producer (one elected lane), warp 1 = MMA issuer
+// (one elected lane; also owns TMEM allocation), warps 2..5 = epilogue (TMEM -> registers -> global).
+// Every barrier wait is bounded; on a timeout the CTA records an error code, drains, frees TMEM and
+// returns, so a logic error can not hang the device.
+//
+// The reference has no GEMM of its own: dense layers go to cuBLAS through nn.Linear and the grouped
+// expert GEMM is a Triton kernel (arctic_training/model/moe/moe_gemm.py:36-166).
+
+#include "common.cuh"
+#include "ptx_sm100.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace atb {
+
+namespace {
+
+constexpr int BM = 128;
+constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+
+template <int BN, int STAGES>
+struct SmemLayout {
+    static constexpr int kABytes = BM * BK * 2;
+    static constexpr int kBBytes = BN * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierOffset = STAGES * kStageBytes;
+    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
+    static constexpr int kTotal = kBarrierOffset + (2 * STAGES + 4) * 8 + 16;
+};
+
+struct GemmParams {
+    bf16* C;
+    int M, N, K;
+    int64_t ldc;
+    int* error_flag;  // device int: 0 ok, otherwise (role << 8) | reason
+};
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                         const GemmParams p) {
+    using L = SmemLayout<BN, STAGES>;
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    // dynamic shared memory is only guaranteed 16-byte aligned: round up to the 1024 bytes that the
+    // 128-byte swizzle pattern needs (the launch reserves the slack).
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full = empty_bar + STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+
+    const int tiles_m = (p.M + BM - 1) / BM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (p.K + BK - 1) / BK;
+    constexpr int GROUP_M = 8;
+    constexpr uint32_t TMEM_COLS = 2 * BN;  // 512 for BN=256, 256 for BN=128
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 1);
+            ptx::mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&tmem_full[a], 1);
+            ptx::mbar_init(&tmem_empty[a], 4);  // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    auto tile_coords = [&](int t, int& tm, int& tn) {
+        const int per_group = GROUP_M * tiles_n;
+        const int g = t / per_group;
+        const int first_m = g * GROUP_M;
+        const int gsz = min(GROUP_M, tiles_m - first_m);
+        const int r = t - g * per_group;
+        tm = first_m + (r % gsz);
+        tn = r / gsz;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer
+        if (lane == 0) {
+            ptx::tma_prefetch_desc(&tmap_a);
+            ptx::tma_prefetch_desc(&tmap_b);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                int tm, tn;
+                tile_coords(t, tm, tn);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, kWaitLimitNs)) {
+                        atomicCAS(p.error_flag, 0, (1 << 8) | 1);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + stage * L::kStageBytes;
+                    uint8_t* sb = sa + L::kABytes;
+                    ptx::mbar_expect_tx(&full_bar[stage], L::kStageBytes);
+                    if constexpr (!A_MN) {
+                        ptx::tma_load_2d(sa, &tmap_a, kb * BK, tm * BM, &full_bar[stage]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BM / 64; ++c)
+                            ptx::tma_load_2d(sa + c * (BK * 128), &tmap_a, tm * BM + c * 64, kb * BK, &full_bar[stage]);
+                    }
+                    if constexpr (!B_MN) {
+                        ptx::tma_load_2d(sb, &tmap_b, kb * BK, tn * BN, &full_bar[stage]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < BN / 64; ++c)
+                            ptx::tma_load_2d(sb + c * (BK * 128), &tmap_b, tn * BN + c * 64, kb * BK, &full_bar[stage]);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+            if (!ok) {
+                // copies already issued still land in this CTA's shared memory: wait for them (bounded)
+                // before the CTA is allowed to retire.
+                for (int s = 0; s < STAGES; ++s) {
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while (!ptx::mbar_try_wait(&full_bar[s], 0) && !ptx::mbar_try_wait(&full_bar[s], 1)) {
+                        if (ptx::globaltimer_ns() - t0 > 100000000ull) break;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(BM, BN, A_MN, B_MN);
+            // K-major operand: rows of 128 bytes, 8-row groups 1024 bytes apart; one UMMA_K step = 32 bytes.
+            // MN-major operand: chunks of 64 (MN) x BK (K) elements, 128 bytes per K row, 8-K groups 1024
+            // bytes apart, chunks BK*128 bytes apart; one UMMA_K step = 16 rows = 2048 bytes.
+            constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, B_LBO = B_MN ? BK * 128 : 16;
+            constexpr uint32_t A_KSTEP = A_MN ? UMMA_K * 128 : UMMA_K * 2, B_KSTEP = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_phase[2] = {0, 0};
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+                const int acc = it & 1;
+                if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase[acc] ^ 1u, abort_flag, kWaitLimitNs)) {
+                    atomicCAS(p.error_flag, 0, (2 << 8) | 1);
+                    ok = false;
+                    break;
+                }
+                acc_phase[acc] ^= 1u;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * BN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, abort_flag, kWaitLimitNs)) {
+                        atomicCAS(p.error_flag, 0, (2 << 8) | 2);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ptx::smem_u32(smem + stage * L::kStageBytes);
+                    const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = ptx::make_smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024);
+                        const uint64_t db = ptx::make_smem_desc_sw128(sb + k * B_KSTEP, B_LBO, 1024);
+                        ptx::mma_bf16_ss(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::mma_commit(&empty_bar[stage]);  // releases the smem slot once these MMAs retire
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) ptx::mma_commit(&tmem_full[acc]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5)
+        const int quarter = warp & 3;  // TMEM lanes [32*quarter, 32*quarter + 32) are visible to this warp
+        uint32_t acc_phase[2] = {0, 0};
+        int it = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            const int acc = it & 1;
+            int tm, tn;
+            tile_coords(t, tm, tn);
+            if (!ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase[acc], abort_flag, kWaitLimitNs)) {
+                if (lane == 0) atomicCAS(p.error_flag, 0, (3 << 8) | 1);
+                ok = false;
+                break;
+            }
+            acc_phase[acc] ^= 1u;
+            ptx::tc_fence_after();
+            const int row = tm * BM + quarter * 32 + lane;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
+            if constexpr (EPI == EPI_SWIGLU) {
+                // columns [128g, 128g+64) gate, [128g+64, 128g+128) up  ->  output columns [64g, 64g+64)
+                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * (BN / 2);
+#pragma unroll 1
+                for (int g = 0; g < BN / 128; ++g) {
+#pragma unroll 1
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t rg[32], ru[32];
+                        ptx::tmem_ld_32x32b_x32(taddr + g * 128 + h * 32, rg);
+                        ptx::tmem_ld_32x32b_x32(taddr + g * 128 + 64 + h * 32, ru);
+                        ptx::tmem_ld_wait();
+                        const int col0 = tn * (BN / 2) + g * 64 + h * 32;
+                        if (row < p.M && col0 < p.N / 2) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                float o[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const float gg = __uint_as_float(rg[v * 8 + j]);
+                                    const float uu = __uint_as_float(ru[v * 8 + j]);
+                                    o[j] = gg / (1.f + __expf(-gg)) * uu;
+                                }
+                                *reinterpret_cast<bf16x8*>(crow + g * 64 + h * 32 + v * 8) = pack8(o);
+                            }
+                        }
+                    }
+                }
+            } else {
+                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * BN;
+#pragma unroll 1
+                for (int c = 0; c < BN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    const int col0 = tn * BN + c * 32;
+                    if (row < p.M) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            if (col0 + v * 8 < p.N) {  // N is a multiple of 8 (checked on the host)
+                                float o[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(r[v * 8 + j]);
+                                bf16x8* dst = reinterpret_cast<bf16x8*>(crow + c * 32 + v * 8);
+                                if constexpr (EPI == EPI_ACCUM) {
+                                    float old[8];
+                                    unpack8(*dst, old);
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) o[j] += old[j];
+                                }
+                                *dst = pack8(o);
+                            }
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&tmem_empty[acc]);
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+
+PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
+    static PFN_cuTensorMapEncodeTiled_v12000 fn = [] {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult qres;
+        cudaError_t err = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres);
+        TORCH_CHECK(err == cudaSuccess && qres == cudaDriverEntryPointSuccess && ptr != nullptr,
+                    "cuTensorMapEncodeTiled is not available from the driver");
+        return reinterpret_cast<PFN_cuTensorMapEncodeTiled_v12000>(ptr);
+    }();
+    return fn;
+}
+
+// 2-D bf16 tensor map over a row-major [rows, cols] matrix with leading dimension `ld` (elements),
+// box = [box_rows, 64 columns], 128-byte swizzle.
+CUtensorMap make_tmap_bf16(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA: base address must be 16-byte aligned");
+    TORCH_CHECK((ld * 2) % 16 == 0, "TMA: row pitch must be a multiple of 16 bytes");
+    CUtensorMap tm;
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = get_encode_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box,
+                                 estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                 CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+    return tm;
+}
+
+at::Tensor& error_flag_for(const at::Device& dev) {
+    static std::vector<at::Tensor> flags(64);
+    auto& f = flags[dev.index() < 0 ? 0 : dev.index()];
+    if (!f.defined()) f = at::zeros({1}, at::TensorOptions().dtype(at::kInt).device(dev));
+    return f;
+}
+
+template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
+void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas) {
+    using L = SmemLayout<BN, STAGES>;
+    auto kernel = gemm_bf16_tcgen05_kernel<BN, STAGES, A_MN, B_MN, EPI>;
+    constexpr int smem_bytes = L::kTotal + 1024;  // slack for the 1024-byte round-up
+    static bool attr_set = false;
+    if (!attr_set) {
+        C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        attr_set = true;
+    }
+    const int tiles = (int)(ceil_div(p.M, BM) * ceil_div(p.N, BN));
+    const int grid = std::max(1, std::min(tiles, max_ctas));
+    kernel<<<grid, 192, smem_bytes, current_stream()>>>(ta, tb, p);
+    ATB_LAUNCH_CHECK();
+}
+
+template <bool A_MN, bool B_MN>
+void dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas) {
+    switch (epi) {
+        case EPI_STORE: launch_gemm<256, 4, A_MN, B_MN, EPI_STORE>(ta, tb, p, max_ctas); break;
+        case EPI_ACCUM: launch_gemm<256, 4, A_MN, B_MN, EPI_ACCUM>(ta, tb, p, max_ctas); break;
+        case EPI_SWIGLU:
+            if constexpr (!A_MN && !B_MN) { launch_gemm<256, 4, false, false, EPI_SWIGLU>(ta, tb, p, max_ctas); break; }
+        default: TORCH_CHECK(false, "gemm: unsupported epilogue ", epi, " for this operand layout");
+    }
+}
+
+}  // namespace
+
+// out = gemm(a, b).  a_mn == false: a is [M, K]; true: a is [K, M].  b_mn == false: b is [N, K]; true: [K, N].
+// epilogue: 0 store, 1 accumulate into `out`, 2 SwiGLU (out is [M, N/2]).
+at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
+                     const c10::optional<at::Tensor>& out_opt, int64_t max_ctas) {
+    ATB_CHECK_CUDA(a); ATB_CHECK_CUDA(b);
+    ATB_CHECK_DTYPE(a, at::kBFloat16); ATB_CHECK_DTYPE(b, at::kBFloat16);
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm: operands must be 2-D");
+    TORCH_CHECK(a.stride(1) == 1 && b.stride(1) == 1, "gemm: operands must have a unit inner stride");
+    const int64_t M = a_mn ? a.size(1) : a.size(0);
+    const int64_t K = a_mn ? a.size(0) : a.size(1);
+    const int64_t N = b_mn ? b.size(1) : b.size(0);
+    const int64_t Kb = b_mn ? b.size(0) : b.size(1);
+    TORCH_CHECK(K == Kb, "gemm: contraction sizes differ (", K, " vs ", Kb, ")");
+    TORCH_CHECK(M > 0 && N > 0 && K > 0, "gemm: empty operand");
+    TORCH_CHECK(N % 8 == 0, "gemm: N must be a multiple of 8");
+    TORCH_CHECK(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm: dimension too large");
+    const int epi = (int)epilogue;
+    if (epi == EPI_SWIGLU) TORCH_CHECK(N % 128 == 0, "gemm: SwiGLU epilogue needs N to be a multiple of 128");
+    c10::cuda::CUDAGuard guard(a.device());
+
+    const int64_t out_cols = epi == EPI_SWIGLU ? N / 2 : N;
+    at::Tensor out;
+    if (out_opt.has_value()) {
+        out = *out_opt;
+        ATB_CHECK_DTYPE(out, at::kBFloat16);
+        TORCH_CHECK(out.dim() == 2 && out.size(0) == M && out.size(1) == out_cols && out.stride(1) == 1,
+                    "gemm: output has the wrong shape");
+        TORCH_CHECK(out.stride(0) % 8 == 0, "gemm: output pitch must be a multiple of 8 elements");
+    } else {
+        TORCH_CHECK(epi != EPI_ACCUM, "gemm: accumulate epilogue needs an output tensor");
+        out = at::empty({M, out_cols}, a.options());
+    }
+    ATB_CHECK_ALIGNED16(out);
+
+    // tensor maps: K-major operand [rows, K] -> box [tile rows, 64 k]; MN-major [K, rows] -> box [64 k, 64 rows]
+    const CUtensorMap ta = a_mn ? make_tmap_bf16(a.data_ptr(), K, M, a.stride(0), BK)
+                                : make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
+    const CUtensorMap tb = b_mn ? make_tmap_bf16(b.data_ptr(), K, N, b.stride(0), BK)
+                                : make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), 256);
+    if (a_mn) TORCH_CHECK(M % 8 == 0, "gemm: MN-major A needs M to be a multiple of 8");
+
+    GemmParams p;
+    p.C = (bf16*)out.data_ptr();
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.ldc = out.stride(0);
+    p.error_flag = error_flag_for(a.device()).data_ptr<int>();
+    const int ctas = max_ctas > 0 ? (int)max_ctas : kNumSMs;
+    if (!a_mn && !b_mn) dispatch_epi<false, false>(epi, ta, tb, p, ctas);
+    else if (!a_mn && b_mn) dispatch_epi<false, true>(epi, ta, tb, p, ctas);
+    else if (a_mn && !b_mn) dispatch_epi<true, false>(epi, ta, tb, p, ctas);
+    else dispatch_epi<true, true>(epi, ta, tb, p, ctas);
+    return out;
+}
+
+// Reads and clears the per-device error word written by kernels whose bounded waits gave up.
+int64_t read_and_clear_error_flag(const at::Tensor& like) {
+    auto& f = error_flag_for(like.device());
+    const int64_t v = f.item<int>();
+    if (v != 0) f.zero_();
+    return v;
+}
+
+}  // namespace atb

@@ -1,0 +1,5 @@
+from .config import EngineConfig
+from .engine import TrainingEngine
+from .engine import initialize
+
+__all__ = ["EngineConfig", "TrainingEngine", "initialize"]

@@ -1,0 +1,74 @@
+"""Typed view of the engine section of a recipe (the ``deepspeed:`` dict of the reference's YAML).
+
+Keys understood (same spelling as the recipes of the reference, arctic_training/config/trainer.py:395-440
+and projects/sequence-parallelism/*.yml): ``zero_optimization.{stage, offload_optimizer.{device,ratio},
+offload_param.device, reduce_bucket_size, stage3_*}``, ``bf16|bfloat16.{enabled,
+bf16_master_weights_and_grads, bf16_optimizer_states}``, ``fp16.enabled``, ``torch_autocast.{enabled,
+dtype}``, ``gradient_clipping``, ``prescale_gradients``, ``gradient_accumulation_steps``,
+``wall_clock_breakdown``, ``communication_data_type``, ``seq_parallel_communication_data_type``.
+Own extension: ``fused_comm`` = ``auto`` | ``off`` (peer-memory kernels vs NCCL-only).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from dataclasses import field
+from typing import Any
+from typing import Dict
+from typing import Optional
+
+import torch
+
+
+@dataclass
+class EngineConfig:
+    zero_stage: int = 0
+    gradient_accumulation_steps: int = 1
+    gradient_clipping: float = 1.0
+    micro_batch_size: int = 1
+    sequence_parallel_size: int = 1
+    bf16: bool = False
+    fp16: bool = False
+    bf16_master_weights_and_grads: bool = False
+    bf16_optimizer_states: bool = False
+    autocast: bool = False
+    autocast_dtype: torch.dtype = torch.bfloat16
+    offload_optimizer: bool = False
+    offload_optimizer_ratio: float = 1.0
+    offload_param: bool = False
+    wall_clock_breakdown: bool = False
+    fused_comm: str = "auto"
+    activation_checkpoint_cpu_offload: bool = False
+    raw: Dict[str, Any] = field(default_factory=dict)
+
+    @classmethod
+    def from_dict(cls, d: Optional[Dict[str, Any]]) -> "EngineConfig":
+        d = dict(d or {})
+        zo = d.get("zero_optimization", {}) or {}
+        bf = d.get("bfloat16", d.get("bf16", {})) or {}
+        fp = d.get("fp16", {}) or {}
+        ac = d.get("torch_autocast", {}) or {}
+        off_o = zo.get("offload_optimizer", {}) or {}
+        off_p = zo.get("offload_param", {}) or {}
+        dt = str(ac.get("dtype", "bfloat16")).replace("torch.", "")
+        return cls(
+            zero_stage=int(zo.get("stage", 0)),
+            gradient_accumulation_steps=int(d.get("gradient_accumulation_steps", 1)),
+            gradient_clipping=float(d.get("gradient_clipping", 0.0) or 0.0),
+            micro_batch_size=int(d.get("train_micro_batch_size_per_gpu", 1)),
+            sequence_parallel_size=int(d.get("sequence_parallel_size", 1)),
+            bf16=bool(bf.get("enabled", False)),
+            fp16=bool(fp.get("enabled", False)),
+            bf16_master_weights_and_grads=bool(bf.get("bf16_master_weights_and_grads", False)),
+            bf16_optimizer_states=bool(bf.get("bf16_optimizer_states", False)),
+            autocast=bool(ac.get("enabled", False)),
+            autocast_dtype={"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float16": torch.float16,
+                            "fp16": torch.float16, "float32": torch.float32}.get(dt, torch.bfloat16),
+            offload_optimizer=str(off_o.get("device", "none")).lower() == "cpu",
+            offload_optimizer_ratio=float(off_o.get("ratio", 1.0)),
+            offload_param=str(off_p.get("device", "none")).lower() == "cpu",
+            wall_clock_breakdown=bool(d.get("wall_clock_breakdown", False)),
+            fused_comm=str(d.get("fused_comm", "auto")),
+            activation_checkpoint_cpu_offload=bool(d.get("activation_checkpoint_cpu_offload", False)),
+            raw=d,
+        )

@@ -1,0 +1,854 @@
+"""The training engine: flat-buffer ZeRO stages 0-3, mixed precision, gradient accumulation and
+clipping, per-layer activation checkpointing with optional host offload, and sharded checkpoints.
+
+It takes the place of the external engine the reference drives through ``deepspeed.initialize``
+(arctic_training/trainer/trainer.py:315-322) and offers the same surface to trainers and checkpoint
+engines: ``backward(loss)``, ``step()``, ``global_steps``, ``is_gradient_accumulation_boundary()``,
+``save_checkpoint`` / ``load_checkpoint``, ``module``, ``lr_scheduler``, ``get_global_grad_norm()``,
+``zero_optimization_stage()``, ``get_wall_clock_timers()``.
+
+Design
+------
+* The model is cut into *units* (one per decoder layer, plus embedding and head).  All parameters of a
+  unit live in one flat low-precision buffer; ``param.data`` are views into it.  The trainable prefix of
+  each unit is covered by fp32 master / Adam state shards (1/world of the unit per rank for stage >= 1).
+* Stage 3 keeps only the shard resident.  Checkpointed units are gathered into one of a few pooled
+  full-size buffers right before they run (forward, and again for recompute + backward) with the next
+  unit prefetched on a communication stream; small or non-checkpointed units stay gathered.
+* Backward of a unit writes into a pooled flat gradient buffer which is then reduced (reduce-scatter
+  for stage >= 1, all-reduce for stage 0) on the communication stream and accumulated into the fp32
+  gradient shard while earlier layers are still computing.
+* The optimizer only ever sees flat fp32 views (one per unit and weight-decay group), so any
+  ``torch.optim.Optimizer`` works; with the framework's fused AdamW the update, the clip factor and
+  the low-precision parameter write happen in one kernel per view.
+"""
+
+from __future__ import annotations
+
+import math
+import os
+import time
+from contextlib import contextmanager
+from contextlib import nullcontext
+from pathlib import Path
+from typing import Any
+from typing import Callable
+from typing import Dict
+from typing import Iterable
+from typing import List
+from typing import Optional
+from typing import Sequence
+from typing import Tuple
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+
+from .. import ops
+from ..logging import logger
+from .config import EngineConfig
+from .timers import TimerGroup
+
+ALIGN = 256  # elements; keeps every shard 16-byte aligned for fp32 and bf16 vector kernels
+
+
+def _is_cuda(t: torch.Tensor) -> bool:
+    return t.is_cuda
+
+
+class _BufferPool:
+    """A few reusable device buffers with events so that a buffer is not reused while a side stream
+    still reads or writes it."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, device: torch.device, count: int) -> None:
+        self.bufs = [torch.empty(numel, dtype=dtype, device=device) for _ in range(count)]
+        self.free = list(range(count))
+        self.events: List[Optional[torch.cuda.Event]] = [None] * count
+
+    def acquire(self) -> Tuple[int, torch.Tensor]:
+        if not self.free:
+            raise RuntimeError("engine buffer pool exhausted (more units alive than pooled buffers)")
+        idx = self.free.pop(0)
+        ev = self.events[idx]
+        if ev is not None:
+            torch.cuda.current_stream().wait_event(ev)
+            self.events[idx] = None
+        return idx, self.bufs[idx]
+
+    def release(self, idx: int, event: Optional["torch.cuda.Event"] = None) -> None:
+        self.events[idx] = event
+        self.free.append(idx)
+
+
+class ZeroUnit:
+    """One sharding / checkpointing unit: a flat parameter buffer plus optimizer-state shards."""
+
+    def __init__(self, name: str, modules: Sequence[nn.Module], checkpointed: bool, index: int) -> None:
+        self.name = name
+        self.modules = list(modules)
+        self.checkpointed = checkpointed
+        self.index = index
+        self.params: List[nn.Parameter] = []
+        self.param_names: List[str] = []
+        self.offsets: List[int] = []
+        self.numel = 0  # padded
+        self.n_train = 0  # elements of the trainable prefix (unpadded)
+        self.shard_size = 0
+        self.flat: Optional[torch.Tensor] = None  # full low-precision buffer (None while released in stage 3)
+        self.shard: Optional[torch.Tensor] = None  # this rank's slice (persistent in stage 3)
+        self.persistent = True
+        self.pool_slot: Optional[int] = None
+        self.gather_event = None
+        self.grad_flat: Optional[torch.Tensor] = None
+        self.grad_slot: Optional[int] = None
+        self.master: Optional[torch.Tensor] = None
+        self.grad_acc: Optional[torch.Tensor] = None
+        self.grad_acc_valid = False
+        self.runs: List[Tuple[int, int, int]] = []  # (start, end, group) inside the local trainable shard
+        self.group: Optional[dist.ProcessGroup] = None
+        self.group_size = 1
+        self.group_rank = 0
+        self.resident = True
+        self.grad_divisor = 1.0
+
+    @property
+    def train_len(self) -> int:
+        """Length of this rank's part of the trainable prefix."""
+        lo = self.group_rank * self.shard_size
+        return max(0, min(self.n_train - lo, self.shard_size))
+
+
+class TrainingEngine:
+    def __init__(
+        self,
+        model: nn.Module,
+        optimizer: Optional[torch.optim.Optimizer] = None,
+        lr_scheduler: Any = None,
+        config: Optional[Dict[str, Any]] = None,
+        dp_group: Optional[dist.ProcessGroup] = None,
+        expert_dp_group: Optional[dist.ProcessGroup] = None,
+        is_expert_param: Optional[Callable[[str, nn.Parameter], bool]] = None,
+        training: bool = True,
+    ) -> None:
+        self.module = model
+        self.optimizer = optimizer
+        self.lr_scheduler = lr_scheduler
+        self.cfg = EngineConfig.from_dict(config)
+        self.training_mode = training
+        self.device = next(model.parameters()).device
+        self.on_gpu = self.device.type == "cuda"
+        self.dist_on = dist.is_initialized() and dist.get_world_size() > 1
+        self.dp_group = dp_group
+        self.expert_dp_group = expert_dp_group
+        self._is_expert_param = is_expert_param or (lambda n, p: False)
+        self.world = dist.get_world_size(dp_group) if self.dist_on else 1
+        self.rank = dist.get_rank(dp_group) if self.dist_on else 0
+        self.global_rank = dist.get_rank() if dist.is_initialized() else 0
+        self.stage = self.cfg.zero_stage if (training and optimizer is not None) else min(self.cfg.zero_stage, 3)
+        if not training and self.stage in (1, 2):
+            self.stage = 0
+        self.gas = max(1, self.cfg.gradient_accumulation_steps)
+        self.global_steps = 0
+        self.micro_steps = 0
+        self.global_samples = 0
+        self.skipped_steps = 0
+        self._grad_norm: Optional[torch.Tensor] = None
+        self.timers = TimerGroup()
+        self.comm_stream = torch.cuda.Stream(device=self.device) if self.on_gpu else None
+        self.sp_size = max(1, self.cfg.sequence_parallel_size)
+        self._dummy = torch.zeros((), device=self.device, requires_grad=True)
+        self.checkpoint_activations = bool(getattr(model, "activation_checkpointing", True)) and training
+        from .activation import ActivationStore
+
+        self.act_store = ActivationStore(self.device, offload=self.cfg.activation_checkpoint_cpu_offload)
+        self.units: List[ZeroUnit] = []
+        self._build_units()
+        self._layout_units()
+        if training and optimizer is not None:
+            self._attach_optimizer()
+        self._wrap_units()
+        self._native_launches = 0
+
+    # ================================================================== construction
+    def _discover_units(self) -> List[Tuple[str, List[nn.Module], bool]]:
+        m = self.module
+        if hasattr(m, "zero_units"):
+            return list(m.zero_units())
+        best, best_n = None, 0
+        for mod in m.modules():
+            if isinstance(mod, nn.ModuleList) and len(mod) > 1:
+                n = sum(p.numel() for p in mod.parameters())
+                if n > best_n:
+                    best, best_n = mod, n
+        units: List[Tuple[str, List[nn.Module], bool]] = []
+        if best is not None:
+            for i, layer in enumerate(best):
+                units.append((f"layer{i}", [layer], True))
+        units.append(("rest", [m], False))
+        return units
+
+    def _build_units(self) -> None:
+        seen: Dict[int, str] = {}
+        names = {id(p): n for n, p in self.module.named_parameters(remove_duplicate=True)}
+        ckpt_ok = self.checkpoint_activations or not self.training_mode
+        for idx, (name, mods, ckpt) in enumerate(self._discover_units()):
+            unit = ZeroUnit(name, mods, bool(ckpt and ckpt_ok), idx)
+            for mod in mods:
+                for p in mod.parameters():
+                    if id(p) in seen:
+                        continue
+                    seen[id(p)] = name
+                    unit.params.append(p)
+            if not unit.params:
+                unit.checkpointed_only = True
+            expert_flags = {self._is_expert_param(names.get(id(p), ""), p) for p in unit.params}
+            unit.is_expert = expert_flags == {True}
+            if True in expert_flags and False in expert_flags:
+                # split: expert parameters get a unit of their own so they can use their own group
+                exp = ZeroUnit(name + ".experts", [], False, idx)
+                exp.params = [p for p in unit.params if self._is_expert_param(names.get(id(p), ""), p)]
+                exp.is_expert = True
+                exp.attached_to = unit
+                unit.params = [p for p in unit.params if not self._is_expert_param(names.get(id(p), ""), p)]
+                unit.is_expert = False
+                unit.expert_unit = exp
+                self.units.append(unit)
+                self.units.append(exp)
+                continue
+            self.units.append(unit)
+        for i, u in enumerate(self.units):
+            u.index = i
+            u.param_names = [names.get(id(p), f"{u.name}.{j}") for j, p in enumerate(u.params)]
+
+    def _group_index_of(self, p: nn.Parameter) -> int:
+        if self.optimizer is None:
+            return 0
+        return self._param_group.get(id(p), -1)
+
+    def _layout_units(self) -> None:
+        self._param_group: Dict[int, int] = {}
+        if self.optimizer is not None:
+            for gi, g in enumerate(self.optimizer.param_groups):
+                for p in g["params"]:
+                    self._param_group[id(p)] = gi
+        max_pool_numel = 0
+        for u in self.units:
+            if getattr(u, "is_expert", False) and self.expert_dp_group is not None:
+                u.group = self.expert_dp_group
+            else:
+                u.group = self.dp_group
+            u.group_size = dist.get_world_size(u.group) if self.dist_on else 1
+            u.group_rank = dist.get_rank(u.group) if self.dist_on else 0
+            shard_ways = u.group_size if self.stage >= 1 else 1
+            if self.stage == 0:
+                u.group_rank_for_shard = 0
+            trainable = [p for p in u.params if p.requires_grad and self._group_index_of(p) >= 0] if self.optimizer else []
+            trainable.sort(key=lambda p: self._group_index_of(p))
+            frozen = [p for p in u.params if not any(p is q for q in trainable)]
+            ordered = trainable + frozen
+            names = dict(zip(map(id, u.params), u.param_names))
+            u.params = ordered
+            u.param_names = [names[id(p)] for p in ordered]
+            off = 0
+            u.offsets = []
+            for p in ordered:
+                u.offsets.append(off)
+                off += p.numel()
+                off = (off + 7) // 8 * 8  # keep every parameter 16-byte aligned (TMA, vector loads)
+            u.n_train = 0
+            if trainable:
+                u.n_train = u.offsets[len(trainable) - 1] + trainable[-1].numel()
+            gran = ALIGN * shard_ways
+            u.numel = max(gran, (off + gran - 1) // gran * gran)
+            u.shard_size = u.numel // shard_ways
+            if self.stage == 0:
+                u.group_rank = 0  # every rank owns the whole unit
+            dtype = u.params[0].dtype if u.params else torch.float32
+            u.dtype = dtype
+            flat = torch.zeros(u.numel, dtype=dtype, device=self.device)
+            for p, o in zip(ordered, u.offsets):
+                flat[o : o + p.numel()].copy_(p.data.reshape(-1))
+                p.data = flat[o : o + p.numel()].view(p.shape)
+            u.flat = flat
+            lo = u.group_rank * u.shard_size
+            u.persistent = not (self.stage == 3 and u.checkpointed and u.numel >= self._persist_threshold())
+            if self.stage == 3 and not u.persistent:
+                u.shard = flat[lo : lo + u.shard_size].clone()
+                max_pool_numel = max(max_pool_numel, u.numel)
+            else:
+                u.shard = flat[lo : lo + u.shard_size]
+            # runs of the local trainable shard by optimizer group
+            u.runs = []
+            if trainable:
+                for p, o in zip(ordered[: len(trainable)], u.offsets):
+                    s, e = max(o, lo) - lo, min(o + p.numel(), lo + u.shard_size) - lo
+                    if e <= s:
+                        continue
+                    gi = self._group_index_of(p)
+                    if u.runs and u.runs[-1][2] == gi:
+                        u.runs[-1] = (u.runs[-1][0], e, gi)
+                    else:
+                        u.runs.append((s, e, gi))
+            dp_replicas = max(1, (dist.get_world_size() if self.dist_on else 1) // self.sp_size)
+            u.grad_divisor = float(dp_replicas)
+        self._param_pool: Optional[_BufferPool] = None
+        if max_pool_numel:
+            dtype = next(u.dtype for u in self.units if not u.persistent)
+            self._param_pool = _BufferPool(max_pool_numel, dtype, self.device, 3)
+            for u in self.units:
+                if not u.persistent:
+                    self._release_params(u)
+        self._grad_pool: Optional[_BufferPool] = None
+        if self.training_mode and self.optimizer is not None:
+            train_units = [u for u in self.units if u.n_train > 0 and u.checkpointed]
+            if train_units:
+                n = max(u.numel for u in train_units)
+                self._grad_pool = _BufferPool(n, train_units[0].dtype, self.device, 3 if self.on_gpu else 1)
+
+    def _persist_threshold(self) -> int:
+        zo = self.cfg.raw.get("zero_optimization", {}) or {}
+        return int(zo.get("stage3_param_persistence_threshold", 0) or 0)
+
+    def _attach_optimizer(self) -> None:
+        """Replace the optimizer's parameters by flat fp32 views over the local shards."""
+        opt = self.optimizer
+        state_dtype = torch.bfloat16 if self.cfg.bf16_optimizer_states else torch.float32
+        master_dtype = torch.bfloat16 if self.cfg.bf16_master_weights_and_grads else torch.float32
+        opt_dev = torch.device("cpu") if self.cfg.offload_optimizer else self.device
+        new_groups: List[List[torch.Tensor]] = [[] for _ in opt.param_groups]
+        self._views: List[Tuple[ZeroUnit, int, int, int, torch.Tensor]] = []
+        for u in self.units:
+            tl = u.train_len
+            if tl <= 0:
+                continue
+            pad = (tl + 3) // 4 * 4
+            u.master = torch.zeros(pad, dtype=master_dtype, device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
+            u.master[:tl].copy_(u.shard[:tl].to(master_dtype))
+            u.grad_acc = torch.zeros(pad, dtype=torch.float32 if master_dtype == torch.float32 else master_dtype,
+                                     device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
+            for s, e, gi in u.runs:
+                view = u.master[s:e]
+                view._atb_unit = u  # type: ignore[attr-defined]
+                view._atb_range = (s, e)  # type: ignore[attr-defined]
+                view._atb_lp = u.shard[s:e] if opt_dev == self.device and master_dtype == torch.float32 and u.dtype == torch.bfloat16 else None  # type: ignore[attr-defined]
+                view._atb_state_dtype = state_dtype  # type: ignore[attr-defined]
+                new_groups[gi].append(view)
+                self._views.append((u, s, e, gi, view))
+        opt.state.clear()
+        for g, params in zip(opt.param_groups, new_groups):
+            g["params"] = params
+
+    # ================================================================== parameter residency (stage 3)
+    def _assign_param_views(self, u: ZeroUnit, flat: torch.Tensor) -> None:
+        for p, o in zip(u.params, u.offsets):
+            p.data = flat[o : o + p.numel()].view(p.shape)
+
+    def _release_params(self, u: ZeroUnit) -> None:
+        if u.persistent or not u.resident and u.flat is None:
+            return
+        if u.pool_slot is not None:
+            ev = None
+            if self.on_gpu:
+                ev = torch.cuda.Event()
+                ev.record()
+            self._param_pool.release(u.pool_slot, ev)
+            u.pool_slot = None
+        u.flat = None
+        u.resident = False
+        empty = torch.empty(0, dtype=u.dtype, device=self.device)
+        for p in u.params:
+            p.data = empty
+
+    def _launch_gather(self, u: ZeroUnit) -> None:
+        """Start the all-gather of a released unit into a pooled buffer (on the communication stream)."""
+        if u.persistent or u.flat is not None:
+            return
+        slot, buf = self._param_pool.acquire()
+        flat = buf[: u.numel]
+        u.pool_slot = slot
+        if self.dist_on and u.group_size > 1:
+            if self.on_gpu:
+                self.comm_stream.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(self.comm_stream):
+                    self._all_gather(flat, u.shard, u.group)
+                    u.gather_event = torch.cuda.Event()
+                    u.gather_event.record()
+            else:
+                self._all_gather(flat, u.shard, u.group)
+        else:
+            flat.copy_(u.shard)
+        u.flat = flat
+
+    def _ensure_resident(self, u: ZeroUnit, prefetch: Optional[ZeroUnit] = None) -> None:
+        if not u.persistent:
+            if u.flat is None:
+                self._launch_gather(u)
+            if u.gather_event is not None:
+                torch.cuda.current_stream().wait_event(u.gather_event)
+                u.gather_event = None
+            if not u.resident:
+                self._assign_param_views(u, u.flat)
+                u.resident = True
+        if prefetch is not None and not prefetch.persistent and prefetch.flat is None and self._param_pool.free:
+            self._launch_gather(prefetch)
+
+    def _neighbour(self, u: ZeroUnit, step: int) -> Optional[ZeroUnit]:
+        i = u.index + step
+        while 0 <= i < len(self.units):
+            cand = self.units[i]
+            if not cand.persistent:
+                return cand
+            i += step
+        return None
+
+    # ================================================================== collectives (NCCL / Gloo baseline)
+    def _all_gather(self, out: torch.Tensor, shard: torch.Tensor, group) -> None:
+        try:
+            dist.all_gather_into_tensor(out, shard, group=group)
+        except (RuntimeError, NotImplementedError):
+            n = dist.get_world_size(group)
+            parts = [out[i * shard.numel() : (i + 1) * shard.numel()] for i in range(n)]
+            dist.all_gather(parts, shard.contiguous(), group=group)
+
+    def _reduce_scatter(self, out: torch.Tensor, full: torch.Tensor, group) -> None:
+        if not self.on_gpu:
+            dist.all_reduce(full, group=group)
+            r = dist.get_rank(group)
+            out.copy_(full[r * out.numel() : (r + 1) * out.numel()])
+            return
+        dist.reduce_scatter_tensor(out, full, group=group)
+
+    # ================================================================== unit execution
+    def _wrap_units(self) -> None:
+        for u in self.units:
+            if not u.checkpointed or not u.modules:
+                continue
+            assert len(u.modules) == 1, "a checkpointed unit wraps exactly one module"
+            mod = u.modules[0]
+            orig = mod.forward
+            engine = self
+
+            def wrapped(x, *args, __orig=orig, __unit=u, **kwargs):
+                if not torch.is_grad_enabled() or not engine.training_mode or not engine.module.training:
+                    engine._ensure_resident(__unit, engine._neighbour(__unit, +1))
+                    if getattr(__unit, "expert_unit", None) is not None:
+                        engine._ensure_resident(__unit.expert_unit)
+                    try:
+                        return __orig(x, *args, **kwargs)
+                    finally:
+                        engine._release_params(__unit)
+                fn = lambda inp: __orig(inp, *args, **kwargs)  # noqa: E731
+                return _CheckpointedUnit.apply(engine, __unit, fn, engine._dummy, x)
+
+            mod.forward = wrapped  # type: ignore[method-assign]
+
+    def _begin_unit_backward(self, u: ZeroUnit) -> None:
+        self._ensure_resident(u, self._neighbour(u, -1))
+        self._prepare_grad_buffer(u)
+        exp = getattr(u, "expert_unit", None)
+        if exp is not None:
+            self._prepare_grad_buffer(exp)
+
+    def _prepare_grad_buffer(self, u: ZeroUnit) -> None:
+        if u.n_train <= 0 or u.grad_flat is not None:
+            return
+        if u.checkpointed:
+            slot, buf = self._grad_pool.acquire()
+            g = buf[: u.numel]
+            g.zero_()
+        else:
+            slot, g = None, torch.zeros(u.numel, dtype=u.dtype, device=self.device)
+        u.grad_flat, u.grad_slot = g, slot
+        for p, o in zip(u.params, u.offsets):
+            if p.requires_grad:
+                p.grad = g[o : o + p.numel()].view(p.shape)
+
+    def _end_unit_backward(self, u: ZeroUnit) -> None:
+        self._reduce_unit(u)
+        exp = getattr(u, "expert_unit", None)
+        if exp is not None:
+            self._reduce_unit(exp)
+        self._release_params(u)
+
+    def _reduce_unit(self, u: ZeroUnit) -> None:
+        """Reduce the unit's flat gradient across its group and accumulate into the fp32 shard."""
+        if u.grad_flat is None:
+            return
+        g = u.grad_flat
+        for p in u.params:
+            p.grad = None
+        tl = u.train_len
+        scale = 1.0 / (u.grad_divisor * self.gas)
+        lo = u.group_rank * u.shard_size
+
+        def work() -> None:
+            if self.dist_on and u.group_size > 1:
+                if self.stage >= 1:
+                    piece = torch.empty(u.shard_size, dtype=g.dtype, device=g.device)
+                    self._reduce_scatter(piece, g, u.group)
+                else:
+                    dist.all_reduce(g, group=u.group)
+                    piece = g[lo : lo + u.shard_size]
+            else:
+                piece = g[lo : lo + u.shard_size]
+            if tl > 0:
+                self._accumulate(u, piece[:tl], scale)
+
+        if self.on_gpu:
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                work()
+                ev = torch.cuda.Event()
+                ev.record()
+            if u.grad_slot is not None:
+                self._grad_pool.release(u.grad_slot, ev)
+            else:
+                g.record_stream(self.comm_stream)
+        else:
+            work()
+            if u.grad_slot is not None:
+                self._grad_pool.release(u.grad_slot, None)
+        u.grad_flat, u.grad_slot = None, None
+
+    def _accumulate(self, u: ZeroUnit, piece: torch.Tensor, scale: float) -> None:
+        acc = u.grad_acc[: piece.numel()]
+        if acc.device != piece.device:
+            tmp = piece.float() * scale
+            if u.grad_acc_valid:
+                acc.add_(tmp.to("cpu", non_blocking=False).to(acc.dtype))
+            else:
+                acc.copy_(tmp.to(acc.dtype))
+        elif acc.dtype == torch.float32 and piece.dtype == torch.bfloat16:
+            ops.accumulate_lp_grad(piece, acc, scale, overwrite=not u.grad_acc_valid)
+        else:
+            if u.grad_acc_valid:
+                acc.add_(piece.to(acc.dtype), alpha=scale)
+            else:
+                acc.copy_(piece.to(acc.dtype) * scale)
+        u.grad_acc_valid = True
+
+    # ================================================================== public training surface
+    def __call__(self, *args, **kwargs):
+        return self.forward(*args, **kwargs)
+
+    def forward(self, *args, **kwargs):
+        with self.autocast():
+            return self.module(*args, **kwargs)
+
+    def autocast(self):
+        if self.cfg.autocast:
+            return torch.autocast(device_type=self.device.type, dtype=self.cfg.autocast_dtype)
+        return nullcontext()
+
+    def train(self, mode: bool = True):
+        self.module.train(mode)
+        return self
+
+    def eval(self):
+        self.module.eval()
+        return self
+
+    def parameters(self):
+        return self.module.parameters()
+
+    def named_parameters(self, *a, **k):
+        return self.module.named_parameters(*a, **k)
+
+    def zero_optimization_stage(self) -> int:
+        return self.stage
+
+    def is_gradient_accumulation_boundary(self) -> bool:
+        return (self.micro_steps + 1) % self.gas == 0
+
+    def get_global_grad_norm(self) -> Optional[float]:
+        return None if self._grad_norm is None else float(self._grad_norm)
+
+    def get_wall_clock_timers(self) -> TimerGroup:
+        return self.timers
+
+    def wall_clock_breakdown(self) -> bool:
+        return self.cfg.wall_clock_breakdown
+
+    def get_lr(self) -> List[float]:
+        return [g["lr"] for g in self.optimizer.param_groups] if self.optimizer else []
+
+    def backward(self, loss: torch.Tensor) -> None:
+        """Back-propagate one micro-batch; gradients end up reduced in the fp32 shards."""
+        for u in self.units:
+            if not u.checkpointed and u.n_train > 0:
+                self._ensure_resident(u)
+                self._prepare_grad_buffer(u)
+        loss.backward()
+        for u in self.units:
+            if u.grad_flat is not None:
+                self._reduce_unit(u)
+
+    def step(self) -> None:
+        boundary = self.is_gradient_accumulation_boundary()
+        self.micro_steps += 1
+        self.global_samples += self.cfg.micro_batch_size * max(1, (dist.get_world_size() if self.dist_on else 1) // self.sp_size)
+        if not boundary:
+            return
+        if self.on_gpu:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
+        self._optimizer_step()
+        self.global_steps += 1
+        if self.lr_scheduler is not None:
+            self.lr_scheduler.step()
+
+    # ---------------------------------------------------------------- optimizer step
+    def _compute_grad_norm(self) -> torch.Tensor:
+        total = torch.zeros((), dtype=torch.float32, device=self.device)
+        expert_total = torch.zeros((), dtype=torch.float32, device=self.device)
+        for u in self.units:
+            if u.grad_acc is None or not u.grad_acc_valid:
+                continue
+            sq = ops.sumsq(u.grad_acc) if u.grad_acc.dtype == torch.float32 else u.grad_acc.float().pow(2).sum()
+            sq = sq.to(self.device)
+            if getattr(u, "is_expert", False) and self.expert_dp_group is not None:
+                expert_total += sq
+            else:
+                total += sq
+        if self.dist_on:
+            if self.stage >= 1:
+                dist.all_reduce(total, group=self.dp_group)
+            if self.expert_dp_group is not None:
+                if self.stage >= 1:
+                    dist.all_reduce(expert_total, group=self.expert_dp_group)
+                # experts differ across expert-parallel ranks: sum their norms over the whole world's EP axis
+                ep_world = (dist.get_world_size() // dist.get_world_size(self.expert_dp_group))
+                if ep_world > 1:
+                    dist.all_reduce(expert_total, group=self._ep_group_for_norm())
+        return (total + expert_total).sqrt()
+
+    def _ep_group_for_norm(self):
+        return getattr(self, "ep_group", None)
+
+    def _optimizer_step(self) -> None:
+        opt = self.optimizer
+        if opt is None:
+            return
+        norm = self._compute_grad_norm()
+        self._grad_norm = norm
+        clip = self.cfg.gradient_clipping
+        coef: Optional[torch.Tensor] = None
+        if clip and clip > 0:
+            coef = torch.clamp(clip / (norm + 1e-6), max=1.0).reshape(1).float()
+        fused = hasattr(opt, "step_flat")
+        for u, s, e, gi, view in self._views:
+            gslice = u.grad_acc[s:e]
+            if not u.grad_acc_valid:
+                gslice.zero_()
+            if fused:
+                view._atb_grad = gslice  # type: ignore[attr-defined]
+            else:
+                view.grad = gslice if coef is None else gslice * coef.to(gslice.device)
+                if view.grad.dtype != view.dtype:
+                    view.grad = view.grad.to(view.dtype)
+        if fused:
+            opt.step_flat(coef)
+            opt._opt_called = True  # keeps torch's scheduler-order check quiet
+        else:
+            opt.step()
+            for u, s, e, gi, view in self._views:
+                view.grad = None
+        # low-precision copies + re-gather
+        for u in self.units:
+            if u.master is None:
+                continue
+            tl = u.train_len
+            if not (fused and getattr(opt, "writes_lp", False) and u.master.device == self.device
+                    and u.master.dtype == torch.float32 and u.dtype == torch.bfloat16):
+                u.shard[:tl].copy_(u.master[:tl].to(self.device, non_blocking=True).to(u.dtype))
+            u.grad_acc_valid = False
+        self._sync_full_params()
+
+    def _sync_full_params(self) -> None:
+        """After an update every persistent unit re-assembles its full buffer from the shards."""
+        if self.stage == 0 or not self.dist_on:
+            return
+        for u in self.units:
+            if u.group_size <= 1 or u.master is None and u.n_train == 0:
+                continue
+            if u.persistent:
+                # shard is a view of flat: in-place all-gather
+                self._all_gather(u.flat, u.shard.clone() if self.on_gpu is False else u.shard, u.group)
+
+    # ================================================================== gathered access (checkpoint export etc.)
+    @contextmanager
+    def gathered_unit(self, u: ZeroUnit):
+        was_released = not u.persistent and u.flat is None
+        self._ensure_resident(u)
+        if self.on_gpu:
+            torch.cuda.current_stream().synchronize()
+        try:
+            yield u
+        finally:
+            if was_released:
+                self._release_params(u)
+
+    def iter_full_named_parameters(self) -> Iterable[Tuple[str, torch.Tensor]]:
+        """Yield ``(name, full tensor)`` for every parameter, gathering stage-3 units one at a time.
+        Every rank must iterate (the gathers are collectives)."""
+        for u in self.units:
+            with self.gathered_unit(u):
+                for n, p in zip(u.param_names, u.params):
+                    yield n, p.data
+
+    # ================================================================== checkpoints (sharded, resumable)
+    def _ckpt_rank_file(self, d: Path) -> Path:
+        return d / f"zero_pp_rank_{self.global_rank}_mp_rank_00_optim_states.pt"
+
+    def save_checkpoint(self, save_dir: Any, tag: Optional[str] = None, client_state: Optional[Dict[str, Any]] = None) -> None:
+        save_dir = Path(save_dir)
+        tag = tag or f"global_step{self.global_steps}"
+        d = save_dir / tag
+        d.mkdir(parents=True, exist_ok=True)
+        if self.on_gpu:
+            torch.cuda.synchronize()
+        units_state = {}
+        for u in self.units:
+            tl = u.train_len
+            st: Dict[str, Any] = {
+                "numel": u.numel, "shard_size": u.shard_size, "n_train": u.n_train,
+                "param_names": u.param_names, "offsets": u.offsets,
+                "shard": u.shard.detach().cpu().clone(),
+            }
+            if u.master is not None:
+                st["master"] = u.master[:tl].detach().cpu().clone()
+            units_state[u.name] = st
+        opt_state = None
+        if self.optimizer is not None:
+            opt_state = self._optimizer_state_for_save()
+        torch.save(
+            {
+                "units": units_state, "optimizer": opt_state, "stage": self.stage, "world": self.world,
+                "group_rank": self.rank,
+            },
+            self._ckpt_rank_file(d),
+        )
+        if self.global_rank == 0:
+            torch.save(
+                {
+                    "lr_scheduler": self.lr_scheduler.state_dict() if self.lr_scheduler is not None else None,
+                    "global_steps": self.global_steps, "micro_steps": self.micro_steps,
+                    "global_samples": self.global_samples, "skipped_steps": self.skipped_steps,
+                    "dp_world_size": self.world, "mp_world_size": 1, "zero_stage": self.stage,
+                    "client_state": client_state or {},
+                    "param_shapes": {n: tuple(p.shape) for u in self.units for n, p in zip(u.param_names, u.params)},
+                },
+                d / "mp_rank_00_model_states.pt",
+            )
+        if self.dist_on:
+            dist.barrier()
+        if self.global_rank == 0:
+            (save_dir / "latest").write_text(tag)
+        if self.dist_on:
+            dist.barrier()
+
+    def _optimizer_state_for_save(self) -> Dict[str, Any]:
+        opt = self.optimizer
+        per_view = []
+        for u, s, e, gi, view in self._views:
+            st = opt.state.get(view, {})
+            per_view.append({
+                "unit": u.name, "range": (s, e), "group": gi,
+                "state": {k: (v.detach().cpu().clone() if torch.is_tensor(v) else v) for k, v in st.items()},
+            })
+        groups = [{k: v for k, v in g.items() if k != "params"} for g in opt.param_groups]
+        return {"views": per_view, "param_groups": groups}
+
+    def load_checkpoint(self, load_dir: Any, tag: Optional[str] = None, load_optimizer_states: bool = True):
+        load_dir = Path(load_dir)
+        if tag is None:
+            latest = load_dir / "latest"
+            if not latest.exists():
+                return None, {}
+            tag = latest.read_text().strip()
+        d = load_dir / tag
+        meta = torch.load(d / "mp_rank_00_model_states.pt", map_location="cpu", weights_only=False)
+        rank_file = self._ckpt_rank_file(d)
+        if not rank_file.exists():
+            raise FileNotFoundError(
+                f"{rank_file} is missing: the checkpoint was written with a different world size "
+                f"({meta.get('dp_world_size')}) than this run ({self.world})"
+            )
+        mine = torch.load(rank_file, map_location="cpu", weights_only=False)
+        if mine["stage"] != self.stage or mine["world"] != self.world:
+            raise RuntimeError("checkpoint was written with another ZeRO stage or world size")
+        for u in self.units:
+            st = mine["units"][u.name]
+            assert st["numel"] == u.numel and st["param_names"] == u.param_names, f"layout of unit {u.name} changed"
+            u.shard.copy_(st["shard"].to(u.shard.dtype))
+            if u.master is not None and "master" in st:
+                u.master[: u.train_len].copy_(st["master"].to(u.master.dtype))
+        if self.stage >= 1 and self.dist_on:
+            self._sync_full_params()
+        if load_optimizer_states and self.optimizer is not None and mine.get("optimizer"):
+            saved = mine["optimizer"]
+            for (u, s, e, gi, view), sv in zip(self._views, saved["views"]):
+                assert sv["unit"] == u.name and tuple(sv["range"]) == (s, e)
+                self.optimizer.state[view] = {
+                    k: (v.to(view.device) if torch.is_tensor(v) and v.dim() > 0 else v) for k, v in sv["state"].items()
+                }
+            for g, sg in zip(self.optimizer.param_groups, saved["param_groups"]):
+                for k, v in sg.items():
+                    g[k] = v
+        if self.lr_scheduler is not None and meta.get("lr_scheduler") is not None:
+            self.lr_scheduler.load_state_dict(meta["lr_scheduler"])
+        self.global_steps = meta["global_steps"]
+        self.micro_steps = meta["micro_steps"]
+        self.global_samples = meta.get("global_samples", 0)
+        self.skipped_steps = meta.get("skipped_steps", 0)
+        return str(d), meta.get("client_state", {})
+
+    def save_pretrained(self, *args, **kwargs):
+        return self.module.save_pretrained(*args, **kwargs)
+
+
+class _CheckpointedUnit(torch.autograd.Function):
+    """Runs one unit without keeping its activations; the backward pass gathers the unit's parameters
+    again, recomputes the forward from the saved (possibly host-resident) input, back-propagates and hands
+    the unit's gradients to the engine for reduction."""
+
+    @staticmethod
+    def forward(ctx, engine: TrainingEngine, unit: ZeroUnit, fn, dummy, x):
+        ctx.engine, ctx.unit, ctx.fn = engine, unit, fn
+        engine._ensure_resident(unit, engine._neighbour(unit, +1))
+        exp = getattr(unit, "expert_unit", None)
+        if exp is not None:
+            engine._ensure_resident(exp)
+        with torch.no_grad():
+            y = fn(x)
+        engine._release_params(unit)
+        ctx.handle = engine.act_store.save(x)
+        ctx.x_requires_grad = x.requires_grad
+        return y
+
+    @staticmethod
+    def backward(ctx, *grads):
+        engine, unit, fn = ctx.engine, ctx.unit, ctx.fn
+        engine._begin_unit_backward(unit)
+        x = ctx.handle.restore().detach()
+        x.requires_grad_(True)
+        with torch.enable_grad():
+            y = fn(x)
+        outs = y if isinstance(y, (tuple, list)) else (y,)
+        pairs = [(o, g) for o, g in zip(outs, grads) if torch.is_tensor(o) and o.requires_grad and g is not None]
+        torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
+        engine._end_unit_backward(unit)
+        gx = x.grad if ctx.x_requires_grad else None
+        ctx.handle = None
+        return None, None, None, None, gx
+
+
+def initialize(
+    model: nn.Module,
+    optimizer: Optional[torch.optim.Optimizer] = None,
+    lr_scheduler: Any = None,
+    config: Optional[Dict[str, Any]] = None,
+    **kwargs: Any,
+) -> Tuple[TrainingEngine, Optional[torch.optim.Optimizer], None, Any]:
+    """Convenience constructor with the return shape of the reference's engine initialiser."""
+    engine = TrainingEngine(model, optimizer, lr_scheduler, config, **kwargs)
+    return engine, engine.optimizer, None, engine.lr_scheduler

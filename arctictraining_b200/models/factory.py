@@ -1,0 +1,152 @@
+"""Model factories.  Parity: arctic_training/model/factory.py:36-97, hf_factory.py:25-89,
+liger_factory.py:24-69.
+
+``huggingface`` builds this framework's native decoder for the supported families (Llama, Qwen2, Qwen3,
+Qwen3-MoE) — weights come from an HF-layout directory, or are random when the recipe names a built-in
+preset or overrides ``num_hidden_layers`` — and falls back to ``transformers.AutoModelForCausalLM`` for
+other architectures.  ``liger`` is kept as a recipe-compatible alias: the fused kernels it stands for
+(RMSNorm, RoPE, SwiGLU, fused linear cross-entropy) are always on in the native model.
+"""
+
+from __future__ import annotations
+
+from abc import ABC
+from abc import abstractmethod
+from pathlib import Path
+from typing import TYPE_CHECKING
+from typing import Any
+from typing import Optional
+
+import torch
+
+from ..callback.mixin import CallbackMixin
+from ..callback.mixin import callback_wrapper
+from ..config.model import ModelConfig
+from ..logging import logger
+from ..registry import RegistryMeta
+from ..registry import _validate_class_attribute_set
+from ..registry import _validate_class_attribute_type
+from ..registry import _validate_class_method
+from .arch import ArchConfig
+from .arch import load_arch_config
+
+if TYPE_CHECKING:
+    from ..trainer.trainer import Trainer
+
+NATIVE_MODEL_TYPES = ("llama", "qwen2", "qwen3", "qwen3_moe", "mistral")
+
+
+class ModelFactory(ABC, CallbackMixin, metaclass=RegistryMeta):
+    """Base class for model creation."""
+
+    name: str
+    """ Name under which the factory is selected in a recipe (``model.type``). """
+
+    config: ModelConfig
+    """ Config class of this factory. """
+
+    @classmethod
+    def _validate_subclass(cls) -> None:
+        _validate_class_attribute_set(cls, "name")
+        _validate_class_attribute_type(cls, "config", ModelConfig)
+        _validate_class_method(cls, "create_config", ["self"])
+        _validate_class_method(cls, "create_model", ["self", "model_config"])
+
+    def __init__(self, trainer: "Trainer", model_config: Optional[ModelConfig] = None) -> None:
+        self._trainer = trainer
+        self.config = model_config if model_config is not None else trainer.config.model
+
+    def __call__(self) -> torch.nn.Module:
+        return self.create_model(model_config=self.create_config())
+
+    @property
+    def trainer(self) -> "Trainer":
+        return self._trainer
+
+    @property
+    def device(self):
+        return self.trainer.device
+
+    @property
+    def world_size(self) -> int:
+        return self.trainer.world_size
+
+    @property
+    def global_rank(self) -> int:
+        return self.trainer.global_rank
+
+    @abstractmethod
+    @callback_wrapper("create-config")
+    def create_config(self) -> Any:
+        raise NotImplementedError
+
+    @abstractmethod
+    @callback_wrapper("create-model")
+    def create_model(self, model_config) -> torch.nn.Module:
+        raise NotImplementedError
+
+
+class HFModelFactory(ModelFactory):
+    name = "huggingface"
+    model_cls = None  # set lazily to CausalLM; subclasses override
+
+    def create_config(self) -> ArchConfig:
+        base = load_arch_config(self.config.name_or_path)
+        cfg = load_arch_config(self.config.name_or_path, self.config.hf_config_kwargs)
+        layers_override = self.config.hf_config_kwargs.get("num_hidden_layers")
+        self.using_random_model = base.get("_source") == "preset" or (
+            layers_override is not None and layers_override != base.get("num_hidden_layers")
+        )
+        return cfg
+
+    def _native_class(self):
+        from .causal_lm import CausalLM
+
+        return self.model_cls or CausalLM
+
+    def create_model(self, model_config) -> torch.nn.Module:
+        dtype = self.config.dtype.value if hasattr(self.config.dtype, "value") else self.config.dtype
+        if model_config.get("model_type") not in NATIVE_MODEL_TYPES:
+            return self._create_transformers_model(model_config, dtype)
+        device = self.device
+        with torch.device(device):
+            model = self._native_class()(model_config, dtype=dtype)
+        model.attn_impl = self.config.attn_implementation
+        if self.using_random_model:
+            model.init_weights(seed=getattr(self.trainer.config, "seed", 42) if self.trainer is not None else 42)
+        else:
+            from .hf_io import load_pretrained_into
+
+            load_pretrained_into(model, Path(str(self.config.name_or_path)), model_config)
+        return model
+
+    def _create_transformers_model(self, model_config, dtype) -> torch.nn.Module:
+        from transformers import AutoConfig
+        from transformers import AutoModelForCausalLM
+
+        hf_cfg = AutoConfig.from_pretrained(self.config.name_or_path)
+        for k, v in self.config.hf_config_kwargs.items():
+            setattr(hf_cfg, k, v)
+        attn = self.config.attn_implementation if self.config.attn_implementation != "native" else "sdpa"
+        if self.using_random_model:
+            model = AutoModelForCausalLM.from_config(hf_cfg, attn_implementation=attn, dtype=dtype)
+        else:
+            model = AutoModelForCausalLM.from_pretrained(
+                self.config.name_or_path, config=hf_cfg, attn_implementation=attn, dtype=dtype
+            )
+        return model.to(self.device)
+
+    def post_create_model_callback(self, model):
+        if self.config.peft_config is not None:
+            from .peft import apply_lora
+
+            trainable, total = apply_lora(model, self.config.peft_config)
+            logger.info(f"Applied PEFT config: total params {total}, trainable {trainable} ({100 * trainable / total:.2f}%)")
+        model.activation_checkpointing = not self.config.disable_activation_checkpoint
+        if hasattr(model, "gradient_checkpointing_enable") and not self.config.disable_activation_checkpoint:
+            model.gradient_checkpointing_enable()
+        return model
+
+
+class LigerModelFactory(HFModelFactory):
+    name = "liger"

@@ -1,0 +1,142 @@
+"""Decoder building blocks shared by the native model families (Llama, Qwen2, Qwen3, Qwen3-MoE).
+
+Weights of projections that are consumed together are stored fused — ``qkv_proj`` (q, k, v rows stacked)
+and ``gate_up_proj`` (gate/up rows block-interleaved, 64 and 64) — so each is one GEMM whose epilogue can
+apply RoPE or SwiGLU.  Conversion to and from the Hugging Face parameter names happens at checkpoint
+load/save time (:mod:`arctictraining_b200.models.hf_io`).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from dataclasses import field
+from typing import Any
+from typing import Dict
+from typing import Optional
+
+import torch
+import torch.nn as nn
+
+from .. import ops
+from .arch import ArchConfig
+
+
+@dataclass
+class ForwardContext:
+    """Per-batch tensors shared by all layers."""
+
+    cos: torch.Tensor  # [B, S, D/2] fp32
+    sin: torch.Tensor
+    cu_seqlens: Optional[torch.Tensor] = None  # packed-sample boundaries over the *full* sequence
+    max_seqlen: Optional[int] = None
+    attn_impl: str = "sdpa"
+    sp: Optional[Any] = None  # UlyssesContext when sequence parallelism is on
+    tiled_mlp: bool = False
+    extras: Dict[str, Any] = field(default_factory=dict)
+
+
+class RMSNorm(nn.Module):
+    def __init__(self, dim: int, eps: float, dtype=None, device=None) -> None:
+        super().__init__()
+        self.weight = nn.Parameter(torch.ones(dim, dtype=dtype, device=device))
+        self.eps = eps
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.rms_norm(x, self.weight, self.eps)
+
+
+class Linear(nn.Module):
+    """``y = x W^T (+ b)`` on this library's GEMM.  ``weight`` is ``[out, in]`` like ``nn.Linear``."""
+
+    def __init__(self, in_features: int, out_features: int, bias: bool = False, dtype=None, device=None) -> None:
+        super().__init__()
+        self.in_features, self.out_features = in_features, out_features
+        self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
+        self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias)
+
+
+class Attention(nn.Module):
+    def __init__(self, cfg: ArchConfig, layer_idx: int, dtype=None, device=None) -> None:
+        super().__init__()
+        self.layer_idx = layer_idx
+        self.hq = cfg["num_attention_heads"]
+        self.hkv = cfg.get("num_key_value_heads") or self.hq
+        self.d = cfg.head_dim_
+        hidden = cfg["hidden_size"]
+        bias = bool(cfg.get("attention_bias", False))
+        self.qkv_proj = Linear(hidden, (self.hq + 2 * self.hkv) * self.d, bias=bias, dtype=dtype, device=device)
+        self.o_proj = Linear(self.hq * self.d, hidden, bias=False, dtype=dtype, device=device)
+        self.qk_norm = bool(cfg.get("qk_norm", False))
+        if self.qk_norm:
+            self.q_norm = RMSNorm(self.d, cfg["rms_norm_eps"], dtype=dtype, device=device)
+            self.k_norm = RMSNorm(self.d, cfg["rms_norm_eps"], dtype=dtype, device=device)
+
+    def project_qkv(self, x: torch.Tensor, ctx: ForwardContext):
+        B, S, _ = x.shape
+        qkv = self.qkv_proj(x)
+        if self.qk_norm:
+            q, k, v = qkv.split([self.hq * self.d, self.hkv * self.d, self.hkv * self.d], dim=-1)
+            q = self.q_norm(q.reshape(B, S, self.hq, self.d))
+            k = self.k_norm(k.reshape(B, S, self.hkv, self.d))
+            q = ops.rope(q, ctx.cos, ctx.sin)
+            k = ops.rope(k, ctx.cos, ctx.sin)
+            v = v.reshape(B, S, self.hkv, self.d)
+        else:
+            q, k, v = ops.rope_qkv(qkv, ctx.cos, ctx.sin, self.hq, self.hkv, self.d)
+        return q, k, v
+
+    def core(self, q, k, v, ctx: ForwardContext) -> torch.Tensor:
+        if ctx.sp is not None:
+            return ctx.sp.attention(q, k, v, ctx)
+        return ops.attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
+
+    def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+        B, S, _ = x.shape
+        q, k, v = self.project_qkv(x, ctx)
+        o = self.core(q, k, v, ctx)
+        return self.o_proj(o.reshape(B, S, self.hq * self.d))
+
+
+class MLP(nn.Module):
+    """SwiGLU feed-forward block with a fused, block-interleaved gate/up weight."""
+
+    def __init__(self, hidden: int, inter: int, dtype=None, device=None) -> None:
+        super().__init__()
+        self.gate_up_proj = Linear(hidden, 2 * inter, dtype=dtype, device=device)
+        self.down_proj = Linear(inter, hidden, dtype=dtype, device=device)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.down_proj(ops.linear_swiglu(x, self.gate_up_proj.weight))
+
+
+class DecoderLayer(nn.Module):
+    def __init__(self, cfg: ArchConfig, layer_idx: int, dtype=None, device=None) -> None:
+        super().__init__()
+        hidden = cfg["hidden_size"]
+        self.layer_idx = layer_idx
+        self.input_layernorm = RMSNorm(hidden, cfg["rms_norm_eps"], dtype=dtype, device=device)
+        self.self_attn = Attention(cfg, layer_idx, dtype=dtype, device=device)
+        self.post_attention_layernorm = RMSNorm(hidden, cfg["rms_norm_eps"], dtype=dtype, device=device)
+        self.mlp = self._build_mlp(cfg, layer_idx, dtype, device)
+
+    @staticmethod
+    def _build_mlp(cfg: ArchConfig, layer_idx: int, dtype, device) -> nn.Module:
+        n_exp = cfg.get("num_experts") or cfg.get("num_local_experts") or 0
+        sparse_step = cfg.get("decoder_sparse_step", 1) or 1
+        if n_exp and layer_idx not in (cfg.get("mlp_only_layers") or []) and (layer_idx + 1) % sparse_step == 0:
+            from .moe import build_moe_block
+
+            return build_moe_block(cfg, dtype=dtype, device=device)
+        return MLP(cfg["hidden_size"], cfg["intermediate_size"], dtype=dtype, device=device)
+
+    def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+        x = x + self.self_attn(self.input_layernorm(x), ctx)
+        h = self.post_attention_layernorm(x)
+        if ctx.tiled_mlp and isinstance(self.mlp, MLP):
+            from ..ops.tiled import tiled_mlp
+
+            return x + tiled_mlp(self.mlp, h)
+        return x + self.mlp(h)

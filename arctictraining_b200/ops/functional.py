@@ -1,0 +1,502 @@
+"""Differentiable front ends of the fused ops.
+
+Each function has one signature and two implementations: the sm_100a kernel from ``csrc`` (used
+whenever the tensors live on a GPU) and the PyTorch reference in :mod:`.reference` (CPU, oracle).
+"""
+
+from __future__ import annotations
+
+import math
+import os
+from typing import Optional
+from typing import Tuple
+
+import torch
+import torch.nn.functional as F
+
+from . import _ext
+from . import reference as ref
+
+IGNORE_INDEX = ref.IGNORE_INDEX
+
+# which GEMM serves nn.Linear-shaped work on the GPU: "tcgen05" (this library's kernel) or "cublas"
+_GEMM_BACKEND = os.getenv("ATB200_GEMM", "tcgen05")
+LAUNCH_COUNTER = {"native": 0}
+
+
+def set_gemm_backend(name: str) -> None:
+    global _GEMM_BACKEND
+    assert name in ("tcgen05", "cublas")
+    _GEMM_BACKEND = name
+
+
+def gemm_backend() -> str:
+    return _GEMM_BACKEND
+
+
+def _use_kernels(t: torch.Tensor) -> bool:
+    return t.is_cuda and _ext.available()
+
+
+def _count(n: int = 1) -> None:
+    LAUNCH_COUNTER["native"] += n
+
+
+# ------------------------------------------------------------------------------------------------ RMSNorm
+class _RMSNormFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, eps):
+        shp = x.shape
+        x2 = x.reshape(-1, shp[-1]).contiguous()
+        y, rstd = _ext.ops().rmsnorm_fwd(x2, weight.contiguous(), eps)
+        _count()
+        ctx.save_for_backward(x2, weight, rstd)
+        ctx.shp = shp
+        return y.view(shp)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, weight, rstd = ctx.saved_tensors
+        dx, dw = _ext.ops().rmsnorm_bwd(dy.reshape(x2.shape).contiguous(), x2, weight.contiguous(), rstd)
+        _count()
+        return dx.view(ctx.shp), dw.to(weight.dtype), None
+
+
+def rms_norm(x: torch.Tensor, weight: torch.Tensor, eps: float) -> torch.Tensor:
+    if _use_kernels(x) and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 and x.shape[-1] <= 16384:
+        return _RMSNormFn.apply(x, weight, eps)
+    return ref.rms_norm(x, weight, eps)
+
+
+# ------------------------------------------------------------------------------------------------ RoPE
+class _QKVRopeFn(torch.autograd.Function):
+    """Rotates the q and k heads of a fused projection output ``[T, (Hq + 2 Hkv) D]`` in place."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, hq, hkv, d):
+        ctx.save_for_backward(cos, sin)
+        ctx.dims = (hq, hkv, d)
+        T = qkv.shape[0]
+        ops = _ext.ops()
+        ops.rope_inplace(qkv[:, : hq * d].unflatten(1, (hq, d)), cos, sin, False)
+        ops.rope_inplace(qkv[:, hq * d : (hq + hkv) * d].unflatten(1, (hkv, d)), cos, sin, False)
+        _count(2)
+        ctx.mark_dirty(qkv)
+        return qkv
+
+    @staticmethod
+    def backward(ctx, dqkv):
+        cos, sin = ctx.saved_tensors
+        hq, hkv, d = ctx.dims
+        dqkv = dqkv.contiguous().clone()
+        ops = _ext.ops()
+        ops.rope_inplace(dqkv[:, : hq * d].unflatten(1, (hq, d)), cos, sin, True)
+        ops.rope_inplace(dqkv[:, hq * d : (hq + hkv) * d].unflatten(1, (hkv, d)), cos, sin, True)
+        _count(2)
+        return dqkv, None, None, None, None, None
+
+
+def rope_qkv(
+    qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int, d: int
+) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """Split a fused projection ``[B, S, (Hq + 2 Hkv) D]`` into rotated q, rotated k and v
+    (``[B, S, heads, D]`` views).  ``cos/sin`` are ``[B, S, D/2]`` fp32."""
+    B, S, _ = qkv.shape
+    if _use_kernels(qkv) and qkv.dtype == torch.bfloat16 and d % 16 == 0 and qkv.is_contiguous():
+        flat = qkv.view(B * S, -1)
+        if not (flat.requires_grad and flat.is_leaf):
+            flat = _QKVRopeFn.apply(
+                flat, cos.reshape(B * S, d // 2).contiguous(), sin.reshape(B * S, d // 2).contiguous(), hq, hkv, d
+            )
+            q, k, v = flat.split([hq * d, hkv * d, hkv * d], dim=-1)
+            return q.view(B, S, hq, d), k.view(B, S, hkv, d), v.view(B, S, hkv, d)
+    q, k, v = qkv.split([hq * d, hkv * d, hkv * d], dim=-1)
+    q = ref.rope_apply(q.view(B, S, hq, d), cos, sin)
+    k = ref.rope_apply(k.view(B, S, hkv, d), cos, sin)
+    return q, k, v.view(B, S, hkv, d)
+
+
+class _RopeFn(torch.autograd.Function):
+    """Out-of-place rotary embedding of one ``[T, heads, D]`` tensor."""
+
+    @staticmethod
+    def forward(ctx, x, cos, sin):
+        ctx.save_for_backward(cos, sin)
+        y = x.contiguous().clone()
+        _ext.ops().rope_inplace(y, cos, sin, False)
+        _count()
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        cos, sin = ctx.saved_tensors
+        dx = dy.contiguous().clone()
+        _ext.ops().rope_inplace(dx, cos, sin, True)
+        _count()
+        return dx, None, None
+
+
+def rope(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor) -> torch.Tensor:
+    """Rotary embedding of ``x [B, S, heads, D]`` with ``cos/sin [B, S, D/2]`` (fp32)."""
+    if _use_kernels(x) and x.dtype == torch.bfloat16 and x.shape[-1] % 16 == 0:
+        B, S, Hh, D = x.shape
+        y = _RopeFn.apply(x.reshape(B * S, Hh, D), cos.reshape(B * S, D // 2).contiguous(), sin.reshape(B * S, D // 2).contiguous())
+        return y.view(B, S, Hh, D)
+    return ref.rope_apply(x, cos, sin)
+
+
+# ------------------------------------------------------------------------------------------------ SwiGLU
+class _SwiGLUFn(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        gu = gu.contiguous()
+        ctx.save_for_backward(gu)
+        _count()
+        return _ext.ops().swiglu_fwd(gu)
+
+    @staticmethod
+    def backward(ctx, dout):
+        (gu,) = ctx.saved_tensors
+        _count()
+        return _ext.ops().swiglu_bwd(dout.contiguous(), gu)
+
+
+def swiglu_interleaved(gu: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` on a block-interleaved gate/up tensor (64 gate columns, 64 up columns, ...)."""
+    if _use_kernels(gu) and gu.dtype == torch.bfloat16 and gu.shape[-1] % 128 == 0:
+        return _SwiGLUFn.apply(gu)
+    return ref.swiglu_interleaved(gu)
+
+
+# ------------------------------------------------------------------------------------------------ GEMM / linear
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    epilogue: int = 0,
+    out: Optional[torch.Tensor] = None,
+) -> torch.Tensor:
+    """Raw tcgen05 GEMM (no autograd).  See ``csrc/gemm_sm100.cu`` for the operand conventions."""
+    _count()
+    return _ext.ops().gemm_bf16(a, b, a_mn, b_mn, epilogue, out, 0)
+
+
+def _gemm_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
+    return (
+        _GEMM_BACKEND == "tcgen05"
+        and x2.dtype == torch.bfloat16
+        and w.dtype == torch.bfloat16
+        and x2.shape[-1] % 8 == 0
+        and w.shape[0] % 8 == 0
+        and x2.shape[0] % 8 == 0
+        and x2.data_ptr() % 16 == 0
+        and w.data_ptr() % 16 == 0
+        and x2.shape[0] > 0
+    )
+
+
+class _LinearFn(torch.autograd.Function):
+    """y = x W^T on the tcgen05 kernel; dgrad and wgrad use the same kernel with MN-major operands."""
+
+    @staticmethod
+    def forward(ctx, x2, w):
+        ctx.save_for_backward(x2, w)
+        return gemm(x2, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = dw = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy, w, False, True)  # [M,N] x [N,K] (B is MN-major)
+        if ctx.needs_input_grad[1]:
+            dw = gemm(dy, x2, True, True)  # dY^T X : both operands MN-major
+        return dx, dw
+
+
+class _LinearSwiGLUFn(torch.autograd.Function):
+    """h = swiglu(x W_gu^T) with the activation applied in the GEMM epilogue (gate/up never hit memory
+    in the forward pass; the backward recomputes them)."""
+
+    @staticmethod
+    def forward(ctx, x2, w_gu):
+        ctx.save_for_backward(x2, w_gu)
+        return gemm(x2, w_gu, epilogue=2)
+
+    @staticmethod
+    def backward(ctx, dh):
+        x2, w_gu = ctx.saved_tensors
+        gu = gemm(x2, w_gu)
+        _count()
+        dgu = _ext.ops().swiglu_bwd(dh.contiguous(), gu)
+        del gu
+        dx = gemm(dgu, w_gu, False, True) if ctx.needs_input_grad[0] else None
+        dw = gemm(dgu, x2, True, True) if ctx.needs_input_grad[1] else None
+        return dx, dw
+
+
+def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+    if _use_kernels(x):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if _gemm_ok(x2, weight):
+            y = _LinearFn.apply(x2, weight)
+            if bias is not None:
+                y = y + bias
+            return y.view(*x.shape[:-1], weight.shape[0])
+    return F.linear(x, weight, bias)
+
+
+def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
+    """``swiglu(x @ W_gate_up^T)`` for a block-interleaved fused gate/up weight ``[2I, H]``."""
+    if _use_kernels(x):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if _gemm_ok(x2, w_gate_up) and w_gate_up.shape[0] % 128 == 0:
+            h = _LinearSwiGLUFn.apply(x2, w_gate_up)
+            return h.view(*x.shape[:-1], w_gate_up.shape[0] // 2)
+    return swiglu_interleaved(F.linear(x, w_gate_up))
+
+
+# ------------------------------------------------------------------------------------------------ attention
+def attention(
+    q: torch.Tensor,
+    k: torch.Tensor,
+    v: torch.Tensor,
+    cu_seqlens: Optional[torch.Tensor] = None,
+    max_seqlen: Optional[int] = None,
+    causal: bool = True,
+    impl: str = "sdpa",
+    scale: Optional[float] = None,
+) -> torch.Tensor:
+    """Causal GQA attention over ``[B, S, H, D]`` tensors; ``cu_seqlens`` marks packed samples (B == 1)."""
+    if q.is_cuda and impl in ("flash_attention_2", "flash_attention_3", "native"):
+        try:
+            from flash_attn import flash_attn_func
+            from flash_attn import flash_attn_varlen_func
+        except ImportError:  # pragma: no cover
+            flash_attn_func = None
+        if flash_attn_func is not None and q.dtype in (torch.bfloat16, torch.float16):
+            if cu_seqlens is not None and cu_seqlens.numel() > 2:
+                B, S, Hq, D = q.shape
+                cu = cu_seqlens.to(torch.int32)
+                o = flash_attn_varlen_func(
+                    q.reshape(B * S, Hq, D), k.reshape(B * S, -1, D), v.reshape(B * S, -1, D),
+                    cu, cu, max_seqlen or S, max_seqlen or S, causal=causal, softmax_scale=scale,
+                )
+                return o.view(B, S, Hq, D)
+            return flash_attn_func(q, k, v, causal=causal, softmax_scale=scale)
+    if cu_seqlens is None or cu_seqlens.numel() <= 2:
+        Hq, Hkv = q.shape[2], k.shape[2]
+        o = F.scaled_dot_product_attention(
+            q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), is_causal=causal, scale=scale,
+            enable_gqa=(Hq != Hkv),
+        )
+        return o.transpose(1, 2)
+    # packed samples without a varlen kernel: attend sample by sample
+    outs = []
+    bounds = cu_seqlens.tolist()
+    Hq, Hkv = q.shape[2], k.shape[2]
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        o = F.scaled_dot_product_attention(
+            q[:, s:e].transpose(1, 2), k[:, s:e].transpose(1, 2), v[:, s:e].transpose(1, 2), is_causal=causal,
+            scale=scale, enable_gqa=(Hq != Hkv),
+        )
+        outs.append(o.transpose(1, 2))
+    return torch.cat(outs, dim=1)
+
+
+# ------------------------------------------------------------------------------------------------ fused linear + CE
+def _ce_chunk_tokens(vocab: int, budget_bytes: int = 1 << 30) -> int:
+    """Tokens per logits tile so that one bf16 tile stays around ``budget_bytes`` (multiple of 256)."""
+    t = max(256, budget_bytes // (2 * vocab))
+    return int(t // 256 * 256)
+
+
+class _FusedLinearCEFn(torch.autograd.Function):
+    """loss_sum = sum_t CE(h_t W^T, y_t), with dh and dW produced tile by tile inside the forward pass
+    so that the ``[tokens, vocab]`` logits never exist as a whole."""
+
+    @staticmethod
+    def forward(ctx, h, weight, labels, chunk):
+        T, H = h.shape
+        use_k = _use_kernels(h) and h.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0
+        need_dh, need_dw = h.requires_grad, weight.requires_grad
+        dh = torch.empty_like(h) if need_dh else None
+        dw = torch.zeros_like(weight) if need_dw else None
+        loss_sum = torch.zeros((), dtype=torch.float32, device=h.device)
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            hc, yc = h[s:e], labels[s:e]
+            if use_k:
+                tcg = _gemm_ok(hc, weight)
+                logits = gemm(hc, weight) if tcg else F.linear(hc, weight)
+                loss_rows, _ = _ext.ops().ce_fwd_bwd(logits, yc, None, None, need_dh or need_dw)
+                _count()
+                loss_sum += loss_rows.sum()
+                if need_dh:
+                    dh[s:e] = gemm(logits, weight, False, True) if tcg else logits @ weight
+                if need_dw:
+                    if tcg:
+                        gemm(logits, hc, True, True, epilogue=1, out=dw)
+                    else:
+                        dw.addmm_(logits.t(), hc)
+            else:
+                logits = F.linear(hc, weight).float()
+                lse = torch.logsumexp(logits, dim=-1)
+                valid = yc != IGNORE_INDEX
+                picked = torch.gather(logits, 1, yc.clamp(min=0).unsqueeze(1)).squeeze(1)
+                loss_sum += ((lse - picked) * valid).sum()
+                if need_dh or need_dw:
+                    g = torch.softmax(logits, dim=-1)
+                    g[torch.arange(e - s, device=h.device), yc.clamp(min=0)] -= 1.0
+                    g = (g * valid.unsqueeze(1)).to(h.dtype)
+                    if need_dh:
+                        dh[s:e] = g @ weight
+                    if need_dw:
+                        dw.addmm_(g.t(), hc)
+            del logits
+        ctx.save_for_backward(dh, dw)
+        return loss_sum
+
+    @staticmethod
+    def backward(ctx, gout):
+        dh, dw = ctx.saved_tensors
+        if dh is not None:
+            dh = dh * gout.to(dh.dtype)
+        if dw is not None:
+            dw = dw * gout.to(dw.dtype)
+        return dh, dw, None, None
+
+
+def fused_linear_cross_entropy(
+    hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, chunk_tokens: Optional[int] = None
+) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Sum of cross-entropy losses of ``hidden @ weight.T`` against ``labels`` (already shifted) and
+    the count of labels different from -100.  Logits are produced and consumed one token tile at a time."""
+    h = hidden.reshape(-1, hidden.shape[-1])
+    y = labels.reshape(-1)
+    if not h.is_contiguous():
+        h = h.contiguous()
+    chunk = chunk_tokens or _ce_chunk_tokens(weight.shape[0])
+    loss_sum = _FusedLinearCEFn.apply(h, weight, y, chunk)
+    return loss_sum, (y != IGNORE_INDEX).sum()
+
+
+class _FusedLinearLogProbFn(torch.autograd.Function):
+    """Per-token log-probabilities ``log softmax(h W^T)[y]`` (0 where ``y == -100``) without keeping the
+    logits; the backward pass recomputes them tile by tile."""
+
+    @staticmethod
+    def forward(ctx, h, weight, labels, chunk):
+        T = h.shape[0]
+        use_k = _use_kernels(h) and h.dtype == torch.bfloat16 and weight.shape[0] % 8 == 0
+        out = torch.empty(T, dtype=torch.float32, device=h.device)
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            hc, yc = h[s:e], labels[s:e]
+            if use_k:
+                logits = gemm(hc, weight) if _gemm_ok(hc, weight) else F.linear(hc, weight)
+                loss_rows, _ = _ext.ops().ce_fwd_bwd(logits, yc, None, None, False)
+                _count()
+                out[s:e] = -loss_rows
+            else:
+                logits = F.linear(hc, weight).float()
+                lp = torch.log_softmax(logits, dim=-1)
+                picked = torch.gather(lp, 1, yc.clamp(min=0).unsqueeze(1)).squeeze(1)
+                out[s:e] = picked * (yc != IGNORE_INDEX)
+            del logits
+        ctx.save_for_backward(h, weight, labels)
+        ctx.chunk, ctx.use_k = chunk, use_k
+        return out
+
+    @staticmethod
+    def backward(ctx, gout):
+        h, weight, labels = ctx.saved_tensors
+        chunk, use_k = ctx.chunk, ctx.use_k
+        T = h.shape[0]
+        need_dh, need_dw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        dh = torch.empty_like(h) if need_dh else None
+        dw = torch.zeros_like(weight) if need_dw else None
+        gout = gout.float().contiguous()
+        for s in range(0, T, chunk):
+            e = min(T, s + chunk)
+            hc, yc = h[s:e], labels[s:e]
+            if use_k:
+                tcg = _gemm_ok(hc, weight)
+                logits = gemm(hc, weight) if tcg else F.linear(hc, weight)
+                # d logp = -(softmax - onehot) * g
+                _ext.ops().ce_fwd_bwd(logits, yc, None, (-gout[s:e]).contiguous(), True)
+                _count()
+                g = logits
+                if need_dh:
+                    dh[s:e] = gemm(g, weight, False, True) if tcg else g @ weight
+                if need_dw:
+                    if tcg:
+                        gemm(g, hc, True, True, epilogue=1, out=dw)
+                    else:
+                        dw.addmm_(g.t(), hc)
+            else:
+                logits = F.linear(hc, weight).float()
+                valid = (yc != IGNORE_INDEX)
+                g = -torch.softmax(logits, dim=-1)
+                g[torch.arange(e - s, device=h.device), yc.clamp(min=0)] += 1.0
+                g = (g * (gout[s:e] * valid).unsqueeze(1)).to(h.dtype)
+                if need_dh:
+                    dh[s:e] = g @ weight
+                if need_dw:
+                    dw.addmm_(g.t(), hc)
+            del logits
+        return dh, dw, None, None
+
+
+def fused_linear_logprobs(
+    hidden: torch.Tensor, weight: torch.Tensor, labels: torch.Tensor, chunk_tokens: Optional[int] = None
+) -> torch.Tensor:
+    """``log p(labels)`` per position for ``hidden @ weight.T`` (same leading shape as ``labels``; 0 at
+    ignored positions).  ``labels`` must already be aligned with ``hidden`` (shifted)."""
+    h = hidden.reshape(-1, hidden.shape[-1])
+    if not h.is_contiguous():
+        h = h.contiguous()
+    y = labels.reshape(-1)
+    chunk = chunk_tokens or _ce_chunk_tokens(weight.shape[0])
+    return _FusedLinearLogProbFn.apply(h, weight, y, chunk).view(labels.shape)
+
+
+# ------------------------------------------------------------------------------------------------ optimizer pieces
+def adamw_step(master, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, grad_scale=None, out_lp=None):
+    """Fused AdamW on flat tensors.  ``grad_scale`` is a python float or a one-element device tensor."""
+    if _use_kernels(master) and master.dtype == torch.float32 and grad.dtype == torch.float32 \
+            and exp_avg.dtype == torch.float32 and (out_lp is None or out_lp.dtype == torch.bfloat16):
+        gs = grad_scale
+        if gs is not None and not torch.is_tensor(gs):
+            gs = torch.full((1,), float(gs), dtype=torch.float32, device=master.device) if gs != 1.0 else None
+        _ext.ops().adamw_step(master, grad, exp_avg, exp_avg_sq, out_lp, lr, beta1, beta2, eps, weight_decay, step, gs)
+        _count()
+        return
+    gs = float(grad_scale) if grad_scale is not None else 1.0
+    ref.adamw_step(master, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, gs, out_lp)
+
+
+def sumsq(x: torch.Tensor) -> torch.Tensor:
+    if _use_kernels(x) and x.dtype == torch.float32 and x.is_contiguous():
+        _count()
+        return _ext.ops().sumsq(x)
+    return x.float().pow(2).sum()
+
+
+def accumulate_lp_grad(src: torch.Tensor, acc: torch.Tensor, scale: float, overwrite: bool) -> None:
+    """``acc (fp32) = [acc +] scale * src`` for a low-precision gradient buffer."""
+    if _use_kernels(src) and src.dtype == torch.bfloat16 and acc.dtype == torch.float32 \
+            and src.data_ptr() % 16 == 0 and acc.data_ptr() % 16 == 0:
+        _ext.ops().accum_bf16(src, acc, scale, overwrite)
+        _count()
+        return
+    if overwrite:
+        acc.copy_(src.to(acc.dtype) * scale)
+    else:
+        acc.add_(src.to(acc.dtype), alpha=scale)

@@ -1,0 +1,5 @@
+from .mesh import ParallelGroups
+from .ulysses import UlyssesContext
+from .ulysses import UlyssesDataLoaderAdapter
+
+__all__ = ["ParallelGroups", "UlyssesContext", "UlyssesDataLoaderAdapter"]

@@ -1,0 +1,183 @@
+"""Ulysses sequence parallelism: every rank holds ``S / P`` tokens for everything except core attention,
+around which an all-to-all re-shards sequence -> heads (each rank then attends over the full sequence with
+``Hq / P`` query heads) and back.
+
+Behaviour parity with what the reference gets from its engine dependency
+(arctic_training/trainer/trainer.py:195-202,339-354; arctic_training/trainer/sft_trainer.py:158-164):
+* :class:`UlyssesDataLoaderAdapter` — one batch per rank is all-gathered over the SP group and the group
+  then works through those batches one after the other (so one dataloader step is ``P`` micro-steps);
+  ``labels`` are shifted into ``shift_labels`` *before* the sequence is cut so no token's target lives on
+  another rank; every tensor is sliced to this rank's chunk; non-tensor entries pass through.
+* KV heads are replicated when there are fewer of them than ranks.
+* ``position_ids`` are gathered so that packed-sample boundaries are known for the whole sequence.
+* the loss is the token-weighted mean over the group.
+"""
+
+from __future__ import annotations
+
+from typing import Any
+from typing import Dict
+from typing import Iterator
+from typing import List
+from typing import Optional
+from typing import Tuple
+
+import torch
+import torch.distributed as dist
+
+from .. import ops
+
+IGNORE_INDEX = -100
+
+
+class _SeqToHead(torch.autograd.Function):
+    """[B, S/P, H, D] -> [B, S, H/P, D] over ``group`` (backward is the inverse exchange)."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _seq_to_head(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _head_to_seq(g.contiguous(), ctx.group), None
+
+
+class _HeadToSeq(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, group):
+        ctx.group = group
+        return _head_to_seq(x, group)
+
+    @staticmethod
+    def backward(ctx, g):
+        return _seq_to_head(g.contiguous(), ctx.group), None
+
+
+def _a2a(x: torch.Tensor, group) -> torch.Tensor:
+    out = torch.empty_like(x)
+    dist.all_to_all_single(out, x, group=group)
+    return out
+
+
+def _seq_to_head(x: torch.Tensor, group) -> torch.Tensor:
+    P = dist.get_world_size(group)
+    B, S_loc, H, D = x.shape
+    send = x.reshape(B, S_loc, P, H // P, D).permute(2, 0, 1, 3, 4).contiguous()  # [P, B, S_loc, H/P, D]
+    recv = _a2a(send, group)  # chunk i: sequence chunk of rank i, my head group
+    return recv.permute(1, 0, 2, 3, 4).reshape(B, P * S_loc, H // P, D)
+
+
+def _head_to_seq(x: torch.Tensor, group) -> torch.Tensor:
+    P = dist.get_world_size(group)
+    B, S, Hl, D = x.shape
+    S_loc = S // P
+    send = x.reshape(B, P, S_loc, Hl, D).permute(1, 0, 2, 3, 4).contiguous()  # [P, B, S_loc, Hl, D]
+    recv = _a2a(send, group)  # chunk j: head group j, my sequence chunk
+    return recv.permute(1, 2, 0, 3, 4).reshape(B, S_loc, P * Hl, D)
+
+
+class _SumOverGroup(torch.autograd.Function):
+    """Forward: all-reduce(sum) so every rank reports the same value; backward: identity, each rank keeps the
+    gradient of its own contribution."""
+
+    @staticmethod
+    def forward(ctx, x, group):
+        y = x.clone()
+        dist.all_reduce(y, group=group)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        return g, None
+
+
+class UlyssesContext:
+    def __init__(self, group, size: int, rank: int, fused: bool = False) -> None:
+        self.group, self.size, self.rank = group, size, rank
+        self.fused = fused
+
+    # -- attention -------------------------------------------------------------------------------
+    def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ctx: Any) -> torch.Tensor:
+        P = self.size
+        Hq, Hkv = q.shape[2], k.shape[2]
+        if Hq % P != 0:
+            raise ValueError(f"query heads ({Hq}) must be divisible by sequence_parallel_size ({P})")
+        if Hkv < P:
+            if P % Hkv != 0:
+                raise ValueError(f"sequence_parallel_size ({P}) must be a multiple of the KV heads ({Hkv})")
+            k = k.repeat_interleave(P // Hkv, dim=2)
+            v = v.repeat_interleave(P // Hkv, dim=2)
+        elif Hkv % P != 0:
+            raise ValueError(f"KV heads ({Hkv}) must be divisible by sequence_parallel_size ({P})")
+        qf = _SeqToHead.apply(q.contiguous(), self.group)
+        kf = _SeqToHead.apply(k.contiguous(), self.group)
+        vf = _SeqToHead.apply(v.contiguous(), self.group)
+        o = ops.attention(qf, kf, vf, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
+        return _HeadToSeq.apply(o.contiguous(), self.group)
+
+    # -- packed-sample boundaries -------------------------------------------------------------------
+    def global_cu_seqlens(self, position_ids: torch.Tensor) -> Tuple[Optional[torch.Tensor], int]:
+        from ..models.causal_lm import cu_seqlens_from_position_ids
+
+        parts = [torch.empty_like(position_ids) for _ in range(self.size)]
+        dist.all_gather(parts, position_ids.contiguous(), group=self.group)
+        full = torch.cat(parts, dim=1)
+        cu = cu_seqlens_from_position_ids(full)
+        max_len = int((cu[1:] - cu[:-1]).max()) if cu is not None else full.shape[1]
+        return cu, max_len
+
+    # -- loss ---------------------------------------------------------------------------------------
+    def aggregate_loss(self, loss_sum: torch.Tensor, num_tokens: torch.Tensor) -> torch.Tensor:
+        """Token-weighted mean over the group: identical value on every rank, local gradient."""
+        n = num_tokens.clone().to(torch.float32)
+        dist.all_reduce(n, group=self.group)
+        total = _SumOverGroup.apply(loss_sum.float(), self.group)
+        return total / n.clamp(min=1.0)
+
+    def mean(self, value: torch.Tensor) -> torch.Tensor:
+        return _SumOverGroup.apply(value, self.group) / self.size
+
+
+def shard_batch_for_rank(batch: Dict[str, Any], sp_rank: int, sp_size: int) -> Dict[str, Any]:
+    """``labels`` -> ``shift_labels`` and cut every tensor's sequence dimension to this rank's chunk."""
+    out: Dict[str, Any] = {}
+    seq_len = None
+    for k, v in batch.items():
+        if torch.is_tensor(v) and v.dim() >= 2:
+            seq_len = v.shape[1]
+            break
+    if seq_len is not None and seq_len % sp_size != 0:
+        raise ValueError(f"sequence length {seq_len} is not divisible by sequence_parallel_size {sp_size}")
+    for k, v in batch.items():
+        if k == "labels":
+            shifted = torch.nn.functional.pad(v[..., 1:], (0, 1), value=IGNORE_INDEX)
+            out["shift_labels"] = _chunk(shifted, sp_rank, sp_size)
+        elif torch.is_tensor(v) and v.dim() >= 2:
+            out[k] = _chunk(v, sp_rank, sp_size)
+        else:
+            out[k] = v
+    return out
+
+
+def _chunk(t: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    n = t.shape[1] // size
+    return t[:, rank * n : (rank + 1) * n].contiguous()
+
+
+class UlyssesDataLoaderAdapter:
+    def __init__(self, dl, sp_rank: int, sp_group, sp_world_size: int, device: torch.device) -> None:
+        self.dl, self.sp_rank, self.sp_group, self.sp_world_size, self.device = dl, sp_rank, sp_group, sp_world_size, device
+
+    def __len__(self) -> int:
+        return len(self.dl) * self.sp_world_size
+
+    def __getattr__(self, name: str) -> Any:
+        return getattr(self.dl, name)
+
+    def __iter__(self) -> Iterator[Dict[str, Any]]:
+        for batch in self.dl:
+            gathered: List[Any] = [None] * self.sp_world_size
+            dist.all_gather_object(gathered, batch, group=self.sp_group)
+            for b in gathered:
+                yield shard_batch_for_rank(b, self.sp_rank, self.sp_world_size)

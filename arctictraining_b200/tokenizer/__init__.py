@@ -1,0 +1,6 @@
+from .factory import FakeTokenizerFactory
+from .factory import HFTokenizerFactory
+from .factory import TokenizerFactory
+from .fake import FakeTokenizer
+
+__all__ = ["FakeTokenizerFactory", "HFTokenizerFactory", "TokenizerFactory", "FakeTokenizer"]

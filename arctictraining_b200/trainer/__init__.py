@@ -1,0 +1,5 @@
+from .sft import CausalTrainer
+from .sft import SFTTrainer
+from .trainer import Trainer
+
+__all__ = ["CausalTrainer", "SFTTrainer", "Trainer"]
