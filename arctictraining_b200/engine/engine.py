@@ -251,6 +251,8 @@ class TrainingEngine:
             u.param_names = [names[id(p)] for p in ordered]
             off = 0
             u.offsets = []
+            u.shapes = [tuple(p.shape) for p in ordered]
+            u.numels = [p.numel() for p in ordered]
             for p in ordered:
                 u.offsets.append(off)
                 off += p.numel()
@@ -340,8 +342,8 @@ class TrainingEngine:
 
     # ================================================================== parameter residency (stage 3)
     def _assign_param_views(self, u: ZeroUnit, flat: torch.Tensor) -> None:
-        for p, o in zip(u.params, u.offsets):
-            p.data = flat[o : o + p.numel()].view(p.shape)
+        for p, o, n, shp in zip(u.params, u.offsets, u.numels, u.shapes):
+            p.data = flat[o : o + n].view(shp)
 
     def _release_params(self, u: ZeroUnit) -> None:
         if u.persistent or not u.resident and u.flat is None:
@@ -459,9 +461,9 @@ class TrainingEngine:
         else:
             slot, g = None, torch.zeros(u.numel, dtype=u.dtype, device=self.device)
         u.grad_flat, u.grad_slot = g, slot
-        for p, o in zip(u.params, u.offsets):
+        for p, o, n, shp in zip(u.params, u.offsets, u.numels, u.shapes):
             if p.requires_grad:
-                p.grad = g[o : o + p.numel()].view(p.shape)
+                p.grad = g[o : o + n].view(shp)
 
     def _end_unit_backward(self, u: ZeroUnit) -> None:
         self._reduce_unit(u)
@@ -735,7 +737,7 @@ class TrainingEngine:
                     "global_samples": self.global_samples, "skipped_steps": self.skipped_steps,
                     "dp_world_size": self.world, "mp_world_size": 1, "zero_stage": self.stage,
                     "client_state": client_state or {},
-                    "param_shapes": {n: tuple(p.shape) for u in self.units for n, p in zip(u.param_names, u.params)},
+                    "param_shapes": {n: shp for u in self.units for n, shp in zip(u.param_names, u.shapes)},
                 },
                 d / "mp_rank_00_model_states.pt",
             )

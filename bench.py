@@ -1,0 +1,293 @@
+#!/usr/bin/env python
+"""Headline benchmark: Llama-3.1-8B supervised fine-tuning throughput (tokens/s) on N B200 GPUs.
+
+Config (the one the baseline names): Llama-3.1-8B architecture, random-init bf16 weights, ZeRO-3, AdamW with
+fp32 master weights, sequence length 8192 packed from variable-length synthetic samples (lengths uniform in
+[256, 4096]), micro-batch 1 per GPU, activation checkpointing.  One step = forward + backward + optimizer
+step.  ``value`` is device-timed (CUDA events, max over ranks) with inputs already on the device; ``e2e`` runs
+the same steps through the public trainer API (``SFTTrainer.step``) including the host->device copy of each
+batch from pinned memory and the device->host read of the loss.
+
+    python bench.py --gpus 1 --steps 5 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 --master-port 29500 \
+        bench.py --gpus 8 --steps 5 --warmup 3
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "llama3.1_8b_sft_tokens_per_s"
+
+
+def parse_args():
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=5)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
+    p.add_argument("--model", type=str, default="llama-3.1-8b")
+    p.add_argument("--seq-len", type=int, default=8192)
+    p.add_argument("--zero-stage", type=int, default=3)
+    p.add_argument("--layers", type=int, default=0, help="override the number of layers (debugging only; marks the result invalid)")
+    p.add_argument("--attn", type=str, default="flash_attention_2")
+    p.add_argument("--gemm", type=str, default=os.getenv("ATB200_GEMM", "tcgen05"), choices=["tcgen05", "cublas"])
+    p.add_argument("--skip-e2e", action="store_true")
+    return p.parse_args()
+
+
+def reference_unavailable() -> None:
+    print(json.dumps({
+        "impl": "reference",
+        "unavailable": "reference cannot be installed offline: its build backend (hatchling) and its hard dependency "
+                       "deepspeed are absent from the wheelhouse, and `import arctic_training` fails without deepspeed",
+    }))
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    FIELDS = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+              "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+              "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self) -> None:
+        self.proc = None
+        self.path = Path(tempfile.mkstemp(prefix="atb_clocks_", suffix=".csv")[1])
+
+    def start(self) -> None:
+        try:
+            self.fh = open(self.path, "w")
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.FIELDS}", "--format=csv,noheader,nounits", "-lms", "200"],
+                stdout=self.fh, stderr=subprocess.DEVNULL,
+            )
+        except Exception:
+            self.proc = None
+
+    def stop(self, gpu_indices) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except Exception:
+            self.proc.kill()
+        self.fh.close()
+        clocks, maxes, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in self.path.read_text().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 8:
+                continue
+            try:
+                idx, sm, mx, power = int(parts[0]), float(parts[1]), float(parts[2]), float(parts[3])
+            except ValueError:
+                continue
+            if idx not in gpu_indices or power < 300.0:  # only samples taken under load
+                continue
+            clocks.append(sm)
+            maxes.append(mx)
+            for n, v in zip(names, parts[4:8]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        try:
+            self.path.unlink()
+        except OSError:
+            pass
+        return {
+            "sm_mhz": statistics.median(clocks) if clocks else None,
+            "sm_max_mhz": max(maxes) if maxes else None,
+            "reasons": sorted(reasons),
+            "samples": len(clocks),
+        }
+
+
+def main() -> None:
+    args = parse_args()
+    if args.impl == "reference":
+        reference_unavailable()
+        return
+
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus and world == 1 and args.gpus > 1:
+        raise SystemExit("for --gpus N > 1 launch with torch.distributed.run (one process per GPU)")
+    os.environ.setdefault("AT_LOG_LEVEL", "WARNING")
+    os.environ.setdefault("PYTORCH_CUDA_ALLOC_CONF", "expandable_segments:True")
+
+    from arctictraining_b200 import ops
+    from arctictraining_b200.comm.dist import init_distributed
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.ops import functional as F_ops
+    from arctictraining_b200.registry import get_registered_trainer
+    from arctictraining_b200.trainer.utils import to_device
+
+    init_distributed(local_rank)
+    F_ops.set_gemm_backend(args.gemm)
+    device = torch.device("cuda", torch.cuda.current_device())
+
+    total_steps = args.warmup + args.steps
+    rows_needed = (2 * total_steps + 4) * world
+    workdir = Path(tempfile.gettempdir()) / f"atb200_bench_{os.getuid()}"
+    hf_kwargs = {"num_hidden_layers": args.layers} if args.layers else {}
+    recipe = {
+        "type": "sft",
+        "micro_batch_size": 1,
+        "epochs": 1,
+        "seed": 42,
+        "model": {"name_or_path": args.model, "dtype": "bf16", "attn_implementation": args.attn, "hf_config_kwargs": hf_kwargs},
+        "data": {
+            "sources": [{"type": "synthetic", "num_samples": rows_needed * 4, "min_length": 256, "max_length": 4096,
+                         "prompt_fraction": 0.5, "seed": 1234}],
+            "cache_dir": str(workdir / "cache"),
+            "max_length": args.seq_len,
+            "pack_samples": True,
+            "pad_to": "max_length",
+            "dl_num_workers": 0,
+            "num_proc": 1,
+        },
+        "optimizer": {"lr": 1e-5, "weight_decay": 0.1},
+        "scheduler": {"name": "constant"},
+        "deepspeed": {"zero_optimization": {"stage": args.zero_stage}, "gradient_clipping": 1.0},
+        "train_log_iter_interval": 0,
+        "train_log_metrics_path": str(workdir / f"metrics_{rank}.jsonl"),
+        "logger": {"level": "WARNING"},
+    }
+    config = get_config(recipe)
+    trainer = get_registered_trainer(config.type)(config)
+    engine = trainer.model
+    engine.train()
+
+    batches = []
+    it = iter(trainer.train_dataloader)
+    for _ in range(2 * total_steps):
+        b = next(it)
+        b.pop("packed_sample_seqlens", None)
+        batches.append(b)
+    tokens_per_step = batches[0]["input_ids"].numel() * world
+    h2d_bytes = sum(v.numel() * v.element_size() for v in batches[0].values() if torch.is_tensor(v))
+
+    def barrier():
+        if world > 1:
+            dist.barrier(device_ids=[device.index])
+        torch.cuda.synchronize()
+
+    def device_step(b):
+        out = engine(**b, use_cache=False)
+        engine.backward(out.loss)
+        engine.step()
+        return out.loss
+
+    # ------------------------------------------------------------------ device-timed region
+    dev_batches = [to_device(b, device) for b in batches[:total_steps]]
+    for b in dev_batches[: args.warmup]:
+        device_step(b)
+    barrier()
+    sampler = ClockSampler()
+    if rank == 0:
+        sampler.start()
+    launches0 = ops.LAUNCH_COUNTER["native"]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    start.record()
+    for b in dev_batches[args.warmup :]:
+        loss = device_step(b)
+    end.record()
+    barrier()
+    ms = start.elapsed_time(end)
+    launches = ops.LAUNCH_COUNTER["native"] - launches0
+    clocks = sampler.stop(set(range(world))) if rank == 0 else {}
+    final_loss = float(loss)
+    err = int(torch.ops.atb200.read_and_clear_error_flag(dev_batches[0]["input_ids"]))
+    del dev_batches
+
+    # ------------------------------------------------------------------ end-to-end through the trainer API
+    e2e_ms = None
+    if not args.skip_e2e:
+        e2e_batches = batches[total_steps : 2 * total_steps]
+        for b in e2e_batches[: min(1, args.warmup)]:
+            trainer.metrics.values.clear() if trainer.metrics.enabled else None
+            trainer.step(dict(b))
+        barrier()
+        t0 = time.perf_counter()
+        for b in e2e_batches[min(1, args.warmup) : min(1, args.warmup) + args.steps]:
+            if trainer.metrics.enabled:
+                trainer.metrics.values.clear()
+            trainer.step(dict(b))  # H2D of the pinned batch, fwd, bwd, optimizer step, loss.item()
+        barrier()
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+
+    stats = torch.tensor([ms, e2e_ms if e2e_ms is not None else 0.0], device=device, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+    ms, e2e_ms_max = float(stats[0]), float(stats[1])
+
+    if rank == 0:
+        ms_per_step = ms / args.steps
+        value = tokens_per_step / (ms_per_step / 1e3)
+        cfg = trainer.model_unwrapped.config
+        result = {
+            "metric": METRIC,
+            "value": round(value, 1),
+            "unit": "tokens/s",
+            "n_gpus": world,
+            "steps": args.steps,
+            "warmup": args.warmup,
+            "ms_per_step": round(ms_per_step, 3),
+            "higher_is_better": True,
+            "scaling": "weak",
+            "vs_baseline": None,
+            "dtype": "bf16",
+            "data": "synthetic uniform token ids, packed variable-length samples; random-init weights",
+            "impl": "native",
+            "config": {
+                "model": args.model,
+                "layers": cfg["num_hidden_layers"],
+                "global_batch": world,
+                "seq_len": args.seq_len,
+                "parallelism": f"zero{args.zero_stage}-dp{world}",
+                "optimizer": "adamw fp32 master",
+                "activation_checkpointing": True,
+                "attention": args.attn,
+                "gemm": args.gemm,
+                "l2_policy": "inputs larger than L2 (16 GB of weights streamed every step)",
+                "valid": not args.layers,
+            },
+            "clocks": clocks,
+            "gpu_launches": int(launches),
+            "final_loss": round(final_loss, 4),
+            "kernel_error_flag": err,
+            "max_memory_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2),
+        }
+        if e2e_ms is not None:
+            e2e_per_step = e2e_ms_max / args.steps
+            result["e2e"] = {
+                "value": round(tokens_per_step / (e2e_per_step / 1e3), 1),
+                "unit": "tokens/s",
+                "ms_per_step": round(e2e_per_step, 3),
+                "h2d_bytes_per_step": int(h2d_bytes),
+                "d2h_bytes_per_step": 4,
+            }
+        print(json.dumps(result), flush=True)
+    if world > 1:
+        dist.barrier(device_ids=[device.index])
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,165 @@
+"""Engine correctness on CPU: the flat-buffer engine must reproduce plain PyTorch training, and the ZeRO
+stages / checkpointing / accumulation variants must agree with each other."""
+
+import copy
+
+import pytest
+import torch
+
+from arctictraining_b200.engine import TrainingEngine
+from arctictraining_b200.models.arch import load_arch_config
+from arctictraining_b200.models.causal_lm import CausalLM
+from arctictraining_b200.optimizer.adam import FusedAdamW
+from arctictraining_b200.optimizer.factory import OptimizerFactory
+
+
+def make_model(seed=0, **overrides):
+    cfg = load_arch_config("tiny-llama", overrides)
+    m = CausalLM(cfg, dtype=torch.float32)
+    m.init_weights(seed=seed)
+    return m
+
+
+def make_engine(model, stage, gas=1, clip=1.0, ckpt=True, lr=1e-2, wd=0.1, tiled=False):
+    model.activation_checkpointing = ckpt
+    model.tiled_mlp = tiled
+    groups = OptimizerFactory.get_optimizer_grouped_params(model, wd)
+    opt = FusedAdamW(groups, lr=lr, betas=(0.9, 0.95))
+    return TrainingEngine(model, opt, None, {
+        "zero_optimization": {"stage": stage}, "gradient_accumulation_steps": gas, "gradient_clipping": clip,
+    })
+
+
+def batches(n, bs=2, seq=32, vocab=1024, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        ids = torch.randint(8, vocab, (bs, seq), generator=g)
+        labels = ids.clone()
+        labels[:, : seq // 2] = -100
+        out.append({"input_ids": ids, "labels": labels})
+    return out
+
+
+def run(engine, data):
+    losses = []
+    for b in data:
+        out = engine(**b)
+        engine.backward(out.loss)
+        engine.step()
+        losses.append(float(out.loss))
+    return losses
+
+
+def full_params(engine):
+    return {n: t.clone() for n, t in engine.iter_full_named_parameters()}
+
+
+def test_engine_matches_plain_pytorch():
+    data = batches(4)
+    ref = make_model()
+    eng_model = copy.deepcopy(ref)
+    groups = OptimizerFactory.get_optimizer_grouped_params(ref, 0.1)
+    opt = torch.optim.AdamW(groups, lr=1e-2, betas=(0.9, 0.95), eps=1e-8)
+    ref_losses = []
+    for b in data:
+        out = ref(**b)
+        opt.zero_grad()
+        out.loss.backward()
+        torch.nn.utils.clip_grad_norm_(ref.parameters(), 1.0)
+        opt.step()
+        ref_losses.append(float(out.loss))
+    engine = make_engine(eng_model, stage=0)
+    losses = run(engine, data)
+    assert losses == pytest.approx(ref_losses, rel=1e-4, abs=1e-5)
+    mine = full_params(engine)
+    for n, p in ref.named_parameters():
+        assert torch.allclose(mine[n], p.data, atol=2e-5, rtol=1e-4), n
+
+
+@pytest.mark.parametrize("stage", [1, 2, 3])
+def test_zero_stages_agree_with_stage0(stage):
+    data = batches(3)
+    base = run(make_engine(make_model(), 0), data)
+    assert run(make_engine(make_model(), stage), data) == pytest.approx(base, rel=1e-5)
+
+
+def test_checkpointing_and_tiled_mlp_do_not_change_results():
+    data = batches(3, seq=160)
+    a = make_engine(make_model(), 3, ckpt=True)
+    b = make_engine(make_model(), 0, ckpt=False)
+    c = make_engine(make_model(), 3, ckpt=True, tiled=True)
+    la, lb, lc = run(a, data), run(b, data), run(c, data)
+    assert la == pytest.approx(lb, rel=1e-5)
+    assert lc == pytest.approx(lb, rel=1e-5)
+    pa, pb, pc = full_params(a), full_params(b), full_params(c)
+    for n in pa:
+        assert (pa[n] - pb[n]).abs().mean() < 1e-5, n
+        # tiling changes the summation order of weight gradients; Adam turns that into small parameter noise
+        assert (pc[n] - pb[n]).abs().mean() < 1e-4, n
+
+
+def test_gradient_accumulation_equals_big_batch():
+    data = batches(4, bs=2)
+    big = [{k: torch.cat([data[i][k], data[i + 1][k]]) for k in data[0]} for i in (0, 2)]
+    e_big = make_engine(make_model(), 0, gas=1)
+    e_acc = make_engine(make_model(), 2, gas=2)
+    run(e_big, big)
+    run(e_acc, data)
+    assert e_acc.global_steps == 2 and e_big.global_steps == 2
+    pb, pa = full_params(e_big), full_params(e_acc)
+    for n in pb:
+        assert torch.allclose(pa[n], pb[n], atol=5e-5, rtol=1e-3), n
+
+
+def test_grad_norm_is_reported_and_clipping_applies():
+    data = batches(1)
+    e = make_engine(make_model(), 0, clip=1e-3, lr=1.0, wd=0.0)
+    before = full_params(e)
+    run(e, data)
+    assert e.get_global_grad_norm() > 1e-3
+    after = full_params(e)
+    # with Adam the first update has magnitude ~lr regardless of the clip, so only check it ran and is finite
+    assert all(torch.isfinite(after[n]).all() for n in after)
+    assert any(not torch.equal(after[n], before[n]) for n in after)
+
+
+def test_frozen_parameters_get_no_state_and_do_not_move():
+    m = make_model()
+    for p in m.model.embed_tokens.parameters():
+        p.requires_grad_(False)
+    e = make_engine(m, 2)
+    emb_before = m.model.embed_tokens.weight.detach().clone()
+    run(e, batches(2))
+    assert torch.equal(m.model.embed_tokens.weight.detach(), emb_before)
+    embed_unit = next(u for u in e.units if u.name == "embed")
+    assert embed_unit.master is None
+
+
+def test_engine_checkpoint_roundtrip(tmp_path):
+    data = batches(4)
+    a = make_engine(make_model(), 2)
+    run(a, data[:2])
+    a.save_checkpoint(tmp_path, tag="t", client_state={"hello": 1})
+    rest_a = run(a, data[2:])
+    b = make_engine(make_model(seed=123), 2)
+    path, cs = b.load_checkpoint(tmp_path)
+    assert cs == {"hello": 1} and b.global_steps == 2
+    rest_b = run(b, data[2:])
+    assert rest_b == rest_a
+    pa, pb = full_params(a), full_params(b)
+    assert all(torch.equal(pa[n], pb[n]) for n in pa)
+
+
+def test_inference_engine_stage3_releases_layers():
+    m = make_model()
+    for p in m.parameters():
+        p.requires_grad_(False)
+    m.eval()
+    ref_out = copy.deepcopy(m)(input_ids=torch.arange(8, 40).unsqueeze(0), return_logits=True).logits
+    e = TrainingEngine(m, None, None, {"zero_optimization": {"stage": 3}}, training=False)
+    with torch.no_grad():
+        out = e(input_ids=torch.arange(8, 40).unsqueeze(0), return_logits=True).logits
+    assert torch.allclose(out, ref_out, atol=1e-5)
+    layer_units = [u for u in e.units if u.name.startswith("layer")]
+    assert all(u.flat is None for u in layer_units)

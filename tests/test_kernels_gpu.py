@@ -1,0 +1,252 @@
+"""Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op."""
+
+import math
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def k():
+    from arctictraining_b200.ops import _ext
+
+    _ext.require()
+    return torch.ops.atb200
+
+
+def _check_flag(x):
+    assert int(torch.ops.atb200.read_and_clear_error_flag(x)) == 0
+
+
+def _rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+@pytest.mark.parametrize("T,H", [(7, 64), (513, 4096), (33, 2048), (5, 8192)])
+def test_rmsnorm_fwd_bwd(k, T, H):
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+    dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    y, rstd = k.rmsnorm_fwd(x, w, 1e-5)
+    xr = x.float().requires_grad_(True)
+    wr = w.float().requires_grad_(True)
+    yr = ref.rms_norm(xr, wr, 1e-5)
+    yr.backward(dy.float())
+    assert _rel(y, yr) < 1e-2
+    dx, dw = k.rmsnorm_bwd(dy, x, w, rstd)
+    assert _rel(dx, xr.grad) < 1e-2
+    assert _rel(dw, wr.grad) < 1e-2
+
+
+def test_rope_matches_reference_and_inverts(k):
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    T, Hq, Hkv, D = 300, 8, 2, 128
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    pos = torch.arange(T, device="cuda").unsqueeze(0)
+    cos, sin = ref.rope_cos_sin(pos, D, 500000.0)
+    q_ref = ref.rope_apply(qkv[:, : Hq * D].reshape(1, T, Hq, D), cos, sin)
+    orig = qkv.clone()
+    k.rope_inplace(qkv[:, : Hq * D].unflatten(1, (Hq, D)), cos[0].contiguous(), sin[0].contiguous(), False)
+    assert _rel(qkv[:, : Hq * D].reshape(1, T, Hq, D), q_ref) < 1e-2
+    assert torch.equal(qkv[:, Hq * D :], orig[:, Hq * D :])  # k and v untouched by this call
+    k.rope_inplace(qkv[:, : Hq * D].unflatten(1, (Hq, D)), cos[0].contiguous(), sin[0].contiguous(), True)
+    assert _rel(qkv, orig) < 2e-2
+
+
+def test_swiglu_fwd_bwd(k):
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    T, I = 257, 1536
+    gu = torch.randn(T, 2 * I, device="cuda", dtype=torch.bfloat16)
+    dout = torch.randn(T, I, device="cuda", dtype=torch.bfloat16)
+    out = k.swiglu_fwd(gu)
+    gr = gu.float().requires_grad_(True)
+    o_ref = ref.swiglu_interleaved(gr)
+    o_ref.backward(dout.float())
+    assert _rel(out, o_ref) < 1e-2
+    assert _rel(k.swiglu_bwd(dout, gu), gr.grad) < 1e-2
+
+
+@pytest.mark.parametrize("n", [1024, 4099, 1 << 20])
+def test_adamw_matches_torch(k, n):
+    torch.manual_seed(0)
+    p = torch.randn(n, device="cuda")
+    g = torch.randn(n, device="cuda")
+    m = torch.zeros(n, device="cuda")
+    v = torch.zeros(n, device="cuda")
+    lp = torch.empty(n, device="cuda", dtype=torch.bfloat16) if n % 4 == 0 else None
+    pr = p.clone().requires_grad_(True)
+    opt = torch.optim.AdamW([pr], lr=1e-2, betas=(0.9, 0.95), eps=1e-8, weight_decay=0.1)
+    scale = torch.tensor([0.5], device="cuda")
+    for step in range(1, 4):
+        pr.grad = g * 0.5
+        opt.step()
+        k.adamw_step(p, g, m, v, lp, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, scale)
+    assert _rel(p, pr.detach()) < 1e-5
+    if lp is not None:
+        assert _rel(lp, p) < 5e-3
+
+
+def test_sumsq_and_accum(k):
+    torch.manual_seed(0)
+    x = torch.randn(1 << 20, device="cuda")
+    assert abs(float(k.sumsq(x)) - float(x.double().pow(2).sum())) / float(x.double().pow(2).sum()) < 1e-5
+    src = torch.randn(10007 * 8, device="cuda", dtype=torch.bfloat16)
+    acc = torch.ones(10007 * 8, device="cuda")
+    k.accum_bf16(src, acc, 0.25, False)
+    assert _rel(acc, 1 + 0.25 * src.float()) < 1e-6
+    k.accum_bf16(src, acc, 2.0, True)
+    assert _rel(acc, 2.0 * src.float()) < 1e-6
+
+
+@pytest.mark.parametrize("T,V", [(9, 1024), (130, 32000), (17, 128256)])
+def test_cross_entropy_kernel(k, T, V):
+    torch.manual_seed(0)
+    logits = (3 * torch.randn(T, V, device="cuda")).bfloat16()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    labels[::4] = -100
+    lr = logits.float().requires_grad_(True)
+    loss_ref = torch.nn.functional.cross_entropy(lr, labels, ignore_index=-100, reduction="sum")
+    loss_ref.backward()
+    scale = torch.tensor([0.5], device="cuda")
+    work = logits.clone()
+    loss, lse = k.ce_fwd_bwd(work, labels, scale, None, True)
+    assert abs(float(loss.sum()) - float(loss_ref)) / float(loss_ref) < 2e-3
+    assert _rel(work, 0.5 * lr.grad) < 2e-2
+    assert torch.all(work[::4] == 0)
+
+
+GEMM_SHAPES = [(128, 256, 64), (256, 512, 128), (300, 264, 200), (1024, 4096, 4096), (8, 8, 8), (4096, 1024, 8192), (520, 1032, 72)]
+
+
+@pytest.mark.parametrize("M,N,K", GEMM_SHAPES)
+def test_gemm_tn(k, M, N, K):
+    torch.manual_seed(0)
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = k.gemm_bf16(a, b, False, False, 0, None, 0)
+    torch.cuda.synchronize()
+    _check_flag(a)
+    ref = a.float() @ b.float().t()
+    assert _rel(c, ref) < 1e-2
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 512, 128), (304, 264, 200), (1024, 2048, 4096)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, True), (True, False), (True, True)])
+def test_gemm_mn_major_operands(k, M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16) if a_mn else torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) if b_mn else torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = k.gemm_bf16(a, b, a_mn, b_mn, 0, None, 0)
+    torch.cuda.synchronize()
+    _check_flag(a)
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    assert _rel(c, af @ bf) < 1e-2
+
+
+def test_gemm_accumulate_and_swiglu_epilogues(k):
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    M, N, K = 384, 768, 256
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (0.1 * torch.randn(N, K, device="cuda")).bfloat16()
+    base = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out = base.clone()
+    k.gemm_bf16(a, b, False, False, 1, out, 0)
+    assert _rel(out, base.float() + a.float() @ b.float().t()) < 1e-2
+    h = k.gemm_bf16(a, b, False, False, 2, None, 0)
+    torch.cuda.synchronize()
+    _check_flag(a)
+    assert h.shape == (M, N // 2)
+    assert _rel(h, ref.swiglu_interleaved(a.float() @ b.float().t())) < 1e-2
+
+
+def test_gemm_is_deterministic(k):
+    torch.manual_seed(0)
+    a = torch.randn(1024, 1024, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(2048, 1024, device="cuda", dtype=torch.bfloat16)
+    c1 = k.gemm_bf16(a, b, False, False, 0, None, 0)
+    c2 = k.gemm_bf16(a, b, False, False, 0, None, 0)
+    assert torch.equal(c1, c2)
+
+
+def test_linear_autograd_matches_torch():
+    from arctictraining_b200 import ops
+
+    torch.manual_seed(0)
+    x = torch.randn(4, 96, 512, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(1024, 512, device="cuda")).bfloat16().requires_grad_(True)
+    y = ops.linear(x, w)
+    g = torch.randn_like(y)
+    y.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    yr = torch.nn.functional.linear(xr, wr)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 1e-2 and _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+
+
+def test_linear_swiglu_autograd():
+    from arctictraining_b200 import ops
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    x = torch.randn(200, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(1024, 256, device="cuda")).bfloat16().requires_grad_(True)
+    h = ops.linear_swiglu(x, w)
+    g = torch.randn_like(h)
+    h.backward(g)
+    xr = x.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    hr = ref.swiglu_interleaved(torch.nn.functional.linear(xr, wr))
+    hr.backward(g.float())
+    assert _rel(h, hr) < 1e-2 and _rel(x.grad, xr.grad) < 2e-2 and _rel(w.grad, wr.grad) < 2e-2
+
+
+def test_fused_linear_cross_entropy_matches_torch():
+    from arctictraining_b200 import ops
+
+    torch.manual_seed(0)
+    T, H, V = 700, 256, 4096
+    h = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(V, H, device="cuda")).bfloat16().requires_grad_(True)
+    y = torch.randint(0, V, (T,), device="cuda")
+    y[:100] = -100
+    loss_sum, n = ops.fused_linear_cross_entropy(h, w, y, chunk_tokens=256)
+    (loss_sum / n).backward()
+    hr = h.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    lr = torch.nn.functional.cross_entropy(hr @ wr.t(), y, ignore_index=-100)
+    lr.backward()
+    assert abs(float(loss_sum / n) - float(lr)) < 2e-2
+    assert _rel(h.grad, hr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
+
+
+def test_fused_linear_logprobs_matches_torch():
+    from arctictraining_b200 import ops
+
+    torch.manual_seed(0)
+    T, H, V = 300, 128, 2048
+    h = torch.randn(T, H, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    w = (0.05 * torch.randn(V, H, device="cuda")).bfloat16().requires_grad_(True)
+    y = torch.randint(0, V, (T,), device="cuda")
+    y[::3] = -100
+    lp = ops.fused_linear_logprobs(h, w, y, chunk_tokens=128)
+    coef = torch.randn(T, device="cuda")
+    (lp * coef).sum().backward()
+    hr = h.detach().float().requires_grad_(True)
+    wr = w.detach().float().requires_grad_(True)
+    lpr = torch.log_softmax(hr @ wr.t(), -1).gather(1, y.clamp(min=0).unsqueeze(1)).squeeze(1) * (y != -100)
+    (lpr * coef).sum().backward()
+    assert _rel(lp, lpr) < 2e-2
+    assert _rel(h.grad, hr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
