@@ -22,6 +22,15 @@ std::tuple<at::Tensor, at::Tensor> ce_fwd_bwd(at::Tensor logits, const at::Tenso
 at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
                      const c10::optional<at::Tensor>& out, int64_t max_ctas);
 int64_t read_and_clear_error_flag(const at::Tensor& like);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_topk_gating_fwd(const at::Tensor& logits, int64_t K, bool normalize);
+at::Tensor moe_topk_gating_bwd(const at::Tensor& dscores, const at::Tensor& probs, const at::Tensor& experts,
+                               const c10::optional<at::Tensor>& dprobs_extra, bool normalize);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_assign_slots(const at::Tensor& experts, int64_t E, int64_t align);
+at::Tensor moe_scatter_fwd(const at::Tensor& x, const at::Tensor& slots, int64_t out_rows);
+at::Tensor moe_scatter_bwd(const at::Tensor& dout, const at::Tensor& slots);
+at::Tensor moe_gather_fwd(const at::Tensor& y, const at::Tensor& slots, const at::Tensor& scores);
+std::tuple<at::Tensor, at::Tensor> moe_gather_bwd(const at::Tensor& dout, const at::Tensor& y, const at::Tensor& slots,
+                                                  const at::Tensor& scores);
 }  // namespace atb
 
 TORCH_LIBRARY(atb200, m) {
@@ -41,4 +50,12 @@ TORCH_LIBRARY(atb200, m) {
     m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas) -> Tensor",
           &atb::gemm_bf16);
     m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);
+    m.def("moe_topk_gating_fwd(Tensor logits, int K, bool normalize) -> (Tensor, Tensor, Tensor)", &atb::moe_topk_gating_fwd);
+    m.def("moe_topk_gating_bwd(Tensor dscores, Tensor probs, Tensor experts, Tensor? dprobs_extra, bool normalize) -> Tensor",
+          &atb::moe_topk_gating_bwd);
+    m.def("moe_assign_slots(Tensor experts, int E, int align) -> (Tensor, Tensor, Tensor)", &atb::moe_assign_slots);
+    m.def("moe_scatter_fwd(Tensor x, Tensor slots, int out_rows) -> Tensor", &atb::moe_scatter_fwd);
+    m.def("moe_scatter_bwd(Tensor dout, Tensor slots) -> Tensor", &atb::moe_scatter_bwd);
+    m.def("moe_gather_fwd(Tensor y, Tensor slots, Tensor scores) -> Tensor", &atb::moe_gather_fwd);
+    m.def("moe_gather_bwd(Tensor dout, Tensor y, Tensor slots, Tensor scores) -> (Tensor, Tensor)", &atb::moe_gather_bwd);
 }

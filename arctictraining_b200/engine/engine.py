@@ -273,7 +273,10 @@ class TrainingEngine:
                 p.data = flat[o : o + p.numel()].view(p.shape)
             u.flat = flat
             lo = u.group_rank * u.shard_size
-            u.persistent = not (self.stage == 3 and u.checkpointed and u.numel >= self._persist_threshold())
+            # a group of one rank has nothing to gather: the shard is the whole unit and stays in place
+            u.persistent = not (
+                self.stage == 3 and u.checkpointed and u.group_size > 1 and u.numel >= self._persist_threshold()
+            )
             if self.stage == 3 and not u.persistent:
                 u.shard = flat[lo : lo + u.shard_size].clone()
                 max_pool_numel = max(max_pool_numel, u.numel)

@@ -1,0 +1,178 @@
+"""ArcticMoE: a mixture-of-experts feed-forward block with expert parallelism.
+
+Behaviour parity: arctic_training/model/moe/moe.py:33-509 — softmax-then-top-k routing with optional
+renormalisation, load-balancing loss applied as an analytic gradient on the router probabilities
+(``grad += freq * loss_coeff / tokens / ep_size``), expert-major token permutation, variable-split
+all-to-all over the expert-parallel group, grouped gate/up GEMM -> SwiGLU -> grouped down GEMM, the inverse
+exchange and a score-weighted combine; optional sigmoid-gated shared expert; routing replay.
+
+Differences by design: slot assignment is deterministic (no atomics), expert segments are padded to
+128-row tiles instead of a globally all-reduced capacity, weights are stored ``[experts, out, in]`` with
+gate/up rows block-interleaved so the grouped GEMM can apply SwiGLU in its epilogue, and token counts stay
+on the device except for the one exchange of split sizes that the NCCL baseline path needs.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Any
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+import torch.nn as nn
+import torch.nn.functional as F
+
+from .. import ops
+from ..models.arch import ArchConfig
+from ..ops import reference as ref
+from . import ops as mops
+from .alltoall import all_to_all_v
+from .grouped import grouped_mlp
+
+SEGMENT_ALIGN = 128
+
+
+@dataclass
+class MoEConfig:
+    model_dim: int
+    intermediate_dim: int
+    num_experts: int
+    top_k: int
+    normalize_topk_scores: bool = True
+    loss_coeff: float = 0.01
+    act_fn: str = "silu"
+    is_gated: bool = True
+    use_shared_expert: bool = False
+    shared_intermediate_dim: int = 0
+    ep_size: int = 1
+    ep_rank: int = 0
+    ep_group: Any = None
+    input_dtype: torch.dtype = torch.bfloat16
+    return_router_scores: bool = False
+    use_fused_kernels: bool = True
+    enable_routing_replay: bool = False
+
+
+class ArcticMoE(nn.Module):
+    def __init__(self, config: MoEConfig, dtype=None, device=None) -> None:
+        super().__init__()
+        c = self._config = config
+        assert c.num_experts % c.ep_size == 0, "num_experts must be divisible by the expert-parallel size"
+        self.num_experts, self.top_k = c.num_experts, c.top_k
+        self.ep_size, self.ep_rank, self.ep_group = c.ep_size, c.ep_rank, c.ep_group
+        self.num_local_experts = c.num_experts // c.ep_size
+        H, I, El = c.model_dim, c.intermediate_dim, self.num_local_experts
+        self.router_gate = nn.Parameter(torch.empty(c.num_experts, H, dtype=dtype, device=device))
+        self.expert_gate_up = nn.Parameter(torch.empty(El, 2 * I, H, dtype=dtype, device=device))
+        self.expert_down = nn.Parameter(torch.empty(El, H, I, dtype=dtype, device=device))
+        for p in (self.expert_gate_up, self.expert_down):
+            p.is_expert_param = True
+        if c.use_shared_expert:
+            Is = c.shared_intermediate_dim or I
+            self.shared_expert_gate_up = nn.Parameter(torch.empty(2 * Is, H, dtype=dtype, device=device))
+            self.shared_expert_down = nn.Parameter(torch.empty(H, Is, dtype=dtype, device=device))
+            self.shared_expert_output_gate = nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+        self.replay_assignments: Optional[torch.Tensor] = None
+        self.recorded_assignments: Optional[torch.Tensor] = None
+        self.last_expert_counts: Optional[torch.Tensor] = None
+        self.pending_aux_loss = None
+
+    @property
+    def local_expert_indices(self) -> range:
+        return range(self.ep_rank * self.num_local_experts, (self.ep_rank + 1) * self.num_local_experts)
+
+    # ------------------------------------------------------------------ routing
+    def route(self, x: torch.Tensor):
+        c = self._config
+        logits = F.linear(x, self.router_gate).float()
+        T = x.shape[0]
+        if c.enable_routing_replay and self.replay_assignments is not None:
+            experts = self.replay_assignments.to(torch.int32)
+            probs = torch.softmax(logits, dim=-1)
+            scores = torch.gather(probs, 1, experts.long())
+            if c.normalize_topk_scores:
+                scores = scores / scores.sum(-1, keepdim=True)
+            lb = None
+        else:
+            # load-balancing term: d(sum_e mean_t(p_te) * freq_e)/dp = freq / T; freq needs the routing itself,
+            # so route once without gradient to count, then with the analytic term attached.
+            lb = None
+            if self.training and c.loss_coeff > 0 and torch.is_grad_enabled():
+                with torch.no_grad():
+                    _, ex0, _ = mops.topk_gating(logits.detach(), self.top_k, c.normalize_topk_scores)
+                    freq = torch.bincount(ex0.reshape(-1).long(), minlength=self.num_experts).float()
+                    freq = freq / freq.sum().clamp(min=1)
+                lb = freq * (c.loss_coeff / T / self.ep_size)
+            scores, experts, probs = mops.topk_gating(logits, self.top_k, c.normalize_topk_scores, lb)
+        if c.enable_routing_replay:
+            self.recorded_assignments = experts.detach()
+        return scores, experts
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, hidden_states: torch.Tensor, *_: Any) -> torch.Tensor:
+        shp = hidden_states.shape
+        x = hidden_states.reshape(-1, shp[-1])
+        T = x.shape[0]
+        scores, experts = self.route(x)
+        if self.ep_size == 1:
+            slots, counts, offsets = mops.assign_slots(experts, self.num_experts, SEGMENT_ALIGN)
+            rows = T * self.top_k + self.num_experts * (SEGMENT_ALIGN - 1)
+            rows = (rows + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
+            permuted = mops.scatter_rows(x, slots, rows)
+            y = grouped_mlp(permuted, offsets, self.expert_gate_up, self.expert_down)
+            out = mops.gather_rows(y, slots, scores)
+        else:
+            out = self._forward_ep(x, scores, experts)
+        self.last_expert_counts = None
+        if self._config.use_shared_expert:
+            sh = F.linear(ops.swiglu_interleaved(F.linear(x, self.shared_expert_gate_up)), self.shared_expert_down)
+            gate = torch.sigmoid(F.linear(x, self.shared_expert_output_gate))
+            out = out + gate * sh
+        return out.view(shp)
+
+    def _forward_ep(self, x: torch.Tensor, scores: torch.Tensor, experts: torch.Tensor) -> torch.Tensor:
+        """Expert parallel path over NCCL: send buffer is (destination rank, local expert)-major, i.e. plain
+        global-expert-major; the receiver regroups rank-major chunks into expert-major tile-aligned segments."""
+        P, El, K = self.ep_size, self.num_local_experts, self.top_k
+        T = x.shape[0]
+        slots, counts, _ = mops.assign_slots(experts, self.num_experts, 1)
+        send = mops.scatter_rows(x, slots, T * K)
+        # counts[src][e] for my local experts from every source rank
+        recv_counts = torch.empty_like(counts)
+        dist.all_to_all_single(recv_counts, counts, group=self.ep_group)  # [P * El]: (src rank, local expert)
+        send_splits = counts.view(P, El).sum(1)
+        recv_splits = recv_counts.view(P, El).sum(1)
+        splits = torch.stack([send_splits, recv_splits]).tolist()  # the one host sync of the baseline path
+        recv = all_to_all_v(send, splits[0], splits[1], self.ep_group)
+        # regroup: received rows are ordered (src, expert); build expert-major aligned slots for them
+        n_recv = recv.shape[0]
+        src_expert = torch.repeat_interleave(
+            torch.arange(P * El, device=x.device, dtype=torch.int32) % El, recv_counts.long(), output_size=n_recv
+        )
+        r_slots, r_counts, r_offsets = mops.assign_slots(src_expert.view(-1, 1), El, SEGMENT_ALIGN)
+        rows = n_recv + El * (SEGMENT_ALIGN - 1)
+        rows = max(SEGMENT_ALIGN, (rows + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN)
+        permuted = mops.scatter_rows(recv, r_slots, rows)
+        y = grouped_mlp(permuted, r_offsets, self.expert_gate_up, self.expert_down)
+        ones = torch.ones(n_recv, 1, dtype=torch.float32, device=x.device)
+        back = mops.gather_rows(y, r_slots, ones)  # undo the regrouping (one source row per received row)
+        returned = all_to_all_v(back, splits[1], splits[0], self.ep_group)
+        return mops.gather_rows(returned, slots, scores)
+
+
+def build_moe_block(cfg: ArchConfig, dtype=None, device=None, ep_size: int = 1, ep_rank: int = 0, ep_group=None) -> ArcticMoE:
+    """ArcticMoE configured from a Hugging Face style architecture dict (Qwen3-MoE naming)."""
+    mc = MoEConfig(
+        model_dim=cfg["hidden_size"],
+        intermediate_dim=cfg.get("moe_intermediate_size") or cfg["intermediate_size"],
+        num_experts=cfg.get("num_experts") or cfg.get("num_local_experts"),
+        top_k=cfg.get("num_experts_per_tok", 2),
+        normalize_topk_scores=bool(cfg.get("norm_topk_prob", True)),
+        loss_coeff=float(cfg.get("router_aux_loss_coef", 0.01) or 0.0),
+        use_shared_expert=bool(cfg.get("shared_expert_intermediate_size")),
+        shared_intermediate_dim=int(cfg.get("shared_expert_intermediate_size") or 0),
+        ep_size=ep_size, ep_rank=ep_rank, ep_group=ep_group,
+        input_dtype=dtype or torch.bfloat16,
+    )
+    return ArcticMoE(mc, dtype=dtype, device=device)

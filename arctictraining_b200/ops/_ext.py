@@ -41,13 +41,32 @@ def lib_path() -> Path:
     return BUILD_DIR / f"{LIB_NAME}.so"
 
 
+def source_hash() -> str:
+    """Content hash of every source and header of the extension (decides whether the library is stale)."""
+    import hashlib
+
+    h = hashlib.sha256()
+    for p in sorted(CSRC.glob("*.cu")) + sorted(CSRC.glob("*.cpp")) + sorted(CSRC.glob("*.cuh")) + sorted(CSRC.glob("*.h")):
+        h.update(p.name.encode())
+        h.update(p.read_bytes())
+    h.update(" ".join(NVCC_FLAGS).encode())
+    return h.hexdigest()
+
+
+def _hash_file() -> Path:
+    return BUILD_DIR / f"{LIB_NAME}.sha256"
+
+
 def _stale() -> bool:
     lib = lib_path()
     if not lib.exists():
         return True
     if os.getenv("ATB200_REBUILD") == "1":
         return True
-    return False
+    try:
+        return _hash_file().read_text().strip() != source_hash()
+    except OSError:
+        return True
 
 
 def build(verbose: bool = False) -> Path:
@@ -68,6 +87,7 @@ def build(verbose: bool = False) -> Path:
         is_python_module=False,
         verbose=verbose,
     )
+    _hash_file().write_text(source_hash())
     global _loaded
     _loaded = True
     return lib_path()

@@ -217,18 +217,23 @@ class _LinearFn(torch.autograd.Function):
 
 
 class _LinearSwiGLUFn(torch.autograd.Function):
-    """h = swiglu(x W_gu^T) with the activation applied in the GEMM epilogue (gate/up never hit memory
-    in the forward pass; the backward recomputes them)."""
+    """h = swiglu(x W_gu^T).  When no gradient is needed (the first pass of a checkpointed layer, evaluation)
+    the activation is applied in the GEMM epilogue and gate/up never reach memory.  When a gradient is
+    needed (the recompute pass that directly precedes the backward) gate/up are kept for the backward, which
+    saves recomputing the largest GEMM of the layer a second time."""
 
     @staticmethod
     def forward(ctx, x2, w_gu):
-        ctx.save_for_backward(x2, w_gu)
-        return gemm(x2, w_gu, epilogue=2)
+        if not (ctx.needs_input_grad[0] or ctx.needs_input_grad[1]):
+            return gemm(x2, w_gu, epilogue=2)
+        gu = gemm(x2, w_gu)
+        ctx.save_for_backward(x2, w_gu, gu)
+        _count()
+        return _ext.ops().swiglu_fwd(gu)
 
     @staticmethod
     def backward(ctx, dh):
-        x2, w_gu = ctx.saved_tensors
-        gu = gemm(x2, w_gu)
+        x2, w_gu, gu = ctx.saved_tensors
         _count()
         dgu = _ext.ops().swiglu_bwd(dh.contiguous(), gu)
         del gu

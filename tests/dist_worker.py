@@ -1,0 +1,128 @@
+"""Worker run by the multi-process CPU tests (Gloo, world size 2..4).  Usage:
+``python tests/dist_worker.py <scenario> <out_dir>`` under the framework's launcher."""
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from arctictraining_b200.comm.dist import init_distributed  # noqa: E402
+from arctictraining_b200.engine import TrainingEngine  # noqa: E402
+from arctictraining_b200.models.arch import load_arch_config  # noqa: E402
+from arctictraining_b200.models.causal_lm import CausalLM  # noqa: E402
+from arctictraining_b200.optimizer.adam import FusedAdamW  # noqa: E402
+from arctictraining_b200.optimizer.factory import OptimizerFactory  # noqa: E402
+
+
+def make_engine(stage, gas=1, seed=0, preset="tiny-llama", **kw):
+    cfg = load_arch_config(preset)
+    m = CausalLM(cfg, dtype=torch.float32)
+    m.init_weights(seed=seed)
+    opt = FusedAdamW(OptimizerFactory.get_optimizer_grouped_params(m, 0.1), lr=1e-2, betas=(0.9, 0.95))
+    return TrainingEngine(m, opt, None, {"zero_optimization": {"stage": stage}, "gradient_accumulation_steps": gas,
+                                         "gradient_clipping": 1.0, **kw})
+
+
+def global_batches(n, world, bs=2, seq=32, vocab=1024, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    out = []
+    for _ in range(n):
+        ids = torch.randint(8, vocab, (bs * world, seq), generator=g)
+        labels = ids.clone()
+        labels[:, : seq // 2] = -100
+        out.append({"input_ids": ids, "labels": labels})
+    return out
+
+
+def scenario_zero(out_dir, stage):
+    rank, world = dist.get_rank(), dist.get_world_size()
+    engine = make_engine(stage)
+    losses = []
+    for b in global_batches(3, world):
+        local = {k: v[rank::world] for k, v in b.items()}
+        # every rank normalises by its own token count; make the counts equal so the mean of means is the global mean
+        out = engine(**local)
+        engine.backward(out.loss)
+        engine.step()
+        t = out.loss.detach().clone()
+        dist.all_reduce(t)
+        losses.append(float(t) / world)
+    released = [u.flat is None for u in engine.units if u.name.startswith("layer")]
+    params = {n: t.clone() for n, t in engine.iter_full_named_parameters()}
+    if rank == 0:
+        torch.save({"losses": losses, "params": params, "released": released, "norm": engine.get_global_grad_norm()},
+                   Path(out_dir) / f"zero{stage}.pt")
+
+
+def scenario_resume(out_dir):
+    rank, world = dist.get_rank(), dist.get_world_size()
+    data = [{k: v[rank::world] for k, v in b.items()} for b in global_batches(4, world)]
+
+    def run(e, items):
+        res = []
+        for b in items:
+            out = e(**b)
+            e.backward(out.loss)
+            e.step()
+            res.append(float(out.loss))
+        return res
+
+    a = make_engine(3)
+    run(a, data[:2])
+    a.save_checkpoint(Path(out_dir) / "ckpt", tag="t", client_state={"k": 1})
+    rest_a = run(a, data[2:])
+    b = make_engine(3, seed=99)
+    _, cs = b.load_checkpoint(Path(out_dir) / "ckpt")
+    rest_b = run(b, data[2:])
+    ok = rest_a == rest_b and cs == {"k": 1}
+    flags = [None] * world
+    dist.all_gather_object(flags, ok)
+    if rank == 0:
+        (Path(out_dir) / "resume.json").write_text(json.dumps({"ok": all(flags), "a": rest_a, "b": rest_b}))
+
+
+def scenario_trainer(out_dir, recipe_path):
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    cfg = get_config(Path(recipe_path))
+    trainer = get_registered_trainer(cfg.type)(cfg)
+    trainer.train()
+
+
+def scenario_rank_failure(out_dir):
+    """Rank 1 raises before the first collective of the step; the launcher must take the job down."""
+    if dist.get_rank() == 1:
+        raise RuntimeError("injected failure on rank 1")
+    import time
+
+    time.sleep(60)
+
+
+def main():
+    scenario, out_dir = sys.argv[1], sys.argv[2]
+    init_distributed(timeout_s=60)
+    if scenario.startswith("zero"):
+        scenario_zero(out_dir, int(scenario[4:]))
+    elif scenario == "resume":
+        scenario_resume(out_dir)
+    elif scenario == "trainer":
+        scenario_trainer(out_dir, sys.argv[3])
+    elif scenario == "rank_failure":
+        scenario_rank_failure(out_dir)
+    else:
+        raise SystemExit(f"unknown scenario {scenario}")
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    # the launcher appends --local_rank=N
+    sys.argv = [a for a in sys.argv if not a.startswith("--local_rank")]
+    main()

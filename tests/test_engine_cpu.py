@@ -151,7 +151,7 @@ def test_engine_checkpoint_roundtrip(tmp_path):
     assert all(torch.equal(pa[n], pb[n]) for n in pa)
 
 
-def test_inference_engine_stage3_releases_layers():
+def test_inference_engine_stage3_matches_plain_forward():
     m = make_model()
     for p in m.parameters():
         p.requires_grad_(False)
@@ -161,5 +161,5 @@ def test_inference_engine_stage3_releases_layers():
     with torch.no_grad():
         out = e(input_ids=torch.arange(8, 40).unsqueeze(0), return_logits=True).logits
     assert torch.allclose(out, ref_out, atol=1e-5)
-    layer_units = [u for u in e.units if u.name.startswith("layer")]
-    assert all(u.flat is None for u in layer_units)
+    # in a group of one rank nothing is gathered or released: the shard is the unit
+    assert all(u.persistent for u in e.units)
