@@ -22,6 +22,8 @@ std::tuple<at::Tensor, at::Tensor> ce_fwd_bwd(at::Tensor logits, const at::Tenso
 at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
                      const c10::optional<at::Tensor>& out, int64_t max_ctas);
 int64_t read_and_clear_error_flag(const at::Tensor& like);
+at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, int64_t mode, bool b_mn,
+                             int64_t epilogue, const c10::optional<at::Tensor>& out);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> moe_topk_gating_fwd(const at::Tensor& logits, int64_t K, bool normalize);
 at::Tensor moe_topk_gating_bwd(const at::Tensor& dscores, const at::Tensor& probs, const at::Tensor& experts,
                                const c10::optional<at::Tensor>& dprobs_extra, bool normalize);
@@ -50,6 +52,8 @@ TORCH_LIBRARY(atb200, m) {
     m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas) -> Tensor",
           &atb::gemm_bf16);
     m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);
+    m.def("gemm_bf16_grouped(Tensor a, Tensor b, Tensor offsets, int mode, bool b_mn, int epilogue, Tensor? out) -> Tensor",
+          &atb::gemm_bf16_grouped);
     m.def("moe_topk_gating_fwd(Tensor logits, int K, bool normalize) -> (Tensor, Tensor, Tensor)", &atb::moe_topk_gating_fwd);
     m.def("moe_topk_gating_bwd(Tensor dscores, Tensor probs, Tensor experts, Tensor? dprobs_extra, bool normalize) -> Tensor",
           &atb::moe_topk_gating_bwd);

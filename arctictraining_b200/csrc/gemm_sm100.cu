@@ -30,6 +30,7 @@ constexpr int BM = 128;
 constexpr int BK = 64;  // 64 bf16 = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr int kMaxGroups = 1024;
 
 enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
 
@@ -39,16 +40,34 @@ struct SmemLayout {
     static constexpr int kBBytes = BN * BK * 2;
     static constexpr int kStageBytes = kABytes + kBBytes;
     static constexpr int kBarrierOffset = STAGES * kStageBytes;
-    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag
-    static constexpr int kTotal = kBarrierOffset + (2 * STAGES + 4) * 8 + 16;
+    // full[STAGES], empty[STAGES], tmem_full[2], tmem_empty[2], tmem slot, abort flag, group offsets
+    static constexpr int kOffsetsOffset = kBarrierOffset + (2 * STAGES + 4) * 8 + 16;
+    static constexpr int kTotal = kOffsetsOffset + (kMaxGroups + 1) * 4;
 };
+
+enum GroupMode : int { GROUP_NONE = 0, GROUP_RAGGED_M = 1, GROUP_RAGGED_K = 2 };
 
 struct GemmParams {
     bf16* C;
-    int M, N, K;
+    int M, N, K;  // per-group extents in the grouped modes (M is unused for GROUP_RAGGED_M)
     int64_t ldc;
     int* error_flag;  // device int: 0 ok, otherwise (role << 8) | reason
+    // grouped GEMM: `group_offsets[g]` is the first row of group g in the ragged operand(s); every group
+    // starts at a multiple of 128 rows.  GROUP_RAGGED_M: A rows are ragged, B holds one matrix per group.
+    // GROUP_RAGGED_K: the contraction runs over the rows of group g; C holds one [M, N] block per group.
+    const int* group_offsets;
+    int num_groups;
+    int group_mode;
 };
+
+// What one output tile reads and writes.
+struct TileInfo {
+    int a_m0, a_k0;  // A: first M coordinate and first contraction coordinate
+    int b_n0, b_k0;  // B: first N coordinate and first contraction coordinate
+    int k_blocks;
+    int c_row0, c_row_limit, c_col0;
+};
+
 
 template <int BN, int STAGES, bool A_MN, bool B_MN, int EPI>
 __global__ void __launch_bounds__(192, 1)
@@ -69,13 +88,13 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
 
-    const int tiles_m = (p.M + BM - 1) / BM;
-    const int tiles_n = (p.N + BN - 1) / BN;
-    const int num_tiles = tiles_m * tiles_n;
-    const int k_blocks = (p.K + BK - 1) / BK;
+    int* s_offsets = reinterpret_cast<int*>(smem + L::kOffsetsOffset);
     constexpr int GROUP_M = 8;
     constexpr uint32_t TMEM_COLS = 2 * BN;  // 512 for BN=256, 256 for BN=128
 
+    if (p.group_mode != GROUP_NONE) {
+        for (int g = threadIdx.x; g <= p.num_groups; g += blockDim.x) s_offsets[g] = p.group_offsets[g];
+    }
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) {
             ptx::mbar_init(&full_bar[s], 1);
@@ -98,14 +117,45 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    auto tile_coords = [&](int t, int& tm, int& tn) {
+    const int total_rows = p.group_mode == GROUP_NONE ? p.M : s_offsets[p.num_groups];
+    const int tiles_m = p.group_mode == GROUP_RAGGED_K ? (p.M + BM - 1) / BM : (total_rows + BM - 1) / BM;
+    const int tiles_n = (p.N + BN - 1) / BN;
+    const int tiles_per_group = tiles_m * tiles_n;  // GROUP_RAGGED_K only
+    const int num_tiles = p.group_mode == GROUP_RAGGED_K ? tiles_per_group * p.num_groups : tiles_m * tiles_n;
+
+    // Maps a linear tile index to its coordinates; returns false for tiles that have no work (empty group).
+    auto get_tile = [&](int t, TileInfo& ti) -> bool {
+        if (p.group_mode == GROUP_RAGGED_K) {
+            const int g = t / tiles_per_group;
+            const int r = t - g * tiles_per_group;
+            const int tm = r % tiles_m, tn = r / tiles_m;
+            const int row0 = s_offsets[g], rows = s_offsets[g + 1] - row0;
+            if (rows <= 0) return false;
+            ti.a_m0 = tm * BM; ti.a_k0 = row0; ti.b_n0 = tn * BN; ti.b_k0 = row0;
+            ti.k_blocks = (rows + BK - 1) / BK;
+            ti.c_row0 = g * p.M + tm * BM; ti.c_row_limit = g * p.M + p.M; ti.c_col0 = tn * BN;
+            return true;
+        }
         const int per_group = GROUP_M * tiles_n;
-        const int g = t / per_group;
-        const int first_m = g * GROUP_M;
+        const int grp = t / per_group;
+        const int first_m = grp * GROUP_M;
         const int gsz = min(GROUP_M, tiles_m - first_m);
-        const int r = t - g * per_group;
-        tm = first_m + (r % gsz);
-        tn = r / gsz;
+        const int r = t - grp * per_group;
+        const int tm = first_m + (r % gsz), tn = r / gsz;
+        ti.a_m0 = tm * BM; ti.a_k0 = 0; ti.b_n0 = tn * BN; ti.b_k0 = 0;
+        ti.k_blocks = (p.K + BK - 1) / BK;
+        ti.c_row0 = tm * BM; ti.c_row_limit = total_rows; ti.c_col0 = tn * BN;
+        if (p.group_mode == GROUP_RAGGED_M) {
+            // binary search for the group that owns row tm * BM (segments are tile aligned)
+            int lo = 0, hi = p.num_groups - 1;
+            const int row = tm * BM;
+            while (lo < hi) {
+                const int mid = (lo + hi + 1) >> 1;
+                if (s_offsets[mid] <= row) lo = mid; else hi = mid - 1;
+            }
+            if constexpr (B_MN) ti.b_k0 = lo * p.K; else ti.b_n0 = lo * p.N + tn * BN;
+        }
+        return true;
     };
 
     if (warp == 0) {
@@ -117,9 +167,9 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t phase = 0;
             bool ok = true;
             for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-                int tm, tn;
-                tile_coords(t, tm, tn);
-                for (int kb = 0; kb < k_blocks; ++kb) {
+                TileInfo ti;
+                if (!get_tile(t, ti)) continue;
+                for (int kb = 0; kb < ti.k_blocks; ++kb) {
                     if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, kWaitLimitNs)) {
                         atomicCAS(p.error_flag, 0, (1 << 8) | 1);
                         ok = false;
@@ -129,18 +179,20 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     uint8_t* sb = sa + L::kABytes;
                     ptx::mbar_expect_tx(&full_bar[stage], L::kStageBytes);
                     if constexpr (!A_MN) {
-                        ptx::tma_load_2d(sa, &tmap_a, kb * BK, tm * BM, &full_bar[stage]);
+                        ptx::tma_load_2d(sa, &tmap_a, ti.a_k0 + kb * BK, ti.a_m0, &full_bar[stage]);
                     } else {
 #pragma unroll
                         for (int c = 0; c < BM / 64; ++c)
-                            ptx::tma_load_2d(sa + c * (BK * 128), &tmap_a, tm * BM + c * 64, kb * BK, &full_bar[stage]);
+                            ptx::tma_load_2d(sa + c * (BK * 128), &tmap_a, ti.a_m0 + c * 64, ti.a_k0 + kb * BK,
+                                             &full_bar[stage]);
                     }
                     if constexpr (!B_MN) {
-                        ptx::tma_load_2d(sb, &tmap_b, kb * BK, tn * BN, &full_bar[stage]);
+                        ptx::tma_load_2d(sb, &tmap_b, ti.b_k0 + kb * BK, ti.b_n0, &full_bar[stage]);
                     } else {
 #pragma unroll
                         for (int c = 0; c < BN / 64; ++c)
-                            ptx::tma_load_2d(sb + c * (BK * 128), &tmap_b, tn * BN + c * 64, kb * BK, &full_bar[stage]);
+                            ptx::tma_load_2d(sb + c * (BK * 128), &tmap_b, ti.b_n0 + c * 64, ti.b_k0 + kb * BK,
+                                             &full_bar[stage]);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -170,8 +222,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             uint32_t acc_phase[2] = {0, 0};
             int it = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                TileInfo ti;
+                if (!get_tile(t, ti)) continue;
+                const int k_blocks = ti.k_blocks;
                 const int acc = it & 1;
+                ++it;
                 if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase[acc] ^ 1u, abort_flag, kWaitLimitNs)) {
                     atomicCAS(p.error_flag, 0, (2 << 8) | 1);
                     ok = false;
@@ -207,10 +263,11 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
         uint32_t acc_phase[2] = {0, 0};
         int it = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++it) {
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            TileInfo ti;
+            if (!get_tile(t, ti)) continue;
             const int acc = it & 1;
-            int tm, tn;
-            tile_coords(t, tm, tn);
+            ++it;
             if (!ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase[acc], abort_flag, kWaitLimitNs)) {
                 if (lane == 0) atomicCAS(p.error_flag, 0, (3 << 8) | 1);
                 ok = false;
@@ -218,11 +275,12 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
             }
             acc_phase[acc] ^= 1u;
             ptx::tc_fence_after();
-            const int row = tm * BM + quarter * 32 + lane;
+            const int row = ti.c_row0 + quarter * 32 + lane;
+            const bool row_ok = row < ti.c_row_limit;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * BN);
             if constexpr (EPI == EPI_SWIGLU) {
                 // columns [128g, 128g+64) gate, [128g+64, 128g+128) up  ->  output columns [64g, 64g+64)
-                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * (BN / 2);
+                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)(ti.c_col0 / 2);
 #pragma unroll 1
                 for (int g = 0; g < BN / 128; ++g) {
 #pragma unroll 1
@@ -231,8 +289,8 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                         ptx::tmem_ld_32x32b_x32(taddr + g * 128 + h * 32, rg);
                         ptx::tmem_ld_32x32b_x32(taddr + g * 128 + 64 + h * 32, ru);
                         ptx::tmem_ld_wait();
-                        const int col0 = tn * (BN / 2) + g * 64 + h * 32;
-                        if (row < p.M && col0 < p.N / 2) {
+                        const int col0 = ti.c_col0 / 2 + g * 64 + h * 32;
+                        if (row_ok && col0 < p.N / 2) {
 #pragma unroll
                             for (int v = 0; v < 4; ++v) {
                                 float o[8];
@@ -248,14 +306,14 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                     }
                 }
             } else {
-                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * BN;
+                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)ti.c_col0;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
                     ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
                     ptx::tmem_ld_wait();
-                    const int col0 = tn * BN + c * 32;
-                    if (row < p.M) {
+                    const int col0 = ti.c_col0 + c * 32;
+                    if (row_ok) {
 #pragma unroll
                         for (int v = 0; v < 4; ++v) {
                             if (col0 + v * 8 < p.N) {  // N is a multiple of 8 (checked on the host)
@@ -336,7 +394,8 @@ void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams&
         C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         attr_set = true;
     }
-    const int tiles = (int)(ceil_div(p.M, BM) * ceil_div(p.N, BN));
+    // the tile count of a grouped GEMM lives on the device: launch one persistent CTA per SM
+    const int tiles = p.group_mode == GROUP_NONE ? (int)(ceil_div(p.M, BM) * ceil_div(p.N, BN)) : max_ctas;
     const int grid = std::max(1, std::min(tiles, max_ctas));
     kernel<<<grid, 192, smem_bytes, current_stream()>>>(ta, tb, p);
     ATB_LAUNCH_CHECK();
@@ -401,11 +460,92 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.ldc = out.stride(0);
     p.error_flag = error_flag_for(a.device()).data_ptr<int>();
+    p.group_offsets = nullptr;
+    p.num_groups = 0;
+    p.group_mode = GROUP_NONE;
     const int ctas = max_ctas > 0 ? (int)max_ctas : kNumSMs;
     if (!a_mn && !b_mn) dispatch_epi<false, false>(epi, ta, tb, p, ctas);
     else if (!a_mn && b_mn) dispatch_epi<false, true>(epi, ta, tb, p, ctas);
     else if (a_mn && !b_mn) dispatch_epi<true, false>(epi, ta, tb, p, ctas);
     else dispatch_epi<true, true>(epi, ta, tb, p, ctas);
+    return out;
+}
+
+// Grouped GEMM over ragged, tile-aligned segments (mixture-of-experts).  `offsets` is int32 [G + 1] on the device:
+// first row of every group in the ragged operand, each a multiple of 128; rows up to offsets[G] are used.
+//   mode 1 (ragged M):  out[r, :] = a[r, :] * B_g^T for r in group g.
+//        a [R, K] (K contiguous); b_mn == false: b is [G * N, K] (forward);  b_mn == true: b is [G * K, N]
+//        (data gradient: b holds the forward weights [G, K_c, N_out] and the contraction runs over their rows).
+//   mode 2 (ragged K):  out_g [M, N] = a[rows_g, :M]^T * b[rows_g, :N]  (weight gradient), out is [G * M, N]
+//        and must be zero-initialised by the caller when groups may be empty.
+// epilogue as in gemm_bf16 (SwiGLU only for mode 1 with b_mn == false).
+at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, int64_t mode,
+                             bool b_mn, int64_t epilogue, const c10::optional<at::Tensor>& out_opt) {
+    ATB_CHECK_CUDA(a); ATB_CHECK_CUDA(b); ATB_CHECK_CUDA(offsets);
+    ATB_CHECK_DTYPE(a, at::kBFloat16); ATB_CHECK_DTYPE(b, at::kBFloat16); ATB_CHECK_DTYPE(offsets, at::kInt);
+    ATB_CHECK_CONTIG(offsets);
+    TORCH_CHECK(a.dim() == 2 && b.dim() == 2 && a.stride(1) == 1 && b.stride(1) == 1, "grouped gemm: operands must be 2-D, unit inner stride");
+    const int64_t G = offsets.numel() - 1;
+    TORCH_CHECK(G >= 1 && G <= kMaxGroups, "grouped gemm: between 1 and 1024 groups");
+    const int epi = (int)epilogue;
+    c10::cuda::CUDAGuard guard(a.device());
+    GemmParams p;
+    p.error_flag = error_flag_for(a.device()).data_ptr<int>();
+    p.group_offsets = offsets.data_ptr<int>();
+    p.num_groups = (int)G;
+    p.group_mode = (int)mode;
+    at::Tensor out;
+    if (mode == GROUP_RAGGED_M) {
+        const int64_t R = a.size(0), K = a.size(1);
+        int64_t N;
+        if (!b_mn) {
+            TORCH_CHECK(b.size(0) % G == 0 && b.size(1) == K, "grouped gemm: b must be [G * N, K]");
+            N = b.size(0) / G;
+        } else {
+            TORCH_CHECK(b.size(0) == G * K, "grouped gemm: b must be [G * K, N]");
+            N = b.size(1);
+        }
+        TORCH_CHECK(R % BM == 0, "grouped gemm: the ragged operand must have a multiple of 128 rows");
+        TORCH_CHECK(N % 8 == 0 && K % 8 == 0, "grouped gemm: N and K must be multiples of 8");
+        if (epi == EPI_SWIGLU) TORCH_CHECK(N % 128 == 0 && !b_mn, "grouped gemm: SwiGLU epilogue needs K-major b and N % 128 == 0");
+        const int64_t out_cols = epi == EPI_SWIGLU ? N / 2 : N;
+        if (out_opt.has_value()) {
+            out = *out_opt;
+            TORCH_CHECK(out.dim() == 2 && out.size(0) == R && out.size(1) == out_cols && out.stride(1) == 1, "grouped gemm: bad output shape");
+        } else {
+            TORCH_CHECK(epi != EPI_ACCUM, "grouped gemm: accumulate needs an output tensor");
+            out = at::zeros({R, out_cols}, a.options());  // rows past offsets[G] stay zero
+        }
+        p.M = (int)R; p.N = (int)N; p.K = (int)K;
+        const CUtensorMap ta = make_tmap_bf16(a.data_ptr(), R, K, a.stride(0), BM);
+        const CUtensorMap tb = b_mn ? make_tmap_bf16(b.data_ptr(), G * K, N, b.stride(0), BK)
+                                    : make_tmap_bf16(b.data_ptr(), G * N, K, b.stride(0), 256);
+        p.C = (bf16*)out.data_ptr();
+        p.ldc = out.stride(0);
+        if (!b_mn) dispatch_epi<false, false>(epi, ta, tb, p, kNumSMs);
+        else dispatch_epi<false, true>(epi, ta, tb, p, kNumSMs);
+    } else if (mode == GROUP_RAGGED_K) {
+        const int64_t R = a.size(0), M = a.size(1), N = b.size(1);
+        TORCH_CHECK(b.size(0) == R, "grouped gemm: both operands must have the same ragged rows");
+        TORCH_CHECK(R % BK == 0 && M % 8 == 0 && N % 8 == 0, "grouped gemm: rows % 64 == 0, M % 8 == 0, N % 8 == 0");
+        TORCH_CHECK(epi == EPI_STORE || epi == EPI_ACCUM, "grouped gemm: weight-gradient mode supports store/accumulate");
+        if (out_opt.has_value()) {
+            out = *out_opt;
+            TORCH_CHECK(out.dim() == 2 && out.size(0) == G * M && out.size(1) == N && out.stride(1) == 1, "grouped gemm: bad output shape");
+        } else {
+            TORCH_CHECK(epi != EPI_ACCUM, "grouped gemm: accumulate needs an output tensor");
+            out = at::zeros({G * M, N}, a.options());
+        }
+        p.M = (int)M; p.N = (int)N; p.K = 0;
+        const CUtensorMap ta = make_tmap_bf16(a.data_ptr(), R, M, a.stride(0), BK);
+        const CUtensorMap tb = make_tmap_bf16(b.data_ptr(), R, N, b.stride(0), BK);
+        p.C = (bf16*)out.data_ptr();
+        p.ldc = out.stride(0);
+        dispatch_epi<true, true>(epi, ta, tb, p, kNumSMs);
+    } else {
+        TORCH_CHECK(false, "grouped gemm: mode must be 1 (ragged M) or 2 (ragged K)");
+    }
+    ATB_CHECK_ALIGNED16(out);
     return out;
 }
 

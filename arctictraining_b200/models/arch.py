@@ -93,7 +93,7 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "tiny-qwen3-moe": _llama(
         64, 2, 4, 2, 128, 1024, 10000.0, 2048,
         architectures=["Qwen3MoeForCausalLM"], model_type="qwen3_moe", head_dim=16, rms_norm_eps=1e-6, qk_norm=True,
-        num_experts=8, num_experts_per_tok=2, moe_intermediate_size=32, norm_topk_prob=True,
+        num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
         router_aux_loss_coef=0.001, decoder_sparse_step=1, mlp_only_layers=[],
     ),
 }

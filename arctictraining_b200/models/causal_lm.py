@@ -110,6 +110,8 @@ class CausalLM(nn.Module):
         self.attn_impl = "sdpa"
         self.tiled_mlp = False
         self.sp_context = None  # set by the trainer when sequence parallelism is on
+        if cfg.is_moe:
+            from ..moe import convert as _moe_convert  # noqa: F401  (registers the HF name converters)
 
     # -- initialisation ---------------------------------------------------------------------------
     @torch.no_grad()

@@ -127,7 +127,7 @@ class DecoderLayer(nn.Module):
         n_exp = cfg.get("num_experts") or cfg.get("num_local_experts") or 0
         sparse_step = cfg.get("decoder_sparse_step", 1) or 1
         if n_exp and layer_idx not in (cfg.get("mlp_only_layers") or []) and (layer_idx + 1) % sparse_step == 0:
-            from .moe import build_moe_block
+            from ..moe.layer import build_moe_block
 
             return build_moe_block(cfg, dtype=dtype, device=device)
         return MLP(cfg["hidden_size"], cfg["intermediate_size"], dtype=dtype, device=device)

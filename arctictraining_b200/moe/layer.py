@@ -139,8 +139,10 @@ class ArcticMoE(nn.Module):
         slots, counts, _ = mops.assign_slots(experts, self.num_experts, 1)
         send = mops.scatter_rows(x, slots, T * K)
         # counts[src][e] for my local experts from every source rank
-        recv_counts = torch.empty_like(counts)
-        dist.all_to_all_single(recv_counts, counts, group=self.ep_group)  # [P * El]: (src rank, local expert)
+        gathered = [torch.empty_like(counts) for _ in range(P)]
+        dist.all_gather(gathered, counts, group=self.ep_group)
+        # [P * El]: (source rank, my local expert)
+        recv_counts = torch.stack(gathered)[:, self.ep_rank * El : (self.ep_rank + 1) * El].reshape(-1).contiguous()
         send_splits = counts.view(P, El).sum(1)
         recv_splits = recv_counts.view(P, El).sum(1)
         splits = torch.stack([send_splits, recv_splits]).tolist()  # the one host sync of the baseline path

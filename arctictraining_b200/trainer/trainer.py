@@ -147,7 +147,7 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
 
         self.use_arctic_moe = self._resolve_arctic_moe()
         if self.use_arctic_moe:
-            from ..models.moe import convert_to_arctic_moe
+            from ..moe.convert import convert_to_arctic_moe
 
             convert_to_arctic_moe(
                 self.model, self.groups, is_resume=self.is_resume,

@@ -250,3 +250,117 @@ def test_fused_linear_logprobs_matches_torch():
     (lpr * coef).sum().backward()
     assert _rel(lp, lpr) < 2e-2
     assert _rel(h.grad, hr.grad) < 3e-2 and _rel(w.grad, wr.grad) < 3e-2
+
+
+# ------------------------------------------------------------------------------------------------ MoE kernels
+def test_moe_gating_kernel_matches_reference(k):
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    for E, K, dtype in [(128, 8, torch.bfloat16), (8, 2, torch.float32), (60, 4, torch.float32)]:
+        logits = torch.randn(777, E, device="cuda", dtype=dtype)
+        probs, scores, experts = k.moe_topk_gating_fwd(logits, K, True)
+        p_ref, s_ref, e_ref = ref.topk_gating(logits, K, True)
+        assert _rel(probs, p_ref) < 1e-5
+        assert torch.equal(experts.long(), e_ref)
+        assert _rel(scores, s_ref) < 1e-5
+
+
+def test_moe_gating_backward_matches_autograd(k):
+    torch.manual_seed(0)
+    T, E, K = 300, 64, 4
+    logits = torch.randn(T, E, device="cuda")
+    probs, scores, experts = k.moe_topk_gating_fwd(logits, K, True)
+    dscores = torch.randn(T, K, device="cuda")
+    extra = torch.rand(E, device="cuda") * 0.01
+    dlogits = k.moe_topk_gating_bwd(dscores, probs, experts, extra, True)
+    lr = logits.clone().requires_grad_(True)
+    pr = torch.softmax(lr, -1)
+    sr = torch.gather(pr, 1, experts.long())
+    sr = sr / sr.sum(-1, keepdim=True)
+    ((sr * dscores).sum() + (pr * extra).sum()).backward()
+    assert _rel(dlogits, lr.grad) < 1e-4
+
+
+def test_moe_slots_scatter_gather_kernels(k):
+    from arctictraining_b200.moe import ops as mops
+
+    torch.manual_seed(0)
+    T, K, E, H = 5000, 8, 128, 256
+    experts = torch.randint(0, E, (T, K), device="cuda", dtype=torch.int32)
+    slots, counts, offsets = k.moe_assign_slots(experts, E, 128)
+    s_ref, c_ref, o_ref = mops.assign_slots(experts.cpu(), E, 128)
+    assert torch.equal(slots.cpu(), s_ref) and torch.equal(counts.cpu(), c_ref) and torch.equal(offsets.cpu(), o_ref)
+    rows = int(offsets[-1])
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    perm = k.moe_scatter_fwd(x, slots, rows)
+    assert torch.equal(perm[slots[:, 3].long()], x)
+    scores = torch.rand(T, K, device="cuda")
+    out = k.moe_gather_fwd(perm, slots, scores)
+    assert _rel(out, x.float() * scores.sum(-1, keepdim=True)) < 1e-2
+    dout = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    dy, dscores = k.moe_gather_bwd(dout, perm, slots, scores)
+    assert _rel(dscores, (dout.float() * x.float()).sum(-1, keepdim=True).expand(T, K)) < 1e-2
+    assert _rel(k.moe_scatter_bwd(dy, slots), dout.float() * scores.sum(-1, keepdim=True)) < 1e-2
+
+
+def test_grouped_mlp_matches_reference_forward_and_backward(k):
+    from arctictraining_b200.moe import ops as mops
+    from arctictraining_b200.moe.grouped import grouped_mlp_reference
+    from arctictraining_b200.moe.grouped_cuda import grouped_mlp_cuda
+
+    torch.manual_seed(0)
+    E, H, I, T, K = 6, 256, 192, 900, 2
+    experts = torch.randint(0, E - 1, (T, K), device="cuda", dtype=torch.int32)  # the last expert stays empty
+    slots, counts, offsets = k.moe_assign_slots(experts, E, 128)
+    rows = T * K + E * 127
+    rows = (rows + 127) // 128 * 128
+    x = (0.5 * torch.randn(T, H, device="cuda")).bfloat16()
+    perm = k.moe_scatter_fwd(x, slots, rows).requires_grad_(True)
+    wgu = (0.05 * torch.randn(E, 2 * I, H, device="cuda")).bfloat16().requires_grad_(True)
+    wd = (0.05 * torch.randn(E, H, I, device="cuda")).bfloat16().requires_grad_(True)
+    y = grouped_mlp_cuda(perm, offsets, wgu, wd)
+    with torch.no_grad():
+        y_nograd = grouped_mlp_cuda(perm.detach(), offsets, wgu.detach(), wd.detach())
+    g = torch.randn_like(y)
+    used = torch.zeros(rows, 1, device="cuda")
+    used[slots.reshape(-1).long()] = 1
+    g = (g * used).bfloat16()  # gradients of padding rows are zero in the real layer
+    y.backward(g)
+    torch.cuda.synchronize()
+    _check_flag(x)
+    pr = perm.detach().float().requires_grad_(True)
+    wgur = wgu.detach().float().requires_grad_(True)
+    wdr = wd.detach().float().requires_grad_(True)
+    yr = grouped_mlp_reference(pr, offsets, wgur, wdr)
+    yr.backward(g.float())
+    assert _rel(y, yr) < 2e-2 and _rel(y_nograd, yr) < 2e-2
+    assert _rel(perm.grad, pr.grad) < 3e-2
+    assert _rel(wgu.grad, wgur.grad) < 3e-2 and _rel(wd.grad, wdr.grad) < 3e-2
+    assert float(wgu.grad[E - 1].abs().max()) == 0.0
+
+
+def test_arctic_moe_layer_on_gpu_matches_cpu_reference():
+    from arctictraining_b200.moe.layer import ArcticMoE
+    from arctictraining_b200.moe.layer import MoEConfig
+
+    torch.manual_seed(0)
+    cfgd = dict(model_dim=256, intermediate_dim=128, num_experts=16, top_k=4, loss_coeff=0.01)
+    cpu = ArcticMoE(MoEConfig(**cfgd), dtype=torch.float32)
+    for p in cpu.parameters():
+        torch.nn.init.normal_(p, std=0.08)
+    gpu = ArcticMoE(MoEConfig(**cfgd), dtype=torch.bfloat16, device="cuda")
+    with torch.no_grad():
+        for a, b in zip(gpu.parameters(), cpu.parameters()):
+            a.copy_(b)
+            b.copy_(a.float().cpu())  # same bf16-rounded weights on both sides
+    x = torch.randn(500, 256)
+    xg = x.cuda().bfloat16().requires_grad_(True)
+    xc = xg.detach().float().cpu().requires_grad_(True)
+    yg, yc = gpu(xg), cpu(xc)
+    yg.float().pow(2).sum().backward()
+    yc.pow(2).sum().backward()
+    assert _rel(yg.cpu(), yc) < 3e-2
+    assert _rel(xg.grad.cpu(), xc.grad) < 5e-2
+    assert _rel(gpu.expert_down.grad.cpu(), cpu.expert_down.grad) < 5e-2
+    assert _rel(gpu.router_gate.grad.cpu(), cpu.router_gate.grad) < 8e-2
