@@ -1,0 +1,114 @@
+"""Symmetric (peer-mapped) device memory and the kernels that communicate through it.
+
+Every rank of a node allocates buffers of identical size through ``torch.distributed._symmetric_memory`` and
+learns the address at which each peer's buffer is mapped into its own address space (NVLink P2P), plus the
+NVSwitch multicast address when the fabric offers one.  The fused kernels of ``csrc/comm_p2p.cu`` take those
+address tables and move data with loads and stores issued from the SMs.
+
+Synchronisation between ranks is a flag exchange (:meth:`SymmetricContext.barrier`) whose device-side wait is
+bounded: when a peer does not show up within ``timeout_s`` the kernel records an error code and returns;
+:meth:`check` turns that into :class:`CommTimeoutError` on the host, and the CUDA context stays usable.
+"""
+
+from __future__ import annotations
+
+import os
+from typing import Dict
+from typing import List
+from typing import Optional
+
+import torch
+import torch.distributed as dist
+
+from ..exceptions import CommTimeoutError
+from ..ops import _ext
+from ..ops.functional import _count
+
+_FLAG_SLOTS = 64
+_MAX_PEERS = 16
+
+
+def symmetric_memory_available(group=None) -> bool:
+    """Peer-mapped memory needs CUDA, an initialised NCCL group confined to one node, and the torch API."""
+    if not (torch.cuda.is_available() and dist.is_initialized() and dist.get_backend() == "nccl"):
+        return False
+    if os.getenv("ATB200_FUSED_COMM", "1") == "0":
+        return False
+    world = dist.get_world_size(group)
+    if world < 2 or world > _MAX_PEERS or world > torch.cuda.device_count():
+        return False
+    try:
+        import torch.distributed._symmetric_memory  # noqa: F401
+    except ImportError:
+        return False
+    return True
+
+
+class SymmetricBuffer:
+    """One symmetric allocation: ``tensor`` is the local part, ``ptrs`` the peers' addresses (CPU int64)."""
+
+    def __init__(self, numel: int, dtype: torch.dtype, group, device: torch.device) -> None:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
+        self.handle = symm_mem.rendezvous(self.tensor, group)
+        self.ptrs = torch.tensor([int(p) for p in self.handle.buffer_ptrs], dtype=torch.int64)
+        try:
+            self.multicast_ptr = int(self.handle.multicast_ptr) if self.handle.has_multicast_support else 0
+        except Exception:
+            self.multicast_ptr = 0
+        self.rank = self.handle.rank
+        self.world = self.handle.world_size
+
+
+class SymmetricContext:
+    """Address tables, flags and barrier epochs of one process group."""
+
+    def __init__(self, group=None, timeout_s: float = 20.0) -> None:
+        _ext.require()
+        self.group = group
+        self.device = torch.device("cuda", torch.cuda.current_device())
+        self.rank = dist.get_rank(group)
+        self.world = dist.get_world_size(group)
+        self.timeout_s = timeout_s
+        self.use_nvls = os.getenv("ATB200_NVLS", "0") == "1"
+        self._flags = SymmetricBuffer(_FLAG_SLOTS * _MAX_PEERS, torch.int32, group, self.device)
+        self._flags.tensor.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=group, device_ids=[self.device.index])
+        self._epochs = [0] * _FLAG_SLOTS
+        self.buffers: Dict[str, SymmetricBuffer] = {}
+
+    def alloc(self, name: str, numel: int, dtype: torch.dtype) -> SymmetricBuffer:
+        buf = SymmetricBuffer(numel, dtype, self.group, self.device)
+        self.buffers[name] = buf
+        return buf
+
+    def barrier(self, slot: int = 0) -> None:
+        """Device-side barrier over the group on the current stream (no host synchronisation)."""
+        self._epochs[slot] += 1
+        _ext.ops().p2p_barrier(self._flags.ptrs, self.rank, slot, self._epochs[slot], self.timeout_s, self._flags.tensor)
+        _count()
+
+    def check(self) -> None:
+        """Raise if a bounded wait of any communication kernel gave up since the last check (synchronises)."""
+        code = int(_ext.ops().comm_read_and_clear_error(self._flags.tensor))
+        if code:
+            raise CommTimeoutError(
+                f"rank {self.rank}: a peer did not reach a device-side barrier within {self.timeout_s}s "
+                f"(code {code:#x}, waiting for peer {(code & 0xff) - 1})"
+            )
+
+    # ------------------------------------------------------------------ collectives on symmetric buffers
+    def all_gather(self, shards: SymmetricBuffer, shard_elem_offset: int, shard_numel: int, out: torch.Tensor) -> None:
+        """``out[p * n : (p + 1) * n] = peer p's shards[offset : offset + n]`` (pull over NVLink)."""
+        _ext.ops().p2p_all_gather(shards.ptrs, shard_elem_offset * out.element_size(), out, shard_numel, self.rank)
+        _count()
+
+    def reduce_scatter_accumulate(self, grads: SymmetricBuffer, elem_offset: int, n: int, acc: torch.Tensor,
+                                  scale: float, overwrite: bool, want_sumsq: bool = False) -> torch.Tensor:
+        """``acc (+)= scale * sum_p peer_p.grads[offset : offset + n]`` in fp32; optionally returns ||acc||^2."""
+        _count()
+        if self.use_nvls and grads.multicast_ptr:
+            return _ext.ops().nvls_reduce_scatter_accum(grads.multicast_ptr, elem_offset, n, acc, scale, overwrite, want_sumsq)
+        return _ext.ops().p2p_reduce_scatter_accum(grads.ptrs, elem_offset, n, acc, scale, overwrite, want_sumsq)

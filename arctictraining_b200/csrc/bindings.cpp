@@ -33,6 +33,24 @@ at::Tensor moe_scatter_bwd(const at::Tensor& dout, const at::Tensor& slots);
 at::Tensor moe_gather_fwd(const at::Tensor& y, const at::Tensor& slots, const at::Tensor& scores);
 std::tuple<at::Tensor, at::Tensor> moe_gather_bwd(const at::Tensor& dout, const at::Tensor& y, const at::Tensor& slots,
                                                   const at::Tensor& scores);
+void p2p_barrier(const at::Tensor& flag_ptrs, int64_t rank, int64_t slot, int64_t epoch, double timeout_s, const at::Tensor& like);
+int64_t comm_read_and_clear_error(const at::Tensor& like);
+void p2p_all_gather(const at::Tensor& shard_ptrs, int64_t shard_byte_offset, at::Tensor full, int64_t shard_numel, int64_t rank);
+at::Tensor p2p_reduce_scatter_accum(const at::Tensor& grad_ptrs, int64_t elem_offset, int64_t n, at::Tensor acc, double scale,
+                                    bool overwrite, bool want_sumsq);
+at::Tensor p2p_reduce_scatter_adamw(const at::Tensor& grad_ptrs, int64_t elem_offset, int64_t n, double scale, at::Tensor master,
+                                    at::Tensor m, at::Tensor v, const c10::optional<at::Tensor>& out_lp, double lr, double beta1,
+                                    double beta2, double eps, double wd, int64_t step);
+at::Tensor nvls_reduce_scatter_accum(int64_t multicast_ptr, int64_t elem_offset, int64_t n, at::Tensor acc, double scale,
+                                     bool overwrite, bool want_sumsq);
+void p2p_seq_to_head(const at::Tensor& x, const at::Tensor& dst_ptrs, int64_t rank, bool reverse);
+std::tuple<at::Tensor, at::Tensor> moe_dest_rows(const at::Tensor& all_counts, const at::Tensor& experts,
+                                                 const at::Tensor& local_slots, const at::Tensor& local_offsets, int64_t rank,
+                                                 int64_t align);
+void p2p_moe_dispatch(const at::Tensor& x, const at::Tensor& experts, const at::Tensor& dest_row, const at::Tensor& dst_ptrs,
+                      int64_t experts_per_rank);
+at::Tensor p2p_moe_combine(const at::Tensor& y_ptrs, const at::Tensor& experts, const at::Tensor& dest_row,
+                           const at::Tensor& scores, int64_t hidden, int64_t experts_per_rank);
 }  // namespace atb
 
 TORCH_LIBRARY(atb200, m) {
@@ -52,6 +70,24 @@ TORCH_LIBRARY(atb200, m) {
     m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas) -> Tensor",
           &atb::gemm_bf16);
     m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);
+    m.def("p2p_barrier(Tensor flag_ptrs, int rank, int slot, int epoch, float timeout_s, Tensor like) -> ()", &atb::p2p_barrier);
+    m.def("comm_read_and_clear_error(Tensor like) -> int", &atb::comm_read_and_clear_error);
+    m.def("p2p_all_gather(Tensor shard_ptrs, int shard_byte_offset, Tensor(a!) full, int shard_numel, int rank) -> ()",
+          &atb::p2p_all_gather);
+    m.def("p2p_reduce_scatter_accum(Tensor grad_ptrs, int elem_offset, int n, Tensor(a!) acc, float scale, bool overwrite, "
+          "bool want_sumsq) -> Tensor", &atb::p2p_reduce_scatter_accum);
+    m.def("p2p_reduce_scatter_adamw(Tensor grad_ptrs, int elem_offset, int n, float scale, Tensor(a!) master, Tensor(b!) m, "
+          "Tensor(c!) v, Tensor? out_lp, float lr, float beta1, float beta2, float eps, float wd, int step) -> Tensor",
+          &atb::p2p_reduce_scatter_adamw);
+    m.def("nvls_reduce_scatter_accum(int multicast_ptr, int elem_offset, int n, Tensor(a!) acc, float scale, bool overwrite, "
+          "bool want_sumsq) -> Tensor", &atb::nvls_reduce_scatter_accum);
+    m.def("p2p_seq_to_head(Tensor x, Tensor dst_ptrs, int rank, bool reverse) -> ()", &atb::p2p_seq_to_head);
+    m.def("moe_dest_rows(Tensor all_counts, Tensor experts, Tensor local_slots, Tensor local_offsets, int rank, int align) -> "
+          "(Tensor, Tensor)", &atb::moe_dest_rows);
+    m.def("p2p_moe_dispatch(Tensor x, Tensor experts, Tensor dest_row, Tensor dst_ptrs, int experts_per_rank) -> ()",
+          &atb::p2p_moe_dispatch);
+    m.def("p2p_moe_combine(Tensor y_ptrs, Tensor experts, Tensor dest_row, Tensor scores, int hidden, int experts_per_rank) -> Tensor",
+          &atb::p2p_moe_combine);
     m.def("gemm_bf16_grouped(Tensor a, Tensor b, Tensor offsets, int mode, bool b_mn, int epilogue, Tensor? out) -> Tensor",
           &atb::gemm_bf16_grouped);
     m.def("moe_topk_gating_fwd(Tensor logits, int K, bool normalize) -> (Tensor, Tensor, Tensor)", &atb::moe_topk_gating_fwd);

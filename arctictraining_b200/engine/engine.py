@@ -296,6 +296,7 @@ class TrainingEngine:
                         u.runs.append((s, e, gi))
             dp_replicas = max(1, (dist.get_world_size() if self.dist_on else 1) // self.sp_size)
             u.grad_divisor = float(dp_replicas)
+        self._setup_fused_comm(max_pool_numel)
         self._param_pool: Optional[_BufferPool] = None
         if max_pool_numel:
             dtype = next(u.dtype for u in self.units if not u.persistent)
@@ -309,6 +310,43 @@ class TrainingEngine:
             if train_units:
                 n = max(u.numel for u in train_units)
                 self._grad_pool = _BufferPool(n, train_units[0].dtype, self.device, 3 if self.on_gpu else 1)
+                if self.symm is not None and train_units[0].dtype == torch.bfloat16:
+                    # gradient buffers that peers read directly: same three slots on every rank
+                    self._grad_symm = [self.symm.alloc(f"grad{i}", n, torch.bfloat16) for i in range(3)]
+                    self._grad_pool.bufs = [b.tensor for b in self._grad_symm]
+
+    def _setup_fused_comm(self, max_pool_numel: int) -> None:
+        """Peer-memory data plane: on when the whole data-parallel group sits on one NVLink node."""
+        from ..comm.symm import SymmetricContext
+        from ..comm.symm import symmetric_memory_available
+
+        self.symm = None
+        self._grad_symm = None
+        self._shard_symm = None
+        want = self.cfg.fused_comm != "off" and self.stage >= 1 and self.expert_dp_group is None
+        if not (want and self.on_gpu and self.dist_on and symmetric_memory_available(self.dp_group)):
+            return
+        try:
+            self.symm = SymmetricContext(self.dp_group)
+        except Exception as exc:  # noqa: BLE001
+            logger.warning(f"peer-memory communication unavailable ({exc}); using NCCL")
+            self.symm = None
+            return
+        if self.stage == 3 and max_pool_numel:
+            # all released units keep their bf16 shards in one symmetric slab so that peers can pull them
+            units = [u for u in self.units if not u.persistent and u.dtype == torch.bfloat16]
+            total = sum(u.shard_size for u in units)
+            if total:
+                self._shard_symm = self.symm.alloc("shards", total, torch.bfloat16)
+                off = 0
+                for u in units:
+                    view = self._shard_symm.tensor[off : off + u.shard_size]
+                    view.copy_(u.shard)
+                    u.shard = view
+                    u.symm_shard_offset = off
+                    off += u.shard_size
+                torch.cuda.synchronize()
+                dist.barrier(group=self.dp_group, device_ids=[self.device.index])
 
     def _persist_threshold(self) -> int:
         zo = self.cfg.raw.get("zero_optimization", {}) or {}
@@ -326,7 +364,7 @@ class TrainingEngine:
             tl = u.train_len
             if tl <= 0:
                 continue
-            pad = (tl + 3) // 4 * 4
+            pad = (tl + 7) // 8 * 8
             u.master = torch.zeros(pad, dtype=master_dtype, device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
             u.master[:tl].copy_(u.shard[:tl].to(master_dtype))
             u.grad_acc = torch.zeros(pad, dtype=torch.float32 if master_dtype == torch.float32 else master_dtype,
@@ -375,7 +413,11 @@ class TrainingEngine:
             if self.on_gpu:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(self.comm_stream):
-                    self._all_gather(flat, u.shard, u.group)
+                    if self._shard_symm is not None and hasattr(u, "symm_shard_offset"):
+                        # shards only change in the optimizer step, which ends with a barrier: pull directly
+                        self.symm.all_gather(self._shard_symm, u.symm_shard_offset, u.shard_size, flat)
+                    else:
+                        self._all_gather(flat, u.shard, u.group)
                     u.gather_event = torch.cuda.Event()
                     u.gather_event.record()
             else:
@@ -486,7 +528,25 @@ class TrainingEngine:
         scale = 1.0 / (u.grad_divisor * self.gas)
         lo = u.group_rank * u.shard_size
 
+        fused = (
+            self.symm is not None and self._grad_symm is not None and u.grad_slot is not None and tl > 0
+            and u.grad_acc is not None and u.grad_acc.device == self.device and u.grad_acc.dtype == torch.float32
+            and u.group_size > 1 and lo % 8 == 0
+        )
+
         def work() -> None:
+            if fused:
+                # every rank has finished writing this unit's gradients -> read my slice from all peers, reduce
+                # in fp32, accumulate; second barrier: nobody still reads a buffer that is about to be reused
+                self.symm.barrier(slot=1)
+                n8 = (tl + 7) // 8 * 8
+                self.symm.reduce_scatter_accumulate(
+                    self._grad_symm[u.grad_slot], lo, min(n8, u.grad_acc.numel() // 8 * 8), u.grad_acc, scale,
+                    overwrite=not u.grad_acc_valid,
+                )
+                u.grad_acc_valid = True
+                self.symm.barrier(slot=2)
+                return
             if self.dist_on and u.group_size > 1:
                 if self.stage >= 1:
                     piece = torch.empty(u.shard_size, dtype=g.dtype, device=g.device)
@@ -667,6 +727,8 @@ class TrainingEngine:
                 u.shard[:tl].copy_(u.master[:tl].to(self.device, non_blocking=True).to(u.dtype))
             u.grad_acc_valid = False
         self._sync_full_params()
+        if self.symm is not None:
+            self.symm.barrier(slot=0)  # shards are final on every rank before anyone pulls them again
 
     def _sync_full_params(self) -> None:
         """After an update every persistent unit re-assembles its full buffer from the shards."""

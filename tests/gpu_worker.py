@@ -1,0 +1,110 @@
+"""Worker for the multi-GPU tests (NCCL, one process per GPU).  ``python tests/gpu_worker.py <scenario> <out_dir>``."""
+
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+ROOT = Path(__file__).resolve().parent.parent
+sys.path.insert(0, str(ROOT))
+
+from arctictraining_b200.comm.dist import init_distributed  # noqa: E402
+from arctictraining_b200.engine import TrainingEngine  # noqa: E402
+from arctictraining_b200.models.arch import load_arch_config  # noqa: E402
+from arctictraining_b200.models.causal_lm import CausalLM  # noqa: E402
+from arctictraining_b200.optimizer.adam import FusedAdamW  # noqa: E402
+from arctictraining_b200.optimizer.factory import OptimizerFactory  # noqa: E402
+
+OVERRIDES = dict(num_hidden_layers=3, hidden_size=512, intermediate_size=1024, num_attention_heads=8,
+                 num_key_value_heads=2, vocab_size=4096)
+
+
+def make_engine(stage, fused, seed=0):
+    cfg = load_arch_config("llama-3.1-8b", OVERRIDES)
+    with torch.device("cuda"):
+        m = CausalLM(cfg, dtype=torch.bfloat16)
+    m.init_weights(seed=seed)
+    m.attn_impl = "sdpa"
+    opt = FusedAdamW(OptimizerFactory.get_optimizer_grouped_params(m, 0.1), lr=1e-3, betas=(0.9, 0.95))
+    return TrainingEngine(m, opt, None, {"zero_optimization": {"stage": stage}, "gradient_clipping": 1.0,
+                                         "bfloat16": {"enabled": True}, "fused_comm": "auto" if fused else "off"})
+
+
+def run(engine, n=3, seed=0):
+    rank, world = dist.get_rank(), dist.get_world_size()
+    g = torch.Generator().manual_seed(seed)
+    losses = []
+    for _ in range(n):
+        ids = torch.randint(8, 4096, (world, 256), generator=g)[rank : rank + 1].cuda()
+        out = engine(input_ids=ids, labels=ids.clone())
+        engine.backward(out.loss)
+        engine.step()
+        losses.append(float(out.loss))
+    torch.cuda.synchronize()
+    return losses
+
+
+def scenario_fused_vs_nccl(out_dir):
+    res = {}
+    for stage in (2, 3):
+        a = make_engine(stage, fused=False)
+        la = run(a)
+        pa = {n: t.float().clone() for n, t in a.iter_full_named_parameters()}
+        b = make_engine(stage, fused=True)
+        assert b.symm is not None, "peer-memory path did not come up"
+        lb = run(b)
+        b.symm.check()
+        pb = {n: t.float().clone() for n, t in b.iter_full_named_parameters()}
+        diff = max(float((pa[n] - pb[n]).abs().max()) for n in pa)
+        res[f"stage{stage}"] = {"nccl": la, "fused": lb, "max_param_diff": diff}
+    if dist.get_rank() == 0:
+        (Path(out_dir) / "fused_vs_nccl.json").write_text(json.dumps(res))
+
+
+def scenario_barrier_timeout(out_dir):
+    """Rank 0 waits at a barrier that rank 1 joins only later: the wait runs out, the host sees an error status,
+    and the context keeps working (plain peer loads, no multicast involved)."""
+    from arctictraining_b200.comm.symm import SymmetricContext
+    from arctictraining_b200.exceptions import CommTimeoutError
+
+    ctx = SymmetricContext(None, timeout_s=0.5)
+    rank = dist.get_rank()
+    ok = True
+    if rank == 0:
+        ctx.barrier(slot=5)
+        try:
+            ctx.check()
+            ok = False
+        except CommTimeoutError:
+            pass
+        # the context is still usable
+        t = torch.ones(4, device="cuda") * 3
+        ok = ok and float(t.sum()) == 12.0
+    dist.barrier()
+    if rank != 0:
+        ctx.barrier(slot=5)  # rank 0's flag is already there: returns at once
+        ctx.check()
+    ctx.timeout_s = 20.0
+    ctx.barrier(slot=6)
+    ctx.check()
+    flags = [None] * dist.get_world_size()
+    dist.all_gather_object(flags, ok)
+    if rank == 0:
+        (Path(out_dir) / "barrier_timeout.json").write_text(json.dumps({"ok": all(flags)}))
+
+
+def main():
+    scenario, out_dir = sys.argv[1], sys.argv[2]
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    init_distributed(timeout_s=120)
+    {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout}[scenario](out_dir)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    sys.argv = [a for a in sys.argv if not a.startswith("--local_rank")]
+    main()

@@ -1,0 +1,38 @@
+"""Multi-GPU tests (child processes, one per GPU, NCCL + peer memory); skipped when fewer than 2 GPUs are visible."""
+
+import json
+import os
+import socket
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+pytestmark = [pytest.mark.gpu, pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs 2 GPUs")]
+
+
+def launch(world, *args, timeout=600):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    cmd = [sys.executable, "-m", "arctictraining_b200.launcher.local", "--num_gpus", str(world), "--master_port", str(port),
+           "--", sys.executable, "-u", str(ROOT / "tests" / "gpu_worker.py"), *map(str, args)]
+    env = {**os.environ, "PYTHONPATH": str(ROOT), "AT_LOG_LEVEL": "WARNING", "NCCL_NVLS_ENABLE": "0"}
+    res = subprocess.run(cmd, cwd=ROOT, env=env, capture_output=True, text=True, timeout=timeout)
+    assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
+
+
+def test_peer_memory_path_matches_nccl(tmp_path):
+    launch(2, "fused_vs_nccl", tmp_path)
+    res = json.loads((tmp_path / "fused_vs_nccl.json").read_text())
+    for stage, r in res.items():
+        assert r["fused"] == pytest.approx(r["nccl"], rel=2e-3), stage
+        assert r["max_param_diff"] < 2e-2, stage
+
+
+def test_bounded_barrier_reports_a_missing_peer(tmp_path):
+    launch(2, "barrier_timeout", tmp_path)
+    assert json.loads((tmp_path / "barrier_timeout.json").read_text())["ok"]
