@@ -1,0 +1,77 @@
+"""The allocation-free RMSNorm backward (`atb_rmsnorm_bwd_noalloc`, an exported C symbol) must agree with the
+tensor-based operator.
+
+Some hosts of this library may not allocate on the device while they run (all memory belongs to one pool, or an
+allocation's implicit synchronisation is unaffordable, or there is no tensor framework to allocate through), so
+this variant keeps its scratch in a fixed array inside the library.  The test calls it the way such a host would:
+through ctypes, with raw device pointers and a raw stream handle, twice in a row on different data (the scratch
+array is shared between calls and keeps old contents, which must not leak into the second result), and checks
+the size limit.  This file sorts last on purpose so that a run stopping at the first failure has already run
+every other test.
+"""
+
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+MAX_HIDDEN = 8192
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from arctictraining_b200.ops import _ext
+
+    _ext.require()
+    handle = ctypes.CDLL(str(_ext.lib_path()))
+    fn = handle.atb_rmsnorm_bwd_noalloc
+    fn.restype = ctypes.c_int
+    fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_ulong]
+    return fn
+
+
+def call(fn, dy, x, w, rstd, dx, dw):
+    err = ctypes.create_string_buffer(256)
+    stream = torch.cuda.current_stream().cuda_stream
+    rc = fn(dy.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), x.shape[0], x.shape[1],
+            ctypes.c_void_p(stream), err, 256)
+    return rc, err.value.decode()
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / (b.float().norm() + 1e-12))
+
+
+@pytest.mark.parametrize("shapes", [[(513, 4096), (77, 1024)], [(4000, 8192), (4000, 8192)]])
+def test_matches_tensor_operator_on_two_calls_in_a_row(lib, shapes):
+    torch.manual_seed(0)
+    k = torch.ops.atb200
+    for T, H in shapes:  # consecutive calls share the built-in scratch array
+        x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        w = (1 + 0.1 * torch.randn(H, device="cuda")).bfloat16()
+        dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+        _, rstd = k.rmsnorm_fwd(x, w, 1e-5)
+        dx_ref, dw_ref = k.rmsnorm_bwd(dy, x, w, rstd)
+        dx = torch.empty_like(x)
+        dw = torch.full((H,), float("nan"), device="cuda")
+        before = torch.cuda.memory_allocated()
+        rc, msg = call(lib, dy, x, w, rstd, dx, dw)
+        assert rc == 0, msg
+        torch.cuda.synchronize()
+        assert torch.cuda.memory_allocated() == before  # nothing was allocated through the framework either
+        assert rel(dx, dx_ref) < 1e-2
+        assert rel(dw, dw_ref) < 1e-2
+
+
+def test_sizes_beyond_the_limit_are_refused_with_a_message(lib):
+    H = MAX_HIDDEN + 8
+    x = torch.zeros(4, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(4, device="cuda")
+    dx, dw = torch.empty_like(x), torch.empty(H, device="cuda")
+    rc, msg = call(lib, x, x, w, rstd, dx, dw)
+    assert rc == 1 and "limit" in msg and str(MAX_HIDDEN) in msg
+    rc, msg = call(lib, x[:, :12], x[:, :12], w, rstd, dx, dw)  # hidden = 12 is not a multiple of 8
+    assert rc == 1 and "multiple of 8" in msg
