@@ -37,11 +37,9 @@ def symmetric_memory_available(group=None) -> bool:
     world = dist.get_world_size(group)
     if world < 2 or world > _MAX_PEERS or world > torch.cuda.device_count():
         return False
-    try:
-        import torch.distributed._symmetric_memory  # noqa: F401
-    except ImportError:
-        return False
-    return True
+    import importlib.util
+
+    return importlib.util.find_spec("torch.distributed._symmetric_memory") is not None
 
 
 class SymmetricBuffer:
@@ -50,6 +48,8 @@ class SymmetricBuffer:
     def __init__(self, numel: int, dtype: torch.dtype, group, device: torch.device) -> None:
         import torch.distributed._symmetric_memory as symm_mem
 
+        if group is None:
+            group = dist.group.WORLD  # the rendezvous wants an explicit group object or name
         self.tensor = symm_mem.empty(numel, dtype=dtype, device=device)
         self.handle = symm_mem.rendezvous(self.tensor, group)
         self.ptrs = torch.tensor([int(p) for p in self.handle.buffer_ptrs], dtype=torch.int64)

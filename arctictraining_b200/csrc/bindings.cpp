@@ -19,6 +19,8 @@ void accum_bf16(const at::Tensor& src, at::Tensor acc, double scale, bool overwr
 std::tuple<at::Tensor, at::Tensor> ce_fwd_bwd(at::Tensor logits, const at::Tensor& labels,
                                               const c10::optional<at::Tensor>& grad_scale,
                                               const c10::optional<at::Tensor>& row_scale, bool write_grad);
+at::Tensor kl_fwd_bwd(at::Tensor student, const at::Tensor& teacher, const c10::optional<at::Tensor>& row_weight,
+                      double temperature, const c10::optional<at::Tensor>& grad_scale, bool write_grad);
 at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
                      const c10::optional<at::Tensor>& out, int64_t max_ctas);
 int64_t read_and_clear_error_flag(const at::Tensor& like);
@@ -67,6 +69,8 @@ TORCH_LIBRARY(atb200, m) {
     m.def("accum_bf16(Tensor src, Tensor(a!) acc, float scale, bool overwrite) -> ()", &atb::accum_bf16);
     m.def("ce_fwd_bwd(Tensor(a!) logits, Tensor labels, Tensor? grad_scale, Tensor? row_scale, bool write_grad) -> (Tensor, Tensor)",
           &atb::ce_fwd_bwd);
+    m.def("kl_fwd_bwd(Tensor(a!) student, Tensor teacher, Tensor? row_weight, float temperature, Tensor? grad_scale, bool write_grad) -> Tensor",
+          &atb::kl_fwd_bwd);
     m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas) -> Tensor",
           &atb::gemm_bf16);
     m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);

@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) features used by this library:
-// mbarrier, TMA bulk tensor copies (never with cluster multicast), tcgen05 MMA / TMEM, peer flags.
+// mbarrier, TMA bulk tensor copies (each CTA fetches its own tiles), tcgen05 MMA / TMEM, peer flags.
 // Every wait is bounded: it gives up after a wall-clock limit and reports failure to the caller.
 #pragma once
 
@@ -74,7 +74,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity
     }
 }
 
-// ---- TMA (bulk tensor copy global -> shared, completion on an mbarrier; no multicast) --------
+// ---- TMA (bulk tensor copy global -> shared of the issuing CTA, completion on an mbarrier) --------
 __device__ __forceinline__ void tma_load_2d(void* smem_dst, const CUtensorMap* tmap, int32_t x, int32_t y,
                                             uint64_t* bar) {
     asm volatile(

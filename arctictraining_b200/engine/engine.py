@@ -216,6 +216,16 @@ class TrainingEngine:
                 self.units.append(exp)
                 continue
             self.units.append(unit)
+        leftovers = [p for p in self.module.parameters() if id(p) not in seen]
+        if leftovers:
+            misc = ZeroUnit("misc", [], False, len(self.units))
+            misc.params = []
+            for p in leftovers:
+                if id(p) not in seen:
+                    seen[id(p)] = "misc"
+                    misc.params.append(p)
+            misc.is_expert = False
+            self.units.append(misc)
         for i, u in enumerate(self.units):
             u.index = i
             u.param_names = [names.get(id(p), f"{u.name}.{j}") for j, p in enumerate(u.params)]
@@ -484,8 +494,17 @@ class TrainingEngine:
                         return __orig(x, *args, **kwargs)
                     finally:
                         engine._release_params(__unit)
-                fn = lambda inp: __orig(inp, *args, **kwargs)  # noqa: E731
-                return _CheckpointedUnit.apply(engine, __unit, fn, engine._dummy, x)
+                # positional tensor arguments that carry gradients (e.g. shared K/V) are routed through autograd
+                t_idx = [i for i, a in enumerate(args) if torch.is_tensor(a) and a.requires_grad]
+                extras = [args[i] for i in t_idx]
+
+                def fn(inp, *ext, __args=args, __idx=tuple(t_idx)):
+                    call_args = list(__args)
+                    for i, e in zip(__idx, ext):
+                        call_args[i] = e
+                    return __orig(inp, *call_args, **kwargs)
+
+                return _CheckpointedUnit.apply(engine, __unit, fn, engine._dummy, x, *extras)
 
             mod.forward = wrapped  # type: ignore[method-assign]
 
@@ -876,20 +895,23 @@ class TrainingEngine:
 class _CheckpointedUnit(torch.autograd.Function):
     """Runs one unit without keeping its activations; the backward pass gathers the unit's parameters
     again, recomputes the forward from the saved (possibly host-resident) input, back-propagates and hands
-    the unit's gradients to the engine for reduction."""
+    the unit's gradients to the engine for reduction.  ``x`` is the hidden state (saved, possibly on the
+    host); further tensor inputs (``extras``) are kept on the device."""
 
     @staticmethod
-    def forward(ctx, engine: TrainingEngine, unit: ZeroUnit, fn, dummy, x):
+    def forward(ctx, engine: TrainingEngine, unit: ZeroUnit, fn, dummy, x, *extras):
         ctx.engine, ctx.unit, ctx.fn = engine, unit, fn
         engine._ensure_resident(unit, engine._neighbour(unit, +1))
         exp = getattr(unit, "expert_unit", None)
         if exp is not None:
             engine._ensure_resident(exp)
         with torch.no_grad():
-            y = fn(x)
+            y = fn(x, *extras)
         engine._release_params(unit)
         ctx.handle = engine.act_store.save(x)
         ctx.x_requires_grad = x.requires_grad
+        ctx.extras = [e.detach() for e in extras]
+        ctx.extras_require_grad = [e.requires_grad for e in extras]
         return y
 
     @staticmethod
@@ -898,15 +920,18 @@ class _CheckpointedUnit(torch.autograd.Function):
         engine._begin_unit_backward(unit)
         x = ctx.handle.restore().detach()
         x.requires_grad_(True)
+        extras = [e.requires_grad_(r) for e, r in zip(ctx.extras, ctx.extras_require_grad)]
         with torch.enable_grad():
-            y = fn(x)
+            y = fn(x, *extras)
         outs = y if isinstance(y, (tuple, list)) else (y,)
         pairs = [(o, g) for o, g in zip(outs, grads) if torch.is_tensor(o) and o.requires_grad and g is not None]
         torch.autograd.backward([o for o, _ in pairs], [g for _, g in pairs])
         engine._end_unit_backward(unit)
         gx = x.grad if ctx.x_requires_grad else None
+        gextras = tuple(e.grad if r else None for e, r in zip(extras, ctx.extras_require_grad))
         ctx.handle = None
-        return None, None, None, None, gx
+        ctx.extras = None
+        return (None, None, None, None, gx) + gextras
 
 
 def initialize(
