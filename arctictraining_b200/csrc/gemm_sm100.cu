@@ -346,6 +346,263 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
     if (warp == 1) ptx::tmem_dealloc(tmem_base, TMEM_COLS);
 }
 
+// ---- CTA-pair variant ---------------------------------------------------------------------------------
+// One 256 x 256 output tile per cluster of two CTAs (`tcgen05.mma.cta_group::2`).  Each CTA stages its own 128 rows
+// of A and its own 128 rows of B (half of the N extent), so the shared-memory traffic per tensor-core cycle drops by a
+// third compared with the single-CTA 128 x 256 tile; the leader CTA (cluster rank 0) issues the MMAs for both, each
+// CTA keeps its 128 accumulator rows in its own TMEM and writes them out itself.  Dense GEMM only (no grouping).
+//
+// Barriers: `full[s]` lives in the leader and counts one expect-tx arrival per CTA plus the bytes of both CTAs'
+// copies; `empty[s]` and `tmem_full[a]` exist in both CTAs and are signalled by the leader's commits (one commit per
+// CTA, addressed through the cluster window); `tmem_empty[a]` lives in the leader and collects the arrivals of the
+// eight epilogue warps of the pair.
+template <int STAGES>
+struct PairSmemLayout {
+    static constexpr int kABytes = 128 * BK * 2;
+    static constexpr int kBBytes = 128 * BK * 2;
+    static constexpr int kStageBytes = kABytes + kBBytes;
+    static constexpr int kBarrierOffset = STAGES * kStageBytes;
+    static constexpr int kTotal = kBarrierOffset + (2 * STAGES + 4) * 8 + 16;
+};
+
+template <int STAGES, bool A_MN, bool B_MN, int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
+gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+                              const GemmParams p) {
+    using L = PairSmemLayout<STAGES>;
+    constexpr int TM = 256, TN = 256;  // tile of the pair
+    extern __shared__ __align__(1024) uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + L::kBarrierOffset);
+    uint64_t* empty_bar = full_bar + STAGES;
+    uint64_t* tmem_full = empty_bar + STAGES;
+    uint64_t* tmem_empty = tmem_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tmem_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const uint32_t cta = ptx::cluster_ctarank();  // 0 = leader
+    const bool leader = cta == 0;
+    constexpr uint32_t TMEM_COLS = 512;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            ptx::mbar_init(&full_bar[s], 2);   // one expect-tx arrival from each CTA of the pair (used in the leader)
+            ptx::mbar_init(&empty_bar[s], 1);  // leader's commit
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(&tmem_full[a], 1);
+            ptx::mbar_init(&tmem_empty[a], 8);  // four epilogue warps in each CTA (used in the leader)
+        }
+        *abort_flag = 0;
+        ptx::fence_barrier_init();
+        ptx::fence_proxy_async_smem();
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc_pair(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();  // the peer's barriers are initialised before anyone signals them
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    const int tiles_m = (p.M + TM - 1) / TM;
+    const int tiles_n = (p.N + TN - 1) / TN;
+    const int num_tiles = tiles_m * tiles_n;
+    const int k_blocks = (p.K + BK - 1) / BK;
+    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    constexpr int GROUP_M = 8;
+    auto tile_coords = [&](int t, int& tm, int& tn) {
+        const int per_group = GROUP_M * tiles_n;
+        const int g = t / per_group;
+        const int first_m = g * GROUP_M;
+        const int gsz = min(GROUP_M, tiles_m - first_m);
+        const int r = t - g * per_group;
+        tm = first_m + (r % gsz);
+        tn = r / gsz;
+    };
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ TMA producer (in both CTAs)
+        if (lane == 0) {
+            ptx::tma_prefetch_desc(&tmap_a);
+            ptx::tma_prefetch_desc(&tmap_b);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters) {
+                int tm, tn;
+                tile_coords(t, tm, tn);
+                const int a_m0 = tm * TM + (int)cta * 128, b_n0 = tn * TN + (int)cta * 128;
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, kWaitLimitNs)) {
+                        atomicCAS(p.error_flag, 0, (0x11 << 8) | 1);
+                        ok = false;
+                        break;
+                    }
+                    uint8_t* sa = smem + stage * L::kStageBytes;
+                    uint8_t* sb = sa + L::kABytes;
+                    ptx::mbar_expect_tx_cluster(ptx::mapa_shared(ptx::smem_u32(&full_bar[stage]), 0), L::kStageBytes);
+                    if constexpr (!A_MN) {
+                        ptx::tma_load_2d_pair(sa, &tmap_a, kb * BK, a_m0, &full_bar[stage]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c)
+                            ptx::tma_load_2d_pair(sa + c * (BK * 128), &tmap_a, a_m0 + c * 64, kb * BK, &full_bar[stage]);
+                    }
+                    if constexpr (!B_MN) {
+                        ptx::tma_load_2d_pair(sb, &tmap_b, kb * BK, b_n0, &full_bar[stage]);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 2; ++c)
+                            ptx::tma_load_2d_pair(sb + c * (BK * 128), &tmap_b, b_n0 + c * 64, kb * BK, &full_bar[stage]);
+                    }
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer (leader CTA only)
+        if (lane == 0 && leader) {
+            constexpr uint32_t idesc = ptx::make_idesc_bf16(TM, TN, A_MN, B_MN);
+            constexpr uint32_t A_LBO = A_MN ? BK * 128 : 16, B_LBO = B_MN ? BK * 128 : 16;
+            constexpr uint32_t A_KSTEP = A_MN ? UMMA_K * 128 : UMMA_K * 2, B_KSTEP = B_MN ? UMMA_K * 128 : UMMA_K * 2;
+            int stage = 0;
+            uint32_t phase = 0;
+            uint32_t acc_phase[2] = {0, 0};
+            int it = 0;
+            bool ok = true;
+            for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+                const int acc = it & 1;
+                if (!ptx::mbar_wait_bounded(&tmem_empty[acc], acc_phase[acc] ^ 1u, abort_flag, kWaitLimitNs)) {
+                    atomicCAS(p.error_flag, 0, (0x12 << 8) | 1);
+                    ok = false;
+                    break;
+                }
+                acc_phase[acc] ^= 1u;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + (uint32_t)(acc * TN);
+                for (int kb = 0; kb < k_blocks; ++kb) {
+                    if (!ptx::mbar_wait_bounded(&full_bar[stage], phase, abort_flag, kWaitLimitNs)) {
+                        atomicCAS(p.error_flag, 0, (0x12 << 8) | 2);
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after();
+                    const uint32_t sa = ptx::smem_u32(smem + stage * L::kStageBytes);
+                    const uint32_t sb = sa + L::kABytes;
+#pragma unroll
+                    for (int k = 0; k < BK / UMMA_K; ++k) {
+                        const uint64_t da = ptx::make_smem_desc_sw128(sa + k * A_KSTEP, A_LBO, 1024);
+                        const uint64_t db = ptx::make_smem_desc_sw128(sb + k * B_KSTEP, B_LBO, 1024);
+                        ptx::mma_bf16_ss_pair(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    const uint32_t eb = ptx::smem_u32(&empty_bar[stage]);
+                    ptx::mma_commit_pair(ptx::mapa_shared(eb, 0));  // frees the slot in both CTAs
+                    ptx::mma_commit_pair(ptx::mapa_shared(eb, 1));
+                    if (++stage == STAGES) { stage = 0; phase ^= 1u; }
+                }
+                if (ok) {
+                    const uint32_t fb = ptx::smem_u32(&tmem_full[acc]);
+                    ptx::mma_commit_pair(ptx::mapa_shared(fb, 0));
+                    ptx::mma_commit_pair(ptx::mapa_shared(fb, 1));
+                }
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ epilogue (warps 2..5 of both CTAs)
+        const int quarter = warp & 3;
+        uint32_t acc_phase[2] = {0, 0};
+        int it = 0;
+        bool ok = true;
+        for (int t = cluster_id; t < num_tiles && ok; t += num_clusters, ++it) {
+            const int acc = it & 1;
+            int tm, tn;
+            tile_coords(t, tm, tn);
+            if (!ptx::mbar_wait_bounded(&tmem_full[acc], acc_phase[acc], abort_flag, kWaitLimitNs)) {
+                if (lane == 0) atomicCAS(p.error_flag, 0, (0x13 << 8) | 1);
+                ok = false;
+                break;
+            }
+            acc_phase[acc] ^= 1u;
+            ptx::tc_fence_after();
+            const int row = tm * TM + (int)cta * 128 + quarter * 32 + lane;
+            const bool row_ok = row < p.M;
+            const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN);
+            if constexpr (EPI == EPI_SWIGLU) {
+                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * (TN / 2);
+#pragma unroll 1
+                for (int g = 0; g < TN / 128; ++g) {
+#pragma unroll 1
+                    for (int h = 0; h < 2; ++h) {
+                        uint32_t rg[32], ru[32];
+                        ptx::tmem_ld_32x32b_x32(taddr + g * 128 + h * 32, rg);
+                        ptx::tmem_ld_32x32b_x32(taddr + g * 128 + 64 + h * 32, ru);
+                        ptx::tmem_ld_wait();
+                        const int col0 = tn * (TN / 2) + g * 64 + h * 32;
+                        if (row_ok && col0 < p.N / 2) {
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) {
+                                float o[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    const float gg = __uint_as_float(rg[v * 8 + j]);
+                                    const float uu = __uint_as_float(ru[v * 8 + j]);
+                                    o[j] = gg / (1.f + __expf(-gg)) * uu;
+                                }
+                                *reinterpret_cast<bf16x8*>(crow + g * 64 + h * 32 + v * 8) = pack8(o);
+                            }
+                        }
+                    }
+                }
+            } else {
+                bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * TN;
+#pragma unroll 1
+                for (int c = 0; c < TN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    const int col0 = tn * TN + c * 32;
+                    if (row_ok) {
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            if (col0 + v * 8 < p.N) {
+                                float o[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(r[v * 8 + j]);
+                                bf16x8* dst = reinterpret_cast<bf16x8*>(crow + c * 32 + v * 8);
+                                if constexpr (EPI == EPI_ACCUM) {
+                                    float old[8];
+                                    unpack8(*dst, old);
+#pragma unroll
+                                    for (int j = 0; j < 8; ++j) o[j] += old[j];
+                                }
+                                *dst = pack8(o);
+                            }
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive_cluster(ptx::mapa_shared(ptx::smem_u32(&tmem_empty[acc]), 0));
+        }
+    }
+
+    // ---------------------------------------------------------------------- teardown
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::cluster_sync();  // no CTA of the pair leaves while the other may still signal its barriers or read its tiles
+    ptx::tc_fence_after();
+    if (warp == 1) {
+        __syncwarp();
+        ptx::tmem_dealloc_pair(tmem_base, TMEM_COLS);
+    }
+}
+
 // ---- host side ----------------------------------------------------------------------------------
 
 PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
@@ -401,6 +658,50 @@ void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams&
     ATB_LAUNCH_CHECK();
 }
 
+template <int STAGES, bool A_MN, bool B_MN, int EPI>
+void launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas) {
+    using L = PairSmemLayout<STAGES>;
+    auto kernel = gemm_bf16_tcgen05_pair_kernel<STAGES, A_MN, B_MN, EPI>;
+    constexpr int smem_bytes = L::kTotal + 1024;
+    // The tile loop is static (cluster i takes tiles i, i + n, ...), so every cluster of the grid must be resident at
+    // once: ask the runtime how many CTA pairs fit on the device (GPCs with an odd SM count leave one SM unpaired).
+    static int max_clusters = 0;
+    if (max_clusters == 0) {
+        C10_CUDA_CHECK(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(kNumSMs / 2 * 2);
+        cfg.blockDim = dim3(192);
+        cfg.dynamicSmemBytes = smem_bytes;
+        cudaLaunchAttribute attr;
+        attr.id = cudaLaunchAttributeClusterDimension;
+        attr.val.clusterDim.x = 2;
+        attr.val.clusterDim.y = 1;
+        attr.val.clusterDim.z = 1;
+        cfg.attrs = &attr;
+        cfg.numAttrs = 1;
+        int n = 0;
+        C10_CUDA_CHECK(cudaOccupancyMaxActiveClusters(&n, kernel, &cfg));
+        max_clusters = std::max(1, n);
+    }
+    const int tiles = (int)(ceil_div(p.M, 256) * ceil_div(p.N, 256));
+    const int clusters = std::max(1, std::min(tiles, std::min(max_ctas / 2, max_clusters)));
+    kernel<<<2 * clusters, 192, smem_bytes, current_stream()>>>(ta, tb, p);
+    ATB_LAUNCH_CHECK();
+}
+
+template <bool A_MN, bool B_MN>
+void dispatch_epi_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas) {
+    switch (epi) {
+        case EPI_STORE: launch_gemm_pair<6, A_MN, B_MN, EPI_STORE>(ta, tb, p, max_ctas); break;
+        case EPI_ACCUM: launch_gemm_pair<6, A_MN, B_MN, EPI_ACCUM>(ta, tb, p, max_ctas); break;
+        case EPI_SWIGLU:
+            if constexpr (!A_MN && !B_MN) { launch_gemm_pair<6, false, false, EPI_SWIGLU>(ta, tb, p, max_ctas); break; }
+        default: TORCH_CHECK(false, "gemm: unsupported epilogue ", epi, " for this operand layout");
+    }
+}
+
+static bool g_use_cta_pairs = true;  // dense GEMMs run on the CTA-pair kernel unless switched off
+
 template <bool A_MN, bool B_MN>
 void dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas) {
     switch (epi) {
@@ -451,8 +752,9 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     // tensor maps: K-major operand [rows, K] -> box [tile rows, 64 k]; MN-major [K, rows] -> box [64 k, 64 rows]
     const CUtensorMap ta = a_mn ? make_tmap_bf16(a.data_ptr(), K, M, a.stride(0), BK)
                                 : make_tmap_bf16(a.data_ptr(), M, K, a.stride(0), BM);
+    const bool pairs = g_use_cta_pairs && max_ctas != 1;
     const CUtensorMap tb = b_mn ? make_tmap_bf16(b.data_ptr(), K, N, b.stride(0), BK)
-                                : make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), 256);
+                                : make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), pairs ? 128 : 256);
     if (a_mn) TORCH_CHECK(M % 8 == 0, "gemm: MN-major A needs M to be a multiple of 8");
 
     GemmParams p;
@@ -464,6 +766,13 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     p.num_groups = 0;
     p.group_mode = GROUP_NONE;
     const int ctas = max_ctas > 0 ? (int)max_ctas : kNumSMs;
+    if (pairs) {
+        if (!a_mn && !b_mn) dispatch_epi_pair<false, false>(epi, ta, tb, p, ctas);
+        else if (!a_mn && b_mn) dispatch_epi_pair<false, true>(epi, ta, tb, p, ctas);
+        else if (a_mn && !b_mn) dispatch_epi_pair<true, false>(epi, ta, tb, p, ctas);
+        else dispatch_epi_pair<true, true>(epi, ta, tb, p, ctas);
+        return out;
+    }
     if (!a_mn && !b_mn) dispatch_epi<false, false>(epi, ta, tb, p, ctas);
     else if (!a_mn && b_mn) dispatch_epi<false, true>(epi, ta, tb, p, ctas);
     else if (a_mn && !b_mn) dispatch_epi<true, false>(epi, ta, tb, p, ctas);
@@ -547,6 +856,13 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
     }
     ATB_CHECK_ALIGNED16(out);
     return out;
+}
+
+// Selects the CTA-pair (cta_group::2, 256 x 256 tile) kernel for dense GEMMs; returns the previous setting.
+bool set_gemm_cta_pairs(bool on) {
+    const bool old = g_use_cta_pairs;
+    g_use_cta_pairs = on;
+    return old;
 }
 
 // Reads and clears the per-device error word written by kernels whose bounded waits gave up.

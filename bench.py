@@ -44,6 +44,7 @@ def parse_args():
     p.add_argument("--attn", type=str, default="flash_attention_2")
     p.add_argument("--gemm", type=str, default=os.getenv("ATB200_GEMM", "tcgen05"), choices=["tcgen05", "cublas"])
     p.add_argument("--skip-e2e", action="store_true")
+    p.add_argument("--no-cta-pairs", action="store_true", help="use the single-CTA 128x256 GEMM tile instead of the CTA-pair kernel")
     return p.parse_args()
 
 
@@ -140,6 +141,10 @@ def main() -> None:
 
     init_distributed(local_rank)
     F_ops.set_gemm_backend(args.gemm)
+    from arctictraining_b200.ops import _ext
+
+    _ext.require()
+    torch.ops.atb200.set_gemm_cta_pairs(not args.no_cta_pairs)
     device = torch.device("cuda", torch.cuda.current_device())
 
     total_steps = args.warmup + args.steps
@@ -264,7 +269,7 @@ def main() -> None:
                 "optimizer": "adamw fp32 master",
                 "activation_checkpointing": True,
                 "attention": args.attn,
-                "gemm": args.gemm,
+                "gemm": args.gemm + ("" if args.gemm != "tcgen05" else ("-1cta" if args.no_cta_pairs else "-2cta")),
                 "l2_policy": "inputs larger than L2 (16 GB of weights streamed every step)",
                 "valid": not args.layers,
             },

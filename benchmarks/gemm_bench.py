@@ -40,9 +40,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--no-cublas", action="store_true")
     ap.add_argument("--out", type=str, default="")
+    ap.add_argument("--pairs", action="store_true", help="use the CTA-pair (cta_group::2) kernel")
     args = ap.parse_args()
     _ext.require()
     k = torch.ops.atb200
+    k.set_gemm_cta_pairs(bool(args.pairs))
     shapes = [tuple(int(x) for x in args.case.split(","))] if args.case else SHAPES
     rows = []
     for M, N, K in shapes:

@@ -364,3 +364,44 @@ def test_arctic_moe_layer_on_gpu_matches_cpu_reference():
     assert _rel(xg.grad.cpu(), xc.grad) < 5e-2
     assert _rel(gpu.expert_down.grad.cpu(), cpu.expert_down.grad) < 5e-2
     assert _rel(gpu.router_gate.grad.cpu(), cpu.router_gate.grad) < 8e-2
+
+
+# ------------------------------------------------------------------------------------------------ CTA-pair GEMM
+@pytest.fixture
+def cta_pairs(k):
+    old = k.set_gemm_cta_pairs(True)
+    yield
+    k.set_gemm_cta_pairs(old)
+
+
+@pytest.mark.parametrize("M,N,K", [(256, 256, 64), (512, 768, 256), (300, 264, 200), (8, 8, 8), (4096, 1024, 4096), (1000, 520, 72)])
+@pytest.mark.parametrize("a_mn,b_mn", [(False, False), (False, True), (True, True)])
+def test_gemm_cta_pair_kernel(k, cta_pairs, M, N, K, a_mn, b_mn):
+    torch.manual_seed(0)
+    if a_mn and M % 8:
+        pytest.skip("MN-major A needs M % 8 == 0")
+    a = torch.randn(K, M, device="cuda", dtype=torch.bfloat16) if a_mn else torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = torch.randn(K, N, device="cuda", dtype=torch.bfloat16) if b_mn else torch.randn(N, K, device="cuda", dtype=torch.bfloat16)
+    c = k.gemm_bf16(a, b, a_mn, b_mn, 0, None, 0)
+    torch.cuda.synchronize()
+    _check_flag(a)
+    af = a.float().t() if a_mn else a.float()
+    bf = b.float() if b_mn else b.float().t()
+    assert _rel(c, af @ bf) < 1e-2
+
+
+def test_gemm_cta_pair_epilogues(k, cta_pairs):
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    M, N, K = 640, 1024, 256
+    a = torch.randn(M, K, device="cuda", dtype=torch.bfloat16)
+    b = (0.1 * torch.randn(N, K, device="cuda")).bfloat16()
+    base = torch.randn(M, N, device="cuda", dtype=torch.bfloat16)
+    out = base.clone()
+    k.gemm_bf16(a, b, False, False, 1, out, 0)
+    assert _rel(out, base.float() + a.float() @ b.float().t()) < 1e-2
+    h = k.gemm_bf16(a, b, False, False, 2, None, 0)
+    torch.cuda.synchronize()
+    _check_flag(a)
+    assert _rel(h, ref.swiglu_interleaved(a.float() @ b.float().t())) < 1e-2
