@@ -1,0 +1,99 @@
+"""Mixture of Block Attention (MoBA): every query attends to its own key block (causally) plus the ``topk - 1`` earlier
+key blocks whose mean key scores highest against the query.
+
+Behaviour parity: projects/moba_attention/moba/moba_naive.py:27-110 (oracle) and moba_efficient.py:31-417 (two varlen
+attention calls merged by their log-sum-exp).  ``moba_attn_naive`` materialises the full score matrix and is the test
+oracle; ``moba_attn_varlen`` computes block gating once and evaluates attention chunk by chunk with a block mask, which
+keeps memory at ``O(chunk x seqlen)`` per head.
+"""
+
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+
+def _gate_mask(q: torch.Tensor, k: torch.Tensor, chunk: int, topk: int) -> torch.Tensor:
+    """``[H, S, num_blocks]`` boolean: which key blocks each query may attend to (own block always included)."""
+    S, H, D = q.shape
+    nblk = math.ceil(S / chunk)
+    pad = nblk * chunk - S
+    kf = k.float()
+    if pad:
+        kf = torch.cat([kf, kf.new_zeros(pad, H, D)], dim=0)
+        counts = torch.full((nblk,), chunk, device=q.device, dtype=torch.float32)
+        counts[-1] = chunk - pad
+    else:
+        counts = torch.full((nblk,), chunk, device=q.device, dtype=torch.float32)
+    means = kf.view(nblk, chunk, H, D).sum(1) / counts.view(-1, 1, 1)  # [N, H, D]
+    gate = torch.einsum("shd,nhd->hsn", q.float(), means)
+    pos = torch.arange(S, device=q.device)
+    blk_of_q = pos // chunk
+    blk = torch.arange(nblk, device=q.device)
+    future = blk.view(1, -1) >= blk_of_q.view(-1, 1)  # current and later blocks are not scored
+    gate = gate.masked_fill(future.unsqueeze(0), float("-inf"))
+    own = blk.view(1, -1) == blk_of_q.view(-1, 1)
+    gate = gate.masked_fill(own.unsqueeze(0), float("inf"))
+    kk = min(topk, nblk)
+    idx = torch.topk(gate, k=kk, dim=-1, sorted=False).indices
+    mask = torch.zeros_like(gate, dtype=torch.bool).scatter_(-1, idx, True)
+    return mask & torch.isfinite(gate).logical_or(own.unsqueeze(0))
+
+
+def moba_attn_naive(q, k, v, cu_seqlens, max_seqlen: int, moba_chunk_size: int, moba_topk: int) -> torch.Tensor:
+    """Brute-force MoBA over packed sequences ``[total, H, D]`` (oracle)."""
+    out = torch.zeros_like(q)
+    scale = q.shape[-1] ** -0.5
+    bounds = cu_seqlens.tolist()
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        q_, k_, v_ = q[s:e], k[s:e], v[s:e]
+        n = e - s
+        allowed_blk = _gate_mask(q_, k_, moba_chunk_size, moba_topk)  # [H, n, N]
+        allowed = allowed_blk.repeat_interleave(moba_chunk_size, dim=-1)[:, :, :n]
+        allowed &= torch.ones(n, n, dtype=torch.bool, device=q.device).tril().unsqueeze(0)
+        scores = torch.einsum("xhd,yhd->hxy", q_.float(), k_.float()) * scale
+        p = scores.masked_fill(~allowed, float("-inf")).softmax(-1)
+        out[s:e] = torch.einsum("hxy,yhd->xhd", p, v_.float()).to(q.dtype)
+    return out
+
+
+def moba_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, moba_chunk_size: int, moba_topk: int,
+                     query_chunk: int = 1024) -> torch.Tensor:
+    """Memory-bounded MoBA: same result as :func:`moba_attn_naive`, evaluated ``query_chunk`` queries at a time."""
+    out = torch.empty_like(q)
+    scale = q.shape[-1] ** -0.5
+    bounds = cu_seqlens.tolist()
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        q_, k_, v_ = q[s:e], k[s:e], v[s:e]
+        n = e - s
+        allowed_blk = _gate_mask(q_, k_, moba_chunk_size, moba_topk)
+        kf, vf = k_.float(), v_.float()
+        for a in range(0, n, query_chunk):
+            b = min(n, a + query_chunk)
+            kv_end = b  # causal: nothing after the last query of the chunk is needed
+            allowed = allowed_blk[:, a:b].repeat_interleave(moba_chunk_size, dim=-1)[:, :, :kv_end]
+            causal = torch.arange(kv_end, device=q.device).view(1, -1) <= torch.arange(a, b, device=q.device).view(-1, 1)
+            scores = torch.einsum("xhd,yhd->hxy", q_[a:b].float(), kf[:kv_end]) * scale
+            p = scores.masked_fill(~(allowed & causal.unsqueeze(0)), float("-inf")).softmax(-1)
+            out[s + a : s + b] = torch.einsum("hxy,yhd->xhd", p, vf[:kv_end]).to(q.dtype)
+    return out
+
+
+class MoBAContext:
+    """Drop-in attention core for the native model: set ``model.sp_context``-style hook via ``install``."""
+
+    def __init__(self, chunk_size: int, topk: int) -> None:
+        self.chunk_size, self.topk = chunk_size, topk
+
+    def attention(self, q, k, v, ctx) -> torch.Tensor:
+        B, S, Hq, D = q.shape
+        rep = Hq // k.shape[2]
+        outs = []
+        for b in range(B):
+            cu = ctx.cu_seqlens if (ctx.cu_seqlens is not None and B == 1) else torch.tensor([0, S], device=q.device)
+            kb = k[b].repeat_interleave(rep, dim=1)
+            vb = v[b].repeat_interleave(rep, dim=1)
+            outs.append(moba_attn_varlen(q[b], kb, vb, cu, S, self.chunk_size, self.topk))
+        return torch.stack(outs, 0)

@@ -1,0 +1,198 @@
+"""Helpers for writing tests against the framework.  Behaviour parity with the subset of
+arctic_training/testing_utils.py:67-1156 that the reference's own tests use: hardware requirement markers, unique
+rendezvous ports per pytest-xdist worker, temp-dir test case, stream capture, subprocess execution with live output,
+tolerant tensor / safetensors comparison, environment patching.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import contextlib
+import io
+import os
+import shutil
+import sys
+import tempfile
+import unittest
+from pathlib import Path
+from typing import Any
+from typing import Dict
+from typing import Iterator
+from typing import List
+from typing import Optional
+from unittest import mock
+
+import torch
+
+DEFAULT_MASTER_PORT = 10999
+
+
+def get_xdist_worker_id() -> int:
+    return int(os.environ.get("PYTEST_XDIST_WORKER", "gw0").replace("gw", "") or 0)
+
+
+def get_unique_port_number() -> int:
+    """A rendezvous port that differs between pytest-xdist workers."""
+    return DEFAULT_MASTER_PORT + get_xdist_worker_id()
+
+
+def _require(cond: bool, reason: str):
+    import pytest
+
+    return pytest.mark.skipif(not cond, reason=reason)
+
+
+def require_torch_gpu(fn):
+    return _require(torch.cuda.is_available(), "test requires a GPU")(fn)
+
+
+def require_torch_multi_gpu(fn):
+    return _require(torch.cuda.device_count() > 1, "test requires multiple GPUs")(fn)
+
+
+def require_torch_non_multi_gpu(fn):
+    return _require(torch.cuda.device_count() < 2, "test requires 0 or 1 GPU")(fn)
+
+
+def torch_assert_equal(actual: Any, expected: Any, **kw: Any) -> None:
+    torch.testing.assert_close(actual, expected, rtol=0.0, atol=0.0, **kw)
+
+
+def torch_assert_close(actual: Any, expected: Any, **kw: Any) -> None:
+    torch.testing.assert_close(actual, expected, **kw)
+
+
+def torch_assert_safetensors_close(path_a: str, path_b: str, rtol: float = 1.6e-2, atol: float = 1e-5) -> None:
+    """Two safetensors files hold the same tensor names with numerically close values."""
+    from safetensors.torch import load_file
+
+    a, b = load_file(path_a), load_file(path_b)
+    assert set(a) == set(b), f"different tensor names: {sorted(set(a) ^ set(b))[:10]}"
+    for k in a:
+        torch.testing.assert_close(a[k].float(), b[k].float(), rtol=rtol, atol=atol, msg=lambda m, k=k: f"{k}: {m}")
+
+
+@contextlib.contextmanager
+def mockenv_context(*remove: str, **update: str) -> Iterator[None]:
+    """Temporarily set / unset environment variables."""
+    env = os.environ
+    stomped = (set(update) | set(remove)) & set(env)
+    saved = {k: env[k] for k in stomped}
+    try:
+        env.update(update)
+        for k in remove:
+            env.pop(k, None)
+        yield
+    finally:
+        for k in set(update) | set(remove):
+            env.pop(k, None)
+        env.update(saved)
+
+
+def mockenv(**kwargs: str):
+    return mock.patch.dict(os.environ, kwargs)
+
+
+class CaptureStd:
+    """Context manager capturing stdout and/or stderr; ``.out`` / ``.err`` hold the text afterwards."""
+
+    def __init__(self, out: bool = True, err: bool = True, replay: bool = True) -> None:
+        self.want_out, self.want_err, self.replay = out, err, replay
+        self.out = self.err = ""
+
+    def __enter__(self) -> "CaptureStd":
+        if self.want_out:
+            self._old_out, sys.stdout = sys.stdout, io.StringIO()
+        if self.want_err:
+            self._old_err, sys.stderr = sys.stderr, io.StringIO()
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        if self.want_out:
+            self.out, sys.stdout = sys.stdout.getvalue(), self._old_out
+            if self.replay:
+                sys.stdout.write(self.out)
+        if self.want_err:
+            self.err, sys.stderr = sys.stderr.getvalue(), self._old_err
+            if self.replay:
+                sys.stderr.write(self.err)
+
+
+class CaptureStdout(CaptureStd):
+    def __init__(self, replay: bool = True) -> None:
+        super().__init__(err=False, replay=replay)
+
+
+class CaptureStderr(CaptureStd):
+    def __init__(self, replay: bool = True) -> None:
+        super().__init__(out=False, replay=replay)
+
+
+class _RunOutput:
+    def __init__(self, returncode: int, stdout: List[str], stderr: List[str]) -> None:
+        self.returncode, self.stdout, self.stderr = returncode, stdout, stderr
+
+
+async def _stream(cmd: List[str], env: Optional[Dict[str, str]], echo: bool, timeout: Optional[float]) -> _RunOutput:
+    proc = await asyncio.create_subprocess_exec(*cmd, stdout=asyncio.subprocess.PIPE, stderr=asyncio.subprocess.PIPE, env=env)
+    out: List[str] = []
+    err: List[str] = []
+
+    async def pump(stream, sink, pipe, label):
+        while True:
+            line = await stream.readline()
+            if not line:
+                break
+            text = line.decode("utf-8", "replace").rstrip()
+            sink.append(text)
+            if echo:
+                print(label, text, file=pipe)
+
+    await asyncio.wait_for(
+        asyncio.gather(pump(proc.stdout, out, sys.stdout, "stdout:"), pump(proc.stderr, err, sys.stderr, "stderr:"), proc.wait()),
+        timeout=timeout,
+    )
+    return _RunOutput(proc.returncode, out, err)
+
+
+def execute_subprocess_async(cmd: List[str], env: Optional[Dict[str, str]] = None, timeout: Optional[float] = 600,
+                             echo: bool = True) -> _RunOutput:
+    """Run ``cmd`` streaming its output live; raises with the captured stderr when it fails."""
+    result = asyncio.run(_stream(cmd, env, echo, timeout))
+    if result.returncode != 0:
+        raise RuntimeError(f"'{' '.join(cmd)}' failed with returncode {result.returncode}\n\n" + "\n".join(result.stderr[-200:]))
+    return result
+
+
+class TestCasePlus(unittest.TestCase):
+    """``unittest.TestCase`` with auto-removed temp dirs and an environment that can import the repository."""
+
+    def setUp(self) -> None:
+        self._teardown_dirs: List[str] = []
+        here = Path(sys.modules[self.__class__.__module__].__file__).resolve()
+        self.test_file_dir = here.parent
+        self.repo_root_dir = next((p for p in here.parents if (p / "arctictraining_b200").is_dir()), here.parent)
+
+    def get_env(self) -> Dict[str, str]:
+        env = dict(os.environ)
+        paths = [str(self.repo_root_dir)] + ([env["PYTHONPATH"]] if env.get("PYTHONPATH") else [])
+        env["PYTHONPATH"] = ":".join(paths)
+        return env
+
+    def get_auto_remove_tmp_dir(self, tmp_dir: Optional[str] = None, before: bool = True, after: bool = True) -> str:
+        if tmp_dir is None:
+            tmp_dir = tempfile.mkdtemp()
+        else:
+            path = Path(tmp_dir).resolve()
+            if before and path.exists():
+                shutil.rmtree(path, ignore_errors=True)
+            path.mkdir(parents=True, exist_ok=True)
+            tmp_dir = str(path)
+        if after:
+            self._teardown_dirs.append(tmp_dir)
+        return tmp_dir
+
+    def tearDown(self) -> None:
+        for d in self._teardown_dirs:
+            shutil.rmtree(d, ignore_errors=True)
+        self._teardown_dirs = []

@@ -1,0 +1,161 @@
+"""Trainer smoke tests and checkpoint round trips on CPU (pattern of the reference's tests/trainer and
+tests/checkpoint: a few iterations on a tiny random model; rebuild and compare weights bit for bit)."""
+
+import json
+from pathlib import Path
+
+import pytest
+import torch
+
+from arctictraining_b200.config.trainer import get_config
+from arctictraining_b200.registry import get_registered_trainer
+
+
+def build(recipe):
+    cfg = get_config(recipe)
+    return get_registered_trainer(cfg.type)(cfg)
+
+
+def test_sft_trainer_runs_and_logs_metrics(tiny_recipe, tmp_path):
+    tr = build(tiny_recipe(exit_iteration=3))
+    tr.train()
+    assert tr.global_step == 3 and tr.early_stop
+    rows = [json.loads(line) for line in Path(tr.config.train_log_metrics_path).read_text().splitlines()]
+    assert [r["iter"] for r in rows] == [1, 2, 3]
+    assert {"loss", "lr", "iter_time", "step_time", "seqlen", "epoch"} <= set(rows[0])
+
+
+def test_overfit_first_batch_reduces_loss(tiny_recipe):
+    tr = build(tiny_recipe(overfit_first_batch=True, exit_iteration=12, optimizer={"lr": 5e-3, "weight_decay": 0.0},
+                           scheduler={"name": "constant"}))
+    tr.train()
+    rows = [json.loads(line) for line in Path(tr.config.train_log_metrics_path).read_text().splitlines()]
+    assert rows[-1]["loss"] < rows[0]["loss"] - 0.5
+
+
+def test_eval_interval_and_gradient_accumulation(tiny_recipe, tmp_path):
+    data = {"sources": [{"type": "synthetic", "num_samples": 32, "min_length": 32, "max_length": 32}],
+            "train_eval_split": [0.75, 0.25], "cache_dir": str(tmp_path / "c"), "max_length": 32, "dl_num_workers": 0}
+    tr = build(tiny_recipe(data=data, eval_interval=2, gradient_accumulation_steps=2, exit_iteration=4))
+    tr.train()
+    assert tr.global_step == 4 and tr.train_batch_idx >= 8
+    assert "loss/eval" in tr.metrics.summary_dict
+
+
+def test_kill_switch_stops_training(tiny_recipe, tmp_path):
+    tr = build(tiny_recipe(exit_iteration=0))
+    Path(tr.config.kill_switch_path).write_text("stop")
+    tr.train()
+    assert tr.early_stop and "kill switch" in tr.early_stop_reason and tr.global_step == 0
+
+
+def test_causal_trainer(tiny_recipe, tmp_path):
+    from datasets import Dataset
+
+    ds_dir = tmp_path / "text_ds"
+    Dataset.from_dict({"text": [" ".join(f"w{i + j}" for j in range(60)) for i in range(24)]}).save_to_disk(str(ds_dir))
+    data = {"sources": [{"type": "huggingface_causal", "name_or_path": str(ds_dir)}], "cache_dir": str(tmp_path / "c"),
+            "max_length": 32, "dl_num_workers": 0}
+    tr = build(tiny_recipe(type="causal", data=data, exit_iteration=2))
+    batch = next(iter(tr.train_dataloader))
+    assert batch["input_ids"].shape == (2, 32) and torch.equal(batch["input_ids"], batch["labels"])
+    tr.train()
+    assert tr.global_step == 2
+
+
+def test_dpo_trainer(tiny_recipe, tmp_path):
+    r = tiny_recipe(type="dpo", micro_batch_size=1, ref_model={"name_or_path": "tiny-llama", "dtype": "fp32"},
+                    data={"sources": [{"type": "synthetic_dpo", "num_samples": 16, "words_per_message": 6}],
+                          "cache_dir": str(tmp_path / "c"), "max_length": 64, "dl_num_workers": 0},
+                    exit_iteration=2, beta=0.5)
+    tr = build(r)
+    batch = next(iter(tr.train_dataloader))
+    first = float(tr.loss(batch))
+    assert first == pytest.approx(0.6931, abs=1e-3)  # policy == reference at the start: -log(sigmoid(0))
+    tr.train()
+    assert tr.global_step == 2
+
+
+def test_dpo_fused_logprobs_match_plain_logits(tiny_recipe, tmp_path):
+    from arctictraining_b200.trainer.dpo import get_logprobs
+
+    r = tiny_recipe(type="dpo", micro_batch_size=1, ref_model={"name_or_path": "tiny-llama", "dtype": "fp32"},
+                    data={"sources": [{"type": "synthetic_dpo", "num_samples": 8, "words_per_message": 6}],
+                          "cache_dir": str(tmp_path / "c"), "max_length": 64, "dl_num_workers": 0})
+    tr = build(r)
+    batch = next(iter(tr.train_dataloader))
+    lp, n = tr.sequence_logprobs(tr.model, batch)
+    logits = tr.model(input_ids=batch["input_ids"], return_logits=True).logits.float()
+    ref_lp, ref_n = get_logprobs(logits, batch["labels"], -100)
+    assert torch.allclose(lp, ref_lp, atol=1e-3) and torch.equal(n, ref_n)
+
+
+def _force_checkpoint(tr):
+    tr.global_step_this_run = 1
+    tr.training_finished = True
+    tr.checkpoint()
+
+
+@pytest.mark.parametrize("stage", [0, 2, 3])
+def test_sharded_checkpoint_resume_is_bit_exact(tiny_recipe, tmp_path, stage):
+    ck = [{"type": "deepspeed", "output_dir": str(tmp_path / "ck"), "auto_resume": True, "save_every_n_steps": 2}]
+    a = build(tiny_recipe(checkpoint=ck, exit_iteration=2, deepspeed={"zero_optimization": {"stage": stage}}))
+    a.train()
+    assert (tmp_path / "ck" / "latest").read_text().startswith("epoch_0_global_step_2")
+    b = build(tiny_recipe(checkpoint=ck, exit_iteration=4, seed=99, deepspeed={"zero_optimization": {"stage": stage}}))
+    assert b.is_resume is False or b.global_step == 2  # resume consumed
+    assert b.global_step == 2 and b.model.global_steps == 2
+    pa = dict(a.model.iter_full_named_parameters())
+    pb = dict(b.model.iter_full_named_parameters())
+    assert all(torch.equal(pa[n], pb[n]) for n in pa)
+    b.train()
+    assert b.global_step == 4
+
+
+def test_hf_checkpoint_reloads_into_an_identical_model(tiny_recipe, tmp_path):
+    ck = [{"type": "huggingface", "output_dir": str(tmp_path / "hf"), "save_end_of_training": True}]
+    a = build(tiny_recipe(checkpoint=ck, exit_iteration=2, deepspeed={"zero_optimization": {"stage": 3}}))
+    a.train()
+    out = tmp_path / "hf" / "global_step_2"
+    assert (out / "config.json").exists() and (out / "model.safetensors").exists()
+    from safetensors.torch import load_file
+
+    names = set(load_file(str(out / "model.safetensors")))
+    assert "model.layers.0.self_attn.q_proj.weight" in names and "model.layers.1.mlp.up_proj.weight" in names
+    b = build(tiny_recipe(model={"name_or_path": str(out), "dtype": "fp32"}, seed=5))
+    pa = dict(a.model.iter_full_named_parameters())
+    pb = dict(b.model.iter_full_named_parameters())
+    assert all(torch.equal(pa[n], pb[n]) for n in pa)
+
+
+def test_lora_trains_only_adapters_and_exports_them(tiny_recipe, tmp_path):
+    ck = [{"type": "huggingface", "output_dir": str(tmp_path / "hf"), "save_end_of_training": True}]
+    tr = build(tiny_recipe(model={"peft_config": {"peft_type": "LORA", "r": 4, "target_modules": ["q_proj", "down_proj"]}},
+                           checkpoint=ck, exit_iteration=2))
+    trainable = [n for n, p in tr.model_unwrapped.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    tr.train()
+    from safetensors.torch import load_file
+
+    saved = load_file(str(tmp_path / "hf" / "global_step_2" / "model.safetensors"))
+    assert saved and all("lora_" in n for n in saved)
+
+
+def test_callbacks_declared_on_a_custom_trainer_fire(tiny_recipe):
+    from arctictraining_b200 import SFTTrainer
+
+    seen = []
+
+    class CountingTrainer(SFTTrainer):
+        name = "counting-sft-test"
+
+        def post_step_callback(self):
+            seen.append(self.global_step)
+
+        def pre_loss_callback(self, batch):
+            seen.append("loss")
+            return batch
+
+    tr = build(tiny_recipe(type="counting-sft-test", exit_iteration=2))
+    tr.train()
+    assert seen == ["loss", 1, "loss", 2]
