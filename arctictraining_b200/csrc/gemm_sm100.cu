@@ -865,6 +865,11 @@ bool set_gemm_cta_pairs(bool on) {
     return old;
 }
 
+CUtensorMap make_tmap_bf16_public(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    return make_tmap_bf16(base, rows, cols, ld, box_rows);
+}
+at::Tensor& gemm_error_flag(const at::Device& dev) { return error_flag_for(dev); }
+
 // Reads and clears the per-device error word written by kernels whose bounded waits gave up.
 int64_t read_and_clear_error_flag(const at::Tensor& like) {
     auto& f = error_flag_for(like.device());

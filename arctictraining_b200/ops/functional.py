@@ -268,6 +268,50 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------------------------ attention
+class _NativeAttentionFn(torch.autograd.Function):
+    """Forward: the package's sm_100a flash-attention kernel (saves the output and the per-row log-sum-exp).
+    Backward: the flash-attn library's variable-length backward, which recomputes probabilities from that
+    log-sum-exp."""
+
+    @staticmethod
+    def forward(ctx, q, k, v, cu, max_seqlen, scale):
+        # q [T, Hq, D], k / v [T, Hkv, D]; token stride may be that of a fused projection output
+        T = q.shape[0]
+        nseq = cu.numel() - 1
+        _count()
+        out, lse = _ext.ops().fmha_fwd(q, k, v, cu, T // 128 + nseq, scale)
+        ctx.save_for_backward(q, k, v, out, lse, cu)
+        ctx.max_seqlen, ctx.scale = max_seqlen, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
+
+        q, k, v, out, lse, cu = ctx.saved_tensors
+        dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
+        _flash_attn_varlen_backward(
+            dout.contiguous(), q, k, v, out, lse, dq, dk, dv, cu, cu, ctx.max_seqlen, ctx.max_seqlen,
+            0.0, ctx.scale, True, -1, -1, 0.0, None, False,
+        )
+        return dq, dk, dv, None, None, None
+
+
+def _native_attention(q, k, v, cu_seqlens, max_seqlen, scale):
+    B, S, Hq, D = q.shape
+    if cu_seqlens is None or B > 1:
+        cu = torch.arange(0, (B + 1) * S, S, device=q.device, dtype=torch.int32)
+        max_seqlen = S
+    else:
+        cu = cu_seqlens.to(torch.int32)
+        max_seqlen = int(max_seqlen or S)
+    scale = float(scale if scale is not None else D ** -0.5)
+    o = _NativeAttentionFn.apply(
+        q.reshape(B * S, Hq, D), k.reshape(B * S, -1, D), v.reshape(B * S, -1, D), cu, max_seqlen, scale
+    )
+    return o.view(B, S, Hq, D)
+
+
 def attention(
     q: torch.Tensor,
     k: torch.Tensor,
@@ -278,7 +322,15 @@ def attention(
     impl: str = "sdpa",
     scale: Optional[float] = None,
 ) -> torch.Tensor:
-    """Causal GQA attention over ``[B, S, H, D]`` tensors; ``cu_seqlens`` marks packed samples (B == 1)."""
+    """Causal GQA attention over ``[B, S, H, D]`` tensors; ``cu_seqlens`` marks packed samples (B == 1).
+
+    ``impl == "native"`` runs this package's tcgen05 forward kernel (head_dim 128, causal, bf16) and falls
+    back to the flash-attn library for shapes the kernel does not cover."""
+    if (
+        impl == "native" and q.is_cuda and causal and q.dtype == torch.bfloat16 and q.shape[-1] == 128
+        and _ext.available()
+    ):
+        return _native_attention(q, k, v, cu_seqlens, max_seqlen, scale)
     if q.is_cuda and impl in ("flash_attention_2", "flash_attention_3", "native"):
         try:
             from flash_attn import flash_attn_func

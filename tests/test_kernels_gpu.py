@@ -405,3 +405,60 @@ def test_gemm_cta_pair_epilogues(k, cta_pairs):
     torch.cuda.synchronize()
     _check_flag(a)
     assert _rel(h, ref.swiglu_interleaved(a.float() @ b.float().t())) < 1e-2
+
+
+@pytest.mark.parametrize(
+    "lens,Hq,Hkv",
+    [([256], 4, 4), ([128, 384], 8, 2), ([100, 37, 411, 129], 4, 1), ([1000], 2, 2), ([1, 127, 128, 129], 4, 2)],
+)
+def test_native_flash_attention_forward(k, lens, Hq, Hkv):
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, device="cuda", dtype=torch.bfloat16)
+    q = qkv[:, : Hq * 128].view(T, Hq, 128)          # strided views of one fused projection output
+    kk = qkv[:, Hq * 128 : (Hq + Hkv) * 128].view(T, Hkv, 128)
+    v = qkv[:, (Hq + Hkv) * 128 :].view(T, Hkv, 128)
+    scale = 128 ** -0.5
+    out, lse = k.fmha_fwd(q, kk, v, cu, T // 128 + len(lens), scale)
+    assert k.read_and_clear_error_flag(out) == 0
+    want = ref.attention(q[None], kk[None], v[None], cu_seqlens=cu.long(), scale=scale)[0]
+    torch.testing.assert_close(out.float(), want.float(), atol=2e-2, rtol=2e-2)
+    # log-sum-exp against fp32 scores
+    qf = q.float().transpose(0, 1)
+    kf = kk.float().transpose(0, 1).repeat_interleave(Hq // Hkv, dim=0)
+    s = torch.matmul(qf, kf.transpose(-1, -2)) * scale
+    seg = ref.segment_ids_from_cu(cu.long(), T)
+    mask = torch.tril(torch.ones(T, T, dtype=torch.bool, device="cuda")) & (seg[:, None] == seg[None, :])
+    want_lse = torch.logsumexp(s.masked_fill(~mask, float("-inf")), dim=-1)
+    torch.testing.assert_close(lse, want_lse, atol=1e-2, rtol=1e-3)
+
+
+def test_native_attention_autograd_matches_reference():
+    from arctictraining_b200.ops import functional as Fn
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(1)
+    S, Hq, Hkv = 640, 4, 2
+    cu = torch.tensor([0, 200, 640], device="cuda", dtype=torch.int32)
+    q = torch.randn(1, S, Hq, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    kk = torch.randn(1, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    v = torch.randn(1, S, Hkv, 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    g = torch.randn(1, S, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    o = Fn.attention(q, kk, v, cu_seqlens=cu, max_seqlen=440, impl="native")
+    o.backward(g)
+    got = [o, q.grad, kk.grad, v.grad]
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, kk, v))
+    o2 = ref.attention(qr, kr, vr, cu_seqlens=cu.long())
+    o2.backward(g.float())
+    for a, b in zip(got, [o2, qr.grad, kr.grad, vr.grad]):
+        torch.testing.assert_close(a.float(), b.float(), atol=5e-2, rtol=5e-2)
+    # batch of equal-length rows without cu_seqlens
+    q2 = torch.randn(2, 256, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    k2 = torch.randn(2, 256, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    v2 = torch.randn(2, 256, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    torch.testing.assert_close(
+        Fn.attention(q2, k2, v2, impl="native").float(), ref.attention(q2, k2, v2).float(), atol=2e-2, rtol=2e-2
+    )
