@@ -6,7 +6,9 @@ offload_param.device, reduce_bucket_size, stage3_*}``, ``bf16|bfloat16.{enabled,
 bf16_master_weights_and_grads, bf16_optimizer_states}``, ``fp16.enabled``, ``torch_autocast.{enabled,
 dtype}``, ``gradient_clipping``, ``prescale_gradients``, ``gradient_accumulation_steps``,
 ``wall_clock_breakdown``, ``communication_data_type``, ``seq_parallel_communication_data_type``.
-Own extension: ``fused_comm`` = ``auto`` | ``off`` (peer-memory kernels vs NCCL-only).
+Own extensions: ``fused_comm`` = ``auto`` | ``off`` (peer-memory kernels vs NCCL-only);
+``activation_checkpoint_keep`` = ``0`` (recompute every layer, the behaviour of the reference) | ``N`` (the last
+N layers keep their activations) | ``auto`` (each step keeps as many layers as the free device memory allows).
 """
 
 from __future__ import annotations
@@ -18,6 +20,14 @@ from typing import Dict
 from typing import Optional
 
 import torch
+
+
+def _parse_keep(v: Any) -> Any:
+    if isinstance(v, str):
+        if v.strip().lower() == "auto":
+            return "auto"
+        return int(v)
+    return int(v or 0)
 
 
 @dataclass
@@ -39,6 +49,8 @@ class EngineConfig:
     wall_clock_breakdown: bool = False
     fused_comm: str = "auto"
     activation_checkpoint_cpu_offload: bool = False
+    activation_checkpoint_keep: Any = 0  # int, or "auto"
+    activation_keep_memory_fraction: float = 0.88
     raw: Dict[str, Any] = field(default_factory=dict)
 
     @classmethod
@@ -70,5 +82,7 @@ class EngineConfig:
             wall_clock_breakdown=bool(d.get("wall_clock_breakdown", False)),
             fused_comm=str(d.get("fused_comm", "auto")),
             activation_checkpoint_cpu_offload=bool(d.get("activation_checkpoint_cpu_offload", False)),
+            activation_checkpoint_keep=_parse_keep(d.get("activation_checkpoint_keep", 0)),
+            activation_keep_memory_fraction=float(d.get("activation_keep_memory_fraction", 0.88)),
             raw=d,
         )

@@ -46,6 +46,7 @@ import torch.nn as nn
 
 from .. import ops
 from ..logging import logger
+from ..exceptions import EngineConfigError
 from .config import EngineConfig
 from .timers import TimerGroup
 
@@ -477,9 +478,13 @@ class TrainingEngine:
 
     # ================================================================== unit execution
     def _wrap_units(self) -> None:
+        self._wrapped_units: List[ZeroUnit] = []
+        self._keep_state: Dict[str, Any] = {"phase": 0, "bytes_per_token": 0.0, "reserve": 0, "limit": 0}
         for u in self.units:
             if not u.checkpointed or not u.modules:
                 continue
+            u.wrapped_index = len(self._wrapped_units)
+            self._wrapped_units.append(u)
             assert len(u.modules) == 1, "a checkpointed unit wraps exactly one module"
             mod = u.modules[0]
             orig = mod.forward
@@ -497,6 +502,8 @@ class TrainingEngine:
                 # positional tensor arguments that carry gradients (e.g. shared K/V) are routed through autograd
                 t_idx = [i for i, a in enumerate(args) if torch.is_tensor(a) and a.requires_grad]
                 extras = [args[i] for i in t_idx]
+                if not extras and engine._keeps_activations(__unit, x):
+                    return engine._run_kept(__unit, __orig, x, args, kwargs)
 
                 def fn(inp, *ext, __args=args, __idx=tuple(t_idx)):
                     call_args = list(__args)
@@ -507,6 +514,74 @@ class TrainingEngine:
                 return _CheckpointedUnit.apply(engine, __unit, fn, engine._dummy, x, *extras)
 
             mod.forward = wrapped  # type: ignore[method-assign]
+
+    # ---------------------------------------------------------------- layers that keep their activations
+    def _keeps_activations(self, u: ZeroUnit, x: torch.Tensor) -> bool:
+        """Whether this unit runs without recomputation in this pass.  A fixed count keeps the last layers (their
+        backward runs first and frees memory early); ``auto`` decides layer by layer from the memory that is
+        free right now, the measured activation bytes per token and the measured head-room that the rest of a
+        step needs on top of what is allocated when the first layer starts."""
+        mode = self.cfg.activation_checkpoint_keep
+        if not mode or getattr(u, "expert_unit", None) is not None or not getattr(u, "keep_ok", True):
+            return False
+        wrapped = self._wrapped_units
+        if mode != "auto":
+            return u.wrapped_index >= len(wrapped) - int(mode)
+        if not self.on_gpu:
+            return False
+        st = self._keep_state
+        if u.wrapped_index == 0:
+            st["alloc0"] = torch.cuda.memory_allocated(self.device)
+            st["kept_bytes"] = 0
+            st["kept_layers"] = 0
+            if st["phase"] < 2:
+                torch.cuda.reset_peak_memory_stats(self.device)
+        if st["phase"] < 2:
+            # two measurement passes (one layer kept, the rest recomputed): the first also sees the buffers that
+            # are allocated lazily during the very first step, so the head-room is taken from the second
+            return u.wrapped_index == 0
+        need = int(st["bytes_per_token"] * (x.numel() // x.shape[-1]))
+        ok = torch.cuda.memory_allocated(self.device) + need + st["reserve"] <= st["limit"]
+        if ok:
+            st["kept_bytes"] += need
+            st["kept_layers"] += 1
+        return ok
+
+    def _run_kept(self, u: ZeroUnit, orig, x: torch.Tensor, args, kwargs):
+        st = self._keep_state
+        measure = self.cfg.activation_checkpoint_keep == "auto" and st["phase"] < 2 and self.on_gpu
+        before = torch.cuda.memory_allocated(self.device) if measure else 0
+        y = orig(_UnitEnter.apply(self, u, self._dummy, x), *args, **kwargs)
+        if not torch.is_tensor(y):
+            raise EngineConfigError(
+                f"unit {u.name} returns {type(y).__name__}; only units with a single tensor output can keep activations"
+            )
+        y = _UnitExit.apply(self, u, y)
+        if measure:
+            tokens = max(1, x.numel() // x.shape[-1])
+            st["bytes_per_token"] = max(1.0, (torch.cuda.memory_allocated(self.device) - before) / tokens)
+        return y
+
+    def _update_keep_state(self) -> None:
+        """End of an optimizer step: turn the step's measured peak into the head-room for the next one."""
+        if self.cfg.activation_checkpoint_keep != "auto" or not self.on_gpu:
+            return
+        st = self._keep_state
+        if "alloc0" not in st:
+            return
+        peak = torch.cuda.max_memory_allocated(self.device)
+        free, total = torch.cuda.mem_get_info(self.device)
+        foreign = max(0, (total - free) - torch.cuda.memory_reserved(self.device))
+        st["limit"] = int(self.cfg.activation_keep_memory_fraction * total) - foreign
+        # everything that was live on top of the start-of-forward level and is not a kept layer
+        reserve = peak - st["alloc0"] - st.get("kept_bytes", 0)
+        if st["phase"] < 2:
+            # includes the one measured layer: errs on the safe side
+            st["reserve"] = int(peak - st["alloc0"]) if st["phase"] == 1 else 0
+            st["phase"] += 1
+        else:
+            st["reserve"] = max(st["reserve"], int(reserve))
+        torch.cuda.reset_peak_memory_stats(self.device)
 
     def _begin_unit_backward(self, u: ZeroUnit) -> None:
         self._ensure_resident(u, self._neighbour(u, -1))
@@ -748,6 +823,7 @@ class TrainingEngine:
         self._sync_full_params()
         if self.symm is not None:
             self.symm.barrier(slot=0)  # shards are final on every rank before anyone pulls them again
+        self._update_keep_state()
 
     def _sync_full_params(self) -> None:
         """After an update every persistent unit re-assembles its full buffer from the shards."""
@@ -932,6 +1008,40 @@ class _CheckpointedUnit(torch.autograd.Function):
         ctx.handle = None
         ctx.extras = None
         return (None, None, None, None, gx) + gextras
+
+
+class _UnitEnter(torch.autograd.Function):
+    """Entry of a unit that keeps its activations: gathers the parameters on the way in; in the backward pass this
+    node runs after all of the unit's own backward operations (and after the accumulation of its parameter
+    gradients, which autograd schedules first), so it reduces the unit's gradients and releases the parameters."""
+
+    @staticmethod
+    def forward(ctx, engine: "TrainingEngine", unit: ZeroUnit, dummy, x):
+        ctx.engine, ctx.unit = engine, unit
+        engine._ensure_resident(unit, engine._neighbour(unit, +1))
+        return x.view_as(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.engine._end_unit_backward(ctx.unit)
+        return None, None, None, g
+
+
+class _UnitExit(torch.autograd.Function):
+    """Exit of a unit that keeps its activations: releases the parameters on the way out; in the backward pass it
+    runs before the unit's operations and gathers the parameters again.  Operations inside the unit must have saved
+    the parameter objects themselves (their storage is re-pointed at the freshly gathered buffer), not views."""
+
+    @staticmethod
+    def forward(ctx, engine: "TrainingEngine", unit: ZeroUnit, y):
+        ctx.engine, ctx.unit = engine, unit
+        engine._release_params(unit)
+        return y.view_as(y)
+
+    @staticmethod
+    def backward(ctx, g):
+        ctx.engine._begin_unit_backward(ctx.unit)
+        return None, None, g
 
 
 def initialize(

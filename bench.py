@@ -41,7 +41,9 @@ def parse_args():
     p.add_argument("--seq-len", type=int, default=8192)
     p.add_argument("--zero-stage", type=int, default=3)
     p.add_argument("--layers", type=int, default=0, help="override the number of layers (debugging only; marks the result invalid)")
-    p.add_argument("--attn", type=str, default="flash_attention_2")
+    p.add_argument("--attn", type=str, default="native")
+    p.add_argument("--keep", type=str, default="auto",
+                   help="layers that keep activations instead of recomputing them: a count, or auto (by free memory)")
     p.add_argument("--gemm", type=str, default=os.getenv("ATB200_GEMM", "tcgen05"), choices=["tcgen05", "cublas"])
     p.add_argument("--skip-e2e", action="store_true")
     p.add_argument("--no-cta-pairs", action="store_true", help="use the single-CTA 128x256 GEMM tile instead of the CTA-pair kernel")
@@ -169,7 +171,8 @@ def main() -> None:
         },
         "optimizer": {"lr": 1e-5, "weight_decay": 0.1},
         "scheduler": {"name": "constant"},
-        "deepspeed": {"zero_optimization": {"stage": args.zero_stage}, "gradient_clipping": 1.0},
+        "deepspeed": {"zero_optimization": {"stage": args.zero_stage}, "gradient_clipping": 1.0,
+                      "activation_checkpoint_keep": args.keep},
         "train_log_iter_interval": 0,
         "train_log_metrics_path": str(workdir / f"metrics_{rank}.jsonl"),
         "logger": {"level": "WARNING"},
@@ -268,6 +271,8 @@ def main() -> None:
                 "parallelism": f"zero{args.zero_stage}-dp{world}",
                 "optimizer": "adamw fp32 master",
                 "activation_checkpointing": True,
+                "layers_keeping_activations": (engine._keep_state.get("kept_layers", 0) if args.keep == "auto"
+                                               else min(int(args.keep), cfg["num_hidden_layers"])),
                 "attention": args.attn,
                 "gemm": args.gemm + ("" if args.gemm != "tcgen05" else ("-1cta" if args.no_cta_pairs else "-2cta")),
                 "l2_policy": "inputs larger than L2 (16 GB of weights streamed every step)",
@@ -277,6 +282,8 @@ def main() -> None:
             "gpu_launches": int(launches),
             "final_loss": round(final_loss, 4),
             "kernel_error_flag": err,
+            "keep_state": {k: (round(v / 2**30, 2) if isinstance(v, (int, float)) and v > 1e6 else v)
+                           for k, v in engine._keep_state.items()},
             "max_memory_gb": round(torch.cuda.max_memory_allocated() / 2**30, 2),
         }
         if e2e_ms is not None:

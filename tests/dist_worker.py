@@ -40,9 +40,9 @@ def global_batches(n, world, bs=2, seq=32, vocab=1024, seed=0):
     return out
 
 
-def scenario_zero(out_dir, stage):
+def scenario_zero(out_dir, stage, keep=0):
     rank, world = dist.get_rank(), dist.get_world_size()
-    engine = make_engine(stage)
+    engine = make_engine(stage, activation_checkpoint_keep=keep)
     losses = []
     for b in global_batches(3, world):
         local = {k: v[rank::world] for k, v in b.items()}
@@ -108,7 +108,9 @@ def scenario_rank_failure(out_dir):
 def main():
     scenario, out_dir = sys.argv[1], sys.argv[2]
     init_distributed(timeout_s=60)
-    if scenario.startswith("zero"):
+    if scenario == "zero3keep":
+        scenario_zero(out_dir, 3, keep=2)  # writes zero3.pt
+    elif scenario.startswith("zero"):
         scenario_zero(out_dir, int(scenario[4:]))
     elif scenario == "resume":
         scenario_resume(out_dir)

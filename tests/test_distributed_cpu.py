@@ -66,6 +66,18 @@ def test_two_ranks_match_single_process(tmp_path, single_process_reference, stag
     assert got["norm"] > 0
 
 
+def test_layers_that_keep_activations_match_under_stage3(tmp_path, single_process_reference):
+    """Stage 3 on two ranks with the last two layers keeping their activations (parameters gathered again before
+    their backward, possibly into another pool buffer) gives the single-process result."""
+    ref_losses, ref_params = single_process_reference
+    launch(2, "zero3keep", tmp_path)
+    got = torch.load(tmp_path / "zero3.pt", weights_only=False)
+    assert got["losses"] == pytest.approx(ref_losses, rel=1e-5)
+    for n, p in ref_params.items():
+        assert (got["params"][n] - p).abs().mean() < 2e-5, n
+    assert all(got["released"])
+
+
 def test_sharded_checkpoint_resume_two_ranks(tmp_path):
     launch(2, "resume", tmp_path)
     res = json.loads((tmp_path / "resume.json").read_text())

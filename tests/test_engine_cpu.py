@@ -20,13 +20,14 @@ def make_model(seed=0, **overrides):
     return m
 
 
-def make_engine(model, stage, gas=1, clip=1.0, ckpt=True, lr=1e-2, wd=0.1, tiled=False):
+def make_engine(model, stage, gas=1, clip=1.0, ckpt=True, lr=1e-2, wd=0.1, tiled=False, keep=0):
     model.activation_checkpointing = ckpt
     model.tiled_mlp = tiled
     groups = OptimizerFactory.get_optimizer_grouped_params(model, wd)
     opt = FusedAdamW(groups, lr=lr, betas=(0.9, 0.95))
     return TrainingEngine(model, opt, None, {
         "zero_optimization": {"stage": stage}, "gradient_accumulation_steps": gas, "gradient_clipping": clip,
+        "activation_checkpoint_keep": keep,
     })
 
 
@@ -97,6 +98,17 @@ def test_checkpointing_and_tiled_mlp_do_not_change_results():
         assert (pa[n] - pb[n]).abs().mean() < 1e-5, n
         # tiling changes the summation order of weight gradients; Adam turns that into small parameter noise
         assert (pc[n] - pb[n]).abs().mean() < 1e-4, n
+
+
+@pytest.mark.parametrize("keep", [1, 2, 100])
+def test_keeping_activations_of_some_layers_does_not_change_results(keep):
+    data = batches(3)
+    a = make_engine(make_model(), 3, ckpt=True, keep=0)
+    b = make_engine(make_model(), 3, ckpt=True, keep=keep, gas=1)
+    assert run(b, data) == pytest.approx(run(a, data), rel=1e-6)
+    pa, pb = full_params(a), full_params(b)
+    for n in pa:
+        assert (pa[n] - pb[n]).abs().max() < 1e-6, n
 
 
 def test_gradient_accumulation_equals_big_batch():
