@@ -22,7 +22,7 @@ std::tuple<at::Tensor, at::Tensor> ce_fwd_bwd(at::Tensor logits, const at::Tenso
 at::Tensor kl_fwd_bwd(at::Tensor student, const at::Tensor& teacher, const c10::optional<at::Tensor>& row_weight,
                       double temperature, const c10::optional<at::Tensor>& grad_scale, bool write_grad);
 at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
-                     const c10::optional<at::Tensor>& out, int64_t max_ctas);
+                     const c10::optional<at::Tensor>& out, int64_t max_ctas, const c10::optional<at::Tensor>& residual);
 int64_t read_and_clear_error_flag(const at::Tensor& like);
 std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                             const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
@@ -74,7 +74,7 @@ TORCH_LIBRARY(atb200, m) {
           &atb::ce_fwd_bwd);
     m.def("kl_fwd_bwd(Tensor(a!) student, Tensor teacher, Tensor? row_weight, float temperature, Tensor? grad_scale, bool write_grad) -> Tensor",
           &atb::kl_fwd_bwd);
-    m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas) -> Tensor",
+    m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas, Tensor? residual=None) -> Tensor",
           &atb::gemm_bf16);
     m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);
     m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor)", &atb::fmha_fwd);

@@ -127,7 +127,18 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
 // writes the bf16 parameter copy.  `grad_scale` is read from device memory so that a clip factor
 // computed on the device needs no host round trip.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, const float* __restrict__ grad,
+__device__ __forceinline__ float4 load_grad4(const float* g, int64_t i) { return reinterpret_cast<const float4*>(g)[i]; }
+__device__ __forceinline__ float4 load_grad4(const bf16* g, int64_t i) {
+    const uint2 raw = reinterpret_cast<const uint2*>(g)[i];
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const bf162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const bf162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ float load_grad1(const float* g, int64_t i) { return g[i]; }
+__device__ __forceinline__ float load_grad1(const bf16* g, int64_t i) { return __bfloat162float(g[i]); }
+
+template <typename G>
+__global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, const G* __restrict__ grad,
                                                     float* __restrict__ m, float* __restrict__ v,
                                                     bf16* __restrict__ out_lp, int64_t n, float lr, float beta1,
                                                     float beta2, float eps, float wd, float bc1, float bc2,
@@ -137,7 +148,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, 
     const float inv_bc1 = 1.f / bc1, inv_sqrt_bc2 = rsqrtf(bc2);
     for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
         float4 p = reinterpret_cast<float4*>(master)[i];
-        float4 g = reinterpret_cast<const float4*>(grad)[i];
+        float4 g = load_grad4(grad, i);
         float4 mm = reinterpret_cast<float4*>(m)[i];
         float4 vv = reinterpret_cast<float4*>(v)[i];
         float* pp = &p.x;
@@ -166,7 +177,7 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, 
     // tail (n not a multiple of 4)
     for (int64_t i = (nvec << 2) + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
          i += (int64_t)gridDim.x * blockDim.x) {
-        const float gk = grad[i] * gs;
+        const float gk = load_grad1(grad, i) * gs;
         const float mk = beta1 * m[i] + (1.f - beta1) * gk;
         const float vk = beta2 * v[i] + (1.f - beta2) * gk * gk;
         const float denom = sqrtf(vk) * inv_sqrt_bc2 + eps;
@@ -179,11 +190,18 @@ __global__ void __launch_bounds__(256) adamw_kernel(float* __restrict__ master, 
 }
 
 // Deterministic squared-norm partials: out[blockIdx.x] = sum of x^2 over this CTA's grid-stride slice.
-__global__ void __launch_bounds__(256) sumsq_kernel(const float* __restrict__ x, int64_t n, float* __restrict__ out) {
+template <typename T>
+__global__ void __launch_bounds__(256) sumsq_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out) {
     __shared__ float scratch[32];
     float acc = 0.f;
-    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n; i += (int64_t)gridDim.x * blockDim.x) {
-        const float f = x[i];
+    const int64_t nvec = ((reinterpret_cast<uintptr_t>(x) & 15) == 0) ? (n >> 2) : 0;
+    for (int64_t i = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < nvec; i += (int64_t)gridDim.x * blockDim.x) {
+        const float4 f = load_grad4(x, i);
+        acc += f.x * f.x + f.y * f.y + f.z * f.z + f.w * f.w;
+    }
+    for (int64_t i = (nvec << 2) + blockIdx.x * (int64_t)blockDim.x + threadIdx.x; i < n;
+         i += (int64_t)gridDim.x * blockDim.x) {
+        const float f = load_grad1(x, i);
         acc += f * f;
     }
     acc = block_sum(acc, scratch);
@@ -332,11 +350,14 @@ void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Ten
                 const c10::optional<at::Tensor>& out_lp, double lr, double beta1, double beta2, double eps,
                 double wd, int64_t step, const c10::optional<at::Tensor>& grad_scale) {
     ATB_CHECK_CUDA(master); ATB_CHECK_CONTIG(master); ATB_CHECK_CONTIG(grad); ATB_CHECK_CONTIG(m); ATB_CHECK_CONTIG(v);
-    ATB_CHECK_DTYPE(master, at::kFloat); ATB_CHECK_DTYPE(grad, at::kFloat);
+    ATB_CHECK_DTYPE(master, at::kFloat);
+    TORCH_CHECK(grad.scalar_type() == at::kFloat || grad.scalar_type() == at::kBFloat16, "adamw: gradient must be fp32 or bf16");
     ATB_CHECK_DTYPE(m, at::kFloat); ATB_CHECK_DTYPE(v, at::kFloat);
     const int64_t n = master.numel();
     TORCH_CHECK(grad.numel() == n && m.numel() == n && v.numel() == n, "adamw: size mismatch");
-    ATB_CHECK_ALIGNED16(master); ATB_CHECK_ALIGNED16(grad); ATB_CHECK_ALIGNED16(m); ATB_CHECK_ALIGNED16(v);
+    ATB_CHECK_ALIGNED16(master); ATB_CHECK_ALIGNED16(m); ATB_CHECK_ALIGNED16(v);
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(grad.data_ptr()) & (grad.scalar_type() == at::kFloat ? 15 : 7)) == 0,
+                "adamw: gradient pointer is not aligned for vector loads");
     bf16* lp = nullptr;
     if (out_lp.has_value()) {
         ATB_CHECK_DTYPE(*out_lp, at::kBFloat16); ATB_CHECK_CONTIG(*out_lp);
@@ -353,18 +374,27 @@ void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Ten
     c10::cuda::CUDAGuard guard(master.device());
     const float bc1 = 1.f - (float)std::pow(beta1, (double)step);
     const float bc2 = 1.f - (float)std::pow(beta2, (double)step);
-    adamw_kernel<<<grid_for(n / 4 + 1), 256, 0, current_stream()>>>(
-        master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), lp, n, (float)lr,
-        (float)beta1, (float)beta2, (float)eps, (float)wd, bc1, bc2, gs);
+    if (grad.scalar_type() == at::kFloat)
+        adamw_kernel<float><<<grid_for(n / 4 + 1), 256, 0, current_stream()>>>(
+            master.data_ptr<float>(), grad.data_ptr<float>(), m.data_ptr<float>(), v.data_ptr<float>(), lp, n, (float)lr,
+            (float)beta1, (float)beta2, (float)eps, (float)wd, bc1, bc2, gs);
+    else
+        adamw_kernel<bf16><<<grid_for(n / 4 + 1), 256, 0, current_stream()>>>(
+            master.data_ptr<float>(), (const bf16*)grad.data_ptr(), m.data_ptr<float>(), v.data_ptr<float>(), lp, n, (float)lr,
+            (float)beta1, (float)beta2, (float)eps, (float)wd, bc1, bc2, gs);
     ATB_LAUNCH_CHECK();
 }
 
 at::Tensor sumsq(const at::Tensor& x) {
-    ATB_CHECK_CUDA(x); ATB_CHECK_CONTIG(x); ATB_CHECK_DTYPE(x, at::kFloat);
+    ATB_CHECK_CUDA(x); ATB_CHECK_CONTIG(x);
+    TORCH_CHECK(x.scalar_type() == at::kFloat || x.scalar_type() == at::kBFloat16, "sumsq: fp32 or bf16 input");
     c10::cuda::CUDAGuard guard(x.device());
-    const int nblk = grid_for(x.numel(), 256, 4);
-    auto partial = at::empty({nblk}, x.options());
-    sumsq_kernel<<<nblk, 256, 0, current_stream()>>>(x.data_ptr<float>(), x.numel(), partial.data_ptr<float>());
+    const int nblk = grid_for(x.numel() / 4 + 1, 256, 4);
+    auto partial = at::empty({nblk}, x.options().dtype(at::kFloat));
+    if (x.scalar_type() == at::kFloat)
+        sumsq_kernel<float><<<nblk, 256, 0, current_stream()>>>(x.data_ptr<float>(), x.numel(), partial.data_ptr<float>());
+    else
+        sumsq_kernel<bf16><<<nblk, 256, 0, current_stream()>>>((const bf16*)x.data_ptr(), x.numel(), partial.data_ptr<float>());
     ATB_LAUNCH_CHECK();
     return partial.sum();
 }

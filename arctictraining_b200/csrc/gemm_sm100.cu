@@ -49,8 +49,9 @@ enum GroupMode : int { GROUP_NONE = 0, GROUP_RAGGED_M = 1, GROUP_RAGGED_K = 2 };
 
 struct GemmParams {
     bf16* C;
+    const bf16* R;  // EPI_ACCUM: C = A B + R (R may be C itself: in-place accumulation, or a residual stream)
     int M, N, K;  // per-group extents in the grouped modes (M is unused for GROUP_RAGGED_M)
-    int64_t ldc;
+    int64_t ldc, ldr;
     int* error_flag;  // device int: 0 ok, otherwise (role << 8) | reason
     // grouped GEMM: `group_offsets[g]` is the first row of group g in the ragged operand(s); every group
     // starts at a multiple of 128 rows.  GROUP_RAGGED_M: A rows are ragged, B holds one matrix per group.
@@ -307,6 +308,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                 }
             } else {
                 bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)ti.c_col0;
+                const bf16* rrow = p.R + (int64_t)row * p.ldr + (int64_t)ti.c_col0;
 #pragma unroll 1
                 for (int c = 0; c < BN / 32; ++c) {
                     uint32_t r[32];
@@ -323,7 +325,7 @@ gemm_bf16_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_a, const __gri
                                 bf16x8* dst = reinterpret_cast<bf16x8*>(crow + c * 32 + v * 8);
                                 if constexpr (EPI == EPI_ACCUM) {
                                     float old[8];
-                                    unpack8(*dst, old);
+                                    unpack8(*reinterpret_cast<const bf16x8*>(rrow + c * 32 + v * 8), old);
 #pragma unroll
                                     for (int j = 0; j < 8; ++j) o[j] += old[j];
                                 }
@@ -560,6 +562,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                 }
             } else {
                 bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * TN;
+                const bf16* rrow = p.R + (int64_t)row * p.ldr + (int64_t)tn * TN;
 #pragma unroll 1
                 for (int c = 0; c < TN / 32; ++c) {
                     uint32_t r[32];
@@ -576,7 +579,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                                 bf16x8* dst = reinterpret_cast<bf16x8*>(crow + c * 32 + v * 8);
                                 if constexpr (EPI == EPI_ACCUM) {
                                     float old[8];
-                                    unpack8(*dst, old);
+                                    unpack8(*reinterpret_cast<const bf16x8*>(rrow + c * 32 + v * 8), old);
 #pragma unroll
                                     for (int j = 0; j < 8; ++j) o[j] += old[j];
                                 }
@@ -718,7 +721,8 @@ void dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const G
 // out = gemm(a, b).  a_mn == false: a is [M, K]; true: a is [K, M].  b_mn == false: b is [N, K]; true: [K, N].
 // epilogue: 0 store, 1 accumulate into `out`, 2 SwiGLU (out is [M, N/2]).
 at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
-                     const c10::optional<at::Tensor>& out_opt, int64_t max_ctas) {
+                     const c10::optional<at::Tensor>& out_opt, int64_t max_ctas,
+                     const c10::optional<at::Tensor>& residual) {
     ATB_CHECK_CUDA(a); ATB_CHECK_CUDA(b);
     ATB_CHECK_DTYPE(a, at::kBFloat16); ATB_CHECK_DTYPE(b, at::kBFloat16);
     TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "gemm: operands must be 2-D");
@@ -744,10 +748,16 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
                     "gemm: output has the wrong shape");
         TORCH_CHECK(out.stride(0) % 8 == 0, "gemm: output pitch must be a multiple of 8 elements");
     } else {
-        TORCH_CHECK(epi != EPI_ACCUM, "gemm: accumulate epilogue needs an output tensor");
+        TORCH_CHECK(epi != EPI_ACCUM || residual.has_value(), "gemm: accumulate epilogue needs an output or a residual tensor");
         out = at::empty({M, out_cols}, a.options());
     }
     ATB_CHECK_ALIGNED16(out);
+    if (residual.has_value()) {
+        TORCH_CHECK(epi == EPI_ACCUM, "gemm: a residual needs the accumulate epilogue");
+        ATB_CHECK_DTYPE(*residual, at::kBFloat16); ATB_CHECK_ALIGNED16(*residual);
+        TORCH_CHECK(residual->dim() == 2 && residual->size(0) == M && residual->size(1) == N && residual->stride(1) == 1 &&
+                    residual->stride(0) % 8 == 0, "gemm: residual has the wrong shape");
+    }
 
     // tensor maps: K-major operand [rows, K] -> box [tile rows, 64 k]; MN-major [K, rows] -> box [64 k, 64 rows]
     const CUtensorMap ta = a_mn ? make_tmap_bf16(a.data_ptr(), K, M, a.stride(0), BK)
@@ -761,6 +771,8 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     p.C = (bf16*)out.data_ptr();
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.ldc = out.stride(0);
+    p.R = residual.has_value() ? (const bf16*)residual->data_ptr() : p.C;
+    p.ldr = residual.has_value() ? residual->stride(0) : p.ldc;
     p.error_flag = error_flag_for(a.device()).data_ptr<int>();
     p.group_offsets = nullptr;
     p.num_groups = 0;
@@ -831,6 +843,8 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
                                     : make_tmap_bf16(b.data_ptr(), G * N, K, b.stride(0), 256);
         p.C = (bf16*)out.data_ptr();
         p.ldc = out.stride(0);
+        p.R = p.C;
+        p.ldr = p.ldc;
         if (!b_mn) dispatch_epi<false, false>(epi, ta, tb, p, kNumSMs);
         else dispatch_epi<false, true>(epi, ta, tb, p, kNumSMs);
     } else if (mode == GROUP_RAGGED_K) {
@@ -850,6 +864,8 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
         const CUtensorMap tb = make_tmap_bf16(b.data_ptr(), R, N, b.stride(0), BK);
         p.C = (bf16*)out.data_ptr();
         p.ldc = out.stride(0);
+        p.R = p.C;
+        p.ldr = p.ldc;
         dispatch_epi<true, true>(epi, ta, tb, p, kNumSMs);
     } else {
         TORCH_CHECK(false, "grouped gemm: mode must be 1 (ragged M) or 2 (ragged K)");

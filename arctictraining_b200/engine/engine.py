@@ -378,8 +378,19 @@ class TrainingEngine:
             pad = (tl + 7) // 8 * 8
             u.master = torch.zeros(pad, dtype=master_dtype, device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
             u.master[:tl].copy_(u.shard[:tl].to(master_dtype))
-            u.grad_acc = torch.zeros(pad, dtype=torch.float32 if master_dtype == torch.float32 else master_dtype,
-                                     device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
+            # Without accumulation steps and without peers to reduce with, the bf16 gradients that autograd writes
+            # are final: the unit's gradient buffer lives for the whole step and the optimizer reads it directly
+            # (no fp32 copy: 4 bytes per parameter less memory and one pass less over the gradients).
+            u.direct_grad = bool(
+                self.gas == 1 and u.group_size == 1 and self.on_gpu and opt_dev == self.device and u.persistent
+                and u.dtype == torch.bfloat16 and master_dtype == torch.float32 and hasattr(opt, "step_flat")
+                and os.getenv("ATB200_DIRECT_GRADS", "1") != "0"
+            )
+            if u.direct_grad:
+                u.grad_acc = torch.zeros(pad, dtype=torch.bfloat16, device=self.device)
+            else:
+                u.grad_acc = torch.zeros(pad, dtype=torch.float32 if master_dtype == torch.float32 else master_dtype,
+                                         device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
             for s, e, gi in u.runs:
                 view = u.master[s:e]
                 view._atb_unit = u  # type: ignore[attr-defined]
@@ -593,6 +604,15 @@ class TrainingEngine:
     def _prepare_grad_buffer(self, u: ZeroUnit) -> None:
         if u.n_train <= 0 or u.grad_flat is not None:
             return
+        if getattr(u, "direct_grad", False):
+            g = u.grad_acc
+            if not u.grad_acc_valid:
+                g.zero_()
+            u.grad_flat, u.grad_slot = g, None
+            for p, o, n, shp in zip(u.params, u.offsets, u.numels, u.shapes):
+                if p.requires_grad:
+                    p.grad = g[o : o + n].view(shp)
+            return
         if u.checkpointed:
             slot, buf = self._grad_pool.acquire()
             g = buf[: u.numel]
@@ -618,6 +638,10 @@ class TrainingEngine:
         g = u.grad_flat
         for p in u.params:
             p.grad = None
+        if getattr(u, "direct_grad", False):
+            u.grad_flat = None
+            u.grad_acc_valid = True
+            return
         tl = u.train_len
         scale = 1.0 / (u.grad_divisor * self.gas)
         lo = u.group_rank * u.shard_size

@@ -54,8 +54,17 @@ class Linear(nn.Module):
         self.weight = nn.Parameter(torch.empty(out_features, in_features, dtype=dtype, device=device))
         self.bias = nn.Parameter(torch.zeros(out_features, dtype=dtype, device=device)) if bias else None
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return ops.linear(x, self.weight, self.bias)
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return ops.linear(x, self.weight, self.bias, residual)
+
+
+def _project_with_residual(proj: nn.Module, x: torch.Tensor, residual: Optional[torch.Tensor]) -> torch.Tensor:
+    """``residual + proj(x)``; a plain :class:`Linear` fuses the addition, any wrapper (adapters) adds afterwards."""
+    if residual is None:
+        return proj(x)
+    if type(proj) is Linear:
+        return proj(x, residual)
+    return residual + proj(x)
 
 
 class Attention(nn.Module):
@@ -93,11 +102,11 @@ class Attention(nn.Module):
             return ctx.sp.attention(q, k, v, ctx)
         return ops.attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
 
-    def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
+    def forward(self, x: torch.Tensor, ctx: ForwardContext, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, S, _ = x.shape
         q, k, v = self.project_qkv(x, ctx)
         o = self.core(q, k, v, ctx)
-        return self.o_proj(o.reshape(B, S, self.hq * self.d))
+        return _project_with_residual(self.o_proj, o.reshape(B, S, self.hq * self.d), residual)
 
 
 class MLP(nn.Module):
@@ -108,8 +117,8 @@ class MLP(nn.Module):
         self.gate_up_proj = Linear(hidden, 2 * inter, dtype=dtype, device=device)
         self.down_proj = Linear(inter, hidden, dtype=dtype, device=device)
 
-    def forward(self, x: torch.Tensor) -> torch.Tensor:
-        return self.down_proj(ops.linear_swiglu(x, self.gate_up_proj.weight))
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        return _project_with_residual(self.down_proj, ops.linear_swiglu(x, self.gate_up_proj.weight), residual)
 
 
 class DecoderLayer(nn.Module):
@@ -133,10 +142,15 @@ class DecoderLayer(nn.Module):
         return MLP(cfg["hidden_size"], cfg["intermediate_size"], dtype=dtype, device=device)
 
     def forward(self, x: torch.Tensor, ctx: ForwardContext) -> torch.Tensor:
-        x = x + self.self_attn(self.input_layernorm(x), ctx)
+        if type(self.self_attn) is Attention:
+            x = self.self_attn(self.input_layernorm(x), ctx, residual=x)
+        else:
+            x = x + self.self_attn(self.input_layernorm(x), ctx)
         h = self.post_attention_layernorm(x)
         if ctx.tiled_mlp and isinstance(self.mlp, MLP):
             from ..ops.tiled import tiled_mlp
 
             return x + tiled_mlp(self.mlp, h)
+        if type(self.mlp) is MLP:
+            return self.mlp(h, residual=x)
         return x + self.mlp(h)

@@ -176,10 +176,12 @@ def gemm(
     b_mn: bool = False,
     epilogue: int = 0,
     out: Optional[torch.Tensor] = None,
+    residual: Optional[torch.Tensor] = None,
 ) -> torch.Tensor:
-    """Raw tcgen05 GEMM (no autograd).  See ``csrc/gemm_sm100.cu`` for the operand conventions."""
+    """Raw tcgen05 GEMM (no autograd).  See ``csrc/gemm_sm100.cu`` for the operand conventions.  With
+    ``epilogue=1`` the product is added to ``out`` in place, or to ``residual`` into a fresh tensor."""
     _count()
-    return _ext.ops().gemm_bf16(a, b, a_mn, b_mn, epilogue, out, 0)
+    return _ext.ops().gemm_bf16(a, b, a_mn, b_mn, epilogue, out, 0, residual)
 
 
 def _gemm_ok(x2: torch.Tensor, w: torch.Tensor) -> bool:
@@ -216,6 +218,23 @@ class _LinearFn(torch.autograd.Function):
         return dx, dw
 
 
+class _LinearResidualFn(torch.autograd.Function):
+    """y = r + x W^T with the addition done in the GEMM epilogue (one pass over the residual stream less)."""
+
+    @staticmethod
+    def forward(ctx, x2, w, r2):
+        ctx.save_for_backward(x2, w)
+        return gemm(x2, w, epilogue=1, residual=r2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy = dy.contiguous()
+        dx = gemm(dy, w, False, True) if ctx.needs_input_grad[0] else None
+        dw = gemm(dy, x2, True, True) if ctx.needs_input_grad[1] else None
+        return dx, dw, (dy if ctx.needs_input_grad[2] else None)
+
+
 class _LinearSwiGLUFn(torch.autograd.Function):
     """h = swiglu(x W_gu^T).  When no gradient is needed (the first pass of a checkpointed layer, evaluation)
     the activation is applied in the GEMM epilogue and gate/up never reach memory.  When a gradient is
@@ -242,17 +261,26 @@ class _LinearSwiGLUFn(torch.autograd.Function):
         return dx, dw
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None) -> torch.Tensor:
+def linear(
+    x: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor] = None, residual: Optional[torch.Tensor] = None
+) -> torch.Tensor:
+    """``x @ W^T (+ bias) (+ residual)``; on the GPU the residual is added in the GEMM epilogue."""
     if _use_kernels(x):
         x2 = x.reshape(-1, x.shape[-1])
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         if _gemm_ok(x2, weight):
+            if residual is not None and bias is None and residual.dtype == torch.bfloat16 and residual.is_contiguous() \
+                    and residual.data_ptr() % 16 == 0:
+                y = _LinearResidualFn.apply(x2, weight, residual.view(-1, weight.shape[0]))
+                return y.view(*x.shape[:-1], weight.shape[0])
             y = _LinearFn.apply(x2, weight)
             if bias is not None:
                 y = y + bias
-            return y.view(*x.shape[:-1], weight.shape[0])
-    return F.linear(x, weight, bias)
+            y = y.view(*x.shape[:-1], weight.shape[0])
+            return y if residual is None else residual + y
+    y = F.linear(x, weight, bias)
+    return y if residual is None else residual + y
 
 
 def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
@@ -527,7 +555,7 @@ def fused_linear_logprobs(
 # ------------------------------------------------------------------------------------------------ optimizer pieces
 def adamw_step(master, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, grad_scale=None, out_lp=None):
     """Fused AdamW on flat tensors.  ``grad_scale`` is a python float or a one-element device tensor."""
-    if _use_kernels(master) and master.dtype == torch.float32 and grad.dtype == torch.float32 \
+    if _use_kernels(master) and master.dtype == torch.float32 and grad.dtype in (torch.float32, torch.bfloat16) \
             and exp_avg.dtype == torch.float32 and (out_lp is None or out_lp.dtype == torch.bfloat16):
         gs = grad_scale
         if gs is not None and not torch.is_tensor(gs):
@@ -540,7 +568,7 @@ def adamw_step(master, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_
 
 
 def sumsq(x: torch.Tensor) -> torch.Tensor:
-    if _use_kernels(x) and x.dtype == torch.float32 and x.is_contiguous():
+    if _use_kernels(x) and x.dtype in (torch.float32, torch.bfloat16) and x.is_contiguous():
         _count()
         return _ext.ops().sumsq(x)
     return x.float().pow(2).sum()

@@ -462,3 +462,22 @@ def test_native_attention_autograd_matches_reference():
     torch.testing.assert_close(
         Fn.attention(q2, k2, v2, impl="native").float(), ref.attention(q2, k2, v2).float(), atol=2e-2, rtol=2e-2
     )
+
+
+def test_linear_with_fused_residual_matches_torch():
+    from arctictraining_b200.ops import functional as Fn
+
+    torch.manual_seed(0)
+    x = (torch.randn(2, 192, 256, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(512, 256, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    r = torch.randn(2, 192, 512, device="cuda").bfloat16().requires_grad_(True)
+    g = torch.randn(2, 192, 512, device="cuda").bfloat16()
+    y = Fn.linear(x, w, None, r)
+    y.backward(g)
+    xr, wr, rr = (t.detach().float().requires_grad_(True) for t in (x, w, r))
+    y2 = rr + xr @ wr.t()
+    y2.backward(g.float())
+    assert _rel(y, y2) < 1e-2
+    assert _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
+    assert torch.equal(r.grad, g)
+    _check_flag(y)
