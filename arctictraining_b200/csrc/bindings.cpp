@@ -11,6 +11,7 @@ std::tuple<at::Tensor, at::Tensor> rmsnorm_bwd(const at::Tensor& dy, const at::T
 void rope_inplace(at::Tensor x, const at::Tensor& cosb, const at::Tensor& sinb, bool inverse);
 at::Tensor swiglu_fwd(const at::Tensor& gu);
 at::Tensor swiglu_bwd(const at::Tensor& dout, const at::Tensor& gu);
+std::tuple<at::Tensor, at::Tensor> swiglu_bwd_recompute(const at::Tensor& dout, const at::Tensor& gu);
 void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,
                 const c10::optional<at::Tensor>& out_lp, double lr, double beta1, double beta2, double eps, double wd,
                 int64_t step, const c10::optional<at::Tensor>& grad_scale);
@@ -64,6 +65,7 @@ TORCH_LIBRARY(atb200, m) {
     m.def("rope_inplace(Tensor(a!) x, Tensor cos, Tensor sin, bool inverse) -> ()", &atb::rope_inplace);
     m.def("swiglu_fwd(Tensor gu) -> Tensor", &atb::swiglu_fwd);
     m.def("swiglu_bwd(Tensor dout, Tensor gu) -> Tensor", &atb::swiglu_bwd);
+    m.def("swiglu_bwd_recompute(Tensor dout, Tensor gu) -> (Tensor, Tensor)", &atb::swiglu_bwd_recompute);
     m.def(
         "adamw_step(Tensor(a!) master, Tensor grad, Tensor(b!) m, Tensor(c!) v, Tensor? out_lp, float lr, float beta1, "
         "float beta2, float eps, float wd, int step, Tensor? grad_scale) -> ()",

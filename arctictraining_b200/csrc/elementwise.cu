@@ -96,8 +96,10 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict_
     }
 }
 
+// `h_out` (optional): also writes h = silu(gate) * up again, for a caller that did not keep it after the forward.
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu,
-                                                         bf16* __restrict__ dgu, int64_t T, int I) {
+                                                         bf16* __restrict__ dgu, bf16* __restrict__ h_out, int64_t T,
+                                                         int I) {
     const int vec_per_row = I >> 3;
     const int64_t total = T * vec_per_row;
     for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
@@ -106,7 +108,7 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
         const int j = (int)(idx % vec_per_row) * 8;
         const int blk = j >> 6, jj = j & 63;
         const int64_t off = t * (2 * (int64_t)I) + blk * 128;
-        float g[8], u[8], d[8], dg[8], du[8];
+        float g[8], u[8], d[8], dg[8], du[8], hh[8];
         unpack8(*reinterpret_cast<const bf16x8*>(gu + off + jj), g);
         unpack8(*reinterpret_cast<const bf16x8*>(gu + off + 64 + jj), u);
         unpack8(*reinterpret_cast<const bf16x8*>(dout + t * (int64_t)I + j), d);
@@ -116,9 +118,11 @@ __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict_
             const float silu = g[k] * sig;
             dg[k] = d[k] * u[k] * (sig * (1.f + g[k] * (1.f - sig)));
             du[k] = d[k] * silu;
+            hh[k] = silu * u[k];
         }
         *reinterpret_cast<bf16x8*>(dgu + off + jj) = pack8(dg);
         *reinterpret_cast<bf16x8*>(dgu + off + 64 + jj) = pack8(du);
+        if (h_out) *reinterpret_cast<bf16x8*>(h_out + t * (int64_t)I + j) = pack8(hh);
     }
 }
 
@@ -340,10 +344,29 @@ at::Tensor swiglu_bwd(const at::Tensor& dout, const at::Tensor& gu) {
     auto dgu = at::empty_like(gu);
     if (T > 0) {
         swiglu_bwd_kernel<<<grid_for(T * (I / 8)), 256, 0, current_stream()>>>(
-            (const bf16*)dout.data_ptr(), (const bf16*)gu.data_ptr(), (bf16*)dgu.data_ptr(), T, I);
+            (const bf16*)dout.data_ptr(), (const bf16*)gu.data_ptr(), (bf16*)dgu.data_ptr(), nullptr, T, I);
         ATB_LAUNCH_CHECK();
     }
     return dgu;
+}
+
+// Backward of the SwiGLU activation that also returns h = silu(gate) * up, for callers that did not keep it.
+std::tuple<at::Tensor, at::Tensor> swiglu_bwd_recompute(const at::Tensor& dout, const at::Tensor& gu) {
+    ATB_CHECK_CUDA(gu); ATB_CHECK_CONTIG(gu); ATB_CHECK_CONTIG(dout);
+    ATB_CHECK_DTYPE(gu, at::kBFloat16); ATB_CHECK_DTYPE(dout, at::kBFloat16);
+    TORCH_CHECK(gu.dim() == 2 && dout.dim() == 2 && gu.size(1) == 2 * dout.size(1) && gu.size(0) == dout.size(0) &&
+                gu.size(1) % 128 == 0, "swiglu_bwd_recompute: shape mismatch");
+    const int64_t T = gu.size(0);
+    const int I = (int)dout.size(1);
+    c10::cuda::CUDAGuard guard(gu.device());
+    auto dgu = at::empty_like(gu);
+    auto h = at::empty_like(dout);
+    if (T > 0) {
+        swiglu_bwd_kernel<<<grid_for(T * (I / 8)), 256, 0, current_stream()>>>(
+            (const bf16*)dout.data_ptr(), (const bf16*)gu.data_ptr(), (bf16*)dgu.data_ptr(), (bf16*)h.data_ptr(), T, I);
+        ATB_LAUNCH_CHECK();
+    }
+    return {dgu, h};
 }
 
 void adamw_step(at::Tensor master, const at::Tensor& grad, at::Tensor m, at::Tensor v,

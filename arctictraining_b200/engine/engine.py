@@ -612,6 +612,7 @@ class TrainingEngine:
             for p, o, n, shp in zip(u.params, u.offsets, u.numels, u.shapes):
                 if p.requires_grad:
                     p.grad = g[o : o + n].view(shp)
+                    p._atb_main_grad = p.grad
             return
         if u.checkpointed:
             slot, buf = self._grad_pool.acquire()
@@ -623,6 +624,7 @@ class TrainingEngine:
         for p, o, n, shp in zip(u.params, u.offsets, u.numels, u.shapes):
             if p.requires_grad:
                 p.grad = g[o : o + n].view(shp)
+                p._atb_main_grad = p.grad
 
     def _end_unit_backward(self, u: ZeroUnit) -> None:
         self._reduce_unit(u)
@@ -638,6 +640,7 @@ class TrainingEngine:
         g = u.grad_flat
         for p in u.params:
             p.grad = None
+            p._atb_main_grad = None
         if getattr(u, "direct_grad", False):
             u.grad_flat = None
             u.grad_acc_valid = True

@@ -118,6 +118,8 @@ class MLP(nn.Module):
         self.down_proj = Linear(inter, hidden, dtype=dtype, device=device)
 
     def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if type(self.down_proj) is Linear and type(self.gate_up_proj) is Linear:
+            return ops.mlp_swiglu(x, self.gate_up_proj.weight, self.down_proj.weight, residual)
         return _project_with_residual(self.down_proj, ops.linear_swiglu(x, self.gate_up_proj.weight), residual)
 
 

@@ -214,7 +214,7 @@ class _LinearFn(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy, w, False, True)  # [M,N] x [N,K] (B is MN-major)
         if ctx.needs_input_grad[1]:
-            dw = gemm(dy, x2, True, True)  # dY^T X : both operands MN-major
+            dw = _wgrad(dy, x2, w)  # dY^T X : both operands MN-major
         return dx, dw
 
 
@@ -231,7 +231,7 @@ class _LinearResidualFn(torch.autograd.Function):
         x2, w = ctx.saved_tensors
         dy = dy.contiguous()
         dx = gemm(dy, w, False, True) if ctx.needs_input_grad[0] else None
-        dw = gemm(dy, x2, True, True) if ctx.needs_input_grad[1] else None
+        dw = _wgrad(dy, x2, w) if ctx.needs_input_grad[1] else None
         return dx, dw, (dy if ctx.needs_input_grad[2] else None)
 
 
@@ -257,8 +257,72 @@ class _LinearSwiGLUFn(torch.autograd.Function):
         dgu = _ext.ops().swiglu_bwd(dh.contiguous(), gu)
         del gu
         dx = gemm(dgu, w_gu, False, True) if ctx.needs_input_grad[0] else None
-        dw = gemm(dgu, x2, True, True) if ctx.needs_input_grad[1] else None
+        dw = _wgrad(dgu, x2, w_gu) if ctx.needs_input_grad[1] else None
         return dx, dw
+
+
+def _wgrad(dy: torch.Tensor, x2: torch.Tensor, w: torch.Tensor) -> Optional[torch.Tensor]:
+    """dW = dY^T X.  When the engine has pointed ``w._atb_main_grad`` at the parameter's slice of its flat gradient
+    buffer, the GEMM accumulates straight into it and autograd gets no gradient to add (saves writing the
+    temporary and a read-modify-write pass over the buffer)."""
+    main = getattr(w, "_atb_main_grad", None)
+    if main is not None and main.dtype == torch.bfloat16 and main.shape == w.shape and main.is_contiguous():
+        gemm(dy, x2, True, True, epilogue=1, out=main)
+        return None
+    return gemm(dy, x2, True, True)
+
+
+class _MLPFn(torch.autograd.Function):
+    """``[r +] swiglu(x W_gu^T) W_down^T`` keeping only x and the gate/up projections: the activation h is produced
+    again by the kernel that back-propagates through it, so a layer that keeps its activations stores one
+    ``[tokens, intermediate]`` tensor less."""
+
+    @staticmethod
+    def forward(ctx, x2, w_gu, w_down, r2):
+        if not any(ctx.needs_input_grad[:3]):
+            h = gemm(x2, w_gu, epilogue=2)
+        else:
+            gu = gemm(x2, w_gu)
+            _count()
+            h = _ext.ops().swiglu_fwd(gu)
+            ctx.save_for_backward(x2, w_gu, w_down, gu)
+        if r2 is None:
+            return gemm(h, w_down)
+        return gemm(h, w_down, epilogue=1, residual=r2)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w_gu, w_down, gu = ctx.saved_tensors
+        dy = dy.contiguous()
+        dh = gemm(dy, w_down, False, True)
+        _count()
+        dgu, h = _ext.ops().swiglu_bwd_recompute(dh, gu)
+        del dh, gu
+        dw_down = _wgrad(dy, h, w_down) if ctx.needs_input_grad[2] else None
+        del h
+        dx = gemm(dgu, w_gu, False, True) if ctx.needs_input_grad[0] else None
+        dw_gu = _wgrad(dgu, x2, w_gu) if ctx.needs_input_grad[1] else None
+        return dx, dw_gu, dw_down, (dy if ctx.needs_input_grad[3] else None)
+
+
+def mlp_swiglu(
+    x: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor, residual: Optional[torch.Tensor] = None
+) -> torch.Tensor:
+    """SwiGLU feed-forward block ``[residual +] swiglu(x W_gu^T) W_down^T`` (block-interleaved gate/up weight)."""
+    if _use_kernels(x):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        if (
+            _gemm_ok(x2, w_gate_up) and w_gate_up.shape[0] % 128 == 0 and w_down.dtype == torch.bfloat16
+            and w_down.shape[0] % 8 == 0 and w_down.data_ptr() % 16 == 0
+            and (residual is None or (residual.dtype == torch.bfloat16 and residual.is_contiguous()
+                                      and residual.data_ptr() % 16 == 0))
+        ):
+            r2 = residual.view(-1, w_down.shape[0]) if residual is not None else None
+            return _MLPFn.apply(x2, w_gate_up, w_down, r2).view(*x.shape[:-1], w_down.shape[0])
+    y = linear(linear_swiglu(x, w_gate_up), w_down)
+    return y if residual is None else residual + y
 
 
 def linear(

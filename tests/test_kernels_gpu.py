@@ -481,3 +481,47 @@ def test_linear_with_fused_residual_matches_torch():
     assert _rel(x.grad, xr.grad) < 1e-2 and _rel(w.grad, wr.grad) < 1e-2
     assert torch.equal(r.grad, g)
     _check_flag(y)
+
+
+@pytest.mark.parametrize("with_residual", [False, True])
+def test_fused_mlp_function_matches_reference(with_residual):
+    from arctictraining_b200.ops import functional as Fn
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(0)
+    H, I, T = 256, 384, 320
+    x = (torch.randn(T, H, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    wgu = (torch.randn(2 * I, H, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    wd = (torch.randn(H, I, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    r = torch.randn(T, H, device="cuda").bfloat16().requires_grad_(True) if with_residual else None
+    g = torch.randn(T, H, device="cuda").bfloat16()
+    y = Fn.mlp_swiglu(x, wgu, wd, r)
+    y.backward(g)
+    xr, wgur, wdr = (t.detach().float().requires_grad_(True) for t in (x, wgu, wd))
+    y2 = ref.swiglu_interleaved(xr @ wgur.t()) @ wdr.t()
+    if with_residual:
+        y2 = y2 + r.detach().float()
+    y2.backward(g.float())
+    assert _rel(y, y2) < 1e-2
+    for a, b in ((x.grad, xr.grad), (wgu.grad, wgur.grad), (wd.grad, wdr.grad)):
+        assert _rel(a, b) < 1.5e-2
+    if with_residual:
+        assert torch.equal(r.grad, g)
+    _check_flag(y)
+
+
+def test_weight_gradient_accumulates_into_the_engine_buffer():
+    from arctictraining_b200.ops import functional as Fn
+
+    torch.manual_seed(0)
+    x = (torch.randn(256, 128, device="cuda") * 0.5).bfloat16().requires_grad_(True)
+    w = (torch.randn(192, 128, device="cuda") * 0.05).bfloat16().requires_grad_(True)
+    g = torch.randn(256, 192, device="cuda").bfloat16()
+    Fn.linear(x, w).backward(g)
+    want = w.grad.clone()
+    w.grad = None
+    main = torch.ones_like(w)
+    w._atb_main_grad = main
+    Fn.linear(x, w).backward(g)
+    assert w.grad is None
+    assert _rel(main - 1, want) < 1e-2
