@@ -49,7 +49,11 @@ at::Tensor p2p_reduce_scatter_adamw(const at::Tensor& grad_ptrs, int64_t elem_of
                                     double beta2, double eps, double wd, int64_t step);
 at::Tensor nvls_reduce_scatter_accum(int64_t multicast_ptr, int64_t elem_offset, int64_t n, at::Tensor acc, double scale,
                                      bool overwrite, bool want_sumsq);
-void p2p_seq_to_head(const at::Tensor& x, const at::Tensor& dst_ptrs, int64_t rank, bool reverse);
+void p2p_seq_to_head(const at::Tensor& x, const at::Tensor& dst_ptrs, int64_t rank, bool reverse, int64_t dst_byte_offset);
+void p2p_qkv_push(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& dst_ptrs,
+                  int64_t dst_byte_offset, int64_t rank);
+at::Tensor p2p_qkv_grad_pull(const at::Tensor& src_ptrs, int64_t src_byte_offset, const at::Tensor& like, int64_t S_loc,
+                             int64_t Hq, int64_t Hkv, int64_t D, int64_t rank);
 std::tuple<at::Tensor, at::Tensor> moe_dest_rows(const at::Tensor& all_counts, const at::Tensor& experts,
                                                  const at::Tensor& local_slots, const at::Tensor& local_offsets, int64_t rank,
                                                  int64_t align);
@@ -92,7 +96,9 @@ TORCH_LIBRARY(atb200, m) {
           &atb::p2p_reduce_scatter_adamw);
     m.def("nvls_reduce_scatter_accum(int multicast_ptr, int elem_offset, int n, Tensor(a!) acc, float scale, bool overwrite, "
           "bool want_sumsq) -> Tensor", &atb::nvls_reduce_scatter_accum);
-    m.def("p2p_seq_to_head(Tensor x, Tensor dst_ptrs, int rank, bool reverse) -> ()", &atb::p2p_seq_to_head);
+    m.def("p2p_seq_to_head(Tensor x, Tensor dst_ptrs, int rank, bool reverse, int dst_byte_offset=0) -> ()", &atb::p2p_seq_to_head);
+    m.def("p2p_qkv_push(Tensor q, Tensor k, Tensor v, Tensor dst_ptrs, int dst_byte_offset, int rank) -> ()", &atb::p2p_qkv_push);
+    m.def("p2p_qkv_grad_pull(Tensor src_ptrs, int src_byte_offset, Tensor like, int S_loc, int Hq, int Hkv, int D, int rank) -> Tensor", &atb::p2p_qkv_grad_pull);
     m.def("moe_dest_rows(Tensor all_counts, Tensor experts, Tensor local_slots, Tensor local_offsets, int rank, int align) -> "
           "(Tensor, Tensor)", &atb::moe_dest_rows);
     m.def("p2p_moe_dispatch(Tensor x, Tensor experts, Tensor dest_row, Tensor dst_ptrs, int experts_per_rank) -> ()",

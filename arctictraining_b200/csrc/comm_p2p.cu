@@ -196,6 +196,80 @@ __global__ void __launch_bounds__(128) p2p_head_to_seq_kernel(const bf16* __rest
     for (int i = threadIdx.x; i < vec_per_tok; i += blockDim.x) out[i] = src[i];
 }
 
+// Fused Q/K/V exchange.  Source: this rank's tokens, all heads (q [S_loc, Hq, D], k / v [S_loc, Hkv, D], each with its
+// own token stride, so views of one fused projection output are fine).  Destination on rank o: one fused buffer
+// [P * S_loc, Hlq + 2 * Hlkv, D] (its q heads, then its k heads, then its v heads) at row rank * S_loc + s.  With
+// fewer KV heads than ranks (rep = P / Hkv > 1) KV head h goes to the rep ranks h * rep ... and Hlkv = 1.
+__global__ void __launch_bounds__(128) p2p_qkv_push_kernel(const bf16* __restrict__ q, const bf16* __restrict__ k,
+                                                           const bf16* __restrict__ v, int64_t q_stride, int64_t k_stride,
+                                                           int64_t v_stride, PeerTable dst, int S_loc, int Hq, int Hkv,
+                                                           int D, int rank, int P) {
+    const int s = blockIdx.x, o = blockIdx.y;
+    const int Hlq = Hq / P;
+    const int rep = Hkv >= P ? 1 : P / Hkv;
+    const int Hlkv = Hkv >= P ? Hkv / P : 1;
+    const int kv_head0 = Hkv >= P ? o * Hlkv : o / rep;
+    const int W = (Hlq + 2 * Hlkv) * D;
+    bf16* drow = reinterpret_cast<bf16*>(dst.ptr[o]) + ((int64_t)rank * S_loc + s) * W;
+    const int nq = Hlq * D / 8, nkv = Hlkv * D / 8;
+    const bf16x8* sq = reinterpret_cast<const bf16x8*>(q + s * q_stride + (int64_t)o * Hlq * D);
+    const bf16x8* sk = reinterpret_cast<const bf16x8*>(k + s * k_stride + (int64_t)kv_head0 * D);
+    const bf16x8* sv = reinterpret_cast<const bf16x8*>(v + s * v_stride + (int64_t)kv_head0 * D);
+    bf16x8* dq = reinterpret_cast<bf16x8*>(drow);
+    bf16x8* dk = reinterpret_cast<bf16x8*>(drow + Hlq * D);
+    bf16x8* dv = reinterpret_cast<bf16x8*>(drow + (Hlq + Hlkv) * D);
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) dq[i] = sq[i];
+    for (int i = threadIdx.x; i < nkv; i += blockDim.x) dk[i] = sk[i];
+    for (int i = threadIdx.x; i < nkv; i += blockDim.x) dv[i] = sv[i];
+}
+
+// Backward of the exchange above: every rank holds d(fused buffer) [P * S_loc, Hlq + 2 * Hlkv, D] in a symmetric
+// buffer; the owner of a sequence chunk pulls its rows from every peer into out [S_loc, Hq + 2 * Hkv, D] and adds
+// the replicas of a replicated KV head in fp32.
+__global__ void __launch_bounds__(128) p2p_qkv_grad_pull_kernel(PeerTable src, bf16* __restrict__ out, int S_loc, int Hq,
+                                                                int Hkv, int D, int rank, int P) {
+    const int s = blockIdx.x, o = blockIdx.y;
+    const int Hlq = Hq / P;
+    const int rep = Hkv >= P ? 1 : P / Hkv;
+    const int Hlkv = Hkv >= P ? Hkv / P : 1;
+    const int W = (Hlq + 2 * Hlkv) * D;
+    const int64_t row = (int64_t)rank * S_loc + s;
+    bf16* orow = out + (int64_t)s * (Hq + 2 * Hkv) * D;
+    const bf16* srow = reinterpret_cast<const bf16*>(src.ptr[o]) + row * W;
+    const int nq = Hlq * D / 8, nkv = Hlkv * D / 8;
+    {
+        const bf16x8* a = reinterpret_cast<const bf16x8*>(srow);
+        bf16x8* b = reinterpret_cast<bf16x8*>(orow + (int64_t)o * Hlq * D);
+        for (int i = threadIdx.x; i < nq; i += blockDim.x) b[i] = a[i];
+    }
+    if (rep == 1) {
+        const bf16x8* ak = reinterpret_cast<const bf16x8*>(srow + Hlq * D);
+        const bf16x8* av = reinterpret_cast<const bf16x8*>(srow + (Hlq + Hlkv) * D);
+        bf16x8* bk = reinterpret_cast<bf16x8*>(orow + (int64_t)(Hq + o * Hlkv) * D);
+        bf16x8* bv = reinterpret_cast<bf16x8*>(orow + (int64_t)(Hq + Hkv + o * Hlkv) * D);
+        for (int i = threadIdx.x; i < nkv; i += blockDim.x) { bk[i] = ak[i]; bv[i] = av[i]; }
+    } else if (o % rep == 0) {
+        const int head = o / rep;
+        bf16x8* bk = reinterpret_cast<bf16x8*>(orow + (int64_t)(Hq + head) * D);
+        bf16x8* bv = reinterpret_cast<bf16x8*>(orow + (int64_t)(Hq + Hkv + head) * D);
+        for (int i = threadIdx.x; i < nkv; i += blockDim.x) {
+            float sk[8] = {0, 0, 0, 0, 0, 0, 0, 0}, sv[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+            for (int j = 0; j < rep; ++j) {
+                const bf16* prow = reinterpret_cast<const bf16*>(src.ptr[o + j]) + row * W;
+                float f[8];
+                unpack8(reinterpret_cast<const bf16x8*>(prow + Hlq * D)[i], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sk[e] += f[e];
+                unpack8(reinterpret_cast<const bf16x8*>(prow + (Hlq + 1) * D)[i], f);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) sv[e] += f[e];
+            }
+            bk[i] = pack8(sk);
+            bv[i] = pack8(sv);
+        }
+    }
+}
+
 // ------------------------------------------------------------------------------------------- MoE exchanges
 // dispatch: token t's k-th copy goes to expert e = experts[t, k], owned by rank e / El.  Its row in the owner's
 // expert-major buffer is dest_row[t, k] (computed from the all-gathered counts, see moe_dest_rows_kernel).
@@ -365,7 +439,7 @@ at::Tensor nvls_reduce_scatter_accum(int64_t multicast_ptr, int64_t elem_offset,
     return want_sumsq ? partial.sum() : at::zeros({}, acc.options());
 }
 
-void p2p_seq_to_head(const at::Tensor& x, const at::Tensor& dst_ptrs, int64_t rank, bool reverse) {
+void p2p_seq_to_head(const at::Tensor& x, const at::Tensor& dst_ptrs, int64_t rank, bool reverse, int64_t dst_byte_offset) {
     // forward: x [S_loc, H, D] -> peers' [P * S_loc, H / P, D];  reverse: x [P * S_loc, H / P, D] -> peers' [S_loc, H, D]
     ATB_CHECK_CUDA(x); ATB_CHECK_CONTIG(x); ATB_CHECK_DTYPE(x, at::kBFloat16); ATB_CHECK_ALIGNED16(x);
     TORCH_CHECK(x.dim() == 3, "ulysses exchange: x must be [tokens, heads, head_dim]");
@@ -377,13 +451,59 @@ void p2p_seq_to_head(const at::Tensor& x, const at::Tensor& dst_ptrs, int64_t ra
     TORCH_CHECK(H % P == 0 && ((H / P) * D) % 8 == 0, "ulysses exchange: heads must divide by the group size");
     if (S_loc == 0) return;
     c10::cuda::CUDAGuard guard(x.device());
-    PeerTable t = make_table(dst_ptrs, 0);
+    TORCH_CHECK(dst_byte_offset % 16 == 0, "ulysses exchange: misaligned destination offset");
+    PeerTable t = make_table(dst_ptrs, dst_byte_offset);
     dim3 grid(S_loc, P);
     if (!reverse)
         p2p_seq_to_head_kernel<<<grid, 128, 0, current_stream()>>>((const bf16*)x.data_ptr(), t, S_loc, H, D, (int)rank, P);
     else
         p2p_head_to_seq_kernel<<<grid, 128, 0, current_stream()>>>((const bf16*)x.data_ptr(), t, S_loc, H, D, (int)rank, P);
     ATB_LAUNCH_CHECK();
+}
+
+static void check_qkv_heads(int Hq, int Hkv, int D, int P) {
+    TORCH_CHECK(Hq % P == 0, "ulysses exchange: query heads must divide by the group size");
+    TORCH_CHECK(Hkv >= P ? Hkv % P == 0 : P % Hkv == 0, "ulysses exchange: KV heads and group size must divide one another");
+    TORCH_CHECK(D % 8 == 0, "ulysses exchange: head_dim must be a multiple of 8");
+}
+
+// q [S_loc, Hq, D], k / v [S_loc, Hkv, D] (dense heads, any token stride that is a multiple of 8 elements).
+void p2p_qkv_push(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const at::Tensor& dst_ptrs,
+                  int64_t dst_byte_offset, int64_t rank) {
+    ATB_CHECK_CUDA(q); ATB_CHECK_DTYPE(q, at::kBFloat16); ATB_CHECK_DTYPE(k, at::kBFloat16); ATB_CHECK_DTYPE(v, at::kBFloat16);
+    TORCH_CHECK(q.dim() == 3 && k.dim() == 3 && v.dim() == 3, "ulysses exchange: [tokens, heads, head_dim] tensors");
+    const int P = (int)dst_ptrs.numel(), S_loc = (int)q.size(0), Hq = (int)q.size(1), Hkv = (int)k.size(1), D = (int)q.size(2);
+    check_qkv_heads(Hq, Hkv, D, P);
+    for (const at::Tensor* t : {&q, &k, &v}) {
+        TORCH_CHECK(t->size(0) == S_loc && t->size(2) == D && t->stride(2) == 1 && t->stride(1) == D && t->stride(0) % 8 == 0,
+                    "ulysses exchange: dense heads and a token stride that is a multiple of 8");
+        TORCH_CHECK((reinterpret_cast<uintptr_t>(t->data_ptr()) & 15) == 0, "ulysses exchange: 16-byte aligned operands");
+    }
+    TORCH_CHECK(v.size(1) == Hkv && dst_byte_offset % 16 == 0, "ulysses exchange: inconsistent arguments");
+    if (S_loc == 0) return;
+    c10::cuda::CUDAGuard guard(q.device());
+    PeerTable t = make_table(dst_ptrs, dst_byte_offset);
+    p2p_qkv_push_kernel<<<dim3(S_loc, P), 128, 0, current_stream()>>>(
+        (const bf16*)q.data_ptr(), (const bf16*)k.data_ptr(), (const bf16*)v.data_ptr(), q.stride(0), k.stride(0), v.stride(0),
+        t, S_loc, Hq, Hkv, D, (int)rank, P);
+    ATB_LAUNCH_CHECK();
+}
+
+// Returns d(qkv) [S_loc, Hq + 2 * Hkv, D] for this rank's tokens from the peers' symmetric gradient buffers.
+at::Tensor p2p_qkv_grad_pull(const at::Tensor& src_ptrs, int64_t src_byte_offset, const at::Tensor& like, int64_t S_loc,
+                             int64_t Hq, int64_t Hkv, int64_t D, int64_t rank) {
+    ATB_CHECK_CUDA(like); ATB_CHECK_DTYPE(like, at::kBFloat16);
+    const int P = (int)src_ptrs.numel();
+    check_qkv_heads((int)Hq, (int)Hkv, (int)D, P);
+    TORCH_CHECK(src_byte_offset % 16 == 0, "ulysses exchange: misaligned source offset");
+    c10::cuda::CUDAGuard guard(like.device());
+    auto out = at::empty({S_loc, Hq + 2 * Hkv, D}, like.options());
+    if (S_loc == 0) return out;
+    PeerTable t = make_table(src_ptrs, src_byte_offset);
+    p2p_qkv_grad_pull_kernel<<<dim3((unsigned)S_loc, P), 128, 0, current_stream()>>>(t, (bf16*)out.data_ptr(), (int)S_loc, (int)Hq,
+                                                                                     (int)Hkv, (int)D, (int)rank, P);
+    ATB_LAUNCH_CHECK();
+    return out;
 }
 
 std::tuple<at::Tensor, at::Tensor> moe_dest_rows(const at::Tensor& all_counts, const at::Tensor& experts,

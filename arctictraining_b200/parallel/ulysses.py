@@ -77,6 +77,13 @@ def _head_to_seq(x: torch.Tensor, group) -> torch.Tensor:
     return recv.permute(1, 2, 0, 3, 4).reshape(B, S_loc, P * Hl, D)
 
 
+def _dense_heads(t: torch.Tensor) -> torch.Tensor:
+    """[S, H, D] with dense heads and an aligned token stride (views of a fused projection qualify), else a copy."""
+    if t.stride(2) == 1 and t.stride(1) == t.shape[2] and t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0:
+        return t
+    return t.contiguous()
+
+
 class _SumOverGroup(torch.autograd.Function):
     """Forward: all-reduce(sum) so every rank reports the same value; backward: identity, each rank keeps the
     gradient of its own contribution."""
@@ -92,10 +99,120 @@ class _SumOverGroup(torch.autograd.Function):
         return g, None
 
 
+class _PeerExchange:
+    """The two Ulysses exchanges as single kernels over NVLink peer memory (no NCCL call, no permute copies).
+
+    Every exchange owns two symmetric buffers used in turn, and ends with one device-side barrier.  Reusing a
+    buffer is safe after two exchanges of the same kind: a rank passes the barrier of exchange n + 1 only after
+    every peer has queued, in stream order, its copy out of the buffer of exchange n.  The received data is copied
+    out of the symmetric buffer at once, so nothing that autograd saves points into memory peers write to."""
+
+    Q_SLOT, O_SLOT, DO_SLOT, DQ_SLOT = 8, 9, 10, 11
+
+    def __init__(self, group) -> None:
+        from ..comm.symm import SymmetricContext
+
+        self.symm = SymmetricContext(group)
+        self.rank, self.size = self.symm.rank, self.symm.world
+        self._bufs: Dict[str, Any] = {}
+        self._turn: Dict[str, int] = {}
+
+    def _buffer(self, name: str, numel: int):
+        """Symmetric buffer ``name`` with room for two exchanges of ``numel`` elements; returns (buffer, byte offset
+        of the half to use now).  Grows collectively: every rank of the group sees the same shapes."""
+        numel = (numel + 127) // 128 * 128
+        buf = self._bufs.get(name)
+        if buf is None or buf.tensor.numel() < 2 * numel:
+            torch.cuda.synchronize()
+            buf = self.symm.alloc(f"ulysses_{name}_{2 * numel}", 2 * numel, torch.bfloat16)
+            self._bufs[name] = buf
+            self._turn[name] = 0
+        half = buf.tensor.numel() // 2
+        turn = self._turn[name]
+        self._turn[name] = turn ^ 1
+        return buf, turn * half
+
+    def _ptrs(self, buf) -> torch.Tensor:
+        return buf.ptrs
+
+    # ---- q, k, v: sequence-sharded -> head-sharded
+    def qkv_seq_to_head(self, q, k, v):
+        S_loc, Hq, D = q.shape
+        Hkv = k.shape[1]
+        P = self.size
+        Hlq, Hlkv = Hq // P, (Hkv // P if Hkv >= P else 1)
+        W = (Hlq + 2 * Hlkv) * D
+        buf, off = self._buffer("qkv", P * S_loc * W)
+        ops._ext.ops().p2p_qkv_push(q, k, v, buf.ptrs, off * 2, self.rank)
+        self.symm.barrier(self.Q_SLOT)
+        return buf.tensor[off : off + P * S_loc * W].view(P * S_loc, Hlq + 2 * Hlkv, D).clone()
+
+    def qkv_grad_head_to_seq(self, g, S_loc: int, Hq: int, Hkv: int, D: int):
+        buf, off = self._buffer("dqkv", g.numel())
+        buf.tensor[off : off + g.numel()].view_as(g).copy_(g)
+        self.symm.barrier(self.DQ_SLOT)
+        return ops._ext.ops().p2p_qkv_grad_pull(buf.ptrs, off * 2, g, S_loc, Hq, Hkv, D, self.rank)
+
+    # ---- attention output: head-sharded -> sequence-sharded (and its gradient the other way)
+    def head_to_seq(self, y, slot_name: str = "o"):
+        S, Hl, D = y.shape
+        P = self.size
+        buf, off = self._buffer(slot_name, S * Hl * D)
+        ops._ext.ops().p2p_seq_to_head(y, buf.ptrs, self.rank, True, off * 2)
+        self.symm.barrier(self.O_SLOT)
+        return buf.tensor[off : off + S * Hl * D].view(S // P, Hl * P, D).clone()
+
+    def seq_to_head(self, x, slot_name: str = "do"):
+        S_loc, H, D = x.shape
+        P = self.size
+        buf, off = self._buffer(slot_name, S_loc * H * D)
+        ops._ext.ops().p2p_seq_to_head(x, buf.ptrs, self.rank, False, off * 2)
+        self.symm.barrier(self.DO_SLOT)
+        return buf.tensor[off : off + S_loc * H * D].view(S_loc * P, H // P, D).clone()
+
+
+class _QKVSeqToHeadPeer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, ex):
+        ctx.ex, ctx.dims = ex, (q.shape[0], q.shape[1], k.shape[1], q.shape[2])
+        return ex.qkv_seq_to_head(q, k, v)
+
+    @staticmethod
+    def backward(ctx, g):
+        S_loc, Hq, Hkv, D = ctx.dims
+        d = ctx.ex.qkv_grad_head_to_seq(g.contiguous(), S_loc, Hq, Hkv, D)
+        return d[:, :Hq], d[:, Hq : Hq + Hkv], d[:, Hq + Hkv :], None
+
+
+class _HeadToSeqPeer(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, y, ex):
+        ctx.ex = ex
+        return ex.head_to_seq(y.contiguous())
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.ex.seq_to_head(g.contiguous()), None
+
+
 class UlyssesContext:
-    def __init__(self, group, size: int, rank: int, fused: bool = False) -> None:
+    def __init__(self, group, size: int, rank: int, fused: Optional[bool] = None) -> None:
         self.group, self.size, self.rank = group, size, rank
-        self.fused = fused
+        self.fused = fused  # None: decide on first use (peer memory available and usable shapes)
+        self._peer: Optional[_PeerExchange] = None
+
+    def _peer_exchange(self, q: torch.Tensor) -> Optional[_PeerExchange]:
+        if self.fused is False or not q.is_cuda or q.dtype != torch.bfloat16 or q.shape[0] != 1:
+            return None
+        if self._peer is None:
+            from ..comm.symm import symmetric_memory_available
+
+            if not symmetric_memory_available(self.group):
+                self.fused = False
+                return None
+            self._peer = _PeerExchange(self.group)
+            self.fused = True
+        return self._peer
 
     # -- attention -------------------------------------------------------------------------------
     def attention(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, ctx: Any) -> torch.Tensor:
@@ -103,6 +220,14 @@ class UlyssesContext:
         Hq, Hkv = q.shape[2], k.shape[2]
         if Hq % P != 0:
             raise ValueError(f"query heads ({Hq}) must be divisible by sequence_parallel_size ({P})")
+        ex = self._peer_exchange(q) if (Hkv % P == 0 or P % Hkv == 0) and q.shape[-1] % 8 == 0 else None
+        if ex is not None:
+            D = q.shape[-1]
+            Hlq, Hlkv = Hq // P, (Hkv // P if Hkv >= P else 1)
+            qkv = _QKVSeqToHeadPeer.apply(_dense_heads(q[0]), _dense_heads(k[0]), _dense_heads(v[0]), ex)
+            qf, kf, vf = qkv[None, :, :Hlq], qkv[None, :, Hlq : Hlq + Hlkv], qkv[None, :, Hlq + Hlkv :]
+            o = ops.attention(qf, kf, vf, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
+            return _HeadToSeqPeer.apply(o[0], ex)[None]
         if Hkv < P:
             if P % Hkv != 0:
                 raise ValueError(f"sequence_parallel_size ({P}) must be a multiple of the KV heads ({Hkv})")

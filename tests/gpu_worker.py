@@ -96,11 +96,50 @@ def scenario_barrier_timeout(out_dir):
         (Path(out_dir) / "barrier_timeout.json").write_text(json.dumps({"ok": all(flags)}))
 
 
+def scenario_ulysses_peer(out_dir):
+    """The peer-memory Ulysses exchange gives the same attention output and input gradients as the NCCL one."""
+    from types import SimpleNamespace
+
+    from arctictraining_b200.parallel.ulysses import UlyssesContext
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    res = {}
+    for name, (Hq, Hkv) in {"kv_split": (4, 2), "kv_replicated": (4, 1)}.items():
+        torch.manual_seed(10 + rank)
+        S_loc, D = 192, 128
+        qkv = torch.randn(1, S_loc, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+        g = torch.randn(1, S_loc, Hq, D, device="cuda", dtype=torch.bfloat16)
+        fctx = SimpleNamespace(cu_seqlens=None, max_seqlen=None, attn_impl="native")
+        outs = []
+        for fused in (False, True):
+            sp = UlyssesContext(dist.group.WORLD, world, rank, fused=None if fused else False)
+            x = qkv.clone().requires_grad_(True)
+            q, k, v = x.view(1, S_loc, Hq + 2 * Hkv, D).split([Hq, Hkv, Hkv], dim=2)
+            for _ in range(3):  # several exchanges in a row exercise the buffer rotation
+                x.grad = None
+                o = sp.attention(q, k, v, fctx)
+                o.backward(g)
+            assert fused is False or sp.fused is True, "peer exchange did not come up"
+            if fused:
+                sp._peer.symm.check()
+            outs.append((o.detach().float(), x.grad.float()))
+        res[name] = {
+            "out_diff": float((outs[0][0] - outs[1][0]).abs().max()),
+            "grad_diff": float((outs[0][1] - outs[1][1]).abs().max()),
+            "grad_scale": float(outs[0][1].abs().max()),
+        }
+    allres = [None] * world
+    dist.all_gather_object(allres, res)
+    if rank == 0:
+        (Path(out_dir) / "ulysses_peer.json").write_text(json.dumps(allres))
+
+
 def main():
     scenario, out_dir = sys.argv[1], sys.argv[2]
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     init_distributed(timeout_s=120)
-    {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout}[scenario](out_dir)
+    {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout,
+     "ulysses_peer": scenario_ulysses_peer}[scenario](out_dir)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -36,3 +36,11 @@ def test_peer_memory_path_matches_nccl(tmp_path):
 def test_bounded_barrier_reports_a_missing_peer(tmp_path):
     launch(2, "barrier_timeout", tmp_path)
     assert json.loads((tmp_path / "barrier_timeout.json").read_text())["ok"]
+
+
+def test_peer_memory_ulysses_exchange_matches_nccl(tmp_path):
+    launch(2, "ulysses_peer", tmp_path)
+    for per_rank in json.loads((tmp_path / "ulysses_peer.json").read_text()):
+        assert per_rank["kv_split"]["out_diff"] == 0.0 and per_rank["kv_split"]["grad_diff"] == 0.0
+        r = per_rank["kv_replicated"]
+        assert r["out_diff"] == 0.0 and r["grad_diff"] <= 2e-2 * r["grad_scale"]
