@@ -112,3 +112,34 @@ class SymmetricContext:
         if self.use_nvls and grads.multicast_ptr:
             return _ext.ops().nvls_reduce_scatter_accum(grads.multicast_ptr, elem_offset, n, acc, scale, overwrite, want_sumsq)
         return _ext.ops().p2p_reduce_scatter_accum(grads.ptrs, elem_offset, n, acc, scale, overwrite, want_sumsq)
+
+
+class RotatingBuffers:
+    """Named symmetric buffers that are used in two halves in turn.
+
+    A kernel pushes into (or peers pull from) one half, a device-side barrier follows, and the consumer copies the
+    data out at once.  Reusing a half is then safe after two exchanges of the same name: a rank passes the barrier
+    of exchange n + 1 only after every peer has queued, in stream order, its copy out of the half of exchange n.
+    Buffers grow collectively, so every rank of the group must ask for the same sizes in the same order."""
+
+    def __init__(self, ctx: SymmetricContext) -> None:
+        self.ctx = ctx
+        self._bufs: Dict[str, SymmetricBuffer] = {}
+        self._turn: Dict[str, int] = {}
+
+    def take(self, name: str, numel: int, dtype: torch.dtype = torch.bfloat16):
+        """Returns ``(buffer, element offset of the half to use now)``."""
+        numel = (numel + 127) // 128 * 128
+        buf = self._bufs.get(name)
+        if buf is None or buf.tensor.numel() < 2 * numel:
+            torch.cuda.synchronize()
+            buf = self.ctx.alloc(f"{name}_{2 * numel}", 2 * numel, dtype)
+            buf.tensor.zero_()
+            torch.cuda.synchronize()
+            dist.barrier(group=self.ctx.group, device_ids=[self.ctx.device.index])
+            self._bufs[name] = buf
+            self._turn[name] = 0
+        half = buf.tensor.numel() // 2
+        turn = self._turn[name]
+        self._turn[name] = turn ^ 1
+        return buf, turn * half

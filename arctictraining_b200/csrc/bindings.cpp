@@ -57,10 +57,13 @@ at::Tensor p2p_qkv_grad_pull(const at::Tensor& src_ptrs, int64_t src_byte_offset
 std::tuple<at::Tensor, at::Tensor> moe_dest_rows(const at::Tensor& all_counts, const at::Tensor& experts,
                                                  const at::Tensor& local_slots, const at::Tensor& local_offsets, int64_t rank,
                                                  int64_t align);
-void p2p_moe_dispatch(const at::Tensor& x, const at::Tensor& experts, const at::Tensor& dest_row, const at::Tensor& dst_ptrs,
-                      int64_t experts_per_rank);
-at::Tensor p2p_moe_combine(const at::Tensor& y_ptrs, const at::Tensor& experts, const at::Tensor& dest_row,
-                           const at::Tensor& scores, int64_t hidden, int64_t experts_per_rank);
+void p2p_moe_dispatch(const at::Tensor& x, const at::Tensor& experts, const at::Tensor& dest_row,
+                      const at::Tensor& dst_ptrs, int64_t dst_byte_offset, int64_t experts_per_rank, int64_t capacity,
+                      const c10::optional<at::Tensor>& pair_scale);
+at::Tensor p2p_moe_combine(const at::Tensor& y_ptrs, int64_t y_byte_offset, const at::Tensor& experts, const at::Tensor& dest_row,
+                           const c10::optional<at::Tensor>& scores, int64_t hidden, int64_t experts_per_rank, int64_t capacity);
+at::Tensor p2p_moe_pair_dot(const at::Tensor& y_ptrs, int64_t y_byte_offset, const at::Tensor& experts, const at::Tensor& dest_row,
+                            const at::Tensor& dout, int64_t experts_per_rank, int64_t capacity);
 }  // namespace atb
 
 TORCH_LIBRARY(atb200, m) {
@@ -101,10 +104,9 @@ TORCH_LIBRARY(atb200, m) {
     m.def("p2p_qkv_grad_pull(Tensor src_ptrs, int src_byte_offset, Tensor like, int S_loc, int Hq, int Hkv, int D, int rank) -> Tensor", &atb::p2p_qkv_grad_pull);
     m.def("moe_dest_rows(Tensor all_counts, Tensor experts, Tensor local_slots, Tensor local_offsets, int rank, int align) -> "
           "(Tensor, Tensor)", &atb::moe_dest_rows);
-    m.def("p2p_moe_dispatch(Tensor x, Tensor experts, Tensor dest_row, Tensor dst_ptrs, int experts_per_rank) -> ()",
-          &atb::p2p_moe_dispatch);
-    m.def("p2p_moe_combine(Tensor y_ptrs, Tensor experts, Tensor dest_row, Tensor scores, int hidden, int experts_per_rank) -> Tensor",
-          &atb::p2p_moe_combine);
+    m.def("p2p_moe_dispatch(Tensor x, Tensor experts, Tensor dest_row, Tensor dst_ptrs, int dst_byte_offset, int experts_per_rank, int capacity, Tensor? pair_scale=None) -> ()", &atb::p2p_moe_dispatch);
+    m.def("p2p_moe_combine(Tensor y_ptrs, int y_byte_offset, Tensor experts, Tensor dest_row, Tensor? scores, int hidden, int experts_per_rank, int capacity) -> Tensor", &atb::p2p_moe_combine);
+    m.def("p2p_moe_pair_dot(Tensor y_ptrs, int y_byte_offset, Tensor experts, Tensor dest_row, Tensor dout, int experts_per_rank, int capacity) -> Tensor", &atb::p2p_moe_pair_dot);
     m.def("gemm_bf16_grouped(Tensor a, Tensor b, Tensor offsets, int mode, bool b_mn, int epilogue, Tensor? out) -> Tensor",
           &atb::gemm_bf16_grouped);
     m.def("moe_topk_gating_fwd(Tensor logits, int K, bool normalize) -> (Tensor, Tensor, Tensor)", &atb::moe_topk_gating_fwd);

@@ -272,35 +272,80 @@ __global__ void __launch_bounds__(128) p2p_qkv_grad_pull_kernel(PeerTable src, b
 
 // ------------------------------------------------------------------------------------------- MoE exchanges
 // dispatch: token t's k-th copy goes to expert e = experts[t, k], owned by rank e / El.  Its row in the owner's
-// expert-major buffer is dest_row[t, k] (computed from the all-gathered counts, see moe_dest_rows_kernel).
+// expert-major buffer is dest_row[t, k] (computed from the all-gathered counts, see moe_dest_rows_kernel).  With
+// `pair_scale` the copy is multiplied by pair_scale[t, k] (the backward pass sends score * d_out this way).  A
+// destination row beyond `capacity` is not written; the error word records it.
 __global__ void __launch_bounds__(256) p2p_moe_dispatch_kernel(const bf16* __restrict__ x, const int* __restrict__ experts,
-                                                               const int* __restrict__ dest_row, PeerTable dst, int H,
-                                                               int K, int El) {
+                                                               const int* __restrict__ dest_row,
+                                                               const float* __restrict__ pair_scale, PeerTable dst, int H,
+                                                               int K, int El, int capacity, int* error_flag) {
     const int64_t t = blockIdx.x;
     const bf16x8* src = reinterpret_cast<const bf16x8*>(x + t * H);
     const int nvec = H >> 3;
     for (int k = 0; k < K; ++k) {
         const int owner = experts[t * K + k] / El;
-        bf16x8* out = reinterpret_cast<bf16x8*>(reinterpret_cast<bf16*>(dst.ptr[owner]) + (int64_t)dest_row[t * K + k] * H);
-        for (int i = threadIdx.x; i < nvec; i += blockDim.x) out[i] = src[i];
+        const int row = dest_row[t * K + k];
+        if (row < 0 || row >= capacity) {
+            if (threadIdx.x == 0) atomicCAS(error_flag, 0, (0x31 << 8) | (owner + 1));
+            continue;
+        }
+        bf16x8* out = reinterpret_cast<bf16x8*>(reinterpret_cast<bf16*>(dst.ptr[owner]) + (int64_t)row * H);
+        if (pair_scale == nullptr) {
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x) out[i] = src[i];
+        } else {
+            const float sc = pair_scale[t * K + k];
+            for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+                float f[8];
+                unpack8(src[i], f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[j] *= sc;
+                out[i] = pack8(f);
+            }
+        }
     }
 }
 
 // combine: the source rank pulls the expert outputs of its (token, k) pairs from the owners and reduces them:
-//   out[t] = sum_k score[t, k] * y_owner[dest_row[t, k]]
+//   out[t] = sum_k score[t, k] * y_owner[dest_row[t, k]]        (score = 1 without `scores`)
+// `pair_dot` (optional, with `dout`): pair_dot[t, k] = < dout[t], y_owner[dest_row[t, k]] >, the gradient of the score.
 __global__ void __launch_bounds__(256) p2p_moe_combine_kernel(PeerTable y, const int* __restrict__ experts,
                                                               const int* __restrict__ dest_row,
                                                               const float* __restrict__ scores, bf16* __restrict__ out,
-                                                              int H, int K, int El) {
+                                                              const bf16* __restrict__ dout, float* __restrict__ pair_dot,
+                                                              int H, int K, int El, int capacity) {
+    __shared__ float scratch[32];
     const int64_t t = blockIdx.x;
     const int nvec = H >> 3;
+    if (pair_dot != nullptr) {
+        for (int k = 0; k < K; ++k) {
+            const int owner = experts[t * K + k] / El;
+            const int row = dest_row[t * K + k];
+            float acc = 0.f;
+            if (row >= 0 && row < capacity) {
+                const bf16x8* yr = reinterpret_cast<const bf16x8*>(reinterpret_cast<const bf16*>(y.ptr[owner]) + (int64_t)row * H);
+                for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
+                    float a[8], b[8];
+                    unpack8(yr[i], a);
+                    unpack8(reinterpret_cast<const bf16x8*>(dout + t * H)[i], b);
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) acc += a[j] * b[j];
+                }
+            }
+            acc = block_sum(acc, scratch);
+            if (threadIdx.x == 0) pair_dot[t * K + k] = acc;
+            __syncthreads();
+        }
+        return;
+    }
     for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
         float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int k = 0; k < K; ++k) {
             const int owner = experts[t * K + k] / El;
-            const float s = scores[t * K + k];
+            const int row = dest_row[t * K + k];
+            if (row < 0 || row >= capacity) continue;
+            const float s = scores ? scores[t * K + k] : 1.f;
             float f[8];
-            unpack8(reinterpret_cast<const bf16x8*>(reinterpret_cast<const bf16*>(y.ptr[owner]) + (int64_t)dest_row[t * K + k] * H)[i], f);
+            unpack8(reinterpret_cast<const bf16x8*>(reinterpret_cast<const bf16*>(y.ptr[owner]) + (int64_t)row * H)[i], f);
 #pragma unroll
             for (int j = 0; j < 8; ++j) acc[j] += s * f[j];
         }
@@ -526,35 +571,66 @@ std::tuple<at::Tensor, at::Tensor> moe_dest_rows(const at::Tensor& all_counts, c
 }
 
 void p2p_moe_dispatch(const at::Tensor& x, const at::Tensor& experts, const at::Tensor& dest_row,
-                      const at::Tensor& dst_ptrs, int64_t experts_per_rank) {
+                      const at::Tensor& dst_ptrs, int64_t dst_byte_offset, int64_t experts_per_rank, int64_t capacity,
+                      const c10::optional<at::Tensor>& pair_scale) {
     ATB_CHECK_CUDA(x); ATB_CHECK_CONTIG(x); ATB_CHECK_DTYPE(x, at::kBFloat16); ATB_CHECK_ALIGNED16(x);
-    ATB_CHECK_DTYPE(experts, at::kInt); ATB_CHECK_DTYPE(dest_row, at::kInt);
+    ATB_CHECK_DTYPE(experts, at::kInt); ATB_CHECK_DTYPE(dest_row, at::kInt); ATB_CHECK_CONTIG(experts); ATB_CHECK_CONTIG(dest_row);
     const int64_t T = x.size(0);
     const int H = (int)x.size(1), K = (int)experts.size(1);
-    TORCH_CHECK(H % 8 == 0, "moe dispatch: hidden size must be a multiple of 8");
+    TORCH_CHECK(H % 8 == 0 && dst_byte_offset % 16 == 0, "moe dispatch: hidden size must be a multiple of 8");
+    const float* ps = nullptr;
+    if (pair_scale.has_value()) {
+        ATB_CHECK_DTYPE(*pair_scale, at::kFloat); ATB_CHECK_CONTIG(*pair_scale);
+        TORCH_CHECK(pair_scale->numel() == experts.numel(), "moe dispatch: one scale per (token, k) pair");
+        ps = pair_scale->data_ptr<float>();
+    }
     if (T == 0) return;
     c10::cuda::CUDAGuard guard(x.device());
-    PeerTable t = make_table(dst_ptrs, 0);
-    p2p_moe_dispatch_kernel<<<(unsigned)T, 256, 0, current_stream()>>>((const bf16*)x.data_ptr(), experts.data_ptr<int>(),
-                                                                       dest_row.data_ptr<int>(), t, H, K, (int)experts_per_rank);
+    PeerTable t = make_table(dst_ptrs, dst_byte_offset);
+    p2p_moe_dispatch_kernel<<<(unsigned)T, 256, 0, current_stream()>>>(
+        (const bf16*)x.data_ptr(), experts.data_ptr<int>(), dest_row.data_ptr<int>(), ps, t, H, K, (int)experts_per_rank,
+        (int)capacity, error_flag_for_comm(x.device()).data_ptr<int>());
     ATB_LAUNCH_CHECK();
 }
 
-at::Tensor p2p_moe_combine(const at::Tensor& y_ptrs, const at::Tensor& experts, const at::Tensor& dest_row,
-                           const at::Tensor& scores, int64_t hidden, int64_t experts_per_rank) {
+at::Tensor p2p_moe_combine(const at::Tensor& y_ptrs, int64_t y_byte_offset, const at::Tensor& experts, const at::Tensor& dest_row,
+                           const c10::optional<at::Tensor>& scores, int64_t hidden, int64_t experts_per_rank, int64_t capacity) {
     ATB_CHECK_CUDA(experts); ATB_CHECK_DTYPE(experts, at::kInt); ATB_CHECK_DTYPE(dest_row, at::kInt);
-    ATB_CHECK_DTYPE(scores, at::kFloat); ATB_CHECK_CONTIG(scores);
+    ATB_CHECK_CONTIG(experts); ATB_CHECK_CONTIG(dest_row);
+    const float* sc = nullptr;
+    if (scores.has_value()) { ATB_CHECK_DTYPE(*scores, at::kFloat); ATB_CHECK_CONTIG(*scores); sc = scores->data_ptr<float>(); }
     const int64_t T = experts.size(0);
     const int K = (int)experts.size(1);
+    TORCH_CHECK(hidden % 8 == 0 && y_byte_offset % 16 == 0, "moe combine: hidden size must be a multiple of 8");
     c10::cuda::CUDAGuard guard(experts.device());
     auto out = at::empty({T, hidden}, experts.options().dtype(at::kBFloat16));
     if (T == 0) return out;
-    PeerTable t = make_table(y_ptrs, 0);
-    p2p_moe_combine_kernel<<<(unsigned)T, 256, 0, current_stream()>>>(t, experts.data_ptr<int>(), dest_row.data_ptr<int>(),
-                                                                      scores.data_ptr<float>(), (bf16*)out.data_ptr(),
-                                                                      (int)hidden, K, (int)experts_per_rank);
+    PeerTable t = make_table(y_ptrs, y_byte_offset);
+    p2p_moe_combine_kernel<<<(unsigned)T, 256, 0, current_stream()>>>(t, experts.data_ptr<int>(), dest_row.data_ptr<int>(), sc,
+                                                                      (bf16*)out.data_ptr(), nullptr, nullptr, (int)hidden, K,
+                                                                      (int)experts_per_rank, (int)capacity);
     ATB_LAUNCH_CHECK();
     return out;
+}
+
+// pair_dot[t, k] = < dout[t], y_owner[dest_row[t, k]] > : the gradient of the combine weights.
+at::Tensor p2p_moe_pair_dot(const at::Tensor& y_ptrs, int64_t y_byte_offset, const at::Tensor& experts, const at::Tensor& dest_row,
+                            const at::Tensor& dout, int64_t experts_per_rank, int64_t capacity) {
+    ATB_CHECK_CUDA(dout); ATB_CHECK_CONTIG(dout); ATB_CHECK_DTYPE(dout, at::kBFloat16); ATB_CHECK_ALIGNED16(dout);
+    ATB_CHECK_DTYPE(experts, at::kInt); ATB_CHECK_DTYPE(dest_row, at::kInt); ATB_CHECK_CONTIG(experts); ATB_CHECK_CONTIG(dest_row);
+    const int64_t T = experts.size(0);
+    const int K = (int)experts.size(1);
+    const int H = (int)dout.size(1);
+    TORCH_CHECK(H % 8 == 0 && y_byte_offset % 16 == 0 && dout.size(0) == T, "moe pair_dot: shape mismatch");
+    c10::cuda::CUDAGuard guard(dout.device());
+    auto dots = at::zeros({T, K}, dout.options().dtype(at::kFloat));
+    if (T == 0) return dots;
+    PeerTable t = make_table(y_ptrs, y_byte_offset);
+    p2p_moe_combine_kernel<<<(unsigned)T, 256, 0, current_stream()>>>(t, experts.data_ptr<int>(), dest_row.data_ptr<int>(), nullptr,
+                                                                      nullptr, (const bf16*)dout.data_ptr(), dots.data_ptr<float>(),
+                                                                      H, K, (int)experts_per_rank, (int)capacity);
+    ATB_LAUNCH_CHECK();
+    return dots;
 }
 
 }  // namespace atb

@@ -136,6 +136,16 @@ class ArcticMoE(nn.Module):
         global-expert-major; the receiver regroups rank-major chunks into expert-major tile-aligned segments."""
         P, El, K = self.ep_size, self.num_local_experts, self.top_k
         T = x.shape[0]
+        if x.is_cuda and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and self.num_experts <= 1024:
+            from .peer import exchange_for
+            from .peer import peer_expert_forward
+
+            ex = exchange_for(self.ep_group)
+            if ex is not None:
+                return peer_expert_forward(
+                    x, scores, experts, self.num_experts, ex, SEGMENT_ALIGN,
+                    lambda tokens, seg: grouped_mlp(tokens, seg, self.expert_gate_up, self.expert_down),
+                ).to(x.dtype)
         slots, counts, _ = mops.assign_slots(experts, self.num_experts, 1)
         send = mops.scatter_rows(x, slots, T * K)
         # counts[src][e] for my local experts from every source rank

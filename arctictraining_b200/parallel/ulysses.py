@@ -110,30 +110,15 @@ class _PeerExchange:
     Q_SLOT, O_SLOT, DO_SLOT, DQ_SLOT = 8, 9, 10, 11
 
     def __init__(self, group) -> None:
+        from ..comm.symm import RotatingBuffers
         from ..comm.symm import SymmetricContext
 
         self.symm = SymmetricContext(group)
         self.rank, self.size = self.symm.rank, self.symm.world
-        self._bufs: Dict[str, Any] = {}
-        self._turn: Dict[str, int] = {}
+        self._rot = RotatingBuffers(self.symm)
 
     def _buffer(self, name: str, numel: int):
-        """Symmetric buffer ``name`` with room for two exchanges of ``numel`` elements; returns (buffer, byte offset
-        of the half to use now).  Grows collectively: every rank of the group sees the same shapes."""
-        numel = (numel + 127) // 128 * 128
-        buf = self._bufs.get(name)
-        if buf is None or buf.tensor.numel() < 2 * numel:
-            torch.cuda.synchronize()
-            buf = self.symm.alloc(f"ulysses_{name}_{2 * numel}", 2 * numel, torch.bfloat16)
-            self._bufs[name] = buf
-            self._turn[name] = 0
-        half = buf.tensor.numel() // 2
-        turn = self._turn[name]
-        self._turn[name] = turn ^ 1
-        return buf, turn * half
-
-    def _ptrs(self, buf) -> torch.Tensor:
-        return buf.ptrs
+        return self._rot.take("ulysses_" + name, numel)
 
     # ---- q, k, v: sequence-sharded -> head-sharded
     def qkv_seq_to_head(self, q, k, v):

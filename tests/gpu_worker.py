@@ -134,12 +134,57 @@ def scenario_ulysses_peer(out_dir):
         (Path(out_dir) / "ulysses_peer.json").write_text(json.dumps(allres))
 
 
+def scenario_moe_peer(out_dir):
+    """Expert-parallel MoE block: the peer-memory dispatch/combine gives the same output and gradients as the NCCL
+    all-to-all path."""
+    from arctictraining_b200.moe.layer import ArcticMoE
+    from arctictraining_b200.moe.layer import MoEConfig
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    res = {}
+    outs = []
+    for fused in (False, True):
+        os.environ["ATB200_FUSED_COMM"] = "1" if fused else "0"
+        import arctictraining_b200.moe.peer as peer
+
+        peer._EXCHANGES.clear()
+        torch.manual_seed(0)
+        mc = MoEConfig(model_dim=256, intermediate_dim=128, num_experts=8, top_k=2, normalize_topk_scores=True,
+                       loss_coeff=0.0, ep_size=world, ep_rank=rank, ep_group=dist.group.WORLD, input_dtype=torch.bfloat16)
+        moe = ArcticMoE(mc, dtype=torch.bfloat16, device="cuda")
+        g = torch.Generator(device="cuda").manual_seed(5)
+        for n, p in sorted(moe.named_parameters()):
+            full = torch.randn(p.shape if "expert" not in n else (8,) + tuple(p.shape[1:]), generator=g, device="cuda") * 0.05
+            p.data.copy_((full[rank * 4 : rank * 4 + 4] if "expert" in n else full).to(p.dtype))
+        torch.manual_seed(100 + rank)
+        x = torch.randn(1, 333, 256, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        gy = torch.randn(1, 333, 256, device="cuda", dtype=torch.bfloat16)
+        for _ in range(3):
+            x.grad = None
+            moe.zero_grad()
+            y = moe(x)
+            y.backward(gy)
+        if fused:
+            assert peer.exchange_for(dist.group.WORLD) is not None, "peer exchange did not come up"
+            peer.check_errors()
+        outs.append((y.detach().float(), x.grad.float(), moe.expert_down.grad.float(), moe.router_gate.grad.float()))
+
+    def rel(a, b):
+        return float((a - b).norm() / (b.norm() + 1e-12))
+
+    res = {k: rel(outs[1][i], outs[0][i]) for i, k in enumerate(["out", "dx", "dw_down", "d_router"])}
+    allres = [None] * world
+    dist.all_gather_object(allres, res)
+    if rank == 0:
+        (Path(out_dir) / "moe_peer.json").write_text(json.dumps(allres))
+
+
 def main():
     scenario, out_dir = sys.argv[1], sys.argv[2]
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     init_distributed(timeout_s=120)
     {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout,
-     "ulysses_peer": scenario_ulysses_peer}[scenario](out_dir)
+     "ulysses_peer": scenario_ulysses_peer, "moe_peer": scenario_moe_peer}[scenario](out_dir)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -91,7 +91,7 @@ def test_moe_dispatch_and_combine_through_peer_buffers(k):
         d, seg = k.moe_dest_rows(all_counts, experts[r], local[r][0], local[r][2], r, 128)
         dests.append(d)
         segs.append(seg)
-        k.p2p_moe_dispatch(xs[r], experts[r], d, ptrs(bufs), El)
+        k.p2p_moe_dispatch(xs[r], experts[r], d, ptrs(bufs), 0, El, rows, None)
     torch.cuda.synchronize()
     # owner-side check: segment of local expert e on rank o holds the rows of rank 0 first, then rank 1, in (token, k) order
     for o in range(P):
@@ -104,6 +104,17 @@ def test_moe_dispatch_and_combine_through_peer_buffers(k):
             assert torch.equal(got, want), (o, el)
     scores = [torch.rand(T, K, device="cuda") for _ in range(P)]
     for r in range(P):
-        out = k.p2p_moe_combine(ptrs(bufs), experts[r], dests[r], scores[r], H, El)
+        out = k.p2p_moe_combine(ptrs(bufs), 0, experts[r], dests[r], scores[r], H, El, rows)
         ref = xs[r].float() * scores[r].sum(-1, keepdim=True)
         assert (out.float() - ref).norm() / ref.norm() < 1e-2
+        # gradient of the combine weights: <dout[t], y[pair]> with y = the dispatched copy of x[t]
+        dout = torch.randn(T, H, device="cuda").bfloat16()
+        dots = k.p2p_moe_pair_dot(ptrs(bufs), 0, experts[r], dests[r], dout, El, rows)
+        want = (dout.float() * xs[r].float()).sum(-1, keepdim=True).expand(T, K)
+        assert torch.allclose(dots, want, atol=1e-2, rtol=1e-3)
+    # scaled dispatch (backward of the combine) and the capacity guard
+    k.comm_read_and_clear_error(xs[0])
+    k.p2p_moe_dispatch(xs[0], experts[0], dests[0], ptrs(bufs), 0, El, rows, scores[0])
+    assert int(k.comm_read_and_clear_error(xs[0])) == 0
+    k.p2p_moe_dispatch(xs[0], experts[0], dests[0], ptrs(bufs), 0, El, 8, None)  # capacity far too small: rows are skipped
+    assert int(k.comm_read_and_clear_error(xs[0])) >> 8 == 0x31

@@ -44,3 +44,10 @@ def test_peer_memory_ulysses_exchange_matches_nccl(tmp_path):
         assert per_rank["kv_split"]["out_diff"] == 0.0 and per_rank["kv_split"]["grad_diff"] == 0.0
         r = per_rank["kv_replicated"]
         assert r["out_diff"] == 0.0 and r["grad_diff"] <= 2e-2 * r["grad_scale"]
+
+
+def test_peer_memory_moe_exchange_matches_all_to_all(tmp_path):
+    launch(2, "moe_peer", tmp_path)
+    for per_rank in json.loads((tmp_path / "moe_peer.json").read_text()):
+        for name, err in per_rank.items():
+            assert err < 2e-2, (name, err)
