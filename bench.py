@@ -46,6 +46,8 @@ def parse_args():
                    help="layers that keep activations instead of recomputing them: a count, or auto (by free memory)")
     p.add_argument("--gemm", type=str, default=os.getenv("ATB200_GEMM", "tcgen05"), choices=["tcgen05", "cublas"])
     p.add_argument("--skip-e2e", action="store_true")
+    p.add_argument("--ep", type=int, default=1, help="expert-parallel size (mixture-of-experts models)")
+    p.add_argument("--sample-max", type=int, default=4096, help="longest synthetic sample that is packed")
     p.add_argument("--no-cta-pairs", action="store_true", help="use the single-CTA 128x256 GEMM tile instead of the CTA-pair kernel")
     return p.parse_args()
 
@@ -158,9 +160,11 @@ def main() -> None:
         "micro_batch_size": 1,
         "epochs": 1,
         "seed": 42,
+        "expert_parallel_size": args.ep,
+        "arctic_moe": "auto",
         "model": {"name_or_path": args.model, "dtype": "bf16", "attn_implementation": args.attn, "hf_config_kwargs": hf_kwargs},
         "data": {
-            "sources": [{"type": "synthetic", "num_samples": rows_needed * 4, "min_length": 256, "max_length": 4096,
+            "sources": [{"type": "synthetic", "num_samples": rows_needed * 4, "min_length": 256, "max_length": min(args.sample_max, args.seq_len),
                          "prompt_fraction": 0.5, "seed": 1234}],
             "cache_dir": str(workdir / "cache"),
             "max_length": args.seq_len,
@@ -250,7 +254,7 @@ def main() -> None:
         value = tokens_per_step / (ms_per_step / 1e3)
         cfg = trainer.model_unwrapped.config
         result = {
-            "metric": METRIC,
+            "metric": METRIC if args.model == "llama-3.1-8b" else args.model.replace("-", "_").replace(".", "_") + "_sft_tokens_per_s",
             "value": round(value, 1),
             "unit": "tokens/s",
             "n_gpus": world,
@@ -268,7 +272,7 @@ def main() -> None:
                 "layers": cfg["num_hidden_layers"],
                 "global_batch": world,
                 "seq_len": args.seq_len,
-                "parallelism": f"zero{args.zero_stage}-dp{world}",
+                "parallelism": f"zero{args.zero_stage}-dp{world}" + (f"-ep{args.ep}" if args.ep > 1 else ""),
                 "optimizer": "adamw fp32 master",
                 "activation_checkpointing": True,
                 "layers_keeping_activations": (engine._keep_state.get("kept_layers", 0) if args.keep == "auto"
