@@ -35,9 +35,11 @@ constexpr int SMEM_Q = 0;
 constexpr int SMEM_KV = TILE_BYTES;                              // stage s: K at +s*2*TILE, V right after K
 constexpr int SMEM_P = SMEM_KV + KV_STAGES * 2 * TILE_BYTES;
 constexpr int SMEM_BAR = SMEM_P + TILE_BYTES;
-constexpr int SMEM_TOTAL = SMEM_BAR + 16 * 8 + 16;
+constexpr int SMEM_XCHG = SMEM_BAR + 16 * 8 + 16;       // float [2 parities][2 halves][128 rows]
+constexpr int SMEM_TOTAL = SMEM_XCHG + 2 * 2 * 128 * 4;
 constexpr uint64_t kAttnWaitNs = 2000000000ull;
 constexpr float kRescaleThreshold = 8.f;  // in log2 units
+constexpr int kAttnThreads = 320;        // TMA warp, MMA warp, eight softmax warps (two per TMEM lane quarter)
 
 struct AttnParams {
     bf16* O;
@@ -49,7 +51,51 @@ struct AttnParams {
     int* error_flag;
 };
 
-__global__ void __launch_bounds__(192, 1)
+// Maximum over 64 score columns of one row in TMEM (raw, unscaled scores); columns >= klimit are ignored when MASK.
+// `col0` is the first of the 64 columns inside the 128-key block.
+template <bool MASK>
+__device__ __forceinline__ float score_row_max(uint32_t s_addr, int col0, int klimit) {
+    uint32_t a[32], b[32];
+    ptx::tmem_ld_32x32b_x32(s_addr, a);
+    ptx::tmem_ld_32x32b_x32(s_addr + 32, b);
+    ptx::tmem_ld_wait();
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+        if (!MASK || col0 + i < klimit) m0 = fmaxf(m0, __uint_as_float(a[i]));
+        if (!MASK || col0 + 32 + i < klimit) m1 = fmaxf(m1, __uint_as_float(b[i]));
+    }
+    return fmaxf(m0, m1);
+}
+
+// p = exp2(s * scale - m) for 64 columns of one row: bf16 into one 64-key chunk of the swizzled P tile (row `crow`,
+// swizzle phase r & 7); returns the sum of the 64 probabilities.
+template <bool MASK>
+__device__ __forceinline__ float score_row_exp(uint32_t s_addr, int col0, int klimit, float scale, float m, uint8_t* crow,
+                                               int r) {
+    uint32_t a[32], b[32];
+    ptx::tmem_ld_32x32b_x32(s_addr, a);
+    ptx::tmem_ld_32x32b_x32(s_addr + 32, b);
+    ptx::tmem_ld_wait();
+    float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {  // eight 16-byte units of 8 probabilities
+        float f8[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+            const int col = u * 8 + i;  // 0..63 inside the chunk
+            const float sv = __uint_as_float(col < 32 ? a[col & 31] : b[col & 31]);
+            float e = exp2f(fmaf(sv, scale, -m));
+            if (MASK && col0 + col >= klimit) e = 0.f;
+            f8[i] = e;
+            if (i & 1) l1 += e; else l0 += e;
+        }
+        *reinterpret_cast<bf16x8*>(crow + ((u ^ (r & 7)) << 4)) = pack8(f8);
+    }
+    return l0 + l1;
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 1)
 fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -62,6 +108,8 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     uint64_t* s_empty = bars + 7;       // [2]
     uint64_t* p_full = bars + 9;        // 1
     uint64_t* pv_done = bars + 10;      // 1
+    uint64_t* max_ready = bars + 11;    // [2]: both column halves have published their row maxima
+    float* xchg = reinterpret_cast<float*>(smem + SMEM_XCHG);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
@@ -87,9 +135,10 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             ptx::mbar_init(&kv_full[i], 1);
             ptx::mbar_init(&kv_empty[i], 1);
             ptx::mbar_init(&s_full[i], 1);
-            ptx::mbar_init(&s_empty[i], 4);
+            ptx::mbar_init(&s_empty[i], 8);
+            ptx::mbar_init(&max_ready[i], 8);
         }
-        ptx::mbar_init(p_full, 4);
+        ptx::mbar_init(p_full, 8);
         ptx::mbar_init(pv_done, 1);
         *abort_flag = 0;
         ptx::fence_barrier_init();
@@ -169,32 +218,34 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         }
     } else {
         // ------------------------------------------------------------------ softmax / correction / epilogue
+        // Two warps share each TMEM lane quarter: for the same 32 query rows one takes key columns 0..63 of every block
+        // (and head-dim columns 0..63 of O), the other the upper halves.  They agree on the row maximum through shared
+        // memory once per block; the row sums are combined at the end.
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
         const int r = quarter * 32 + lane;          // row of the query block owned by this thread
         const int qidx = qb * BQ + r;               // position inside the sequence
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        uint8_t* prow = smem + SMEM_P + r * 128;    // row r of both P chunks (chunk stride CHUNK_BYTES)
+        const int col0 = half * 64;
+        uint8_t* crow = smem + SMEM_P + half * CHUNK_BYTES + r * 128;  // row r of this half's 64-key chunk of P
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
             const int st = j & 1;
             if (!ptx::mbar_wait_bounded(&s_full[st], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
             ptx::tc_fence_after();
-            const uint32_t s_addr = tmem_base + lane_addr + st * 128;
+            const uint32_t s_addr = tmem_base + lane_addr + st * 128 + col0;
             const int kbase = j * BKV;
             const int klimit = min(seqlen, qidx + 1) - kbase;  // columns c < klimit are visible to this row
-            // pass 1: row maximum of the (scaled) scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(s_addr + c * 32, v);
-                ptx::tmem_ld_wait();
-#pragma unroll
-                for (int i = 0; i < 32; ++i)
-                    if (c * 32 + i < klimit) mx = fmaxf(mx, __uint_as_float(v[i]));
-            }
-            mx *= p.scale_log2;
+            // only the diagonal block and the block that holds the end of the sequence need masking (uniform per CTA)
+            const bool need_mask = kbase + BKV > min(seqlen, qb * BQ + 1);
+            // pass 1: row maximum of the scores, agreed between the two halves
+            float mx = need_mask ? score_row_max<true>(s_addr, col0, klimit) : score_row_max<false>(s_addr, col0, klimit);
+            xchg[(st * 2 + half) * 128 + r] = mx;
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&max_ready[st]);
+            if (!ptx::mbar_wait_bounded(&max_ready[st], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+            mx = fmaxf(mx, xchg[(st * 2 + (half ^ 1)) * 128 + r]) * p.scale_log2;
             // previous P V must have retired before P is overwritten or O is touched
             if (j > 0 && !ptx::mbar_wait_bounded(pv_done, (j - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
             ptx::tc_fence_after();
@@ -204,13 +255,13 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                 const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
                 if (j > 0) {
 #pragma unroll 1
-                    for (int c = 0; c < 4; ++c) {
+                    for (int c = 0; c < 2; ++c) {
                         uint32_t v[32];
-                        ptx::tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+                        ptx::tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, v);
                         ptx::tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        ptx::tmem_st_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+                        ptx::tmem_st_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, v);
                     }
                     ptx::tmem_st_wait();
                 }
@@ -218,28 +269,8 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                 m_used = m_new;
             }
             // pass 2: probabilities -> bf16 -> swizzled shared memory; running sum
-#pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(s_addr + c * 32, v);
-                ptx::tmem_ld_wait();
-                float pr[32];
-#pragma unroll
-                for (int i = 0; i < 32; ++i) {
-                    const float e = (c * 32 + i < klimit) ? exp2f(__uint_as_float(v[i]) * p.scale_log2 - m_used) : 0.f;
-                    pr[i] = e;
-                    l += e;
-                }
-#pragma unroll
-                for (int u = 0; u < 4; ++u) {  // four 16-byte units of 8 probabilities
-                    float f8[8];
-#pragma unroll
-                    for (int i = 0; i < 8; ++i) f8[i] = pr[u * 8 + i];
-                    const int unit = (c * 32 + u * 8) >> 3;          // 0..15 along the key dimension
-                    const int chunk = unit >> 3, in_row = unit & 7;  // two chunks of 64 keys
-                    *reinterpret_cast<bf16x8*>(prow + chunk * CHUNK_BYTES + ((in_row ^ (r & 7)) << 4)) = pack8(f8);
-                }
-            }
+            l += need_mask ? score_row_exp<true>(s_addr, col0, klimit, p.scale_log2, m_used, crow, r)
+                           : score_row_exp<false>(s_addr, col0, klimit, p.scale_log2, m_used, crow, r);
             ptx::tc_fence_before();
             ptx::fence_proxy_async_smem();  // generic-proxy writes of P become visible to the tensor core
             __syncwarp();
@@ -249,17 +280,26 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             }
         }
         if (ok && !ptx::mbar_wait_bounded(pv_done, (n_kv - 1) & 1, abort_flag, kAttnWaitNs)) ok = false;
+        if (ok) {
+            // combine the row sums of the two halves (both used the same maxima); parity slot of a block not in use
+            const int st = n_kv & 1;
+            xchg[(st * 2 + half) * 128 + r] = l;
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&max_ready[st]);
+            if (!ptx::mbar_wait_bounded(&max_ready[st], (n_kv >> 1) & 1, abort_flag, kAttnWaitNs)) ok = false;
+            else l += xchg[(st * 2 + (half ^ 1)) * 128 + r];
+        }
         if (!ok) {
             if (lane == 0) atomicCAS(p.error_flag, 0, (0x23 << 8) | 1);
         } else {
             ptx::tc_fence_after();
             const float inv_l = 1.f / l;
             const bool valid = qidx < seqlen;
-            bf16* orow = p.O + (int64_t)(tok0 + qidx) * p.o_row_stride + (int64_t)h * HD;
+            bf16* orow = p.O + (int64_t)(tok0 + qidx) * p.o_row_stride + (int64_t)h * HD + col0;
 #pragma unroll 1
-            for (int c = 0; c < 4; ++c) {
+            for (int c = 0; c < 2; ++c) {
                 uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(tmem_o + lane_addr + c * 32, v);
+                ptx::tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, v);
                 ptx::tmem_ld_wait();
                 if (valid) {
 #pragma unroll
@@ -271,7 +311,7 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                     }
                 }
             }
-            if (valid) p.lse[(int64_t)h * p.T + tok0 + qidx] = (m_used + log2f(l)) * 0.6931471805599453f;
+            if (valid && half == 0) p.lse[(int64_t)h * p.T + tok0 + qidx] = (m_used + log2f(l)) * 0.6931471805599453f;
         }
     }
 
@@ -325,7 +365,7 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
         attr_set = true;
     }
     dim3 grid((unsigned)max_blocks, (unsigned)Hq);
-    fmha_fwd_tcgen05_kernel<<<grid, 192, smem_bytes, current_stream()>>>(tq, tk, tv, p);
+    fmha_fwd_tcgen05_kernel<<<grid, kAttnThreads, smem_bytes, current_stream()>>>(tq, tk, tv, p);
     ATB_LAUNCH_CHECK();
     return {out, lse};
 }

@@ -59,6 +59,17 @@ struct GemmParams {
     const int* group_offsets;
     int num_groups;
     int group_mode;
+    // A operand assembled from several tensors along K (CTA-pair kernel, K-major A): k in [j * a_seg_len, (j + 1) *
+    // a_seg_len) comes from tensor map j of `SegMaps`, rows a_seg_row0 + m.  0 = A is the single tensor of tmap_a.
+    int a_seg_len;
+    int a_seg_row0;
+};
+
+constexpr int kMaxSegs = 8;
+// Tensor maps of the K segments of A.  They may describe other GPUs' memory (peer mappings): the loads are plain
+// per-CTA-pair TMA tile loads, each tile is fetched by the one pair that needs it.
+struct SegMaps {
+    CUtensorMap m[kMaxSegs];
 };
 
 // What one output tile reads and writes.
@@ -370,7 +381,7 @@ struct PairSmemLayout {
 template <int STAGES, bool A_MN, bool B_MN, int EPI>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(192, 1)
 gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
-                              const GemmParams p) {
+                              const GemmParams p, const __grid_constant__ SegMaps segs) {
     using L = PairSmemLayout<STAGES>;
     constexpr int TM = 256, TN = 256;  // tile of the pair
     extern __shared__ __align__(1024) uint8_t smem_raw[];
@@ -449,7 +460,13 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                     uint8_t* sb = sa + L::kABytes;
                     ptx::mbar_expect_tx_cluster(ptx::mapa_shared(ptx::smem_u32(&full_bar[stage]), 0), L::kStageBytes);
                     if constexpr (!A_MN) {
-                        ptx::tma_load_2d_pair(sa, &tmap_a, kb * BK, a_m0, &full_bar[stage]);
+                        if (p.a_seg_len > 0) {
+                            const int seg = (kb * BK) / p.a_seg_len;
+                            ptx::tma_load_2d_pair(sa, &segs.m[seg], kb * BK - seg * p.a_seg_len, p.a_seg_row0 + a_m0,
+                                                  &full_bar[stage]);
+                        } else {
+                            ptx::tma_load_2d_pair(sa, &tmap_a, kb * BK, a_m0, &full_bar[stage]);
+                        }
                     } else {
 #pragma unroll
                         for (int c = 0; c < 2; ++c)
@@ -661,8 +678,11 @@ void launch_gemm(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams&
     ATB_LAUNCH_CHECK();
 }
 
+static const SegMaps kNoSegs = {};
+
 template <int STAGES, bool A_MN, bool B_MN, int EPI>
-void launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas) {
+void launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas,
+                      const SegMaps& segs = kNoSegs) {
     using L = PairSmemLayout<STAGES>;
     auto kernel = gemm_bf16_tcgen05_pair_kernel<STAGES, A_MN, B_MN, EPI>;
     constexpr int smem_bytes = L::kTotal + 1024;
@@ -688,7 +708,7 @@ void launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
     }
     const int tiles = (int)(ceil_div(p.M, 256) * ceil_div(p.N, 256));
     const int clusters = std::max(1, std::min(tiles, std::min(max_ctas / 2, max_clusters)));
-    kernel<<<2 * clusters, 192, smem_bytes, current_stream()>>>(ta, tb, p);
+    kernel<<<2 * clusters, 192, smem_bytes, current_stream()>>>(ta, tb, p, segs);
     ATB_LAUNCH_CHECK();
 }
 
@@ -773,6 +793,8 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     p.ldc = out.stride(0);
     p.R = residual.has_value() ? (const bf16*)residual->data_ptr() : p.C;
     p.ldr = residual.has_value() ? residual->stride(0) : p.ldc;
+    p.a_seg_len = 0;
+    p.a_seg_row0 = 0;
     p.error_flag = error_flag_for(a.device()).data_ptr<int>();
     p.group_offsets = nullptr;
     p.num_groups = 0;
@@ -845,6 +867,8 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
         p.ldc = out.stride(0);
         p.R = p.C;
         p.ldr = p.ldc;
+        p.a_seg_len = 0;
+        p.a_seg_row0 = 0;
         if (!b_mn) dispatch_epi<false, false>(epi, ta, tb, p, kNumSMs);
         else dispatch_epi<false, true>(epi, ta, tb, p, kNumSMs);
     } else if (mode == GROUP_RAGGED_K) {
@@ -866,6 +890,8 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
         p.ldc = out.stride(0);
         p.R = p.C;
         p.ldr = p.ldc;
+        p.a_seg_len = 0;
+        p.a_seg_row0 = 0;
         dispatch_epi<true, true>(epi, ta, tb, p, kNumSMs);
     } else {
         TORCH_CHECK(false, "grouped gemm: mode must be 1 (ragged M) or 2 (ragged K)");
@@ -875,6 +901,54 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
 }
 
 // Selects the CTA-pair (cta_group::2, 256 x 256 tile) kernel for dense GEMMs; returns the previous setting.
+// out = A b^T (+ residual) where A [M, P * seg_cols] is never materialised: its K segment j is rows
+// [row0, row0 + M) of the [rows_total, seg_cols] bf16 tensor at a_ptrs[j] + a_byte_offset, which may be another GPU's
+// memory mapped into this process (the head-sharded attention outputs of the Ulysses peers: the head -> sequence
+// all-to-all happens inside the GEMM's operand fetch).  b is [N, P * seg_cols].
+at::Tensor gemm_bf16_peer_a(const at::Tensor& a_ptrs, int64_t a_byte_offset, int64_t rows_total, int64_t seg_cols,
+                            int64_t row0, int64_t M, const at::Tensor& b, const c10::optional<at::Tensor>& residual) {
+    ATB_CHECK_CUDA(b); ATB_CHECK_DTYPE(b, at::kBFloat16);
+    TORCH_CHECK(a_ptrs.device().is_cpu() && a_ptrs.scalar_type() == at::kLong, "peer pointers: int64 CPU tensor");
+    const int P = (int)a_ptrs.numel();
+    TORCH_CHECK(P >= 1 && P <= kMaxSegs, "gemm_peer_a: 1..8 segments");
+    TORCH_CHECK(seg_cols % BK == 0 && a_byte_offset % 16 == 0, "gemm_peer_a: segment width must be a multiple of 64");
+    TORCH_CHECK(b.dim() == 2 && b.stride(1) == 1 && b.size(1) == P * seg_cols && b.stride(0) % 8 == 0, "gemm_peer_a: b must be [N, P * seg_cols]");
+    TORCH_CHECK(M > 0 && row0 >= 0 && row0 + M <= rows_total && M < (1ll << 31), "gemm_peer_a: row range outside the segment tensors");
+    const int64_t N = b.size(0), K = P * seg_cols;
+    TORCH_CHECK(N % 8 == 0, "gemm_peer_a: N must be a multiple of 8");
+    c10::cuda::CUDAGuard guard(b.device());
+    auto out = at::empty({M, N}, b.options());
+    SegMaps segs = {};
+    for (int j = 0; j < P; ++j)
+        segs.m[j] = make_tmap_bf16(reinterpret_cast<void*>(a_ptrs.data_ptr<int64_t>()[j] + a_byte_offset), rows_total, seg_cols,
+                                   seg_cols, 128);
+    const CUtensorMap tb = make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), 128);
+    GemmParams p;
+    p.C = (bf16*)out.data_ptr();
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.ldc = out.stride(0);
+    p.R = p.C;
+    p.ldr = p.ldc;
+    int epi = EPI_STORE;
+    if (residual.has_value()) {
+        ATB_CHECK_DTYPE(*residual, at::kBFloat16); ATB_CHECK_ALIGNED16(*residual);
+        TORCH_CHECK(residual->dim() == 2 && residual->size(0) == M && residual->size(1) == N && residual->stride(1) == 1 &&
+                    residual->stride(0) % 8 == 0, "gemm_peer_a: residual has the wrong shape");
+        p.R = (const bf16*)residual->data_ptr();
+        p.ldr = residual->stride(0);
+        epi = EPI_ACCUM;
+    }
+    p.error_flag = error_flag_for(b.device()).data_ptr<int>();
+    p.group_offsets = nullptr;
+    p.num_groups = 0;
+    p.group_mode = GROUP_NONE;
+    p.a_seg_len = (int)seg_cols;
+    p.a_seg_row0 = (int)row0;
+    if (epi == EPI_STORE) launch_gemm_pair<6, false, false, EPI_STORE>(segs.m[0], tb, p, kNumSMs, segs);
+    else launch_gemm_pair<6, false, false, EPI_ACCUM>(segs.m[0], tb, p, kNumSMs, segs);
+    return out;
+}
+
 bool set_gemm_cta_pairs(bool on) {
     const bool old = g_use_cta_pairs;
     g_use_cta_pairs = on;

@@ -105,6 +105,10 @@ class Attention(nn.Module):
     def forward(self, x: torch.Tensor, ctx: ForwardContext, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, S, _ = x.shape
         q, k, v = self.project_qkv(x, ctx)
+        if ctx.sp is not None and type(self.o_proj) is Linear and self.o_proj.bias is None and hasattr(ctx.sp, "attention_project"):
+            fused = ctx.sp.attention_project(q, k, v, ctx, self.o_proj.weight, residual)
+            if fused is not None:
+                return fused
         o = self.core(q, k, v, ctx)
         return _project_with_residual(self.o_proj, o.reshape(B, S, self.hq * self.d), residual)
 

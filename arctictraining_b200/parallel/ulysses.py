@@ -107,7 +107,7 @@ class _PeerExchange:
     every peer has queued, in stream order, its copy out of the buffer of exchange n.  The received data is copied
     out of the symmetric buffer at once, so nothing that autograd saves points into memory peers write to."""
 
-    Q_SLOT, O_SLOT, DO_SLOT, DQ_SLOT = 8, 9, 10, 11
+    Q_SLOT, O_SLOT, DO_SLOT, DQ_SLOT, OP_SLOT = 8, 9, 10, 11, 12
 
     def __init__(self, group) -> None:
         from ..comm.symm import RotatingBuffers
@@ -146,6 +146,20 @@ class _PeerExchange:
         ops._ext.ops().p2p_seq_to_head(y, buf.ptrs, self.rank, True, off * 2)
         self.symm.barrier(self.O_SLOT)
         return buf.tensor[off : off + S * Hl * D].view(S // P, Hl * P, D).clone()
+
+    def head_to_seq_project(self, y, weight, residual):
+        """``[residual +] head_to_seq(y) @ weight.T`` without materialising the exchanged activations: every rank
+        publishes its head-sharded attention output, and the projection GEMM fetches each K slice of its A operand
+        (one head group per peer) straight from the owner's memory with TMA tile loads."""
+        S, Hl, D = y.shape
+        P = self.size
+        buf, off = self._buffer("o_src", S * Hl * D)
+        buf.tensor[off : off + S * Hl * D].view(S, Hl, D).copy_(y)
+        self.symm.barrier(self.OP_SLOT)
+        ops.functional._count()
+        return ops._ext.ops().gemm_bf16_peer_a(
+            buf.ptrs, off * 2, S, Hl * D, self.rank * (S // P), S // P, weight, residual
+        )
 
     def seq_to_head(self, x, slot_name: str = "do"):
         S_loc, H, D = x.shape
@@ -225,6 +239,30 @@ class UlyssesContext:
         vf = _SeqToHead.apply(v.contiguous(), self.group)
         o = ops.attention(qf, kf, vf, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
         return _HeadToSeq.apply(o.contiguous(), self.group)
+
+    def attention_project(self, q, k, v, ctx: Any, w_out: torch.Tensor, residual: Optional[torch.Tensor]):
+        """Attention followed by the output projection with the head -> sequence exchange folded into the projection
+        GEMM's operand fetch.  Forward only (no autograd graph); returns ``None`` when the fused path does not apply
+        so that the caller can fall back to :meth:`attention` plus a linear layer."""
+        P = self.size
+        Hq, Hkv, D = q.shape[2], k.shape[2], q.shape[-1]
+        if torch.is_grad_enabled() or P > 8 or Hq % P or (Hq // P * D) % 64 or w_out.dtype != torch.bfloat16:
+            return None
+        if not ((Hkv % P == 0 or P % Hkv == 0) and D % 8 == 0) or w_out.shape[0] % 8 or not w_out.is_contiguous():
+            return None
+        ex = self._peer_exchange(q)
+        if ex is None:
+            return None
+        Hlq, Hlkv = Hq // P, (Hkv // P if Hkv >= P else 1)
+        qkv = ex.qkv_seq_to_head(_dense_heads(q[0]), _dense_heads(k[0]), _dense_heads(v[0]))
+        qf, kf, vf = qkv[None, :, :Hlq], qkv[None, :, Hlq : Hlq + Hlkv], qkv[None, :, Hlq + Hlkv :]
+        o = ops.attention(qf, kf, vf, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
+        res2 = None
+        if residual is not None:
+            if residual.dtype != torch.bfloat16 or not residual.is_contiguous():
+                return ex.head_to_seq_project(o[0].contiguous(), w_out, None)[None] + residual
+            res2 = residual.view(-1, residual.shape[-1])
+        return ex.head_to_seq_project(o[0].contiguous(), w_out, res2)[None]
 
     # -- packed-sample boundaries -------------------------------------------------------------------
     def global_cu_seqlens(self, position_ids: torch.Tensor) -> Tuple[Optional[torch.Tensor], int]:

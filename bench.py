@@ -46,6 +46,9 @@ def parse_args():
                    help="layers that keep activations instead of recomputing them: a count, or auto (by free memory)")
     p.add_argument("--gemm", type=str, default=os.getenv("ATB200_GEMM", "tcgen05"), choices=["tcgen05", "cublas"])
     p.add_argument("--skip-e2e", action="store_true")
+    p.add_argument("--torch-profile", type=str, default=None,
+                   help="write a torch.profiler kernel table of the timed steps of rank 0 to this file (the number "
+                        "printed by such a run is not a benchmark value)")
     p.add_argument("--ep", type=int, default=1, help="expert-parallel size (mixture-of-experts models)")
     p.add_argument("--sample-max", type=int, default=4096, help="longest synthetic sample that is packed")
     p.add_argument("--no-cta-pairs", action="store_true", help="use the single-CTA 128x256 GEMM tile instead of the CTA-pair kernel")
@@ -216,10 +219,21 @@ def main() -> None:
         sampler.start()
     launches0 = ops.LAUNCH_COUNTER["native"]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    prof = None
+    if args.torch_profile and rank == 0:
+        from torch.profiler import ProfilerActivity
+        from torch.profiler import profile
+
+        prof = profile(activities=[ProfilerActivity.CPU, ProfilerActivity.CUDA])
+        prof.__enter__()
     start.record()
     for b in dev_batches[args.warmup :]:
         loss = device_step(b)
     end.record()
+    if prof is not None:
+        torch.cuda.synchronize()
+        prof.__exit__(None, None, None)
+        Path(args.torch_profile).write_text(prof.key_averages().table(sort_by="cuda_time_total", row_limit=60, max_name_column_width=90))
     barrier()
     ms = start.elapsed_time(end)
     launches = ops.LAUNCH_COUNTER["native"] - launches0

@@ -123,6 +123,16 @@ def scenario_ulysses_peer(out_dir):
             if fused:
                 sp._peer.symm.check()
             outs.append((o.detach().float(), x.grad.float()))
+        # forward-only path with the exchange folded into the output projection GEMM
+        w = (torch.randn(384, Hq * D, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3)) * 0.05).bfloat16()
+        resid = torch.randn(1, S_loc, 384, device="cuda", dtype=torch.bfloat16)
+        with torch.no_grad():
+            fused = sp.attention_project(q, k, v, fctx, w, resid)
+            plain = resid + torch.nn.functional.linear(sp.attention(q, k, v, fctx).reshape(1, S_loc, Hq * D), w)
+        assert fused is not None, "fused projection path did not apply"
+        sp._peer.symm.check()
+        proj_err = float((fused.float() - plain.float()).norm() / plain.float().norm())
+        res[name + "_proj_err"] = proj_err
         res[name] = {
             "out_diff": float((outs[0][0] - outs[1][0]).abs().max()),
             "grad_diff": float((outs[0][1] - outs[1][1]).abs().max()),

@@ -44,6 +44,7 @@ def test_peer_memory_ulysses_exchange_matches_nccl(tmp_path):
         assert per_rank["kv_split"]["out_diff"] == 0.0 and per_rank["kv_split"]["grad_diff"] == 0.0
         r = per_rank["kv_replicated"]
         assert r["out_diff"] == 0.0 and r["grad_diff"] <= 2e-2 * r["grad_scale"]
+        assert per_rank["kv_split_proj_err"] < 1e-2 and per_rank["kv_replicated_proj_err"] < 1e-2
 
 
 def test_peer_memory_moe_exchange_matches_all_to_all(tmp_path):
