@@ -63,6 +63,16 @@ struct GemmParams {
     // a_seg_len) comes from tensor map j of `SegMaps`, rows a_seg_row0 + m.  0 = A is the single tensor of tmap_a.
     int a_seg_len;
     int a_seg_row0;
+    // Staged gather of A (CTA-pair kernel): the last `stage_ctas` CTAs of the grid do not compute; they copy the K
+    // segments of A from `stage_src[j]` (peer memory) into the local matrix that tmap_a describes and count finished
+    // segments per 256-row tile in `stage_flags`; a computing pair starts a tile once its rows have all arrived.
+    int stage_ctas;
+    int stage_segs;
+    const bf16* stage_src[8];
+    int64_t stage_src_ld;
+    bf16* stage_dst;
+    int64_t stage_dst_ld;
+    int* stage_flags;
 };
 
 constexpr int kMaxSegs = 8;
@@ -426,7 +436,8 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
     const int tiles_n = (p.N + TN - 1) / TN;
     const int num_tiles = tiles_m * tiles_n;
     const int k_blocks = (p.K + BK - 1) / BK;
-    const int cluster_id = blockIdx.x >> 1, num_clusters = gridDim.x >> 1;
+    const int cluster_id = blockIdx.x >> 1, num_clusters = (gridDim.x - p.stage_ctas) >> 1;
+    const bool is_stager = cluster_id >= num_clusters;
     constexpr int GROUP_M = 8;
     auto tile_coords = [&](int t, int& tm, int& tn) {
         const int per_group = GROUP_M * tiles_n;
@@ -438,7 +449,65 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         tn = r / gsz;
     };
 
-    if (warp == 0) {
+    if (is_stager) {
+        // ------------------------------------------------------------------ gather of A from the peers
+        // One thread streams the segments through this CTA's (otherwise idle) tile buffers with bulk copies: a chunk of
+        // rows is contiguous at the owner, lands in shared memory, and is written row by row into the local matrix.
+        // Several chunks are in flight; the only waits are on this CTA's own copies (bounded).
+        if (threadIdx.x == 0) {
+            constexpr int NBUF = STAGES < 6 ? STAGES : 6;
+            constexpr uint32_t BUF_BYTES = 32768;
+            const int sidx = (int)blockIdx.x - 2 * num_clusters;
+            const int P = p.stage_segs;
+            const uint32_t seg_bytes = (uint32_t)p.a_seg_len * 2;
+            const int rows_per_chunk = max(1, (int)(BUF_BYTES / seg_bytes));
+            uint32_t ph[NBUF];
+            for (int i = 0; i < NBUF; ++i) ph[i] = 0;
+            bool ok = true;
+            for (int item = sidx; item < tiles_m * P && ok; item += p.stage_ctas) {
+                const int mt = item / P;
+                const int j = (item - mt * P + mt) % P;  // consecutive tiles start at different peers
+                const int r0 = mt * TM, nrows = min(TM, p.M - r0);
+                const uint8_t* src = reinterpret_cast<const uint8_t*>(p.stage_src[j] + (int64_t)(p.a_seg_row0 + r0) * p.stage_src_ld);
+                bf16* dst = p.stage_dst + (int64_t)r0 * p.stage_dst_ld + (int64_t)j * p.a_seg_len;
+                const int nchunks = (nrows + rows_per_chunk - 1) / rows_per_chunk;
+                // software pipeline: loads run LEAD chunks ahead of the stores; one bulk group is committed per step
+                constexpr int LEAD = NBUF / 2;
+                for (int c = 0; c < nchunks + LEAD && ok; ++c) {
+                    if (c < nchunks) {
+                        const int b = c % NBUF;
+                        // buffer b was last read by the stores of chunk c - NBUF, committed at step c - NBUF + LEAD:
+                        // NBUF - LEAD - 1 groups have been committed since
+                        ptx::bulk_wait_read<NBUF - LEAD - 1>();
+                        const int rows = min(rows_per_chunk, nrows - c * rows_per_chunk);
+                        const uint32_t bytes = (uint32_t)rows * seg_bytes;
+                        ptx::mbar_expect_tx(&empty_bar[b], bytes);
+                        ptx::bulk_load(smem + b * BUF_BYTES, src + (int64_t)c * rows_per_chunk * seg_bytes, bytes, &empty_bar[b]);
+                    }
+                    const int d = c - LEAD;
+                    if (d >= 0) {
+                        const int b = d % NBUF;
+                        if (!ptx::mbar_wait_bounded(&empty_bar[b], ph[b], abort_flag, kWaitLimitNs)) {
+                            atomicCAS(p.error_flag, 0, (0x15 << 8) | 1);
+                            ok = false;
+                            break;
+                        }
+                        ph[b] ^= 1u;
+                        const int rows = min(rows_per_chunk, nrows - d * rows_per_chunk);
+                        for (int rr = 0; rr < rows; ++rr)
+                            ptx::bulk_store(dst + (int64_t)(d * rows_per_chunk + rr) * p.stage_dst_ld,
+                                            smem + b * BUF_BYTES + rr * seg_bytes, seg_bytes);
+                    }
+                    ptx::bulk_commit();  // one group per step (possibly empty) keeps the wait arithmetic uniform
+                }
+                ptx::bulk_wait<0>();      // the rows of this item are written
+                ptx::fence_proxy_async_all();
+                __threadfence();
+                atomicAdd(&p.stage_flags[mt], 1);
+            }
+            ptx::bulk_wait<0>();
+        }
+    } else if (warp == 0) {
         // ------------------------------------------------------------------ TMA producer (in both CTAs)
         if (lane == 0) {
             ptx::tma_prefetch_desc(&tmap_a);
@@ -450,6 +519,20 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                 int tm, tn;
                 tile_coords(t, tm, tn);
                 const int a_m0 = tm * TM + (int)cta * 128, b_n0 = tn * TN + (int)cta * 128;
+                if (p.stage_ctas > 0) {
+                    // rows of this tile are being gathered by the staging CTAs: wait (bounded) until all segments landed
+                    const uint64_t t0 = ptx::globaltimer_ns();
+                    while (ptx::ld_acquire_gpu(reinterpret_cast<const uint32_t*>(p.stage_flags) + tm) < (uint32_t)p.stage_segs) {
+                        if (*abort_flag || ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
+                            *abort_flag = 1;
+                            atomicCAS(p.error_flag, 0, (0x14 << 8) | 1);
+                            ok = false;
+                            break;
+                        }
+                    }
+                    if (!ok) break;
+                    ptx::fence_proxy_async_all();  // the gathered rows were written with ordinary stores; TMA reads them next
+                }
                 for (int kb = 0; kb < k_blocks; ++kb) {
                     if (!ptx::mbar_wait_bounded(&empty_bar[stage], phase ^ 1u, abort_flag, kWaitLimitNs)) {
                         atomicCAS(p.error_flag, 0, (0x11 << 8) | 1);
@@ -460,7 +543,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                     uint8_t* sb = sa + L::kABytes;
                     ptx::mbar_expect_tx_cluster(ptx::mapa_shared(ptx::smem_u32(&full_bar[stage]), 0), L::kStageBytes);
                     if constexpr (!A_MN) {
-                        if (p.a_seg_len > 0) {
+                        if (p.a_seg_len > 0 && p.stage_ctas == 0) {
                             const int seg = (kb * BK) / p.a_seg_len;
                             ptx::tma_load_2d_pair(sa, &segs.m[seg], kb * BK - seg * p.a_seg_len, p.a_seg_row0 + a_m0,
                                                   &full_bar[stage]);
@@ -707,8 +790,10 @@ void launch_gemm_pair(const CUtensorMap& ta, const CUtensorMap& tb, const GemmPa
         max_clusters = std::max(1, n);
     }
     const int tiles = (int)(ceil_div(p.M, 256) * ceil_div(p.N, 256));
-    const int clusters = std::max(1, std::min(tiles, std::min(max_ctas / 2, max_clusters)));
-    kernel<<<2 * clusters, 192, smem_bytes, current_stream()>>>(ta, tb, p, segs);
+    const int stage_clusters = p.stage_ctas / 2;  // staging CTAs share the resident-cluster budget with the computing pairs
+    TORCH_CHECK(p.stage_ctas % 2 == 0 && stage_clusters < max_clusters, "gemm: too many staging CTAs");
+    const int clusters = std::max(1, std::min(tiles, std::min(max_ctas / 2, max_clusters - stage_clusters)));
+    kernel<<<2 * (clusters + stage_clusters), 192, smem_bytes, current_stream()>>>(ta, tb, p, segs);
     ATB_LAUNCH_CHECK();
 }
 
@@ -795,6 +880,8 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     p.ldr = residual.has_value() ? residual->stride(0) : p.ldc;
     p.a_seg_len = 0;
     p.a_seg_row0 = 0;
+    p.stage_ctas = 0;
+    p.stage_segs = 0;
     p.error_flag = error_flag_for(a.device()).data_ptr<int>();
     p.group_offsets = nullptr;
     p.num_groups = 0;
@@ -869,6 +956,8 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
         p.ldr = p.ldc;
         p.a_seg_len = 0;
         p.a_seg_row0 = 0;
+        p.stage_ctas = 0;
+        p.stage_segs = 0;
         if (!b_mn) dispatch_epi<false, false>(epi, ta, tb, p, kNumSMs);
         else dispatch_epi<false, true>(epi, ta, tb, p, kNumSMs);
     } else if (mode == GROUP_RAGGED_K) {
@@ -892,6 +981,8 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
         p.ldr = p.ldc;
         p.a_seg_len = 0;
         p.a_seg_row0 = 0;
+        p.stage_ctas = 0;
+        p.stage_segs = 0;
         dispatch_epi<true, true>(epi, ta, tb, p, kNumSMs);
     } else {
         TORCH_CHECK(false, "grouped gemm: mode must be 1 (ragged M) or 2 (ragged K)");
@@ -901,12 +992,18 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
 }
 
 // Selects the CTA-pair (cta_group::2, 256 x 256 tile) kernel for dense GEMMs; returns the previous setting.
-// out = A b^T (+ residual) where A [M, P * seg_cols] is never materialised: its K segment j is rows
-// [row0, row0 + M) of the [rows_total, seg_cols] bf16 tensor at a_ptrs[j] + a_byte_offset, which may be another GPU's
-// memory mapped into this process (the head-sharded attention outputs of the Ulysses peers: the head -> sequence
-// all-to-all happens inside the GEMM's operand fetch).  b is [N, P * seg_cols].
-at::Tensor gemm_bf16_peer_a(const at::Tensor& a_ptrs, int64_t a_byte_offset, int64_t rows_total, int64_t seg_cols,
-                            int64_t row0, int64_t M, const at::Tensor& b, const c10::optional<at::Tensor>& residual) {
+// out = A b^T (+ residual) where K segment j of A [M, P * seg_cols] is rows [row0, row0 + M) of the [rows_total,
+// seg_cols] bf16 tensor at a_ptrs[j] + a_byte_offset, which may be another GPU's memory mapped into this process (the
+// head-sharded attention outputs of the Ulysses peers: the head -> sequence all-to-all happens inside the GEMM).
+// b is [N, P * seg_cols].  Returns (out, a_local).
+//   stage_ctas > 0: that many CTAs of the same launch copy the segments into a_local [M, K] (each remote byte crosses
+//     NVLink once) while the other CTAs multiply tiles whose rows have arrived; a_local is the gathered operand, which
+//     a caller needs again for the weight gradient.
+//   stage_ctas == 0: every CTA pair fetches its A tiles from the owners directly with TMA; nothing is materialised
+//     (a_local is empty), but a tile crosses the link once per column tile of the output.
+std::tuple<at::Tensor, at::Tensor> gemm_bf16_peer_a(const at::Tensor& a_ptrs, int64_t a_byte_offset, int64_t rows_total,
+                                                    int64_t seg_cols, int64_t row0, int64_t M, const at::Tensor& b,
+                                                    const c10::optional<at::Tensor>& residual, int64_t stage_ctas) {
     ATB_CHECK_CUDA(b); ATB_CHECK_DTYPE(b, at::kBFloat16);
     TORCH_CHECK(a_ptrs.device().is_cpu() && a_ptrs.scalar_type() == at::kLong, "peer pointers: int64 CPU tensor");
     const int P = (int)a_ptrs.numel();
@@ -914,16 +1011,37 @@ at::Tensor gemm_bf16_peer_a(const at::Tensor& a_ptrs, int64_t a_byte_offset, int
     TORCH_CHECK(seg_cols % BK == 0 && a_byte_offset % 16 == 0, "gemm_peer_a: segment width must be a multiple of 64");
     TORCH_CHECK(b.dim() == 2 && b.stride(1) == 1 && b.size(1) == P * seg_cols && b.stride(0) % 8 == 0, "gemm_peer_a: b must be [N, P * seg_cols]");
     TORCH_CHECK(M > 0 && row0 >= 0 && row0 + M <= rows_total && M < (1ll << 31), "gemm_peer_a: row range outside the segment tensors");
+    TORCH_CHECK(stage_ctas >= 0 && stage_ctas % 2 == 0 && stage_ctas <= 64, "gemm_peer_a: staging CTAs: even, at most 64");
     const int64_t N = b.size(0), K = P * seg_cols;
     TORCH_CHECK(N % 8 == 0, "gemm_peer_a: N must be a multiple of 8");
     c10::cuda::CUDAGuard guard(b.device());
     auto out = at::empty({M, N}, b.options());
+    at::Tensor a_local = at::empty({stage_ctas > 0 ? M : 0, K}, b.options());
+    at::Tensor flags;
     SegMaps segs = {};
-    for (int j = 0; j < P; ++j)
-        segs.m[j] = make_tmap_bf16(reinterpret_cast<void*>(a_ptrs.data_ptr<int64_t>()[j] + a_byte_offset), rows_total, seg_cols,
-                                   seg_cols, 128);
-    const CUtensorMap tb = make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), 128);
     GemmParams p;
+    p.a_seg_len = (int)seg_cols;
+    p.a_seg_row0 = (int)row0;
+    p.stage_ctas = (int)stage_ctas;
+    p.stage_segs = P;
+    CUtensorMap ta;
+    if (stage_ctas > 0) {
+        flags = at::zeros({(int64_t)ceil_div(M, 256)}, b.options().dtype(at::kInt));
+        for (int j = 0; j < P; ++j)
+            p.stage_src[j] = reinterpret_cast<const bf16*>(a_ptrs.data_ptr<int64_t>()[j] + a_byte_offset);
+        p.stage_src_ld = seg_cols;
+        p.stage_dst = (bf16*)a_local.data_ptr();
+        p.stage_dst_ld = K;
+        p.stage_flags = flags.data_ptr<int>();
+        ta = make_tmap_bf16(a_local.data_ptr(), M, K, K, 128);
+        p.a_seg_len = (int)seg_cols;  // the staging CTAs need the segment width; the TMA producer reads a_local
+    } else {
+        for (int j = 0; j < P; ++j)
+            segs.m[j] = make_tmap_bf16(reinterpret_cast<void*>(a_ptrs.data_ptr<int64_t>()[j] + a_byte_offset), rows_total,
+                                       seg_cols, seg_cols, 128);
+        ta = segs.m[0];
+    }
+    const CUtensorMap tb = make_tmap_bf16(b.data_ptr(), N, K, b.stride(0), 128);
     p.C = (bf16*)out.data_ptr();
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.ldc = out.stride(0);
@@ -942,11 +1060,9 @@ at::Tensor gemm_bf16_peer_a(const at::Tensor& a_ptrs, int64_t a_byte_offset, int
     p.group_offsets = nullptr;
     p.num_groups = 0;
     p.group_mode = GROUP_NONE;
-    p.a_seg_len = (int)seg_cols;
-    p.a_seg_row0 = (int)row0;
-    if (epi == EPI_STORE) launch_gemm_pair<6, false, false, EPI_STORE>(segs.m[0], tb, p, kNumSMs, segs);
-    else launch_gemm_pair<6, false, false, EPI_ACCUM>(segs.m[0], tb, p, kNumSMs, segs);
-    return out;
+    if (epi == EPI_STORE) launch_gemm_pair<6, false, false, EPI_STORE>(ta, tb, p, kNumSMs, segs);
+    else launch_gemm_pair<6, false, false, EPI_ACCUM>(ta, tb, p, kNumSMs, segs);
+    return {out, a_local};
 }
 
 bool set_gemm_cta_pairs(bool on) {

@@ -15,6 +15,7 @@ Behaviour parity with what the reference gets from its engine dependency
 
 from __future__ import annotations
 
+import os
 from typing import Any
 from typing import Dict
 from typing import Iterator
@@ -147,18 +148,22 @@ class _PeerExchange:
         self.symm.barrier(self.O_SLOT)
         return buf.tensor[off : off + S * Hl * D].view(S // P, Hl * P, D).clone()
 
-    def head_to_seq_project(self, y, weight, residual):
-        """``[residual +] head_to_seq(y) @ weight.T`` without materialising the exchanged activations: every rank
-        publishes its head-sharded attention output, and the projection GEMM fetches each K slice of its A operand
-        (one head group per peer) straight from the owner's memory with TMA tile loads."""
+    def head_to_seq_project(self, y, weight, residual, stage_ctas: Optional[int] = None):
+        """``[residual +] head_to_seq(y) @ weight.T`` in one kernel: every rank publishes its head-sharded attention
+        output; in the projection GEMM a few CTAs gather this rank's rows from the owners over NVLink into a local
+        matrix (each byte crosses the link once) while the other CTAs multiply the row tiles that have arrived.
+        Returns ``(out, gathered)``; ``gathered`` is the exchanged activation ``[S / P, H * D]`` (empty with
+        ``stage_ctas=0``, where every CTA pair fetches its operand tiles from the owners with TMA instead)."""
         S, Hl, D = y.shape
         P = self.size
+        if stage_ctas is None:
+            stage_ctas = int(os.getenv("ATB200_STAGE_CTAS", "16"))
         buf, off = self._buffer("o_src", S * Hl * D)
         buf.tensor[off : off + S * Hl * D].view(S, Hl, D).copy_(y)
         self.symm.barrier(self.OP_SLOT)
         ops.functional._count()
         return ops._ext.ops().gemm_bf16_peer_a(
-            buf.ptrs, off * 2, S, Hl * D, self.rank * (S // P), S // P, weight, residual
+            buf.ptrs, off * 2, S, Hl * D, self.rank * (S // P), S // P, weight, residual, stage_ctas
         )
 
     def seq_to_head(self, x, slot_name: str = "do"):
@@ -192,6 +197,33 @@ class _HeadToSeqPeer(torch.autograd.Function):
     @staticmethod
     def backward(ctx, g):
         return ctx.ex.seq_to_head(g.contiguous()), None
+
+
+class _HeadToSeqProjectPeer(torch.autograd.Function):
+    """``[r +] head_to_seq(y) W^T`` with the exchange inside the projection GEMM; keeps the gathered activations for
+    the weight gradient.  Backward: dA = dOut W goes back to the head owners with the push exchange."""
+
+    @staticmethod
+    def forward(ctx, y, w, r2, ex):
+        out, gathered = ex.head_to_seq_project(y.contiguous(), w, r2)
+        ctx.save_for_backward(gathered, w)
+        ctx.ex, ctx.shape = ex, y.shape
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        from ..ops.functional import _wgrad
+        from ..ops.functional import gemm
+
+        gathered, w = ctx.saved_tensors
+        dout = dout.contiguous()
+        S, Hl, D = ctx.shape
+        dy = None
+        if ctx.needs_input_grad[0]:
+            da = gemm(dout, w, False, True)  # [S / P, H * D]
+            dy = ctx.ex.seq_to_head(da.view(da.shape[0], -1, D))
+        dw = _wgrad(dout, gathered, w) if ctx.needs_input_grad[1] else None
+        return dy, dw, (dout if ctx.needs_input_grad[2] else None), None
 
 
 class UlyssesContext:
@@ -241,28 +273,26 @@ class UlyssesContext:
         return _HeadToSeq.apply(o.contiguous(), self.group)
 
     def attention_project(self, q, k, v, ctx: Any, w_out: torch.Tensor, residual: Optional[torch.Tensor]):
-        """Attention followed by the output projection with the head -> sequence exchange folded into the projection
-        GEMM's operand fetch.  Forward only (no autograd graph); returns ``None`` when the fused path does not apply
-        so that the caller can fall back to :meth:`attention` plus a linear layer."""
+        """Attention followed by the output projection with the head -> sequence exchange done inside the projection
+        GEMM.  Returns ``None`` when the fused path does not apply, so that the caller can fall back to
+        :meth:`attention` plus a linear layer."""
         P = self.size
         Hq, Hkv, D = q.shape[2], k.shape[2], q.shape[-1]
-        if torch.is_grad_enabled() or P > 8 or Hq % P or (Hq // P * D) % 64 or w_out.dtype != torch.bfloat16:
+        if P > 8 or Hq % P or (Hq // P * D) % 64 or w_out.dtype != torch.bfloat16 or os.getenv("ATB200_FUSED_PROJ", "1") == "0":
             return None
         if not ((Hkv % P == 0 or P % Hkv == 0) and D % 8 == 0) or w_out.shape[0] % 8 or not w_out.is_contiguous():
+            return None
+        if residual is not None and (residual.dtype != torch.bfloat16 or not residual.is_contiguous()):
             return None
         ex = self._peer_exchange(q)
         if ex is None:
             return None
         Hlq, Hlkv = Hq // P, (Hkv // P if Hkv >= P else 1)
-        qkv = ex.qkv_seq_to_head(_dense_heads(q[0]), _dense_heads(k[0]), _dense_heads(v[0]))
+        qkv = _QKVSeqToHeadPeer.apply(_dense_heads(q[0]), _dense_heads(k[0]), _dense_heads(v[0]), ex)
         qf, kf, vf = qkv[None, :, :Hlq], qkv[None, :, Hlq : Hlq + Hlkv], qkv[None, :, Hlq + Hlkv :]
         o = ops.attention(qf, kf, vf, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
-        res2 = None
-        if residual is not None:
-            if residual.dtype != torch.bfloat16 or not residual.is_contiguous():
-                return ex.head_to_seq_project(o[0].contiguous(), w_out, None)[None] + residual
-            res2 = residual.view(-1, residual.shape[-1])
-        return ex.head_to_seq_project(o[0].contiguous(), w_out, res2)[None]
+        res2 = residual.view(-1, residual.shape[-1]) if residual is not None else None
+        return _HeadToSeqProjectPeer.apply(o[0], w_out, res2, ex)[None]
 
     # -- packed-sample boundaries -------------------------------------------------------------------
     def global_cu_seqlens(self, position_ids: torch.Tensor) -> Tuple[Optional[torch.Tensor], int]:

@@ -123,15 +123,26 @@ def scenario_ulysses_peer(out_dir):
             if fused:
                 sp._peer.symm.check()
             outs.append((o.detach().float(), x.grad.float()))
-        # forward-only path with the exchange folded into the output projection GEMM
+        # the exchange folded into the output projection GEMM, forward and backward
         w = (torch.randn(384, Hq * D, device="cuda", generator=torch.Generator(device="cuda").manual_seed(3)) * 0.05).bfloat16()
         resid = torch.randn(1, S_loc, 384, device="cuda", dtype=torch.bfloat16)
-        with torch.no_grad():
-            fused = sp.attention_project(q, k, v, fctx, w, resid)
-            plain = resid + torch.nn.functional.linear(sp.attention(q, k, v, fctx).reshape(1, S_loc, Hq * D), w)
-        assert fused is not None, "fused projection path did not apply"
+        gout = torch.randn(1, S_loc, 384, device="cuda", dtype=torch.bfloat16)
+        got = []
+        for use_fused in (True, False):
+            x2 = qkv.clone().requires_grad_(True)
+            w2 = w.clone().requires_grad_(True)
+            r2 = resid.clone().requires_grad_(True)
+            q2, k2, v2 = x2.view(1, S_loc, Hq + 2 * Hkv, D).split([Hq, Hkv, Hkv], dim=2)
+            if use_fused:
+                out = sp.attention_project(q2, k2, v2, fctx, w2, r2)
+                assert out is not None, "fused projection path did not apply"
+            else:
+                out = r2 + torch.nn.functional.linear(sp.attention(q2, k2, v2, fctx).reshape(1, S_loc, Hq * D), w2)
+            out.backward(gout)
+            got.append([t.detach().float() for t in (out, x2.grad, w2.grad, r2.grad)])
         sp._peer.symm.check()
-        proj_err = float((fused.float() - plain.float()).norm() / plain.float().norm())
+        assert int(torch.ops.atb200.read_and_clear_error_flag(w)) == 0
+        proj_err = max(float((a - b).norm() / (b.norm() + 1e-12)) for a, b in zip(*got))
         res[name + "_proj_err"] = proj_err
         res[name] = {
             "out_diff": float((outs[0][0] - outs[1][0]).abs().max()),
