@@ -267,6 +267,19 @@ class SwiftKVModelFactory(HFModelFactory):
         return model
 
 
+def build_swiftkv_model(checkpoint_dir: str, dtype=torch.bfloat16, device: str = "cuda") -> "SwiftKVForCausalLM":
+    """Load an exported SwiftKV checkpoint (HF layout, SwiftKV fields in ``config.json``) for evaluation."""
+    from arctictraining_b200.models.arch import load_arch_config
+    from arctictraining_b200.models.hf_io import load_pretrained_into
+
+    cfg = load_arch_config(checkpoint_dir)
+    with torch.device(device):
+        model = SwiftKVForCausalLM(cfg, dtype=dtype)
+    load_pretrained_into(model, checkpoint_dir, cfg)
+    model.swiftkv(True)
+    return model
+
+
 # ------------------------------------------------------------------------------------------------ tiled KL loss
 class _FusedLinearKLFn(torch.autograd.Function):
     """mean over rows of ``weight_t * T^2 * KL(softmax(h_t W^T / T) || softmax(h_s W^T / T))`` with the student
