@@ -127,18 +127,31 @@ class RotatingBuffers:
         self._bufs: Dict[str, SymmetricBuffer] = {}
         self._turn: Dict[str, int] = {}
 
+    def reserve(self, name: str, numel: int, dtype: torch.dtype = torch.bfloat16) -> None:
+        """Make sure buffer ``name`` can hold two exchanges of ``numel`` elements without taking a turn.  Forward
+        passes reserve the buffers of their backward passes, so that no collective allocation happens on an autograd
+        worker thread."""
+        numel = (numel + 127) // 128 * 128
+        buf = self._bufs.get(name)
+        if buf is None or buf.tensor.numel() < 2 * numel:
+            self._allocate(name, numel, dtype)
+
+    def _allocate(self, name: str, numel: int, dtype: torch.dtype) -> SymmetricBuffer:
+        torch.cuda.synchronize()
+        buf = self.ctx.alloc(f"{name}_{2 * numel}", 2 * numel, dtype)
+        buf.tensor.zero_()
+        torch.cuda.synchronize()
+        dist.barrier(group=self.ctx.group, device_ids=[self.ctx.device.index])
+        self._bufs[name] = buf
+        self._turn[name] = 0
+        return buf
+
     def take(self, name: str, numel: int, dtype: torch.dtype = torch.bfloat16):
         """Returns ``(buffer, element offset of the half to use now)``."""
         numel = (numel + 127) // 128 * 128
         buf = self._bufs.get(name)
         if buf is None or buf.tensor.numel() < 2 * numel:
-            torch.cuda.synchronize()
-            buf = self.ctx.alloc(f"{name}_{2 * numel}", 2 * numel, dtype)
-            buf.tensor.zero_()
-            torch.cuda.synchronize()
-            dist.barrier(group=self.ctx.group, device_ids=[self.ctx.device.index])
-            self._bufs[name] = buf
-            self._turn[name] = 0
+            buf = self._allocate(name, numel, dtype)
         half = buf.tensor.numel() // 2
         turn = self._turn[name]
         self._turn[name] = turn ^ 1

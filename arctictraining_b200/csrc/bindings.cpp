@@ -25,6 +25,8 @@ at::Tensor kl_fwd_bwd(at::Tensor student, const at::Tensor& teacher, const c10::
 at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b_mn, int64_t epilogue,
                      const c10::optional<at::Tensor>& out, int64_t max_ctas, const c10::optional<at::Tensor>& residual);
 int64_t read_and_clear_error_flag(const at::Tensor& like);
+void gemm_bf16_push_heads(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dst_ptrs, int64_t dst_byte_offset,
+                          int64_t rank, int64_t Hq, int64_t Hkv, int64_t D);
 std::tuple<at::Tensor, at::Tensor> gemm_bf16_peer_a(const at::Tensor& a_ptrs, int64_t a_byte_offset, int64_t rows_total,
                                                     int64_t seg_cols, int64_t row0, int64_t M, const at::Tensor& b,
                                                     const c10::optional<at::Tensor>& residual, int64_t stage_ctas);
@@ -89,6 +91,7 @@ TORCH_LIBRARY(atb200, m) {
     m.def("gemm_bf16(Tensor a, Tensor b, bool a_mn, bool b_mn, int epilogue, Tensor? out, int max_ctas, Tensor? residual=None) -> Tensor",
           &atb::gemm_bf16);
     m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);
+    m.def("gemm_bf16_push_heads(Tensor x, Tensor w, Tensor dst_ptrs, int dst_byte_offset, int rank, int Hq, int Hkv, int D) -> ()", &atb::gemm_bf16_push_heads);
     m.def("gemm_bf16_peer_a(Tensor a_ptrs, int a_byte_offset, int rows_total, int seg_cols, int row0, int M, Tensor b, Tensor? residual=None, int stage_ctas=16) -> (Tensor, Tensor)", &atb::gemm_bf16_peer_a);
     m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor)", &atb::fmha_fwd);
     m.def("set_gemm_cta_pairs(bool on) -> bool", &atb::set_gemm_cta_pairs);

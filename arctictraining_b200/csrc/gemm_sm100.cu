@@ -32,7 +32,7 @@ constexpr int UMMA_K = 16;
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 constexpr int kMaxGroups = 1024;
 
-enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2 };
+enum Epilogue : int { EPI_STORE = 0, EPI_ACCUM = 1, EPI_SWIGLU = 2, EPI_PUSH_HEADS = 3 };
 
 template <int BN, int STAGES>
 struct SmemLayout {
@@ -73,6 +73,12 @@ struct GemmParams {
     bf16* stage_dst;
     int64_t stage_dst_ld;
     int* stage_flags;
+    // EPI_PUSH_HEADS (CTA-pair kernel): the output is a fused q|k|v projection [rows, (Hq + 2 Hkv) D] that is not
+    // stored here: every 32-column piece goes to the rank that owns its head, into that rank's buffer
+    // [P * rows_per_rank, Hlq + 2 Hlkv, D] at row push_rank * rows_per_rank + row (sequence -> head exchange of Ulysses
+    // done by the epilogue stores).  KV heads are replicated when there are fewer of them than ranks.
+    bf16* push_dst[8];
+    int push_ranks, push_rank, push_hq, push_hkv, push_d, push_rows;
 };
 
 constexpr int kMaxSegs = 8;
@@ -634,6 +640,46 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
             const int row = tm * TM + (int)cta * 128 + quarter * 32 + lane;
             const bool row_ok = row < p.M;
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * TN);
+            if constexpr (EPI == EPI_PUSH_HEADS) {
+                const int P = p.push_ranks, D = p.push_d, Hq = p.push_hq, Hkv = p.push_hkv;
+                const int Hlq = Hq / P, rep = Hkv >= P ? 1 : P / Hkv, Hlkv = Hkv >= P ? Hkv / P : 1;
+                const int W = (Hlq + 2 * Hlkv) * D;
+                const int64_t drow = ((int64_t)p.push_rank * p.push_rows + row) * W;
+#pragma unroll 1
+                for (int c = 0; c < TN / 32; ++c) {
+                    uint32_t r[32];
+                    ptx::tmem_ld_32x32b_x32(taddr + c * 32, r);
+                    ptx::tmem_ld_wait();
+                    const int col0 = tn * TN + c * 32;
+                    if (row_ok && col0 < p.N) {
+                        // which head does this 32-column piece belong to, and who owns it
+                        const int head = col0 / D, within = col0 - head * D;
+                        int first_owner, owners, dcol;
+                        if (head < Hq) {
+                            first_owner = head / Hlq; owners = 1; dcol = (head - first_owner * Hlq) * D + within;
+                        } else {
+                            const int is_v = head >= Hq + Hkv;
+                            const int kvh = head - Hq - is_v * Hkv;
+                            first_owner = rep > 1 ? kvh * rep : kvh / Hlkv;
+                            owners = rep;
+                            dcol = (Hlq + is_v * Hlkv + (rep > 1 ? 0 : kvh - first_owner * Hlkv)) * D + within;
+                        }
+                        bf16x8 packed[4];
+#pragma unroll
+                        for (int v = 0; v < 4; ++v) {
+                            float o[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(r[v * 8 + j]);
+                            packed[v] = pack8(o);
+                        }
+                        for (int o = first_owner; o < first_owner + owners; ++o) {
+                            bf16x8* dst = reinterpret_cast<bf16x8*>(p.push_dst[o] + drow + dcol);
+#pragma unroll
+                            for (int v = 0; v < 4; ++v) dst[v] = packed[v];
+                        }
+                    }
+                }
+            } else
             if constexpr (EPI == EPI_SWIGLU) {
                 bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * (TN / 2);
 #pragma unroll 1
@@ -725,6 +771,13 @@ PFN_cuTensorMapEncodeTiled_v12000 get_encode_fn() {
 CUtensorMap make_tmap_bf16(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
     TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0, "TMA: base address must be 16-byte aligned");
     TORCH_CHECK((ld * 2) % 16 == 0, "TMA: row pitch must be a multiple of 16 bytes");
+    // cuTensorMapEncodeTiled is a driver call and needs a context bound to this thread; a fresh thread (an autograd
+    // worker on device 0, which never had to switch devices) has none until the first runtime call.
+    static thread_local bool context_bound = false;
+    if (!context_bound) {
+        C10_CUDA_CHECK(cudaFree(nullptr));
+        context_bound = true;
+    }
     CUtensorMap tm;
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
@@ -733,7 +786,12 @@ CUtensorMap make_tmap_bf16(const void* base, int64_t rows, int64_t cols, int64_t
     CUresult r = get_encode_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), gdim, gstride, box,
                                  estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                  CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled failed with code ", (int)r);
+    if (r != CUDA_SUCCESS) {
+        char msg[256];
+        snprintf(msg, sizeof(msg), "cuTensorMapEncodeTiled failed with code %d (base %p, rows %lld, cols %lld, pitch %lld, box rows %d)",
+                 (int)r, base, (long long)rows, (long long)cols, (long long)ld, box_rows);
+        TORCH_CHECK(false, msg);
+    }
     return tm;
 }
 
@@ -992,6 +1050,36 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
 }
 
 // Selects the CTA-pair (cta_group::2, 256 x 256 tile) kernel for dense GEMMs; returns the previous setting.
+// Fused q|k|v projection + Ulysses sequence -> head exchange: x [rows, K] times w [(Hq + 2 Hkv) D, K]^T, where the
+// epilogue stores every head's columns into the owning rank's buffer (dst_ptrs[o] + dst_byte_offset, laid out
+// [P * rows, Hlq + 2 Hlkv, D], this rank's rows at rank * rows).  Nothing is written locally.  The caller separates
+// launches on different ranks from the consumers of the buffers with a device barrier.
+void gemm_bf16_push_heads(const at::Tensor& x, const at::Tensor& w, const at::Tensor& dst_ptrs, int64_t dst_byte_offset,
+                          int64_t rank, int64_t Hq, int64_t Hkv, int64_t D) {
+    ATB_CHECK_CUDA(x); ATB_CHECK_CUDA(w); ATB_CHECK_DTYPE(x, at::kBFloat16); ATB_CHECK_DTYPE(w, at::kBFloat16);
+    TORCH_CHECK(x.dim() == 2 && w.dim() == 2 && x.stride(1) == 1 && w.stride(1) == 1 && x.size(1) == w.size(1), "push_heads: x [rows, K], w [N, K]");
+    TORCH_CHECK(dst_ptrs.device().is_cpu() && dst_ptrs.scalar_type() == at::kLong, "peer pointers: int64 CPU tensor");
+    const int P = (int)dst_ptrs.numel();
+    const int64_t M = x.size(0), N = w.size(0), K = x.size(1);
+    TORCH_CHECK(P >= 1 && P <= 8 && Hq % P == 0 && (Hkv >= P ? Hkv % P == 0 : P % Hkv == 0), "push_heads: heads and ranks must divide");
+    TORCH_CHECK(N == (Hq + 2 * Hkv) * D && D % 32 == 0 && K % 8 == 0 && dst_byte_offset % 16 == 0, "push_heads: shape mismatch");
+    TORCH_CHECK(x.stride(0) % 8 == 0 && w.stride(0) % 8 == 0, "push_heads: row pitches must be multiples of 8 elements");
+    ATB_CHECK_ALIGNED16(x); ATB_CHECK_ALIGNED16(w);
+    if (M == 0) return;
+    c10::cuda::CUDAGuard guard(x.device());
+    const CUtensorMap ta = make_tmap_bf16(x.data_ptr(), M, K, x.stride(0), 128);
+    const CUtensorMap tb = make_tmap_bf16(w.data_ptr(), N, K, w.stride(0), 128);
+    GemmParams p;
+    p.C = nullptr; p.R = nullptr; p.ldc = 0; p.ldr = 0;
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.error_flag = error_flag_for(x.device()).data_ptr<int>();
+    p.group_offsets = nullptr; p.num_groups = 0; p.group_mode = GROUP_NONE;
+    p.a_seg_len = 0; p.a_seg_row0 = 0; p.stage_ctas = 0; p.stage_segs = 0;
+    for (int o = 0; o < P; ++o) p.push_dst[o] = reinterpret_cast<bf16*>(dst_ptrs.data_ptr<int64_t>()[o] + dst_byte_offset);
+    p.push_ranks = P; p.push_rank = (int)rank; p.push_hq = (int)Hq; p.push_hkv = (int)Hkv; p.push_d = (int)D; p.push_rows = (int)M;
+    launch_gemm_pair<6, false, false, EPI_PUSH_HEADS>(ta, tb, p, kNumSMs);
+}
+
 // out = A b^T (+ residual) where K segment j of A [M, P * seg_cols] is rows [row0, row0 + M) of the [rows_total,
 // seg_cols] bf16 tensor at a_ptrs[j] + a_byte_offset, which may be another GPU's memory mapped into this process (the
 // head-sharded attention outputs of the Ulysses peers: the head -> sequence all-to-all happens inside the GEMM).

@@ -154,6 +154,7 @@ class TrainingEngine:
         self.global_samples = 0
         self.skipped_steps = 0
         self._grad_norm: Optional[torch.Tensor] = None
+        self._single_pass_sumsq: Optional[torch.Tensor] = None
         self.timers = TimerGroup()
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.on_gpu else None
         self.sp_size = max(1, self.cfg.sequence_parallel_size)
@@ -376,6 +377,7 @@ class TrainingEngine:
             if tl <= 0:
                 continue
             pad = (tl + 7) // 8 * 8
+            u.view_list = []
             u.master = torch.zeros(pad, dtype=master_dtype, device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
             u.master[:tl].copy_(u.shard[:tl].to(master_dtype))
             # Without accumulation steps and without peers to reduce with, the bf16 gradients that autograd writes
@@ -399,6 +401,7 @@ class TrainingEngine:
                 view._atb_state_dtype = state_dtype  # type: ignore[attr-defined]
                 new_groups[gi].append(view)
                 self._views.append((u, s, e, gi, view))
+                u.view_list.append((s, e, gi, view))
         opt.state.clear()
         for g, params in zip(opt.param_groups, new_groups):
             g["params"] = params
@@ -655,7 +658,29 @@ class TrainingEngine:
             and u.group_size > 1 and lo % 8 == 0
         )
 
+        single_pass = fused and self._single_pass_update_ok(u)
+
         def work() -> None:
+            if single_pass:
+                # no clipping, no accumulation steps: the reduction feeds AdamW directly (one pass over the gradients:
+                # peer loads -> fp32 sum -> moments, master weights and the bf16 shard), the fp32 gradient shard is
+                # never written
+                self.symm.barrier(slot=1)
+                opt = self.optimizer
+                for s, e, gi, view in u.view_list:
+                    group = opt.param_groups[gi]
+                    st = opt._state_for(view)
+                    st["step"] += 1
+                    b1, b2 = group["betas"]
+                    ss = torch.ops.atb200.p2p_reduce_scatter_adamw(
+                        self._grad_symm[u.grad_slot].ptrs, lo + s, e - s, scale, view, st["exp_avg"], st["exp_avg_sq"],
+                        view._atb_lp, float(group["lr"]), b1, b2, group["eps"], group["weight_decay"], st["step"],
+                    )
+                    self._single_pass_sumsq = ss if self._single_pass_sumsq is None else self._single_pass_sumsq + ss
+                    ops.functional._count()
+                u.stepped_in_backward = True
+                self.symm.barrier(slot=2)
+                return
             if fused:
                 # every rank has finished writing this unit's gradients -> read my slice from all peers, reduce
                 # in fp32, accumulate; second barrier: nobody still reads a buffer that is about to be reused
@@ -695,6 +720,20 @@ class TrainingEngine:
             if u.grad_slot is not None:
                 self._grad_pool.release(u.grad_slot, None)
         u.grad_flat, u.grad_slot = None, None
+
+    def _single_pass_update_ok(self, u: ZeroUnit) -> bool:
+        """Reduce-scatter and AdamW in one kernel: only without clipping (the clip factor needs the global norm of all
+        gradients first) and without accumulation steps, for fp32 states on the device and 8-aligned parameter runs."""
+        opt = self.optimizer
+        if (self.cfg.gradient_clipping and self.cfg.gradient_clipping > 0) or self.gas != 1 or not hasattr(opt, "step_flat"):
+            return False
+        if os.getenv("ATB200_SINGLE_PASS_UPDATE", "1") == "0" or not getattr(u, "view_list", None):
+            return False
+        if getattr(u, "is_expert", False) or u.master is None or u.master.dtype != torch.float32 or u.master.device != self.device:
+            return False
+        if self.cfg.bf16_optimizer_states:
+            return False
+        return all(s % 8 == 0 and (e - s) % 8 == 0 and view._atb_lp is not None for s, e, gi, view in u.view_list)
 
     def _accumulate(self, u: ZeroUnit, piece: torch.Tensor, scale: float) -> None:
         acc = u.grad_acc[: piece.numel()]
@@ -786,6 +825,9 @@ class TrainingEngine:
     def _compute_grad_norm(self) -> torch.Tensor:
         total = torch.zeros((), dtype=torch.float32, device=self.device)
         expert_total = torch.zeros((), dtype=torch.float32, device=self.device)
+        if self._single_pass_sumsq is not None:
+            total += self._single_pass_sumsq.to(self.device)
+            self._single_pass_sumsq = None
         for u in self.units:
             if u.grad_acc is None or not u.grad_acc_valid:
                 continue
@@ -822,6 +864,12 @@ class TrainingEngine:
             coef = torch.clamp(clip / (norm + 1e-6), max=1.0).reshape(1).float()
         fused = hasattr(opt, "step_flat")
         for u, s, e, gi, view in self._views:
+            if getattr(u, "stepped_in_backward", False):
+                view._atb_grad = None  # type: ignore[attr-defined]
+                view.grad = None
+                view._atb_skip = True  # type: ignore[attr-defined]
+                continue
+            view._atb_skip = False  # type: ignore[attr-defined]
             gslice = u.grad_acc[s:e]
             if not u.grad_acc_valid:
                 gslice.zero_()
@@ -847,6 +895,7 @@ class TrainingEngine:
                     and u.master.dtype == torch.float32 and u.dtype == torch.bfloat16):
                 u.shard[:tl].copy_(u.master[:tl].to(self.device, non_blocking=True).to(u.dtype))
             u.grad_acc_valid = False
+            u.stepped_in_backward = False
         self._sync_full_params()
         if self.symm is not None:
             self.symm.barrier(slot=0)  # shards are final on every rank before anyone pulls them again

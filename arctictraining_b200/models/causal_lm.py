@@ -67,8 +67,11 @@ class DecoderModel(nn.Module):
 
     def make_context(self, position_ids: torch.Tensor, attn_impl: str, **kw: Any) -> ForwardContext:
         cfg = self.cfg
-        cos, sin = ref.rope_cos_sin(position_ids, cfg.head_dim_, float(cfg.get("rope_theta") or 10000.0), cfg.get("rope_scaling"))
-        return ForwardContext(cos=cos, sin=sin, attn_impl=attn_impl, **kw)
+        def rope_fn(pos: torch.Tensor):
+            return ref.rope_cos_sin(pos, cfg.head_dim_, float(cfg.get("rope_theta") or 10000.0), cfg.get("rope_scaling"))
+
+        cos, sin = rope_fn(position_ids)
+        return ForwardContext(cos=cos, sin=sin, attn_impl=attn_impl, rope_fn=rope_fn, **kw)
 
     def forward(
         self,

@@ -33,6 +33,8 @@ class ForwardContext:
     sp: Optional[Any] = None  # UlyssesContext when sequence parallelism is on
     tiled_mlp: bool = False
     extras: Dict[str, Any] = field(default_factory=dict)
+    # rotary tables for arbitrary positions (used for the whole sequence when rotation happens after the Ulysses exchange)
+    rope_fn: Optional[Any] = None
 
 
 class RMSNorm(nn.Module):
@@ -104,6 +106,14 @@ class Attention(nn.Module):
 
     def forward(self, x: torch.Tensor, ctx: ForwardContext, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, S, _ = x.shape
+        if (
+            ctx.sp is not None and hasattr(ctx.sp, "fused_attention_block") and not self.qk_norm
+            and type(self.qkv_proj) is Linear and self.qkv_proj.bias is None
+            and type(self.o_proj) is Linear and self.o_proj.bias is None
+        ):
+            fused = ctx.sp.fused_attention_block(x, self.qkv_proj.weight, self.o_proj.weight, ctx, self.hq, self.hkv, self.d, residual)
+            if fused is not None:
+                return fused
         q, k, v = self.project_qkv(x, ctx)
         if ctx.sp is not None and type(self.o_proj) is Linear and self.o_proj.bias is None and hasattr(ctx.sp, "attention_project"):
             fused = ctx.sp.attention_project(q, k, v, ctx, self.o_proj.weight, residual)

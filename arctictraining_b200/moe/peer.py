@@ -90,6 +90,8 @@ class _DispatchFn(torch.autograd.Function):
     def forward(ctx, x, experts, dest, valid, ex: PeerMoEExchange, cap: int, El: int):
         H = x.shape[1]
         buf, off = ex.rot.take("moe_xin", cap * H)
+        for name in ("moe_dxin", "moe_yout", "moe_dyin"):  # buffers of the backward pass: allocate on this thread
+            ex.rot.reserve(name, cap * H)
         _count()
         _ext.ops().p2p_moe_dispatch(x.contiguous(), experts, dest, buf.ptrs, off * 2, El, cap, None)
         ex.symm.barrier(ex.D_SLOT)

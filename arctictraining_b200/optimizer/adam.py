@@ -42,6 +42,8 @@ class FusedAdamW(torch.optim.Optimizer):
         for group in self.param_groups:
             b1, b2 = group["betas"]
             for p in group["params"]:
+                if getattr(p, "_atb_skip", False):
+                    continue  # updated during the backward pass by the fused reduce-scatter + AdamW kernel
                 g = getattr(p, "_atb_grad", None)
                 if g is None:
                     g = p.grad

@@ -121,6 +121,9 @@ class _PeerExchange:
     def _buffer(self, name: str, numel: int):
         return self._rot.take("ulysses_" + name, numel)
 
+    def _reserve(self, name: str, numel: int) -> None:
+        self._rot.reserve("ulysses_" + name, numel)
+
     # ---- q, k, v: sequence-sharded -> head-sharded
     def qkv_seq_to_head(self, q, k, v):
         S_loc, Hq, D = q.shape
@@ -129,6 +132,7 @@ class _PeerExchange:
         Hlq, Hlkv = Hq // P, (Hkv // P if Hkv >= P else 1)
         W = (Hlq + 2 * Hlkv) * D
         buf, off = self._buffer("qkv", P * S_loc * W)
+        self._reserve("dqkv", P * S_loc * W)  # the backward pass publishes d(qkv) of the same size
         ops._ext.ops().p2p_qkv_push(q, k, v, buf.ptrs, off * 2, self.rank)
         self.symm.barrier(self.Q_SLOT)
         return buf.tensor[off : off + P * S_loc * W].view(P * S_loc, Hlq + 2 * Hlkv, D).clone()
@@ -144,6 +148,7 @@ class _PeerExchange:
         S, Hl, D = y.shape
         P = self.size
         buf, off = self._buffer(slot_name, S * Hl * D)
+        self._reserve("do", S * Hl * D)
         ops._ext.ops().p2p_seq_to_head(y, buf.ptrs, self.rank, True, off * 2)
         self.symm.barrier(self.O_SLOT)
         return buf.tensor[off : off + S * Hl * D].view(S // P, Hl * P, D).clone()
@@ -159,6 +164,7 @@ class _PeerExchange:
         if stage_ctas is None:
             stage_ctas = int(os.getenv("ATB200_STAGE_CTAS", "16"))
         buf, off = self._buffer("o_src", S * Hl * D)
+        self._reserve("do", S * Hl * D)
         buf.tensor[off : off + S * Hl * D].view(S, Hl, D).copy_(y)
         self.symm.barrier(self.OP_SLOT)
         ops.functional._count()
@@ -199,6 +205,39 @@ class _HeadToSeqPeer(torch.autograd.Function):
         return ctx.ex.seq_to_head(g.contiguous()), None
 
 
+class _QKVProjectPushPeer(torch.autograd.Function):
+    """Fused q|k|v projection whose GEMM epilogue stores every head's columns into the memory of the rank that owns the
+    head (sequence -> head exchange without a separate kernel or a local copy of the projection).  Returns the fused
+    ``[S, Hlq + 2 Hlkv, D]`` buffer of this rank's heads over the whole sequence, before rotary embedding."""
+
+    @staticmethod
+    def forward(ctx, x2, w, ex, Hq, Hkv, D):
+        S_loc = x2.shape[0]
+        P = ex.size
+        Hlq, Hlkv = Hq // P, (Hkv // P if Hkv >= P else 1)
+        Wl = (Hlq + 2 * Hlkv) * D
+        buf, off = ex._buffer("qkv", P * S_loc * Wl)
+        ex._reserve("dqkv", P * S_loc * Wl)
+        ops.functional._count()
+        ops._ext.ops().gemm_bf16_push_heads(x2, w, buf.ptrs, off * 2, ex.rank, Hq, Hkv, D)
+        ex.symm.barrier(ex.Q_SLOT)
+        ctx.save_for_backward(x2, w)
+        ctx.ex, ctx.dims = ex, (S_loc, Hq, Hkv, D)
+        return buf.tensor[off : off + P * S_loc * Wl].view(P * S_loc, Hlq + 2 * Hlkv, D).clone()
+
+    @staticmethod
+    def backward(ctx, g):
+        from ..ops.functional import _wgrad
+        from ..ops.functional import gemm
+
+        x2, w = ctx.saved_tensors
+        S_loc, Hq, Hkv, D = ctx.dims
+        d = ctx.ex.qkv_grad_head_to_seq(g.contiguous(), S_loc, Hq, Hkv, D).view(S_loc, -1)
+        dx = gemm(d, w, False, True) if ctx.needs_input_grad[0] else None
+        dw = _wgrad(d, x2, w) if ctx.needs_input_grad[1] else None
+        return dx, dw, None, None, None, None
+
+
 class _HeadToSeqProjectPeer(torch.autograd.Function):
     """``[r +] head_to_seq(y) W^T`` with the exchange inside the projection GEMM; keeps the gathered activations for
     the weight gradient.  Backward: dA = dOut W goes back to the head owners with the push exchange."""
@@ -231,6 +270,7 @@ class UlyssesContext:
         self.group, self.size, self.rank = group, size, rank
         self.fused = fused  # None: decide on first use (peer memory available and usable shapes)
         self._peer: Optional[_PeerExchange] = None
+        self.fused_block_calls = 0  # attention blocks that ran with both exchanges inside GEMMs
 
     def _peer_exchange(self, q: torch.Tensor) -> Optional[_PeerExchange]:
         if self.fused is False or not q.is_cuda or q.dtype != torch.bfloat16 or q.shape[0] != 1:
@@ -272,6 +312,42 @@ class UlyssesContext:
         o = ops.attention(qf, kf, vf, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
         return _HeadToSeq.apply(o.contiguous(), self.group)
 
+    def fused_attention_block(self, x, w_qkv, w_out, ctx: Any, Hq: int, Hkv: int, D: int, residual):
+        """Whole attention block of a layer with both Ulysses exchanges inside GEMMs: the q|k|v projection pushes its
+        output to the head owners from its epilogue, rotary embedding is applied after the exchange (with the positions
+        of the whole sequence), and the output projection gathers its operand from the owners.  ``None`` = not
+        applicable (caller falls back to separate projection, exchange and attention)."""
+        P = self.size
+        if os.getenv("ATB200_FUSED_QKV", "1") == "0" or os.getenv("ATB200_FUSED_PROJ", "1") == "0":
+            return None
+        if x.shape[0] != 1 or x.dtype != torch.bfloat16 or not x.is_cuda or P > 8 or Hq % P or D % 32 or (Hq // P * D) % 64:
+            return None
+        if not (Hkv % P == 0 or P % Hkv == 0) or w_qkv.dtype != torch.bfloat16 or w_out.dtype != torch.bfloat16:
+            return None
+        if ctx.rope_fn is None or getattr(self, "global_position_ids", None) is None or x.shape[1] % 8 or x.shape[2] % 8:
+            return None
+        if residual is not None and (residual.dtype != torch.bfloat16 or not residual.is_contiguous()):
+            return None
+        if not (w_qkv.is_contiguous() and w_out.is_contiguous() and w_out.shape[0] % 8 == 0):
+            return None
+        ex = self._peer_exchange(x.view(1, x.shape[1], 1, -1))
+        if ex is None:
+            return None
+        S_loc = x.shape[1]
+        if self.global_position_ids.shape[1] != S_loc * P:
+            return None
+        if "rope_global" not in ctx.extras:
+            ctx.extras["rope_global"] = ctx.rope_fn(self.global_position_ids)
+        cos, sin = ctx.extras["rope_global"]
+        Hlq, Hlkv = Hq // P, (Hkv // P if Hkv >= P else 1)
+        self.fused_block_calls += 1
+        x2 = x[0] if x[0].is_contiguous() else x[0].contiguous()
+        recv = _QKVProjectPushPeer.apply(x2, w_qkv, ex, Hq, Hkv, D)
+        q, k, v = ops.rope_qkv(recv.view(1, S_loc * P, (Hlq + 2 * Hlkv) * D), cos, sin, Hlq, Hlkv, D)
+        o = ops.attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
+        res2 = residual.view(-1, residual.shape[-1]) if residual is not None else None
+        return _HeadToSeqProjectPeer.apply(o[0], w_out, res2, ex)[None]
+
     def attention_project(self, q, k, v, ctx: Any, w_out: torch.Tensor, residual: Optional[torch.Tensor]):
         """Attention followed by the output projection with the head -> sequence exchange done inside the projection
         GEMM.  Returns ``None`` when the fused path does not apply, so that the caller can fall back to
@@ -301,6 +377,7 @@ class UlyssesContext:
         parts = [torch.empty_like(position_ids) for _ in range(self.size)]
         dist.all_gather(parts, position_ids.contiguous(), group=self.group)
         full = torch.cat(parts, dim=1)
+        self.global_position_ids = full
         cu = cu_seqlens_from_position_ids(full)
         max_len = int((cu[1:] - cu[:-1]).max()) if cu is not None else full.shape[1]
         return cu, max_len

@@ -129,6 +129,7 @@ def main() -> None:
                        "parallelism": f"ulysses-sp{world} + zero3", "tiled_mlp": not args.no_tiled_mlp,
                        "tiled_cross_entropy": True, "activation_offload": args.act_offload, "attention": args.attn,
                        "peer_memory_exchange": bool(world > 1 and trainer.sp_context.fused),
+                       "attention_blocks_with_exchange_in_gemm": trainer.sp_context.fused_block_calls if world > 1 else 0,
                        "layers_keeping_activations": eng._keep_state.get("kept_layers", 0)},
             "max_memory_gib_per_gpu": round(float(mem), 2), "gpu_launches": ops.LAUNCH_COUNTER["native"] - launches0,
             "kernel_error_flag": err,

@@ -22,14 +22,14 @@ OVERRIDES = dict(num_hidden_layers=3, hidden_size=512, intermediate_size=1024, n
                  num_key_value_heads=2, vocab_size=4096)
 
 
-def make_engine(stage, fused, seed=0):
+def make_engine(stage, fused, seed=0, clip=1.0):
     cfg = load_arch_config("llama-3.1-8b", OVERRIDES)
     with torch.device("cuda"):
         m = CausalLM(cfg, dtype=torch.bfloat16)
     m.init_weights(seed=seed)
     m.attn_impl = "sdpa"
     opt = FusedAdamW(OptimizerFactory.get_optimizer_grouped_params(m, 0.1), lr=1e-3, betas=(0.9, 0.95))
-    return TrainingEngine(m, opt, None, {"zero_optimization": {"stage": stage}, "gradient_clipping": 1.0,
+    return TrainingEngine(m, opt, None, {"zero_optimization": {"stage": stage}, "gradient_clipping": clip,
                                          "bfloat16": {"enabled": True}, "fused_comm": "auto" if fused else "off"})
 
 
@@ -47,19 +47,30 @@ def run(engine, n=3, seed=0):
     return losses
 
 
+class pytest_approx:
+    def __init__(self, v, rel=2e-2):
+        self.v, self.rel = v, rel
+
+    def __eq__(self, other):
+        return abs(other - self.v) <= self.rel * abs(self.v)
+
+
 def scenario_fused_vs_nccl(out_dir):
     res = {}
-    for stage in (2, 3):
-        a = make_engine(stage, fused=False)
+    for stage, clip in ((2, 1.0), (3, 1.0), (3, 0.0)):
+        a = make_engine(stage, fused=False, clip=clip)
         la = run(a)
         pa = {n: t.float().clone() for n, t in a.iter_full_named_parameters()}
-        b = make_engine(stage, fused=True)
+        b = make_engine(stage, fused=True, clip=clip)
         assert b.symm is not None, "peer-memory path did not come up"
         lb = run(b)
         b.symm.check()
+        if clip == 0.0:  # without clipping the reduce-scatter feeds AdamW in the same kernel
+            assert all(b._single_pass_update_ok(u) for u in b.units if u.grad_slot is None and u.checkpointed and u.n_train > 0)
+            assert float(b.get_global_grad_norm()) == pytest_approx(float(a.get_global_grad_norm()))
         pb = {n: t.float().clone() for n, t in b.iter_full_named_parameters()}
         diff = max(float((pa[n] - pb[n]).abs().max()) for n in pa)
-        res[f"stage{stage}"] = {"nccl": la, "fused": lb, "max_param_diff": diff}
+        res[f"stage{stage}_clip{clip}"] = {"nccl": la, "fused": lb, "max_param_diff": diff}
     if dist.get_rank() == 0:
         (Path(out_dir) / "fused_vs_nccl.json").write_text(json.dumps(res))
 
@@ -155,6 +166,51 @@ def scenario_ulysses_peer(out_dir):
         (Path(out_dir) / "ulysses_peer.json").write_text(json.dumps(allres))
 
 
+def scenario_fused_attention_block(out_dir):
+    """A whole attention block under Ulysses: q|k|v projection pushing from its epilogue + rotary embedding after the
+    exchange + gathering output projection, against projection / NCCL all-to-all / attention / projection."""
+    from arctictraining_b200.models.arch import load_arch_config
+    from arctictraining_b200.models.causal_lm import CausalLM
+    from arctictraining_b200.parallel.ulysses import UlyssesContext
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    res = {}
+    for name, (Hq, Hkv) in {"kv_split": (4, 2), "kv_replicated": (4, 1)}.items():
+        cfg = load_arch_config("llama-3.1-8b", dict(num_hidden_layers=1, hidden_size=512, intermediate_size=1024,
+                                                    num_attention_heads=Hq, num_key_value_heads=Hkv, vocab_size=1024,
+                                                    head_dim=128))
+        S_loc = 256
+        got = []
+        for fused in (True, False):
+            with torch.device("cuda"):
+                m = CausalLM(cfg, dtype=torch.bfloat16)
+            m.init_weights(seed=0)
+            m.attn_impl = "native"
+            m.sp_context = UlyssesContext(dist.group.WORLD, world, rank, fused=None if fused else False)
+            attn = m.model.layers[0].self_attn
+            torch.manual_seed(7 + rank)
+            x = torch.randn(1, S_loc, 512, device="cuda", dtype=torch.bfloat16).requires_grad_(True)
+            resid = torch.randn(1, S_loc, 512, device="cuda", dtype=torch.bfloat16)
+            gout = torch.randn(1, S_loc, 512, device="cuda", dtype=torch.bfloat16)
+            pos = (torch.arange(S_loc, device="cuda") + rank * S_loc)[None]
+            ctx = m.build_context(pos)
+            for _ in range(2):
+                x.grad = None
+                m.zero_grad()
+                y = attn(x, ctx, residual=resid)
+                y.backward(gout)
+            if fused:
+                assert "rope_global" in ctx.extras, "fused attention block was not taken"
+                m.sp_context._peer.symm.check()
+            assert int(torch.ops.atb200.read_and_clear_error_flag(x)) == 0
+            got.append([t.detach().float() for t in (y, x.grad, attn.qkv_proj.weight.grad, attn.o_proj.weight.grad)])
+        res[name] = max(float((a - b).norm() / (b.norm() + 1e-12)) for a, b in zip(*got))
+    allres = [None] * world
+    dist.all_gather_object(allres, res)
+    if rank == 0:
+        (Path(out_dir) / "fused_attention_block.json").write_text(json.dumps(allres))
+
+
 def scenario_moe_peer(out_dir):
     """Expert-parallel MoE block: the peer-memory dispatch/combine gives the same output and gradients as the NCCL
     all-to-all path."""
@@ -203,9 +259,11 @@ def scenario_moe_peer(out_dir):
 def main():
     scenario, out_dir = sys.argv[1], sys.argv[2]
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+    torch._C._set_print_stack_traces_on_fatal_signal(True)  # a crash in native code reports where
     init_distributed(timeout_s=120)
     {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout,
-     "ulysses_peer": scenario_ulysses_peer, "moe_peer": scenario_moe_peer}[scenario](out_dir)
+     "ulysses_peer": scenario_ulysses_peer, "moe_peer": scenario_moe_peer,
+     "fused_attention_block": scenario_fused_attention_block}[scenario](out_dir)
     dist.barrier()
     dist.destroy_process_group()
 

@@ -52,3 +52,10 @@ def test_peer_memory_moe_exchange_matches_all_to_all(tmp_path):
     for per_rank in json.loads((tmp_path / "moe_peer.json").read_text()):
         for name, err in per_rank.items():
             assert err < 2e-2, (name, err)
+
+
+def test_attention_block_with_exchanges_inside_the_gemms(tmp_path):
+    launch(2, "fused_attention_block", tmp_path)
+    for per_rank in json.loads((tmp_path / "fused_attention_block.json").read_text()):
+        for name, err in per_rank.items():
+            assert err < 1e-2, (name, err)
