@@ -69,6 +69,20 @@ def _stale() -> bool:
         return True
 
 
+def _shared_libstdcxx_flags() -> list:
+    """Link against the system's shared libstdc++ explicitly.  A toolchain that only ships the static archive would
+    otherwise put a second copy of the C++ runtime into the extension, and stream formatting inside error messages then
+    runs on facets of the wrong copy (observed as a crash while an exception text was being built)."""
+    import glob
+
+    for pattern in ("/usr/lib/x86_64-linux-gnu/libstdc++.so.6", "/usr/lib64/libstdc++.so.6", "/usr/lib/*/libstdc++.so.6"):
+        hits = glob.glob(pattern)
+        if hits:
+            d = os.path.dirname(hits[0])
+            return [f"-L{d}", "-l:libstdc++.so.6"]
+    return []
+
+
 def build(verbose: bool = False) -> Path:
     """Compile every ``.cu``/``.cpp`` under ``csrc`` for sm_100a into one shared object."""
     from torch.utils import cpp_extension
@@ -81,7 +95,7 @@ def build(verbose: bool = False) -> Path:
         sources=sources(),
         extra_cflags=["-O3", "-std=c++17"],
         extra_cuda_cflags=NVCC_FLAGS,
-        extra_ldflags=["-lcuda"] if os.path.exists("/usr/local/cuda/lib64/stubs/libcuda.so") and False else [],
+        extra_ldflags=_shared_libstdcxx_flags(),
         extra_include_paths=[str(CSRC)],
         build_directory=str(BUILD_DIR),
         is_python_module=False,

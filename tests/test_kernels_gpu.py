@@ -525,3 +525,12 @@ def test_weight_gradient_accumulates_into_the_engine_buffer():
     Fn.linear(x, w).backward(g)
     assert w.grad is None
     assert _rel(main - 1, want) < 1e-2
+
+
+def test_argument_errors_raise_with_a_readable_message(k):
+    a = torch.randn(128, 64, device="cuda").bfloat16()
+    b = torch.randn(128, 64, device="cuda").bfloat16()
+    with pytest.raises(RuntimeError, match="unsupported epilogue 7"):
+        k.gemm_bf16(a, b, False, False, 7, None, 0, None)
+    with pytest.raises(RuntimeError, match="head_dim must be 128"):
+        k.fmha_fwd(a.view(128, 1, 64), b.view(128, 1, 64), b.view(128, 1, 64), torch.tensor([0, 128], device="cuda", dtype=torch.int32), 2, 0.1)
