@@ -41,6 +41,15 @@ constexpr uint64_t kAttnWaitNs = 2000000000ull;
 constexpr float kRescaleThreshold = 8.f;  // in log2 units
 constexpr int kAttnThreads = 320;        // TMA warp, MMA warp, eight softmax warps (two per TMEM lane quarter)
 
+#ifdef ATB_ATTN_PROFILE
+__device__ long long g_attn_prof[16];
+#define PROF_T() clock64()
+#define PROF_ADD(i, t0) do { if (prof_on) atomicAdd((unsigned long long*)&g_attn_prof[i], (unsigned long long)(clock64() - (t0))); } while (0)
+#else
+#define PROF_T() 0ll
+#define PROF_ADD(i, t0) do { (void)(t0); } while (0)
+#endif
+
 struct AttnParams {
     bf16* O;
     float* lse;           // [Hq, T]
@@ -128,6 +137,9 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     }
     if (seq < 0) return;  // padding CTA of the upper-bound grid (uniform for the whole CTA)
     const int n_kv = qb + 1;  // causal: key blocks 0..qb
+#ifdef ATB_ATTN_PROFILE
+    const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 32 || threadIdx.x == 64);
+#endif
 
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1);
@@ -200,9 +212,13 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             };
             if (ok) ok = issue_qk(0);
             for (int j = 0; j < n_kv && ok; ++j) {
+                const long long tq0 = PROF_T();
                 if (j + 1 < n_kv) ok = issue_qk(j + 1);
+                PROF_ADD(1, tq0);
                 if (!ok) break;
+                const long long tp0 = PROF_T();
                 if (!ptx::mbar_wait_bounded(p_full, j & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+                PROF_ADD(0, tp0);
                 ptx::tc_fence_after();
                 const uint32_t vs = ptx::smem_u32(smem + SMEM_KV + (j & 1) * 2 * TILE_BYTES + TILE_BYTES);
 #pragma unroll
@@ -232,7 +248,10 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         bool ok = true;
         for (int j = 0; j < n_kv && ok; ++j) {
             const int st = j & 1;
+            const long long ts0 = PROF_T();
             if (!ptx::mbar_wait_bounded(&s_full[st], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+            PROF_ADD(2, ts0);
+            PROF_ADD(8, PROF_T() - 1);
             ptx::tc_fence_after();
             const uint32_t s_addr = tmem_base + lane_addr + st * 128 + col0;
             const int kbase = j * BKV;
@@ -240,15 +259,22 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             // only the diagonal block and the block that holds the end of the sequence need masking (uniform per CTA)
             const bool need_mask = kbase + BKV > min(seqlen, qb * BQ + 1);
             // pass 1: row maximum of the scores, agreed between the two halves
+            const long long t10 = PROF_T();
             float mx = need_mask ? score_row_max<true>(s_addr, col0, klimit) : score_row_max<false>(s_addr, col0, klimit);
+            PROF_ADD(3, t10);
             xchg[(st * 2 + half) * 128 + r] = mx;
             __syncwarp();
+            const long long tx0 = PROF_T();
             if (lane == 0) ptx::mbar_arrive(&max_ready[st]);
             if (!ptx::mbar_wait_bounded(&max_ready[st], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+            PROF_ADD(4, tx0);
             mx = fmaxf(mx, xchg[(st * 2 + (half ^ 1)) * 128 + r]) * p.scale_log2;
             // previous P V must have retired before P is overwritten or O is touched
+            const long long tv0 = PROF_T();
             if (j > 0 && !ptx::mbar_wait_bounded(pv_done, (j - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+            PROF_ADD(5, tv0);
             ptx::tc_fence_after();
+            const long long tr0 = PROF_T();
             const bool grow = mx > m_used + kRescaleThreshold || m_used == -INFINITY;
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? fmaxf(mx, m_used) : m_used;
@@ -268,6 +294,8 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                 l *= alpha;
                 m_used = m_new;
             }
+            PROF_ADD(6, tr0);
+            const long long t20 = PROF_T();
             // pass 2: probabilities -> bf16 -> swizzled shared memory; running sum
             l += need_mask ? score_row_exp<true>(s_addr, col0, klimit, p.scale_log2, m_used, crow, r)
                            : score_row_exp<false>(s_addr, col0, klimit, p.scale_log2, m_used, crow, r);
@@ -278,6 +306,7 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                 ptx::mbar_arrive(&s_empty[st]);
                 ptx::mbar_arrive(p_full);
             }
+            PROF_ADD(7, t20);
         }
         if (ok && !ptx::mbar_wait_bounded(pv_done, (n_kv - 1) & 1, abort_flag, kAttnWaitNs)) ok = false;
         if (ok) {
@@ -325,6 +354,18 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
 }
 
 }  // namespace
+
+#ifdef ATB_ATTN_PROFILE
+at::Tensor fmha_read_profile() {
+    long long h[16];
+    C10_CUDA_CHECK(cudaMemcpyFromSymbol(h, g_attn_prof, sizeof(h)));
+    long long z[16] = {0};
+    C10_CUDA_CHECK(cudaMemcpyToSymbol(g_attn_prof, z, sizeof(z)));
+    auto out = at::empty({16}, at::kLong);
+    for (int i = 0; i < 16; ++i) out.data_ptr<int64_t>()[i] = h[i];
+    return out;
+}
+#endif
 
 // q [T, Hq, 128], k / v [T, Hkv, 128] bf16 (token stride may exceed heads * 128: views of a fused projection are fine),
 // cu_seqlens int32 [nseq + 1] on the device.  Returns (out [T, Hq, 128] bf16, lse [Hq, T] fp32).

@@ -30,6 +30,9 @@ void gemm_bf16_push_heads(const at::Tensor& x, const at::Tensor& w, const at::Te
 std::tuple<at::Tensor, at::Tensor> gemm_bf16_peer_a(const at::Tensor& a_ptrs, int64_t a_byte_offset, int64_t rows_total,
                                                     int64_t seg_cols, int64_t row0, int64_t M, const at::Tensor& b,
                                                     const c10::optional<at::Tensor>& residual, int64_t stage_ctas);
+#ifdef ATB_ATTN_PROFILE
+at::Tensor fmha_read_profile();
+#endif
 std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                             const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
 bool set_gemm_cta_pairs(bool on);
@@ -93,6 +96,9 @@ TORCH_LIBRARY(atb200, m) {
     m.def("read_and_clear_error_flag(Tensor like) -> int", &atb::read_and_clear_error_flag);
     m.def("gemm_bf16_push_heads(Tensor x, Tensor w, Tensor dst_ptrs, int dst_byte_offset, int rank, int Hq, int Hkv, int D) -> ()", &atb::gemm_bf16_push_heads);
     m.def("gemm_bf16_peer_a(Tensor a_ptrs, int a_byte_offset, int rows_total, int seg_cols, int row0, int M, Tensor b, Tensor? residual=None, int stage_ctas=16) -> (Tensor, Tensor)", &atb::gemm_bf16_peer_a);
+#ifdef ATB_ATTN_PROFILE
+    m.def("fmha_read_profile() -> Tensor", &atb::fmha_read_profile);
+#endif
     m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor)", &atb::fmha_fwd);
     m.def("set_gemm_cta_pairs(bool on) -> bool", &atb::set_gemm_cta_pairs);
     m.def("p2p_barrier(Tensor flag_ptrs, int rank, int slot, int epoch, float timeout_s, Tensor like) -> ()", &atb::p2p_barrier);

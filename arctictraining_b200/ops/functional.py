@@ -628,6 +628,17 @@ def adamw_step(master, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_
         _count()
         return
     gs = float(grad_scale) if grad_scale is not None else 1.0
+    if (
+        master.device.type == "cpu" and master.dtype == torch.float32 and grad.dtype == torch.float32
+        and grad.device.type == "cpu" and exp_avg.dtype == torch.float32 and exp_avg_sq.dtype == torch.float32
+        and (out_lp is None or (out_lp.device.type == "cpu" and out_lp.dtype == torch.bfloat16))
+        and master.is_contiguous() and grad.is_contiguous()
+    ):
+        from . import _ext_cpu
+
+        if _ext_cpu.available():
+            _ext_cpu.ops().cpu_adamw_step(master, grad, exp_avg, exp_avg_sq, out_lp, lr, beta1, beta2, eps, weight_decay, step, gs)
+            return
     ref.adamw_step(master, grad, exp_avg, exp_avg_sq, lr, beta1, beta2, eps, weight_decay, step, gs, out_lp)
 
 

@@ -16,7 +16,7 @@ def main() -> int:
     problems = []
     for path in ROOT.rglob("*"):
         rel = path.relative_to(ROOT)
-        if any(part in {".git", "_work", "gpurun_out", "baseline", "build", "__pycache__"} for part in rel.parts):
+        if rel.parts[0].startswith(("_", "gpu")) or any(part in {".git", "baseline", "build", "__pycache__"} for part in rel.parts):
             continue
         if path.suffix == ".py":
             try:

@@ -53,3 +53,28 @@ def test_small_helpers(capsys):
         print("hello")
     assert cs.out.strip() == "hello"
     assert get_unique_port_number() >= 10999
+
+
+def test_host_adamw_extension_matches_reference_update():
+    import torch
+
+    from arctictraining_b200.ops import _ext_cpu
+    from arctictraining_b200.ops import reference as ref
+
+    if not _ext_cpu.available():
+        import pytest
+
+        pytest.skip("no C++ compiler for the host extension")
+    torch.manual_seed(0)
+    n = 200_003  # not a multiple of the chunk or vector width
+    p, g, m = torch.randn(n), torch.randn(n) * 0.1, torch.randn(n) * 0.01
+    v = torch.rand(n) * 0.01
+    lp = torch.empty(n, dtype=torch.bfloat16)
+    p2, m2, v2 = p.clone(), m.clone(), v.clone()
+    lp2 = torch.empty(n, dtype=torch.bfloat16)
+    for step in (1, 2, 3):
+        _ext_cpu.ops().cpu_adamw_step(p, g, m, v, lp, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 0.5)
+        ref.adamw_step(p2, g, m2, v2, 1e-2, 0.9, 0.95, 1e-8, 0.1, step, 0.5, lp2)
+    assert torch.allclose(p, p2, atol=1e-6, rtol=1e-5)
+    assert torch.allclose(m, m2, atol=1e-7, rtol=1e-5) and torch.allclose(v, v2, atol=1e-9, rtol=1e-5)
+    assert (lp.float() - lp2.float()).abs().max() <= 2 ** -7 * p.abs().max()
