@@ -2,15 +2,17 @@
 //
 //   O[t, h, :] = softmax_j<=t ( Q[t, h, :] . K[j, g(h), :] * scale ) V[j, g(h), :]     within each packed sequence
 //
-// One CTA per (sequence, block of 128 queries, query head).  Warp 0 streams K/V blocks of 128 keys with TMA into a
-// two-stage shared-memory ring, warp 1 issues the two GEMMs of every block on the tensor cores (S = Q K^T into one of
-// two TMEM score buffers, O += P V into a TMEM accumulator), warps 2..5 own one query row per thread: they read the
-// scores from TMEM, keep the running maximum and sum in registers (no cross-thread reduction is needed because a
-// thread sees its whole row), write the bf16 probabilities into shared memory in the swizzled layout the tensor core
-// expects, and rescale the accumulator only when the running maximum has grown by more than 2^8 (the final division
-// by the row sum makes the result independent of which maximum was used).  The score GEMM of block j+1 overlaps the
-// softmax of block j.  Output: O (bf16) and the log-sum-exp per (head, token) in fp32, the layout the backward pass
-// of the flash-attn library expects, which serves as backward for now.
+// One CTA per (sequence, block of 128 queries, query head).  Warp 0 streams K and V blocks of 128 keys with TMA into
+// two-stage rings (K and V have their own barriers: a K slot is free again as soon as its scores are computed), warp 1
+// issues the GEMMs on the tensor cores, and two groups of four warps do the softmax: group 0 takes the even key blocks,
+// group 1 the odd ones.  Each group has its own score buffer and its own output accumulator in TMEM (4 x 128 columns),
+// its own running maximum / sum and its own probability tile in shared memory, so the groups never wait for one another
+// and the exponentials of one block overlap the barrier latencies and GEMMs of the other; the two partial results are
+// merged at the end (O = (O_0 2^(m_0 - m) + O_1 2^(m_1 - m)) / l).  A thread owns one query row: it reads the 128 scores
+// once from TMEM, needs no cross-thread reduction, writes bf16 probabilities in the swizzled layout the tensor core
+// expects, and rescales its accumulator only when the running maximum has grown by more than 2^8.
+// Output: O (bf16) and the log-sum-exp per (head, token) in fp32, the layout the backward pass of the flash-attn
+// library expects, which serves as backward for now.
 //
 // The reference obtains attention from the flash-attn package or PyTorch SDPA through Hugging Face
 // (arctic_training/config/model.py:48,85-98).  All barrier waits are bounded.
@@ -30,16 +32,16 @@ namespace {
 constexpr int BQ = 128, BKV = 128, HD = 128;
 constexpr int CHUNK_BYTES = 128 * 128;        // [128 rows][64 bf16]
 constexpr int TILE_BYTES = 2 * CHUNK_BYTES;   // 128 x 128 bf16
-constexpr int KV_STAGES = 2;
 constexpr int SMEM_Q = 0;
-constexpr int SMEM_KV = TILE_BYTES;                              // stage s: K at +s*2*TILE, V right after K
-constexpr int SMEM_P = SMEM_KV + KV_STAGES * 2 * TILE_BYTES;
-constexpr int SMEM_BAR = SMEM_P + TILE_BYTES;
-constexpr int SMEM_XCHG = SMEM_BAR + 16 * 8 + 16;       // float [2 parities][2 halves][128 rows]
-constexpr int SMEM_TOTAL = SMEM_XCHG + 2 * 2 * 128 * 4;
+constexpr int SMEM_K = TILE_BYTES;                  // two stages
+constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;     // two stages
+constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;     // one probability tile per softmax group
+constexpr int SMEM_BAR = SMEM_P + 2 * TILE_BYTES;   // 224 KB of tiles
+constexpr int SMEM_XCHG = SMEM_BAR + 24 * 8;        // float2 [2 groups][128 rows]: (maximum, sum) for the final merge
+constexpr int SMEM_TOTAL = SMEM_XCHG + 2 * 128 * 8;
 constexpr uint64_t kAttnWaitNs = 2000000000ull;
 constexpr float kRescaleThreshold = 8.f;  // in log2 units
-constexpr int kAttnThreads = 320;        // TMA warp, MMA warp, eight softmax warps (two per TMEM lane quarter)
+constexpr int kAttnThreads = 320;         // TMA warp, MMA warp, two softmax groups of four warps
 
 #ifdef ATB_ATTN_PROFILE
 __device__ long long g_attn_prof[16];
@@ -60,74 +62,31 @@ struct AttnParams {
     int* error_flag;
 };
 
-// Maximum over 64 score columns of one row in TMEM (raw, unscaled scores); columns >= klimit are ignored when MASK.
-// `col0` is the first of the 64 columns inside the 128-key block.
-template <bool MASK>
-__device__ __forceinline__ float score_row_max(uint32_t s_addr, int col0, int klimit) {
-    uint32_t a[32], b[32];
-    ptx::tmem_ld_32x32b_x32(s_addr, a);
-    ptx::tmem_ld_32x32b_x32(s_addr + 32, b);
-    ptx::tmem_ld_wait();
-    float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-    for (int i = 0; i < 32; ++i) {
-        if (!MASK || col0 + i < klimit) m0 = fmaxf(m0, __uint_as_float(a[i]));
-        if (!MASK || col0 + 32 + i < klimit) m1 = fmaxf(m1, __uint_as_float(b[i]));
-    }
-    return fmaxf(m0, m1);
-}
-
-// p = exp2(s * scale - m) for 64 columns of one row: bf16 into one 64-key chunk of the swizzled P tile (row `crow`,
-// swizzle phase r & 7); returns the sum of the 64 probabilities.
-template <bool MASK>
-__device__ __forceinline__ float score_row_exp(uint32_t s_addr, int col0, int klimit, float scale, float m, uint8_t* crow,
-                                               int r) {
-    uint32_t a[32], b[32];
-    ptx::tmem_ld_32x32b_x32(s_addr, a);
-    ptx::tmem_ld_32x32b_x32(s_addr + 32, b);
-    ptx::tmem_ld_wait();
-    float l0 = 0.f, l1 = 0.f;
-#pragma unroll
-    for (int u = 0; u < 8; ++u) {  // eight 16-byte units of 8 probabilities
-        float f8[8];
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-            const int col = u * 8 + i;  // 0..63 inside the chunk
-            const float sv = __uint_as_float(col < 32 ? a[col & 31] : b[col & 31]);
-            float e = exp2f(fmaf(sv, scale, -m));
-            if (MASK && col0 + col >= klimit) e = 0.f;
-            f8[i] = e;
-            if (i & 1) l1 += e; else l0 += e;
-        }
-        *reinterpret_cast<bf16x8*>(crow + ((u ^ (r & 7)) << 4)) = pack8(f8);
-    }
-    return l0 + l1;
-}
-
 __global__ void __launch_bounds__(kAttnThreads, 1)
 fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid_constant__ CUtensorMap tmap_k,
                         const __grid_constant__ CUtensorMap tmap_v, const AttnParams p) {
-    extern __shared__ __align__(1024) uint8_t smem_raw[];
-    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    extern __shared__ __align__(1024) uint8_t smem[];
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_BAR);
-    uint64_t* q_full = bars;            // 1
-    uint64_t* kv_full = bars + 1;       // [2]
-    uint64_t* kv_empty = bars + 3;      // [2]
-    uint64_t* s_full = bars + 5;        // [2]
-    uint64_t* s_empty = bars + 7;       // [2]
-    uint64_t* p_full = bars + 9;        // 1
-    uint64_t* pv_done = bars + 10;      // 1
-    uint64_t* max_ready = bars + 11;    // [2]: both column halves have published their row maxima
-    float* xchg = reinterpret_cast<float*>(smem + SMEM_XCHG);
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 16);
+    uint64_t* q_full = bars;          // 1
+    uint64_t* k_full = bars + 1;      // [2]
+    uint64_t* k_empty = bars + 3;     // [2]
+    uint64_t* v_full = bars + 5;      // [2]
+    uint64_t* v_empty = bars + 7;     // [2]
+    uint64_t* s_full = bars + 9;      // [2] scores of a block are in the group's TMEM buffer
+    uint64_t* s_empty = bars + 11;    // [2] the group has copied the scores into registers
+    uint64_t* p_full = bars + 13;     // [2] the group's probability tile is written
+    uint64_t* pv_done = bars + 15;    // [2] the group's last P V has retired
+    uint64_t* merge_ready = bars + 17;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 20);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float2* xchg = reinterpret_cast<float2*>(smem + SMEM_XCHG);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int h = blockIdx.y;
     const int hkv = h / (p.Hq / p.Hkv);
 
-    // ---- which (sequence, query block) is this CTA?  longest (most key blocks) first within the launch order
-    int rem = (int)(gridDim.x - 1 - blockIdx.x);
+    // ---- which (sequence, query block) is this CTA?  Blocks with the most key blocks come first in launch order.
+    int rem = (int)blockIdx.x;
     int seq = -1, qb = 0, tok0 = 0, seqlen = 0;
     for (int s = p.nseq - 1; s >= 0; --s) {
         const int a = p.cu_seqlens[s], b = p.cu_seqlens[s + 1];
@@ -136,6 +95,10 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         rem -= nb;
     }
     if (seq < 0) return;  // padding CTA of the upper-bound grid (uniform for the whole CTA)
+    if ((ptx::smem_u32(smem) & 1023u) != 0) {  // the swizzled tiles need 1024-byte alignment
+        if (threadIdx.x == 0) atomicCAS(p.error_flag, 0, (0x20 << 8) | 1);
+        return;
+    }
     const int n_kv = qb + 1;  // causal: key blocks 0..qb
 #ifdef ATB_ATTN_PROFILE
     const bool prof_on = blockIdx.x == 0 && blockIdx.y == 0 && (threadIdx.x & 31) == 0 && (threadIdx.x == 32 || threadIdx.x == 64);
@@ -144,14 +107,16 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     if (threadIdx.x == 0) {
         ptx::mbar_init(q_full, 1);
         for (int i = 0; i < 2; ++i) {
-            ptx::mbar_init(&kv_full[i], 1);
-            ptx::mbar_init(&kv_empty[i], 1);
+            ptx::mbar_init(&k_full[i], 1);
+            ptx::mbar_init(&k_empty[i], 1);
+            ptx::mbar_init(&v_full[i], 1);
+            ptx::mbar_init(&v_empty[i], 1);
             ptx::mbar_init(&s_full[i], 1);
-            ptx::mbar_init(&s_empty[i], 8);
-            ptx::mbar_init(&max_ready[i], 8);
+            ptx::mbar_init(&s_empty[i], 4);
+            ptx::mbar_init(&p_full[i], 4);
+            ptx::mbar_init(&pv_done[i], 1);
         }
-        ptx::mbar_init(p_full, 8);
-        ptx::mbar_init(pv_done, 1);
+        ptx::mbar_init(merge_ready, 8);
         *abort_flag = 0;
         ptx::fence_barrier_init();
         ptx::fence_proxy_async_smem();
@@ -163,44 +128,56 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
     ptx::tc_fence_before();
     __syncthreads();
     ptx::tc_fence_after();
-    const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_o = tmem_base + 256;
+    const uint32_t tmem_base = *tmem_slot;  // columns: S_0 [0,128) S_1 [128,256) O_0 [256,384) O_1 [384,512)
 
     if (warp == 0) {
+        // Two independent producers: lane 0 streams Q and the K ring, lane 1 the V ring.  A K slot is free as soon as
+        // the scores of its block are computed, a V slot only after the block's P V: with one thread feeding both rings
+        // in order the next K would wait behind the V slot and its load latency would be exposed in every iteration.
         if (lane == 0) {
             ptx::tma_prefetch_desc(&tmap_q);
             ptx::tma_prefetch_desc(&tmap_k);
-            ptx::tma_prefetch_desc(&tmap_v);
             ptx::mbar_expect_tx(q_full, TILE_BYTES);
             for (int c = 0; c < 2; ++c)
                 ptx::tma_load_2d(smem + SMEM_Q + c * CHUNK_BYTES, &tmap_q, h * HD + c * 64, tok0 + qb * BQ, q_full);
             for (int j = 0; j < n_kv; ++j) {
                 const int st = j & 1;
-                if (!ptx::mbar_wait_bounded(&kv_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag, kAttnWaitNs)) {
+                if (!ptx::mbar_wait_bounded(&k_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag, kAttnWaitNs)) {
                     atomicCAS(p.error_flag, 0, (0x21 << 8) | 1);
                     break;
                 }
-                uint8_t* ks = smem + SMEM_KV + st * 2 * TILE_BYTES;
-                uint8_t* vs = ks + TILE_BYTES;
-                ptx::mbar_expect_tx(&kv_full[st], 2 * TILE_BYTES);
-                for (int c = 0; c < 2; ++c) {
-                    ptx::tma_load_2d(ks + c * CHUNK_BYTES, &tmap_k, hkv * HD + c * 64, tok0 + j * BKV, &kv_full[st]);
-                    ptx::tma_load_2d(vs + c * CHUNK_BYTES, &tmap_v, hkv * HD + c * 64, tok0 + j * BKV, &kv_full[st]);
+                ptx::mbar_expect_tx(&k_full[st], TILE_BYTES);
+                for (int c = 0; c < 2; ++c)
+                    ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + c * CHUNK_BYTES, &tmap_k, hkv * HD + c * 64, tok0 + j * BKV,
+                                     &k_full[st]);
+            }
+        } else if (lane == 1) {
+            ptx::tma_prefetch_desc(&tmap_v);
+            for (int j = 0; j < n_kv; ++j) {
+                const int st = j & 1;
+                if (!ptx::mbar_wait_bounded(&v_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag, kAttnWaitNs)) {
+                    atomicCAS(p.error_flag, 0, (0x21 << 8) | 2);
+                    break;
                 }
+                ptx::mbar_expect_tx(&v_full[st], TILE_BYTES);
+                for (int c = 0; c < 2; ++c)
+                    ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES + c * CHUNK_BYTES, &tmap_v, hkv * HD + c * 64, tok0 + j * BKV,
+                                     &v_full[st]);
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             constexpr uint32_t idesc_qk = ptx::make_idesc_bf16(BQ, BKV, false, false);
             constexpr uint32_t idesc_pv = ptx::make_idesc_bf16(BQ, HD, false, true);
-            const uint32_t qs = ptx::smem_u32(smem + SMEM_Q), ps = ptx::smem_u32(smem + SMEM_P);
+            const uint32_t qs = ptx::smem_u32(smem + SMEM_Q);
             bool ok = ptx::mbar_wait_bounded(q_full, 0, abort_flag, kAttnWaitNs);
-            auto issue_qk = [&](int j) -> bool {
+            auto issue_qk = [&](int j) -> bool {  // S_{j&1} = Q K_j^T
                 const int st = j & 1;
-                if (!ptx::mbar_wait_bounded(&kv_full[st], (j >> 1) & 1, abort_flag, kAttnWaitNs)) return false;
-                if (!ptx::mbar_wait_bounded(&s_empty[st], ((j >> 1) & 1) ^ 1u, abort_flag, kAttnWaitNs)) return false;
+                const uint32_t ph = (j >> 1) & 1;
+                if (!ptx::mbar_wait_bounded(&k_full[st], ph, abort_flag, kAttnWaitNs)) return false;
+                if (!ptx::mbar_wait_bounded(&s_empty[st], ph ^ 1u, abort_flag, kAttnWaitNs)) return false;
                 ptx::tc_fence_after();
-                const uint32_t ks = ptx::smem_u32(smem + SMEM_KV + st * 2 * TILE_BYTES);
+                const uint32_t ks = ptx::smem_u32(smem + SMEM_K + st * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < HD / 16; ++k) {
                     const uint32_t off = (k >> 2) * CHUNK_BYTES + (k & 3) * 32;
@@ -208,70 +185,90 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
                                      ptx::make_smem_desc_sw128(ks + off, 16, 1024), idesc_qk, k != 0);
                 }
                 ptx::mma_commit(&s_full[st]);
+                ptx::mma_commit(&k_empty[st]);
                 return true;
             };
-            if (ok) ok = issue_qk(0);
-            for (int j = 0; j < n_kv && ok; ++j) {
-                const long long tq0 = PROF_T();
-                if (j + 1 < n_kv) ok = issue_qk(j + 1);
-                PROF_ADD(1, tq0);
-                if (!ok) break;
+            auto issue_pv = [&](int j) -> bool {  // O_{j&1} += P_{j&1} V_j
+                const int st = j & 1;
+                const uint32_t ph = (j >> 1) & 1;
                 const long long tp0 = PROF_T();
-                if (!ptx::mbar_wait_bounded(p_full, j & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+                if (!ptx::mbar_wait_bounded(&p_full[st], ph, abort_flag, kAttnWaitNs)) return false;
                 PROF_ADD(0, tp0);
+                if (!ptx::mbar_wait_bounded(&v_full[st], ph, abort_flag, kAttnWaitNs)) return false;
                 ptx::tc_fence_after();
-                const uint32_t vs = ptx::smem_u32(smem + SMEM_KV + (j & 1) * 2 * TILE_BYTES + TILE_BYTES);
+                const uint32_t ps = ptx::smem_u32(smem + SMEM_P + st * TILE_BYTES);
+                const uint32_t vs = ptx::smem_u32(smem + SMEM_V + st * TILE_BYTES);
 #pragma unroll
                 for (int k = 0; k < BKV / 16; ++k) {
                     const uint32_t poff = (k >> 2) * CHUNK_BYTES + (k & 3) * 32;
-                    ptx::mma_bf16_ss(tmem_o, ptx::make_smem_desc_sw128(ps + poff, 16, 1024),
-                                     ptx::make_smem_desc_sw128(vs + k * 2048, CHUNK_BYTES, 1024), idesc_pv, (j | k) != 0);
+                    ptx::mma_bf16_ss(tmem_base + 256 + st * 128, ptx::make_smem_desc_sw128(ps + poff, 16, 1024),
+                                     ptx::make_smem_desc_sw128(vs + k * 2048, CHUNK_BYTES, 1024), idesc_pv, (j >= 2 || k != 0) ? 1u : 0u);
                 }
-                ptx::mma_commit(pv_done);
-                ptx::mma_commit(&kv_empty[j & 1]);
+                ptx::mma_commit(&pv_done[st]);
+                ptx::mma_commit(&v_empty[st]);
+                return true;
+            };
+            if (ok) ok = issue_qk(0);
+            if (ok && n_kv > 1) ok = issue_qk(1);
+            for (int j = 0; j < n_kv && ok; ++j) {
+                const long long tq0 = PROF_T();
+                if (j + 2 < n_kv) ok = issue_qk(j + 2);  // needs only that the group has copied S_j out of TMEM
+                PROF_ADD(1, tq0);
+                if (ok) ok = issue_pv(j);
             }
             if (!ok) atomicCAS(p.error_flag, 0, (0x22 << 8) | 1);
         }
     } else {
-        // ------------------------------------------------------------------ softmax / correction / epilogue
-        // Two warps share each TMEM lane quarter: for the same 32 query rows one takes key columns 0..63 of every block
-        // (and head-dim columns 0..63 of O), the other the upper halves.  They agree on the row maximum through shared
-        // memory once per block; the row sums are combined at the end.
-        const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        // ------------------------------------------------------------------ softmax groups / merge / epilogue
+        const int g = (warp - 2) >> 2;              // group: key blocks j with j % 2 == g
+        const int quarter = warp & 3;               // TMEM lane quarter this warp may access
         const int r = quarter * 32 + lane;          // row of the query block owned by this thread
         const int qidx = qb * BQ + r;               // position inside the sequence
         const uint32_t lane_addr = (uint32_t)(quarter * 32) << 16;
-        const int col0 = half * 64;
-        uint8_t* crow = smem + SMEM_P + half * CHUNK_BYTES + r * 128;  // row r of this half's 64-key chunk of P
+        const uint32_t s_addr = tmem_base + lane_addr + g * 128;
+        const uint32_t o_addr = tmem_base + lane_addr + 256 + g * 128;
+        uint8_t* prow = smem + SMEM_P + g * TILE_BYTES + r * 128;  // row r of both 64-key chunks of the group's P tile
+        const int n_mine = (n_kv - g + 1) / 2;      // blocks of this group
         float m_used = -INFINITY, l = 0.f;
         bool ok = true;
-        for (int j = 0; j < n_kv && ok; ++j) {
-            const int st = j & 1;
+        for (int it = 0; it < n_mine && ok; ++it) {
+            const int j = 2 * it + g;
+            const uint32_t ph = it & 1;
             const long long ts0 = PROF_T();
-            if (!ptx::mbar_wait_bounded(&s_full[st], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+            if (!ptx::mbar_wait_bounded(&s_full[g], ph, abort_flag, kAttnWaitNs)) { ok = false; break; }
             PROF_ADD(2, ts0);
             PROF_ADD(8, PROF_T() - 1);
             ptx::tc_fence_after();
-            const uint32_t s_addr = tmem_base + lane_addr + st * 128 + col0;
+            const long long t10 = PROF_T();
+            uint32_t s[128];
+#pragma unroll
+            for (int c = 0; c < 4; ++c) ptx::tmem_ld_32x32b_x32(s_addr + c * 32, *reinterpret_cast<uint32_t(*)[32]>(&s[c * 32]));
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(&s_empty[g]);  // the next scores of this group may be computed
             const int kbase = j * BKV;
             const int klimit = min(seqlen, qidx + 1) - kbase;  // columns c < klimit are visible to this row
             // only the diagonal block and the block that holds the end of the sequence need masking (uniform per CTA)
             const bool need_mask = kbase + BKV > min(seqlen, qb * BQ + 1);
-            // pass 1: row maximum of the scores, agreed between the two halves
-            const long long t10 = PROF_T();
-            float mx = need_mask ? score_row_max<true>(s_addr, col0, klimit) : score_row_max<false>(s_addr, col0, klimit);
+            float mx0 = -INFINITY, mx1 = -INFINITY, mx2 = -INFINITY, mx3 = -INFINITY;
+            if (need_mask) {
+#pragma unroll
+                for (int i = 0; i < 128; ++i)
+                    if (i >= klimit) s[i] = 0xff800000u;  // -inf
+            }
+#pragma unroll
+            for (int i = 0; i < 32; ++i) {
+                mx0 = fmaxf(mx0, __uint_as_float(s[i]));
+                mx1 = fmaxf(mx1, __uint_as_float(s[32 + i]));
+                mx2 = fmaxf(mx2, __uint_as_float(s[64 + i]));
+                mx3 = fmaxf(mx3, __uint_as_float(s[96 + i]));
+            }
+            const float mx = fmaxf(fmaxf(mx0, mx1), fmaxf(mx2, mx3)) * p.scale_log2;
             PROF_ADD(3, t10);
-            xchg[(st * 2 + half) * 128 + r] = mx;
-            __syncwarp();
-            const long long tx0 = PROF_T();
-            if (lane == 0) ptx::mbar_arrive(&max_ready[st]);
-            if (!ptx::mbar_wait_bounded(&max_ready[st], (j >> 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
-            PROF_ADD(4, tx0);
-            mx = fmaxf(mx, xchg[(st * 2 + (half ^ 1)) * 128 + r]) * p.scale_log2;
-            // previous P V must have retired before P is overwritten or O is touched
+            // the group's previous P V must have retired before its P tile is overwritten or its accumulator is touched
             const long long tv0 = PROF_T();
-            if (j > 0 && !ptx::mbar_wait_bounded(pv_done, (j - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
+            if (it > 0 && !ptx::mbar_wait_bounded(&pv_done[g], (it - 1) & 1, abort_flag, kAttnWaitNs)) { ok = false; break; }
             PROF_ADD(5, tv0);
             ptx::tc_fence_after();
             const long long tr0 = PROF_T();
@@ -279,15 +276,15 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             if (__any_sync(0xffffffffu, grow)) {
                 const float m_new = grow ? fmaxf(mx, m_used) : m_used;
                 const float alpha = (m_used == -INFINITY) ? 0.f : exp2f(m_used - m_new);
-                if (j > 0) {
+                if (it > 0) {
 #pragma unroll 1
-                    for (int c = 0; c < 2; ++c) {
+                    for (int c = 0; c < 4; ++c) {
                         uint32_t v[32];
-                        ptx::tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, v);
+                        ptx::tmem_ld_32x32b_x32(o_addr + c * 32, v);
                         ptx::tmem_ld_wait();
 #pragma unroll
                         for (int i = 0; i < 32; ++i) v[i] = __float_as_uint(__uint_as_float(v[i]) * alpha);
-                        ptx::tmem_st_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, v);
+                        ptx::tmem_st_32x32b_x32(o_addr + c * 32, v);
                     }
                     ptx::tmem_st_wait();
                 }
@@ -296,51 +293,73 @@ fmha_fwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
             }
             PROF_ADD(6, tr0);
             const long long t20 = PROF_T();
-            // pass 2: probabilities -> bf16 -> swizzled shared memory; running sum
-            l += need_mask ? score_row_exp<true>(s_addr, col0, klimit, p.scale_log2, m_used, crow, r)
-                           : score_row_exp<false>(s_addr, col0, klimit, p.scale_log2, m_used, crow, r);
+            // probabilities -> bf16 -> swizzled shared memory; running sum (masked scores are -inf: exp2 gives 0)
+            float l0 = 0.f, l1 = 0.f;
+#pragma unroll
+            for (int u = 0; u < 16; ++u) {  // sixteen 16-byte units of 8 probabilities
+                float f8[8];
+#pragma unroll
+                for (int i = 0; i < 8; ++i) {
+                    const float e = exp2f(fmaf(__uint_as_float(s[u * 8 + i]), p.scale_log2, -m_used));
+                    f8[i] = e;
+                    if (i & 1) l1 += e; else l0 += e;
+                }
+                *reinterpret_cast<bf16x8*>(prow + (u >> 3) * CHUNK_BYTES + (((u & 7) ^ (r & 7)) << 4)) = pack8(f8);
+            }
+            l += l0 + l1;
             ptx::tc_fence_before();
             ptx::fence_proxy_async_smem();  // generic-proxy writes of P become visible to the tensor core
             __syncwarp();
-            if (lane == 0) {
-                ptx::mbar_arrive(&s_empty[st]);
-                ptx::mbar_arrive(p_full);
-            }
+            if (lane == 0) ptx::mbar_arrive(&p_full[g]);
             PROF_ADD(7, t20);
         }
-        if (ok && !ptx::mbar_wait_bounded(pv_done, (n_kv - 1) & 1, abort_flag, kAttnWaitNs)) ok = false;
+        // ---- merge the two groups' partial results; group g stores head-dim columns [64 g, 64 g + 64)
+        if (ok && n_mine > 0 && !ptx::mbar_wait_bounded(&pv_done[g], (n_mine - 1) & 1, abort_flag, kAttnWaitNs)) ok = false;
+        const int n_other = n_kv - n_mine;
+        if (ok && n_other > 0 && !ptx::mbar_wait_bounded(&pv_done[g ^ 1], (n_other - 1) & 1, abort_flag, kAttnWaitNs)) ok = false;
         if (ok) {
-            // combine the row sums of the two halves (both used the same maxima); parity slot of a block not in use
-            const int st = n_kv & 1;
-            xchg[(st * 2 + half) * 128 + r] = l;
+            xchg[g * 128 + r] = make_float2(m_used, l);
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(&max_ready[st]);
-            if (!ptx::mbar_wait_bounded(&max_ready[st], (n_kv >> 1) & 1, abort_flag, kAttnWaitNs)) ok = false;
-            else l += xchg[(st * 2 + (half ^ 1)) * 128 + r];
+            if (lane == 0) ptx::mbar_arrive(merge_ready);
+            if (!ptx::mbar_wait_bounded(merge_ready, 0, abort_flag, kAttnWaitNs)) ok = false;
         }
         if (!ok) {
             if (lane == 0) atomicCAS(p.error_flag, 0, (0x23 << 8) | 1);
         } else {
             ptx::tc_fence_after();
-            const float inv_l = 1.f / l;
+            const float2 other = xchg[(g ^ 1) * 128 + r];
+            const float m = fmaxf(m_used, other.x);
+            const float a_self = n_mine > 0 ? exp2f(m_used - m) : 0.f;
+            const float a_other = n_other > 0 ? exp2f(other.x - m) : 0.f;
+            const float l_tot = l * a_self + other.y * a_other;
+            const float inv_l = 1.f / l_tot;
+            const float w_self = a_self * inv_l, w_other = a_other * inv_l;
             const bool valid = qidx < seqlen;
-            bf16* orow = p.O + (int64_t)(tok0 + qidx) * p.o_row_stride + (int64_t)h * HD + col0;
+            const uint32_t o_self = tmem_base + lane_addr + 256 + g * 128 + g * 64;
+            const uint32_t o_oth = tmem_base + lane_addr + 256 + (g ^ 1) * 128 + g * 64;
+            bf16* orow = p.O + (int64_t)(tok0 + qidx) * p.o_row_stride + (int64_t)h * HD + g * 64;
 #pragma unroll 1
             for (int c = 0; c < 2; ++c) {
-                uint32_t v[32];
-                ptx::tmem_ld_32x32b_x32(tmem_o + lane_addr + col0 + c * 32, v);
+                uint32_t a[32], b[32];
+                if (n_mine > 0) ptx::tmem_ld_32x32b_x32(o_self + c * 32, a);
+                if (n_other > 0) ptx::tmem_ld_32x32b_x32(o_oth + c * 32, b);
                 ptx::tmem_ld_wait();
                 if (valid) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
                         float f8[8];
 #pragma unroll
-                        for (int i = 0; i < 8; ++i) f8[i] = __uint_as_float(v[u * 8 + i]) * inv_l;
+                        for (int i = 0; i < 8; ++i) {
+                            float acc = 0.f;
+                            if (n_mine > 0) acc = __uint_as_float(a[u * 8 + i]) * w_self;
+                            if (n_other > 0) acc = fmaf(__uint_as_float(b[u * 8 + i]), w_other, acc);
+                            f8[i] = acc;
+                        }
                         *reinterpret_cast<bf16x8*>(orow + c * 32 + u * 8) = pack8(f8);
                     }
                 }
             }
-            if (valid && half == 0) p.lse[(int64_t)h * p.T + tok0 + qidx] = (m_used + log2f(l)) * 0.6931471805599453f;
+            if (valid && g == 0) p.lse[(int64_t)h * p.T + tok0 + qidx] = (m + log2f(l_tot)) * 0.6931471805599453f;
         }
     }
 
@@ -400,7 +419,7 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
     p.scale_log2 = (float)(softmax_scale * 1.4426950408889634);
     p.error_flag = gemm_error_flag(q.device()).data_ptr<int>();
     static bool attr_set = false;
-    constexpr int smem_bytes = SMEM_TOTAL + 1024;
+    constexpr int smem_bytes = SMEM_TOTAL;
     if (!attr_set) {
         C10_CUDA_CHECK(cudaFuncSetAttribute(fmha_fwd_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_bytes));
         attr_set = true;
