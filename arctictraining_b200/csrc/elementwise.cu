@@ -12,34 +12,74 @@
 namespace atb {
 
 // ---------------------------------------------------------------------------------------------
-// RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * w ; one CTA per row.
+// RMSNorm forward: y = x * rsqrt(mean(x^2) + eps) * w.  A CTA of 128 threads walks rows blockIdx.x, + gridDim.x, ...;
+// a row lives in registers between the reduction and the scaling (one read of x), the weight vector is read once per
+// CTA, and the next row is already in flight while the current one is reduced.
 // ---------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(256) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
-                                                          bf16* __restrict__ y, float* __restrict__ rstd, int H,
+template <int VPT>
+__global__ void __launch_bounds__(128) rmsnorm_fwd_kernel(const bf16* __restrict__ x, const bf16* __restrict__ w,
+                                                          bf16* __restrict__ y, float* __restrict__ rstd, int64_t T, int H,
                                                           float eps) {
-    __shared__ float scratch[32];
-    const int64_t row = blockIdx.x;
-    const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * H);
-    const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
-    bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * H);
+    __shared__ float scratch[2][4];
     const int nvec = H >> 3;
-    float ss = 0.f;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-        float f[8];
-        unpack8(xr[i], f);
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float wreg[VPT][8];
+    const bf16x8* wr = reinterpret_cast<const bf16x8*>(w);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) ss += f[j] * f[j];
+    for (int v = 0; v < VPT; ++v) {
+        const int i = threadIdx.x + v * 128;
+        if (i < nvec) unpack8(wr[i], wreg[v]);
     }
-    ss = block_sum(ss, scratch);
-    const float r = rsqrtf(ss / (float)H + eps);
-    if (threadIdx.x == 0 && rstd != nullptr) rstd[row] = r;
-    for (int i = threadIdx.x; i < nvec; i += blockDim.x) {
-        float f[8], g[8];
-        unpack8(xr[i], f);
-        unpack8(wr[i], g);
+    bf16x8 cur[VPT], nxt[VPT];
+    int64_t row = blockIdx.x;
+    if (row < T) {
+        const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * H);
 #pragma unroll
-        for (int j = 0; j < 8; ++j) f[j] = f[j] * r * g[j];
-        yr[i] = pack8(f);
+        for (int v = 0; v < VPT; ++v) {
+            const int i = threadIdx.x + v * 128;
+            if (i < nvec) cur[v] = xr[i];
+        }
+    }
+    int parity = 0;
+    for (; row < T; row += gridDim.x, parity ^= 1) {
+        const int64_t next = row + gridDim.x;
+        if (next < T) {
+            const bf16x8* xn = reinterpret_cast<const bf16x8*>(x + next * H);
+#pragma unroll
+            for (int v = 0; v < VPT; ++v) {
+                const int i = threadIdx.x + v * 128;
+                if (i < nvec) nxt[v] = xn[i];
+            }
+        }
+        float f[VPT][8];
+        float ss = 0.f;
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int i = threadIdx.x + v * 128;
+            if (i < nvec) {
+                unpack8(cur[v], f[v]);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) ss += f[v][j] * f[v][j];
+            }
+        }
+        ss = warp_sum(ss);
+        if (lane == 0) scratch[parity][warp] = ss;
+        __syncthreads();  // one barrier per row: the scratch slots alternate
+        ss = scratch[parity][0] + scratch[parity][1] + scratch[parity][2] + scratch[parity][3];
+        const float r = rsqrtf(ss / (float)H + eps);
+        if (threadIdx.x == 0 && rstd != nullptr) rstd[row] = r;
+        bf16x8* yr = reinterpret_cast<bf16x8*>(y + row * H);
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int i = threadIdx.x + v * 128;
+            if (i < nvec) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) f[v][j] = f[v][j] * r * wreg[v][j];
+                yr[i] = pack8(f[v]);
+            }
+        }
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) cur[v] = nxt[v];
     }
 }
 
@@ -247,16 +287,27 @@ std::tuple<at::Tensor, at::Tensor> rmsnorm_fwd(const at::Tensor& x, const at::Te
     ATB_CHECK_CUDA(x); ATB_CHECK_CONTIG(x); ATB_CHECK_CONTIG(w);
     ATB_CHECK_DTYPE(x, at::kBFloat16); ATB_CHECK_DTYPE(w, at::kBFloat16);
     const int H = (int)x.size(-1);
-    TORCH_CHECK(H % 8 == 0 && w.numel() == H, "rmsnorm: hidden size must be a multiple of 8 and match the weight");
+    TORCH_CHECK(H % 8 == 0 && H <= 16384 && w.numel() == H, "rmsnorm: hidden size must be a multiple of 8, at most 16384, and match the weight");
     ATB_CHECK_ALIGNED16(x); ATB_CHECK_ALIGNED16(w);
     const int64_t T = x.numel() / H;
     c10::cuda::CUDAGuard guard(x.device());
     auto y = at::empty_like(x);
     auto rstd = at::empty({T}, x.options().dtype(at::kFloat));
     if (T > 0) {
-        rmsnorm_fwd_kernel<<<(unsigned)T, 256, 0, current_stream()>>>(
-            (const bf16*)x.data_ptr(), (const bf16*)w.data_ptr(), (bf16*)y.data_ptr(), rstd.data_ptr<float>(), H,
-            (float)eps);
+        const int nvec = H / 8;
+        const int vpt = (int)ceil_div(nvec, 128);
+        const unsigned grid = (unsigned)std::min<int64_t>(T, (int64_t)kNumSMs * 16);
+        auto launch = [&](auto tag) {
+            constexpr int V = decltype(tag)::value;
+            rmsnorm_fwd_kernel<V><<<grid, 128, 0, current_stream()>>>(
+                (const bf16*)x.data_ptr(), (const bf16*)w.data_ptr(), (bf16*)y.data_ptr(), rstd.data_ptr<float>(), T, H,
+                (float)eps);
+        };
+        if (vpt <= 1) launch(std::integral_constant<int, 1>{});
+        else if (vpt <= 2) launch(std::integral_constant<int, 2>{});
+        else if (vpt <= 4) launch(std::integral_constant<int, 4>{});
+        else if (vpt <= 8) launch(std::integral_constant<int, 8>{});
+        else launch(std::integral_constant<int, 16>{});
         ATB_LAUNCH_CHECK();
     }
     return {y, rstd};

@@ -24,9 +24,29 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
         for (int j = 0; j < 8; ++j) dwacc[v][j] = 0.f;
         if (i < nvec) unpack8(wr[i], wreg[v]);
     }
+    // the raw vectors of the next row are requested before the current row's block-wide reduction, so that memory
+    // latency overlaps the barriers
+    bf16x8 xc[VPT], gc[VPT], xn[VPT], gn[VPT];
+    if ((int64_t)blockIdx.x < T) {
+        const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + (int64_t)blockIdx.x * H);
+        const bf16x8* gr = reinterpret_cast<const bf16x8*>(dy + (int64_t)blockIdx.x * H);
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) {
+            const int i = threadIdx.x + v * 256;
+            if (i < nvec) { xc[v] = xr[i]; gc[v] = gr[i]; }
+        }
+    }
     for (int64_t row = blockIdx.x; row < T; row += gridDim.x) {
-        const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + row * H);
-        const bf16x8* gr = reinterpret_cast<const bf16x8*>(dy + row * H);
+        const int64_t next = row + gridDim.x;
+        if (next < T) {
+            const bf16x8* xr = reinterpret_cast<const bf16x8*>(x + next * H);
+            const bf16x8* gr = reinterpret_cast<const bf16x8*>(dy + next * H);
+#pragma unroll
+            for (int v = 0; v < VPT; ++v) {
+                const int i = threadIdx.x + v * 256;
+                if (i < nvec) { xn[v] = xr[i]; gn[v] = gr[i]; }
+            }
+        }
         bf16x8* dxr = reinterpret_cast<bf16x8*>(dx + row * H);
         const float r = rstd[row];
         float xf[VPT][8], gf[VPT][8];
@@ -35,8 +55,8 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
         for (int v = 0; v < VPT; ++v) {
             const int i = threadIdx.x + v * 256;
             if (i < nvec) {
-                unpack8(xr[i], xf[v]);
-                unpack8(gr[i], gf[v]);
+                unpack8(xc[v], xf[v]);
+                unpack8(gc[v], gf[v]);
 #pragma unroll
                 for (int j = 0; j < 8; ++j) {
                     dwacc[v][j] += gf[v][j] * xf[v][j] * r;
@@ -57,6 +77,8 @@ __global__ void __launch_bounds__(256) rmsnorm_bwd_kernel(const bf16* __restrict
                 dxr[i] = pack8(o);
             }
         }
+#pragma unroll
+        for (int v = 0; v < VPT; ++v) { xc[v] = xn[v]; gc[v] = gn[v]; }
     }
     float* out = dw_partial + (int64_t)blockIdx.x * H;
 #pragma unroll
