@@ -536,7 +536,7 @@ class TrainingEngine:
         free right now, the measured activation bytes per token and the measured head-room that the rest of a
         step needs on top of what is allocated when the first layer starts."""
         mode = self.cfg.activation_checkpoint_keep
-        if not mode or getattr(u, "expert_unit", None) is not None or not getattr(u, "keep_ok", True):
+        if not mode or not getattr(u, "keep_ok", True):
             return False
         wrapped = self._wrapped_units
         if mode != "auto":
@@ -602,6 +602,7 @@ class TrainingEngine:
         self._prepare_grad_buffer(u)
         exp = getattr(u, "expert_unit", None)
         if exp is not None:
+            self._ensure_resident(exp)
             self._prepare_grad_buffer(exp)
 
     def _prepare_grad_buffer(self, u: ZeroUnit) -> None:
@@ -1095,6 +1096,8 @@ class _UnitEnter(torch.autograd.Function):
     def forward(ctx, engine: "TrainingEngine", unit: ZeroUnit, dummy, x):
         ctx.engine, ctx.unit = engine, unit
         engine._ensure_resident(unit, engine._neighbour(unit, +1))
+        if getattr(unit, "expert_unit", None) is not None:
+            engine._ensure_resident(unit.expert_unit)
         return x.view_as(x)
 
     @staticmethod

@@ -31,7 +31,7 @@ def build(verbose: bool = False) -> Path:
     cpp_extension.load(
         name=LIB_NAME,
         sources=sorted(str(p) for p in CSRC.glob("*.cpp")),
-        extra_cflags=["-O3", "-std=c++17", "-fopenmp-simd", "-ffast-math", "-fno-finite-math-only"],
+        extra_cflags=["-O3", "-std=c++17", "-fopenmp-simd", "-ffp-contract=off"],
         extra_ldflags=_shared_libstdcxx_flags(),
         build_directory=str(BUILD_DIR),
         is_python_module=False,
