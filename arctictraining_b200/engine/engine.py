@@ -832,7 +832,7 @@ class TrainingEngine:
         for u in self.units:
             if u.grad_acc is None or not u.grad_acc_valid:
                 continue
-            sq = ops.sumsq(u.grad_acc) if u.grad_acc.dtype == torch.float32 else u.grad_acc.float().pow(2).sum()
+            sq = ops.sumsq(u.grad_acc)  # fp32 or bf16 on the kernel; other cases fall back inside
             sq = sq.to(self.device)
             if getattr(u, "is_expert", False) and self.expert_dp_group is not None:
                 expert_total += sq
