@@ -534,3 +534,23 @@ def test_argument_errors_raise_with_a_readable_message(k):
         k.gemm_bf16(a, b, False, False, 7, None, 0, None)
     with pytest.raises(RuntimeError, match="head_dim must be 128"):
         k.fmha_fwd(a.view(128, 1, 64), b.view(128, 1, 64), b.view(128, 1, 64), torch.tensor([0, 128], device="cuda", dtype=torch.int32), 2, 0.1)
+
+
+def test_native_attention_dense_backward_matches_reference():
+    """Unpacked sequences: own forward kernel, backward through the dense library path (output + log-sum-exp handed over)."""
+    from arctictraining_b200.ops import functional as Fn
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(2)
+    B, S, Hq, Hkv = 2, 384, 4, 2
+    qkv = torch.randn(B, S, (Hq + 2 * Hkv) * 128, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+    q, kk, v = qkv.view(B, S, Hq + 2 * Hkv, 128).split([Hq, Hkv, Hkv], dim=2)  # strided views of a fused buffer
+    g = torch.randn(B, S, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    o = Fn.attention(q, kk, v, impl="native")
+    o.backward(g)
+    x2 = qkv.detach().float().requires_grad_(True)
+    q2, k2, v2 = x2.view(B, S, Hq + 2 * Hkv, 128).split([Hq, Hkv, Hkv], dim=2)
+    o2 = ref.attention(q2, k2, v2)
+    o2.backward(g.float())
+    assert _rel(o, o2) < 1e-2
+    assert _rel(qkv.grad, x2.grad) < 2e-2
