@@ -132,3 +132,23 @@ def test_user_module_next_to_recipe_is_imported_with_sibling_imports(tiny_recipe
 def test_missing_custom_code_file_raises(tiny_recipe):
     with pytest.raises(FileNotFoundError):
         get_config(tiny_recipe(code="/definitely/not/here.py"))
+
+
+def test_every_shipped_recipe_validates(tmp_path, monkeypatch):
+    """All recipes under projects/ build a typed config (trainer class found, sub-configs resolved, engine section
+    built); only recipes that point at a checkpoint produced by an earlier stage are skipped."""
+    import glob
+    from pathlib import Path
+
+    from arctictraining_b200.config.trainer import get_config
+
+    root = Path(__file__).resolve().parent.parent
+    monkeypatch.chdir(tmp_path)
+    recipes = sorted(glob.glob(str(root / "projects" / "**" / "*.y*ml"), recursive=True))
+    assert len(recipes) >= 20
+    for path in recipes:
+        if "/data/" in Path(path).read_text() and "excot" in path and "dpo" in Path(path).name:
+            continue
+        cfg = get_config(path)
+        assert cfg.type, path
+        assert cfg.deepspeed["train_micro_batch_size_per_gpu"] == cfg.micro_batch_size, path
