@@ -553,16 +553,9 @@ class TrainingEngine:
         if st["phase"] < 2:
             # two measurement passes (one layer kept, the rest recomputed): the first also sees the buffers that
             # are allocated lazily during the very first step, so the head-room is taken from the second
-            if u.wrapped_index == 0:
-                st["step_tokens"] = x.numel() // x.shape[-1]
             return u.wrapped_index == 0
-        tokens = x.numel() // x.shape[-1]
-        if u.wrapped_index == 0:
-            st["step_tokens"] = tokens
-        need = int(st["bytes_per_token"] * tokens)
-        # the head-room was measured on batches of `reserve_tokens` tokens; a longer batch needs proportionally more
-        reserve = st["reserve"] * max(1.0, tokens / max(1, st.get("reserve_tokens", tokens)))
-        ok = torch.cuda.memory_allocated(self.device) + need + reserve <= st["limit"]
+        need = int(st["bytes_per_token"] * (x.numel() // x.shape[-1]))
+        ok = torch.cuda.memory_allocated(self.device) + need + st["reserve"] <= st["limit"]
         if ok:
             st["kept_bytes"] += need
             st["kept_layers"] += 1
@@ -599,12 +592,9 @@ class TrainingEngine:
         if st["phase"] < 2:
             # includes the one measured layer: errs on the safe side
             st["reserve"] = int(peak - st["alloc0"]) if st["phase"] == 1 else 0
-            st["reserve_tokens"] = st.get("step_tokens", 1)
             st["phase"] += 1
         else:
-            # compare at the token count the stored head-room refers to
-            scale = max(1.0, st.get("step_tokens", 1) / max(1, st.get("reserve_tokens", 1)))
-            st["reserve"] = max(st["reserve"], int(reserve / scale))
+            st["reserve"] = max(st["reserve"], int(reserve))
         torch.cuda.reset_peak_memory_stats(self.device)
 
     def _begin_unit_backward(self, u: ZeroUnit) -> None:

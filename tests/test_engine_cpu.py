@@ -175,47 +175,3 @@ def test_inference_engine_stage3_matches_plain_forward():
     assert torch.allclose(out, ref_out, atol=1e-5)
     # in a group of one rank nothing is gathered or released: the shard is the unit
     assert all(u.persistent for u in e.units)
-
-
-def test_auto_keep_policy_follows_measured_memory(monkeypatch):
-    """The memory-driven choice of layers that keep activations, driven with a fake allocator: two measuring steps,
-    then as many layers as fit under the limit, and proportionally more head-room for a longer batch."""
-    engine = make_engine(make_model(), 3, keep="auto")
-    GiB = 1 << 30
-    mem = {"alloc": 100 * GiB, "peak": 100 * GiB}
-    monkeypatch.setattr(torch.cuda, "memory_allocated", lambda *_: mem["alloc"])
-    monkeypatch.setattr(torch.cuda, "max_memory_allocated", lambda *_: mem["peak"])
-    monkeypatch.setattr(torch.cuda, "memory_reserved", lambda *_: mem["alloc"])
-    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda *_: (180 * GiB - mem["alloc"], 180 * GiB))
-    monkeypatch.setattr(torch.cuda, "reset_peak_memory_stats", lambda *_: None)
-    engine.on_gpu = True
-    units = engine._wrapped_units
-    x = torch.zeros(1, 1024, 64)
-
-    def one_step(tokens, per_layer=4 * GiB, transient=6 * GiB):
-        xs = torch.zeros(1, tokens, 64)
-        mem["alloc"] = 100 * GiB
-        kept = []
-        for u in units:
-            k = engine._keeps_activations(u, xs)
-            kept.append(k)
-            if k:
-                mem["alloc"] += per_layer * tokens // 1024
-        mem["peak"] = mem["alloc"] + transient * tokens // 1024
-        engine._update_keep_state()
-        return kept
-
-    st = engine._keep_state
-    assert one_step(1024) == [True] + [False] * (len(units) - 1) and st["phase"] == 1
-    st["bytes_per_token"] = 4 * GiB / 1024  # what _run_kept measures on the first layer
-    assert one_step(1024) == [True] + [False] * (len(units) - 1) and st["phase"] == 2
-    assert st["reserve"] == 10 * GiB and st["reserve_tokens"] == 1024  # one kept layer + transient
-    limit = st["limit"]
-    assert limit == int(0.88 * 180 * GiB)
-    kept = one_step(1024)
-    # layer i is kept while 100 + 4 * (i + 1) + 10 <= 158.4 GiB
-    assert kept == [100 + 4 * (i + 1) + 10 <= limit / GiB for i in range(len(units))]
-    # a batch twice as long: activations and head-room double
-    kept = one_step(2048)
-    assert kept == [100 + 8 * (i + 1) + 20 <= limit / GiB for i in range(len(units))]
-    engine.on_gpu = False
