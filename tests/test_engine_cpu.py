@@ -175,3 +175,45 @@ def test_inference_engine_stage3_matches_plain_forward():
     assert torch.allclose(out, ref_out, atol=1e-5)
     # in a group of one rank nothing is gathered or released: the shard is the unit
     assert all(u.persistent for u in e.units)
+
+
+def test_auto_keep_policy_follows_measured_memory(monkeypatch):
+    """The memory-driven choice of layers that keep activations, driven with a fake allocator: two measuring steps
+    (one layer kept), then as many layers as fit under the limit next to the measured head-room."""
+    engine = make_engine(make_model(), 3, keep="auto")
+    GiB = 1 << 30
+    mem = {"alloc": 100 * GiB, "peak": 100 * GiB}
+    monkeypatch.setattr(torch.cuda, "memory_allocated", lambda *_: mem["alloc"])
+    monkeypatch.setattr(torch.cuda, "max_memory_allocated", lambda *_: mem["peak"])
+    monkeypatch.setattr(torch.cuda, "memory_reserved", lambda *_: mem["alloc"])
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda *_: (180 * GiB - mem["alloc"], 180 * GiB))
+    monkeypatch.setattr(torch.cuda, "reset_peak_memory_stats", lambda *_: None)
+    engine.on_gpu = True
+    units = engine._wrapped_units
+    xs = torch.zeros(1, 1024, 64)
+
+    def one_step(per_layer, transient=6 * GiB):
+        mem["alloc"] = 100 * GiB
+        kept = []
+        for u in units:
+            k = engine._keeps_activations(u, xs)
+            kept.append(k)
+            if k:
+                mem["alloc"] += per_layer
+        mem["peak"] = mem["alloc"] + transient
+        engine._update_keep_state()
+        return kept
+
+    st = engine._keep_state
+    assert one_step(4 * GiB) == [True] + [False] * (len(units) - 1) and st["phase"] == 1
+    st["bytes_per_token"] = 30 * GiB / 1024  # what _run_kept would measure on the first layer
+    assert one_step(30 * GiB) == [True] + [False] * (len(units) - 1) and st["phase"] == 2
+    assert st["reserve"] == 36 * GiB  # one kept layer + transient: errs on the safe side
+    assert st["limit"] == int(0.88 * 180 * GiB)
+    # 100 + 30 (i + 1) + 36 GiB must stay under 158.4 GiB: not even the first layer fits
+    assert one_step(30 * GiB) == [False] * len(units)
+    st["bytes_per_token"] = 4 * GiB / 1024
+    st["reserve"] = 10 * GiB
+    kept = one_step(4 * GiB)
+    assert kept == [100 + 4 * (i + 1) + 10 <= st["limit"] / GiB for i in range(len(units))] and all(kept)
+    engine.on_gpu = False
