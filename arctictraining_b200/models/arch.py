@@ -71,6 +71,20 @@ PRESETS: Dict[str, Dict[str, Any]] = {
     "tiny-llama": _llama(64, 2, 4, 2, 128, 1024, 10000.0, 2048),
     "llama-3.1-8b": _llama(4096, 32, 32, 8, 14336, 128256, 500000.0, 131072, bos_token_id=128000, eos_token_id=128001),
     "llama-3.1-70b": _llama(8192, 80, 64, 8, 28672, 128256, 500000.0, 131072),
+    "llama-3.1-405b": _llama(16384, 126, 128, 8, 53248, 128256, 500000.0, 131072),
+    "llama-3.3-70b": _llama(8192, 80, 64, 8, 28672, 128256, 500000.0, 131072),
+    "llama-3.2-3b": _llama(3072, 28, 24, 8, 8192, 128256, 500000.0, 131072, tie_word_embeddings=True, head_dim=128),
+    "mistral-7b": _llama(
+        4096, 32, 32, 8, 14336, 32768, 1000000.0, 32768, architectures=["MistralForCausalLM"], model_type="mistral",
+    ),
+    "qwen2.5-32b": _llama(
+        5120, 64, 40, 8, 27648, 152064, 1000000.0, 32768,
+        architectures=["Qwen2ForCausalLM"], model_type="qwen2", attention_bias=True, rms_norm_eps=1e-6,
+    ),
+    "qwen3-8b": _llama(
+        4096, 36, 32, 8, 12288, 151936, 1000000.0, 40960,
+        architectures=["Qwen3ForCausalLM"], model_type="qwen3", head_dim=128, rms_norm_eps=1e-6, qk_norm=True,
+    ),
     "llama-3.2-1b": _llama(2048, 16, 32, 8, 8192, 128256, 500000.0, 131072, tie_word_embeddings=True, head_dim=64),
     "qwen2.5-7b": _llama(
         3584, 28, 28, 4, 18944, 152064, 1000000.0, 32768,
