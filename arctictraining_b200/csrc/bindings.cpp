@@ -35,6 +35,9 @@ at::Tensor fmha_read_profile();
 #endif
 std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tensor& k, const at::Tensor& v,
                                             const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
+std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
+                                                         const at::Tensor& v, const at::Tensor& out, const at::Tensor& lse,
+                                                         const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
 bool set_gemm_cta_pairs(bool on);
 at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, int64_t mode, bool b_mn,
                              int64_t epilogue, const c10::optional<at::Tensor>& out);
@@ -100,6 +103,7 @@ TORCH_LIBRARY(atb200, m) {
     m.def("fmha_read_profile() -> Tensor", &atb::fmha_read_profile);
 #endif
     m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor)", &atb::fmha_fwd);
+    m.def("fmha_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor, Tensor)", &atb::fmha_bwd);
     m.def("set_gemm_cta_pairs(bool on) -> bool", &atb::set_gemm_cta_pairs);
     m.def("p2p_barrier(Tensor flag_ptrs, int rank, int slot, int epoch, float timeout_s, Tensor like) -> ()", &atb::p2p_barrier);
     m.def("comm_read_and_clear_error(Tensor like) -> int", &atb::comm_read_and_clear_error);

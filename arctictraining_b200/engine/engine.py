@@ -270,6 +270,8 @@ class TrainingEngine:
                 off += p.numel()
                 off = (off + 7) // 8 * 8  # keep every parameter 16-byte aligned (TMA, vector loads)
             u.n_train = 0
+            u.n_trainable_params = len(trainable)
+            u.param_group_index = [self._group_index_of(p) for p in trainable]
             if trainable:
                 u.n_train = u.offsets[len(trainable) - 1] + trainable[-1].numel()
             gran = ALIGN * shard_ways
@@ -295,17 +297,7 @@ class TrainingEngine:
             else:
                 u.shard = flat[lo : lo + u.shard_size]
             # runs of the local trainable shard by optimizer group
-            u.runs = []
-            if trainable:
-                for p, o in zip(ordered[: len(trainable)], u.offsets):
-                    s, e = max(o, lo) - lo, min(o + p.numel(), lo + u.shard_size) - lo
-                    if e <= s:
-                        continue
-                    gi = self._group_index_of(p)
-                    if u.runs and u.runs[-1][2] == gi:
-                        u.runs[-1] = (u.runs[-1][0], e, gi)
-                    else:
-                        u.runs.append((s, e, gi))
+            u.runs = self._runs_of_rank(u, u.group_rank)
             dp_replicas = max(1, (dist.get_world_size() if self.dist_on else 1) // self.sp_size)
             u.grad_divisor = float(dp_replicas)
         self._setup_fused_comm(max_pool_numel)
@@ -326,6 +318,23 @@ class TrainingEngine:
                     # gradient buffers that peers read directly: same three slots on every rank
                     self._grad_symm = [self.symm.alloc(f"grad{i}", n, torch.bfloat16) for i in range(3)]
                     self._grad_pool.bufs = [b.tensor for b in self._grad_symm]
+
+    @staticmethod
+    def _runs_of_rank(u: ZeroUnit, group_rank: int) -> List[Tuple[int, int, int]]:
+        """``(start, end, optimizer group)`` runs of the trainable prefix inside the shard of ``group_rank``.  The layout
+        is the same on every rank, so any rank can compute the runs of any other (decisions that must agree across
+        the group are taken over all ranks' runs)."""
+        lo = group_rank * u.shard_size
+        runs: List[Tuple[int, int, int]] = []
+        for o, n, gi in zip(u.offsets[: u.n_trainable_params], u.numels, u.param_group_index):
+            s, e = max(o, lo) - lo, min(o + n, lo + u.shard_size) - lo
+            if e <= s:
+                continue
+            if runs and runs[-1][2] == gi:
+                runs[-1] = (runs[-1][0], e, gi)
+            else:
+                runs.append((s, e, gi))
+        return runs
 
     def _setup_fused_comm(self, max_pool_numel: int) -> None:
         """Peer-memory data plane: on when the whole data-parallel group sits on one NVLink node."""
@@ -653,12 +662,9 @@ class TrainingEngine:
         scale = 1.0 / (u.grad_divisor * self.gas)
         lo = u.group_rank * u.shard_size
 
-        fused = (
-            self.symm is not None and self._grad_symm is not None and u.grad_slot is not None and tl > 0
-            and u.grad_acc is not None and u.grad_acc.device == self.device and u.grad_acc.dtype == torch.float32
-            and u.group_size > 1 and lo % 8 == 0
-        )
-
+        # Both decisions use values that are equal on every rank of the group: a rank whose shard holds no trainable
+        # element (a partly frozen unit: LoRA, SwiftKV) still joins the barriers and skips the arithmetic.
+        fused = self._fused_reduce_ok(u)
         single_pass = fused and self._single_pass_update_ok(u)
 
         def work() -> None:
@@ -668,7 +674,7 @@ class TrainingEngine:
                 # never written
                 self.symm.barrier(slot=1)
                 opt = self.optimizer
-                for s, e, gi, view in u.view_list:
+                for s, e, gi, view in (getattr(u, "view_list", None) or []):
                     group = opt.param_groups[gi]
                     st = opt._state_for(view)
                     st["step"] += 1
@@ -686,12 +692,13 @@ class TrainingEngine:
                 # every rank has finished writing this unit's gradients -> read my slice from all peers, reduce
                 # in fp32, accumulate; second barrier: nobody still reads a buffer that is about to be reused
                 self.symm.barrier(slot=1)
-                n8 = (tl + 7) // 8 * 8
-                self.symm.reduce_scatter_accumulate(
-                    self._grad_symm[u.grad_slot], lo, min(n8, u.grad_acc.numel() // 8 * 8), u.grad_acc, scale,
-                    overwrite=not u.grad_acc_valid,
-                )
-                u.grad_acc_valid = True
+                if tl > 0:
+                    n8 = (tl + 7) // 8 * 8
+                    self.symm.reduce_scatter_accumulate(
+                        self._grad_symm[u.grad_slot], lo, min(n8, u.grad_acc.numel() // 8 * 8), u.grad_acc, scale,
+                        overwrite=not u.grad_acc_valid,
+                    )
+                    u.grad_acc_valid = True
                 self.symm.barrier(slot=2)
                 return
             if self.dist_on and u.group_size > 1:
@@ -722,19 +729,37 @@ class TrainingEngine:
                 self._grad_pool.release(u.grad_slot, None)
         u.grad_flat, u.grad_slot = None, None
 
+    def _states_on_device_fp32(self) -> bool:
+        """fp32 master weights and gradient shards that live on the device (the same answer on every rank)."""
+        return not self.cfg.offload_optimizer and not self.cfg.bf16_master_weights_and_grads
+
+    def _fused_reduce_ok(self, u: ZeroUnit) -> bool:
+        """Whether this unit's gradients are reduced by the peer-memory kernel (between two device barriers) instead
+        of NCCL.  Every input is the same on all ranks of the unit's group: taking the decision from rank-local
+        values (for instance the length of the local trainable slice, which is zero on the ranks behind a frozen
+        tail) would send some ranks into the barriers and the others into a collective nobody else joins."""
+        return bool(
+            self.symm is not None and self._grad_symm is not None and u.checkpointed and u.n_train > 0
+            and self._states_on_device_fp32() and u.group_size > 1 and u.dtype == torch.bfloat16
+            and u.shard_size % 8 == 0
+        )
+
     def _single_pass_update_ok(self, u: ZeroUnit) -> bool:
         """Reduce-scatter and AdamW in one kernel: only without clipping (the clip factor needs the global norm of all
-        gradients first) and without accumulation steps, for fp32 states on the device and 8-aligned parameter runs."""
+        gradients first) and without accumulation steps, for fp32 states on the device and 8-aligned parameter runs
+        on every rank of the group (group-uniform, like :meth:`_fused_reduce_ok`)."""
         opt = self.optimizer
         if (self.cfg.gradient_clipping and self.cfg.gradient_clipping > 0) or self.gas != 1 or not hasattr(opt, "step_flat"):
             return False
-        if os.getenv("ATB200_SINGLE_PASS_UPDATE", "1") == "0" or not getattr(u, "view_list", None):
+        if os.getenv("ATB200_SINGLE_PASS_UPDATE", "1") == "0" or u.n_train <= 0:
             return False
-        if getattr(u, "is_expert", False) or u.master is None or u.master.dtype != torch.float32 or u.master.device != self.device:
+        if getattr(u, "is_expert", False) or not self._states_on_device_fp32() or u.dtype != torch.bfloat16:
             return False
         if self.cfg.bf16_optimizer_states:
             return False
-        return all(s % 8 == 0 and (e - s) % 8 == 0 and view._atb_lp is not None for s, e, gi, view in u.view_list)
+        return all(
+            s % 8 == 0 and (e - s) % 8 == 0 for r in range(u.group_size) for s, e, gi in self._runs_of_rank(u, r)
+        )
 
     def _accumulate(self, u: ZeroUnit, piece: torch.Tensor, scale: float) -> None:
         acc = u.grad_acc[: piece.numel()]
@@ -817,10 +842,28 @@ class TrainingEngine:
             return
         if self.on_gpu:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
+        self.check_device_errors()
         self._optimizer_step()
         self.global_steps += 1
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
+
+    def _read_error_words(self) -> Tuple[int, int]:
+        from ..comm.errors import read_error_words
+
+        return read_error_words(self._dummy)
+
+    def check_device_errors(self) -> None:
+        """Raise if a kernel of this device gave up a bounded wait since the last check (a barrier a peer never
+        reached, a staging or tensor-core wait, an expert-parallel buffer overflow).  Runs before every optimizer
+        step and before every checkpoint: gradients reduced from stale peer buffers or a partial GEMM output must
+        not reach the weights or the disk.  Costs one device synchronisation."""
+        if not self.on_gpu:
+            return
+        from ..comm.errors import raise_for_error_words
+
+        kernel_code, comm_code = self._read_error_words()
+        raise_for_error_words(kernel_code, comm_code, self.global_rank)
 
     # ---------------------------------------------------------------- optimizer step
     def _compute_grad_norm(self) -> torch.Tensor:
@@ -945,6 +988,7 @@ class TrainingEngine:
         d.mkdir(parents=True, exist_ok=True)
         if self.on_gpu:
             torch.cuda.synchronize()
+        self.check_device_errors()
         units_state = {}
         for u in self.units:
             tl = u.train_len

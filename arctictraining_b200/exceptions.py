@@ -15,3 +15,7 @@ class CommTimeoutError(RuntimeError):
 
 class EngineConfigError(ValueError):
     """The engine section of a recipe asks for a combination that is not supported."""
+
+
+class KernelWaitError(RuntimeError):
+    """A bounded barrier wait inside a compute kernel (GEMM, attention) ran out; its output is incomplete."""

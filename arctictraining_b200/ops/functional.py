@@ -361,9 +361,11 @@ def linear_swiglu(x: torch.Tensor, w_gate_up: torch.Tensor) -> torch.Tensor:
 
 # ------------------------------------------------------------------------------------------------ attention
 class _NativeAttentionFn(torch.autograd.Function):
-    """Forward: the package's sm_100a flash-attention kernel (saves the output and the per-row log-sum-exp).
-    Backward: the flash-attn library's variable-length backward, which recomputes probabilities from that
-    log-sum-exp."""
+    """Forward and backward: the package's sm_100a flash-attention kernels.  The forward saves the output and the
+    per-row log-sum-exp; the backward recomputes the probabilities from them on the tensor cores.
+
+    ``ATB200_ATTN_BWD=cudnn`` / ``flash`` selects a library backward (cuDNN's fused kernel for unpacked sequences,
+    flash-attn's variable-length kernel) for comparisons; the default is the own kernel."""
 
     @staticmethod
     def forward(ctx, q, k, v, cu, max_seqlen, scale, dense_rows=0):
@@ -380,10 +382,16 @@ class _NativeAttentionFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dout):
         q, k, v, out, lse, cu = ctx.saved_tensors
-        if ctx.dense_rows and os.getenv("ATB200_ATTN_BWD", "cudnn") == "cudnn":
-            grads = _cudnn_dense_attention_backward(dout, q, k, v, out, lse, ctx.dense_rows, ctx.scale)
-            if grads is not None:
-                return grads + (None, None, None, None)
+        which = os.getenv("ATB200_ATTN_BWD", "native")
+        if which == "native":
+            _count(3)
+            T = q.shape[0]
+            if dout.stride(-1) != 1 or dout.stride(1) != dout.shape[2] or dout.stride(0) % 8 != 0 or dout.data_ptr() % 16:
+                dout = dout.contiguous()
+            dq, dk, dv = _ext.ops().fmha_bwd(dout, q, k, v, out, lse, cu, T // 128 + cu.numel() - 1, ctx.scale)
+            return dq, dk, dv, None, None, None, None
+        if which == "cudnn" and ctx.dense_rows and _cudnn_dense_backward_applicable(q, k, v):
+            return _cudnn_dense_attention_backward(dout, q, k, v, out, lse, ctx.dense_rows, ctx.scale) + (None,) * 4
         from flash_attn.flash_attn_interface import _flash_attn_varlen_backward
 
         dq, dk, dv = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
@@ -394,36 +402,33 @@ class _NativeAttentionFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
-_CUDNN_PHILOX = {}
+def _cudnn_dense_backward_applicable(q, k, v) -> bool:
+    """Explicit preconditions of the cuDNN comparison path: the operator exists and the [T, H, D] operands can be
+    viewed as [rows, S, H, D] (dense heads).  Errors raised by the operator itself are not caught."""
+    if getattr(torch.ops.aten, "_scaled_dot_product_cudnn_attention_backward", None) is None:
+        return False
+    return all(t.stride(-1) == 1 and t.stride(1) == t.shape[2] for t in (q, k, v))
 
 
 def _cudnn_dense_attention_backward(dout, q, k, v, out, lse, rows: int, scale: float):
     """Backward of causal attention over ``rows`` equally long, unpacked sequences through cuDNN's fused kernel (a
-    library kernel, several times faster on this GPU than the flash-attn 2 backward), fed with the output and the
-    log-sum-exp of this package's forward kernel.  Returns ``None`` when the operator is not available."""
-    op = getattr(torch.ops.aten, "_scaled_dot_product_cudnn_attention_backward", None)
-    if op is None:
-        return None
+    library kernel kept for comparisons), fed with the output and the log-sum-exp of this package's forward kernel."""
+    op = torch.ops.aten._scaled_dot_product_cudnn_attention_backward
     T, Hq, D = q.shape
     S = T // rows
-    dev = q.device
-    try:
-        if dev not in _CUDNN_PHILOX:  # placeholders for the (unused, dropout is off) random-number state
-            t = torch.zeros(1, 1, 128, D, device=dev, dtype=q.dtype)
-            fo = torch.ops.aten._scaled_dot_product_cudnn_attention(t, t, t, None, True, 0.0, True, False, scale=1.0)
-            _CUDNN_PHILOX[dev] = (fo[6], fo[7])
-        seed, offset = _CUDNN_PHILOX[dev]
+    # placeholders for the (unused, dropout is off) random-number state
+    t = torch.zeros(1, 1, 128, D, device=q.device, dtype=q.dtype)
+    fo = torch.ops.aten._scaled_dot_product_cudnn_attention(t, t, t, None, True, 0.0, True, False, scale=1.0)
+    seed, offset = fo[6], fo[7]
 
-        def bhsd(t):
-            return t.view(rows, S, t.shape[1], D).transpose(1, 2)
+    def bhsd(t):
+        return t.as_strided((rows, t.shape[1], S, D), (S * t.stride(0), t.stride(1), t.stride(0), 1), t.storage_offset())
 
-        lse4 = lse.view(Hq, rows, S).permute(1, 0, 2).unsqueeze(-1).contiguous()
-        gq, gk, gv = op(bhsd(dout.contiguous()), bhsd(q), bhsd(k), bhsd(v), bhsd(out), lse4, seed, offset, None, None, None,
-                        S, S, 0.0, True, scale=scale)
-        return (gq.transpose(1, 2).reshape(T, Hq, D), gk.transpose(1, 2).reshape(T, -1, D),
-                gv.transpose(1, 2).reshape(T, -1, D))
-    except (RuntimeError, TypeError):
-        return None
+    lse4 = lse.view(Hq, rows, S).permute(1, 0, 2).unsqueeze(-1).contiguous()
+    gq, gk, gv = op(bhsd(dout.contiguous()), bhsd(q), bhsd(k), bhsd(v), bhsd(out), lse4, seed, offset, None, None, None,
+                    S, S, 0.0, True, scale=scale)
+    return (gq.transpose(1, 2).reshape(T, Hq, D), gk.transpose(1, 2).reshape(T, -1, D),
+            gv.transpose(1, 2).reshape(T, -1, D))
 
 
 def _native_attention(q, k, v, cu_seqlens, max_seqlen, scale):

@@ -315,11 +315,7 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
             loss = self.loss(batch)
         self.backward(loss)
         self.metrics.record("loss", loss.item() if torch.is_tensor(loss) else loss)
-        self.model.step()
-        if self.use_arctic_moe and self.model.global_steps % 25 == 1:
-            from ..moe.peer import check_errors
-
-            check_errors()
+        self.model.step()  # reads the kernels' error words (bounded waits, expert-buffer overflow) before the update
         self.checkpoint()
         self.global_step = self.model.global_steps
         self.global_step_this_run = self.global_step - self.global_step_at_start_this_run

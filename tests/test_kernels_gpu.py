@@ -537,7 +537,7 @@ def test_argument_errors_raise_with_a_readable_message(k):
 
 
 def test_native_attention_dense_backward_matches_reference():
-    """Unpacked sequences: own forward kernel, backward through the dense library path (output + log-sum-exp handed over)."""
+    """Unpacked sequences (a batch of rows, strided views of a fused projection) through the autograd function."""
     from arctictraining_b200.ops import functional as Fn
     from arctictraining_b200.ops import reference as ref
 
@@ -554,3 +554,114 @@ def test_native_attention_dense_backward_matches_reference():
     o2.backward(g.float())
     assert _rel(o, o2) < 1e-2
     assert _rel(qkv.grad, x2.grad) < 2e-2
+
+
+def _attention_grads_fp32_chunked(q, kk, v, g, scale, chunk=4096):
+    """fp32 causal attention (one unpacked sequence) with its gradients, query chunk by query chunk, so that a long
+    sequence never needs the full score matrix.  q / g [T, Hq, D], kk / v [T, Hkv, D].  Returns (o, lse, dq, dk, dv)."""
+    T, Hq, D = q.shape
+    Hkv = kk.shape[1]
+    o = torch.empty(T, Hq, D, device=q.device)
+    lse = torch.empty(Hq, T, device=q.device)
+    dq = torch.empty(T, Hq, D, device=q.device)
+    dk = torch.zeros(T, Hkv, D, device=q.device)
+    dv = torch.zeros(T, Hkv, D, device=q.device)
+    pos = torch.arange(T, device=q.device)
+    for h in range(Hq):
+        hk = h // (Hq // Hkv)
+        kf, vf = kk[:, hk].float(), v[:, hk].float()
+        for a in range(0, T, chunk):
+            b = min(T, a + chunk)
+            qf, gf = q[a:b, h].float(), g[a:b, h].float()
+            s = (qf @ kf[:b].t()) * scale
+            s.masked_fill_(pos[None, :b] > pos[a:b, None], float("-inf"))
+            l = torch.logsumexp(s, dim=-1)
+            p = torch.exp(s - l[:, None])
+            oc = p @ vf[:b]
+            dp = gf @ vf[:b].t()
+            ds = p * (dp - (gf * oc).sum(-1, keepdim=True))
+            o[a:b, h], lse[h, a:b] = oc, l
+            dq[a:b, h] = (ds @ kf[:b]) * scale
+            dk[:b, hk] += (ds.t() @ qf) * scale
+            dv[:b, hk] += p.t() @ gf
+    return o, lse, dq, dk, dv
+
+
+@pytest.mark.parametrize(
+    "lens,Hq,Hkv",
+    [([256], 4, 4), ([128, 384], 8, 2), ([100, 37, 411, 129], 4, 1), ([1000], 2, 2), ([1, 127, 128, 129], 4, 2),
+     ([2048, 700], 8, 2)],
+)
+def test_native_flash_attention_backward(k, lens, Hq, Hkv):
+    """dq / dk / dv of the tcgen05 backward kernel against fp32 autograd of the reference attention."""
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(3)
+    T = sum(lens)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * 128, device="cuda", dtype=torch.bfloat16)
+    q = qkv[:, : Hq * 128].view(T, Hq, 128)          # strided views of one fused projection output
+    kk = qkv[:, Hq * 128 : (Hq + Hkv) * 128].view(T, Hkv, 128)
+    v = qkv[:, (Hq + Hkv) * 128 :].view(T, Hkv, 128)
+    g = torch.randn(T, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    scale = 128 ** -0.5
+    nblk = T // 128 + len(lens)
+    out, lse = k.fmha_fwd(q, kk, v, cu, nblk, scale)
+    dq, dk, dv = k.fmha_bwd(g, q, kk, v, out, lse, cu, nblk, scale)
+    torch.cuda.synchronize()
+    _check_flag(out)
+    qr, kr, vr = (t.detach().float().requires_grad_(True) for t in (q, kk, v))
+    o2 = ref.attention(qr[None], kr[None], vr[None], cu_seqlens=cu.long(), scale=scale)[0]
+    o2.backward(g.float())
+    for name, a, b in (("dq", dq, qr.grad), ("dk", dk, kr.grad), ("dv", dv, vr.grad)):
+        assert torch.isfinite(a.float()).all(), name
+        assert _rel(a, b) < 2e-2, (name, _rel(a, b))
+        torch.testing.assert_close(a.float(), b, atol=6e-2, rtol=6e-2, msg=lambda m: f"{name}: {m}")
+    # dk and dv are accumulated in a fixed order: bit-identical on a second run; dq to fp32 rounding of its sum
+    dq2, dk2, dv2 = k.fmha_bwd(g, q, kk, v, out, lse, cu, nblk, scale)
+    assert torch.equal(dk, dk2) and torch.equal(dv, dv2)
+    torch.testing.assert_close(dq2.float(), dq.float(), atol=1e-2, rtol=1e-2)
+
+
+def test_native_flash_attention_long_sequence_forward_and_backward(k):
+    """65 536 tokens (64-bit offsets, log-sum-exp layout, 512 key blocks) against a chunked fp32 reference."""
+    torch.manual_seed(4)
+    T, Hq, Hkv = 65536, 2, 1
+    q = torch.randn(T, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    kk = torch.randn(T, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, Hkv, 128, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(T, Hq, 128, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0, T], device="cuda", dtype=torch.int32)
+    scale = 128 ** -0.5
+    out, lse = k.fmha_fwd(q, kk, v, cu, T // 128 + 1, scale)
+    dq, dk, dv = k.fmha_bwd(g, q, kk, v, out, lse, cu, T // 128 + 1, scale)
+    torch.cuda.synchronize()
+    _check_flag(out)
+    o2, lse2, dq2, dk2, dv2 = _attention_grads_fp32_chunked(q, kk, v, g, scale)
+    torch.testing.assert_close(lse, lse2, atol=1e-2, rtol=1e-3)
+    assert _rel(out, o2) < 1e-2
+    for name, a, b in (("dq", dq, dq2), ("dk", dk, dk2), ("dv", dv, dv2)):
+        assert _rel(a, b) < 2e-2, (name, _rel(a, b))
+
+
+def test_native_flash_attention_forward_262144_tokens_sampled_rows(k):
+    """Forward at 262 144 tokens: three blocks of query rows (first, middle, last) against fp32."""
+    torch.manual_seed(5)
+    T = 262144
+    q = torch.randn(T, 1, 128, device="cuda", dtype=torch.bfloat16)
+    kk = torch.randn(T, 1, 128, device="cuda", dtype=torch.bfloat16)
+    v = torch.randn(T, 1, 128, device="cuda", dtype=torch.bfloat16)
+    cu = torch.tensor([0, T], device="cuda", dtype=torch.int32)
+    scale = 128 ** -0.5
+    out, lse = k.fmha_fwd(q, kk, v, cu, T // 128 + 1, scale)
+    torch.cuda.synchronize()
+    _check_flag(out)
+    pos = torch.arange(T, device="cuda")
+    for a in (0, T // 2 - 300, T - 1024):
+        b = a + 1024
+        s = (q[a:b, 0].float() @ kk[:b, 0].float().t()) * scale
+        s.masked_fill_(pos[None, :b] > pos[a:b, None], float("-inf"))
+        want_lse = torch.logsumexp(s, dim=-1)
+        want = torch.softmax(s, dim=-1) @ v[:b, 0].float()
+        torch.testing.assert_close(lse[0, a:b], want_lse, atol=1e-2, rtol=1e-3)
+        assert _rel(out[a:b, 0], want) < 1e-2
