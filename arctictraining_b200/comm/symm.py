@@ -88,7 +88,7 @@ class SymmetricContext:
         """Device-side barrier over the group on the current stream (no host synchronisation)."""
         self._epochs[slot] += 1
         _ext.ops().p2p_barrier(self._flags.ptrs, self.rank, slot, self._epochs[slot], self.timeout_s, self._flags.tensor)
-        _count()
+        _count(comm="p2p_barrier")
 
     def check(self) -> None:
         """Raise if a bounded wait of any communication kernel gave up since the last check (synchronises)."""
@@ -103,12 +103,12 @@ class SymmetricContext:
     def all_gather(self, shards: SymmetricBuffer, shard_elem_offset: int, shard_numel: int, out: torch.Tensor) -> None:
         """``out[p * n : (p + 1) * n] = peer p's shards[offset : offset + n]`` (pull over NVLink)."""
         _ext.ops().p2p_all_gather(shards.ptrs, shard_elem_offset * out.element_size(), out, shard_numel, self.rank)
-        _count()
+        _count(comm="p2p_all_gather")
 
     def reduce_scatter_accumulate(self, grads: SymmetricBuffer, elem_offset: int, n: int, acc: torch.Tensor,
                                   scale: float, overwrite: bool, want_sumsq: bool = False) -> torch.Tensor:
         """``acc (+)= scale * sum_p peer_p.grads[offset : offset + n]`` in fp32; optionally returns ||acc||^2."""
-        _count()
+        _count(comm="nvls_reduce_scatter" if self.use_nvls and grads.multicast_ptr else "p2p_reduce_scatter")
         if self.use_nvls and grads.multicast_ptr:
             return _ext.ops().nvls_reduce_scatter_accum(grads.multicast_ptr, elem_offset, n, acc, scale, overwrite, want_sumsq)
         return _ext.ops().p2p_reduce_scatter_accum(grads.ptrs, elem_offset, n, acc, scale, overwrite, want_sumsq)

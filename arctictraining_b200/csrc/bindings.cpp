@@ -38,6 +38,7 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
 std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
                                                          const at::Tensor& v, const at::Tensor& out, const at::Tensor& lse,
                                                          const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
+at::Tensor fmha_bwd_read_profile(const at::Tensor& like);
 bool set_gemm_cta_pairs(bool on);
 at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, int64_t mode, bool b_mn,
                              int64_t epilogue, const c10::optional<at::Tensor>& out);
@@ -103,6 +104,7 @@ TORCH_LIBRARY(atb200, m) {
     m.def("fmha_read_profile() -> Tensor", &atb::fmha_read_profile);
 #endif
     m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor)", &atb::fmha_fwd);
+    m.def("fmha_bwd_read_profile(Tensor like) -> Tensor", &atb::fmha_bwd_read_profile);
     m.def("fmha_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor, Tensor)", &atb::fmha_bwd);
     m.def("set_gemm_cta_pairs(bool on) -> bool", &atb::set_gemm_cta_pairs);
     m.def("p2p_barrier(Tensor flag_ptrs, int rank, int slot, int epoch, float timeout_s, Tensor like) -> ()", &atb::p2p_barrier);

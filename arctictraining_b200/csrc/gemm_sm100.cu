@@ -1162,6 +1162,22 @@ bool set_gemm_cta_pairs(bool on) {
 CUtensorMap make_tmap_bf16_public(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
     return make_tmap_bf16(base, rows, cols, ld, box_rows);
 }
+// 2-D fp32 tensor map over a row-major [rows, cols] matrix (leading dimension `ld` elements), box = [box_rows, 32 columns]
+// (128 bytes), 128-byte swizzle: the staging layout of reductions into an fp32 accumulator.
+CUtensorMap make_tmap_f32_public(const void* base, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    TORCH_CHECK((reinterpret_cast<uintptr_t>(base) & 15) == 0 && (ld * 4) % 16 == 0, "TMA: fp32 base / pitch must be 16-byte aligned");
+    C10_CUDA_CHECK(cudaFree(nullptr));  // binds a context to this thread (see make_tmap_bf16)
+    CUtensorMap tm;
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1u, 1u};
+    CUresult r = get_encode_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<void*>(base), gdim, gstride, box, estr,
+                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                 CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    TORCH_CHECK(r == CUDA_SUCCESS, "cuTensorMapEncodeTiled (fp32) failed with code ", (int)r);
+    return tm;
+}
 at::Tensor& gemm_error_flag(const at::Device& dev) { return error_flag_for(dev); }
 
 // Reads and clears the per-device error word written by kernels whose bounded waits gave up.

@@ -111,6 +111,11 @@ class ZeroUnit:
         self.group_rank = 0
         self.resident = True
         self.grad_divisor = 1.0
+        self.host_states = False  # master weights, moments and the gradient shard live in pinned host memory
+        self.host_params = False  # the low-precision shard lives in pinned host memory (parameter offload)
+        self.grad_event = None    # completion of the asynchronous device -> host copy of the gradient shard
+        self.grad_sumsq = None    # sum of squares of that shard, computed on the device before it left
+        self.lp_stage: Optional[torch.Tensor] = None  # pinned bf16 buffer the host optimizer writes updated weights to
 
     @property
     def train_len(self) -> int:
@@ -244,6 +249,7 @@ class TrainingEngine:
                 for p in g["params"]:
                     self._param_group[id(p)] = gi
         max_pool_numel = 0
+        self._decide_host_placement()
         for u in self.units:
             if getattr(u, "is_expert", False) and self.expert_dp_group is not None:
                 u.group = self.expert_dp_group
@@ -288,11 +294,19 @@ class TrainingEngine:
             u.flat = flat
             lo = u.group_rank * u.shard_size
             # a group of one rank has nothing to gather: the shard is the whole unit and stays in place
+            u.host_params = bool(self.cfg.offload_param and self.stage == 3 and u.checkpointed and self.on_gpu)
             u.persistent = not (
-                self.stage == 3 and u.checkpointed and u.group_size > 1 and u.numel >= self._persist_threshold()
+                self.stage == 3 and u.checkpointed and (u.group_size > 1 or u.host_params)
+                and u.numel >= self._persist_threshold()
             )
+            u.host_params = u.host_params and not u.persistent
             if self.stage == 3 and not u.persistent:
-                u.shard = flat[lo : lo + u.shard_size].clone()
+                if u.host_params:
+                    # parameter offload: the shard waits in pinned host memory and is copied in right before use
+                    u.shard = torch.empty(u.shard_size, dtype=dtype, device="cpu", pin_memory=True)
+                    u.shard.copy_(flat[lo : lo + u.shard_size])
+                else:
+                    u.shard = flat[lo : lo + u.shard_size].clone()
                 max_pool_numel = max(max_pool_numel, u.numel)
             else:
                 u.shard = flat[lo : lo + u.shard_size]
@@ -336,6 +350,26 @@ class TrainingEngine:
                 runs.append((s, e, gi))
         return runs
 
+    def _decide_host_placement(self) -> None:
+        """``zero_optimization.offload_optimizer``: which units keep master weights, moments and gradient shards in
+        host memory.  ``ratio`` is the fraction of the trainable elements that is offloaded (units are taken in
+        model order until the fraction is reached); the rest is updated on the device.  The decision uses sizes
+        that are the same on every rank (the unit's trainable length, not the local slice of it).  The reference
+        passes these keys to its engine (projects/sequence-parallelism/run-h100-sp1-llama-8b.yml:8-14,
+        news/qwen3-32b-dgx-station/run-qwen3-32b.yml:7-12)."""
+        for u in self.units:
+            u.host_states = False
+        if not (self.cfg.offload_optimizer and self.training_mode and self.optimizer is not None):
+            return
+        pg = {id(p) for g in self.optimizer.param_groups for p in g["params"]}
+        sizes = [sum(p.numel() for p in u.params if p.requires_grad and id(p) in pg) for u in self.units]
+        total = float(sum(sizes)) or 1.0
+        ratio = min(1.0, max(0.0, self.cfg.offload_optimizer_ratio))
+        done = 0
+        for u, n in zip(self.units, sizes):
+            u.host_states = n > 0 and done < ratio * total - 0.5
+            done += n
+
     def _setup_fused_comm(self, max_pool_numel: int) -> None:
         """Peer-memory data plane: on when the whole data-parallel group sits on one NVLink node."""
         from ..comm.symm import SymmetricContext
@@ -355,7 +389,7 @@ class TrainingEngine:
             return
         if self.stage == 3 and max_pool_numel:
             # all released units keep their bf16 shards in one symmetric slab so that peers can pull them
-            units = [u for u in self.units if not u.persistent and u.dtype == torch.bfloat16]
+            units = [u for u in self.units if not u.persistent and u.dtype == torch.bfloat16 and not u.host_params]
             total = sum(u.shard_size for u in units)
             if total:
                 self._shard_symm = self.symm.alloc("shards", total, torch.bfloat16)
@@ -378,13 +412,13 @@ class TrainingEngine:
         opt = self.optimizer
         state_dtype = torch.bfloat16 if self.cfg.bf16_optimizer_states else torch.float32
         master_dtype = torch.bfloat16 if self.cfg.bf16_master_weights_and_grads else torch.float32
-        opt_dev = torch.device("cpu") if self.cfg.offload_optimizer else self.device
         new_groups: List[List[torch.Tensor]] = [[] for _ in opt.param_groups]
         self._views: List[Tuple[ZeroUnit, int, int, int, torch.Tensor]] = []
         for u in self.units:
             tl = u.train_len
             if tl <= 0:
                 continue
+            opt_dev = torch.device("cpu") if u.host_states else self.device
             pad = (tl + 7) // 8 * 8
             u.view_list = []
             u.master = torch.zeros(pad, dtype=master_dtype, device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
@@ -402,11 +436,22 @@ class TrainingEngine:
             else:
                 u.grad_acc = torch.zeros(pad, dtype=torch.float32 if master_dtype == torch.float32 else master_dtype,
                                          device=opt_dev, pin_memory=(opt_dev.type == "cpu" and self.on_gpu))
+            lp_ok = master_dtype == torch.float32 and u.dtype == torch.bfloat16
+            lp_target = None  # where the optimizer kernel writes the rounded weights in the same pass
+            if lp_ok and opt_dev == self.device and not u.host_params:
+                lp_target = u.shard
+            elif lp_ok and opt_dev.type == "cpu" and self.on_gpu:
+                if u.host_params:
+                    lp_target = u.shard  # host optimizer -> host shard: the update never touches the device
+                else:
+                    u.lp_stage = torch.empty(pad, dtype=torch.bfloat16, device="cpu", pin_memory=True)
+                    lp_target = u.lp_stage
+            u.lp_in_step = lp_target is not None
             for s, e, gi in u.runs:
                 view = u.master[s:e]
                 view._atb_unit = u  # type: ignore[attr-defined]
                 view._atb_range = (s, e)  # type: ignore[attr-defined]
-                view._atb_lp = u.shard[s:e] if opt_dev == self.device and master_dtype == torch.float32 and u.dtype == torch.bfloat16 else None  # type: ignore[attr-defined]
+                view._atb_lp = lp_target[s:e] if lp_target is not None else None  # type: ignore[attr-defined]
                 view._atb_state_dtype = state_dtype  # type: ignore[attr-defined]
                 new_groups[gi].append(view)
                 self._views.append((u, s, e, gi, view))
@@ -443,7 +488,18 @@ class TrainingEngine:
         slot, buf = self._param_pool.acquire()
         flat = buf[: u.numel]
         u.pool_slot = slot
-        if self.dist_on and u.group_size > 1:
+        if u.host_params:
+            # parameter offload: pinned host shard -> own slice of the pooled buffer (then the usual all-gather, in
+            # place), all on the communication stream so that the copy of the next unit runs under this one's compute
+            lo = u.group_rank * u.shard_size
+            self.comm_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(self.comm_stream):
+                flat[lo : lo + u.shard_size].copy_(u.shard, non_blocking=True)
+                if self.dist_on and u.group_size > 1:
+                    self._all_gather(flat, flat[lo : lo + u.shard_size], u.group)
+                u.gather_event = torch.cuda.Event()
+                u.gather_event.record()
+        elif self.dist_on and u.group_size > 1:
             if self.on_gpu:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
                 with torch.cuda.stream(self.comm_stream):
@@ -684,7 +740,7 @@ class TrainingEngine:
                         view._atb_lp, float(group["lr"]), b1, b2, group["eps"], group["weight_decay"], st["step"],
                     )
                     self._single_pass_sumsq = ss if self._single_pass_sumsq is None else self._single_pass_sumsq + ss
-                    ops.functional._count()
+                    ops.functional._count(comm="p2p_reduce_scatter_adamw")
                 u.stepped_in_backward = True
                 self.symm.barrier(slot=2)
                 return
@@ -729,9 +785,9 @@ class TrainingEngine:
                 self._grad_pool.release(u.grad_slot, None)
         u.grad_flat, u.grad_slot = None, None
 
-    def _states_on_device_fp32(self) -> bool:
+    def _states_on_device_fp32(self, u: ZeroUnit) -> bool:
         """fp32 master weights and gradient shards that live on the device (the same answer on every rank)."""
-        return not self.cfg.offload_optimizer and not self.cfg.bf16_master_weights_and_grads
+        return not u.host_states and not self.cfg.bf16_master_weights_and_grads
 
     def _fused_reduce_ok(self, u: ZeroUnit) -> bool:
         """Whether this unit's gradients are reduced by the peer-memory kernel (between two device barriers) instead
@@ -740,7 +796,7 @@ class TrainingEngine:
         tail) would send some ranks into the barriers and the others into a collective nobody else joins."""
         return bool(
             self.symm is not None and self._grad_symm is not None and u.checkpointed and u.n_train > 0
-            and self._states_on_device_fp32() and u.group_size > 1 and u.dtype == torch.bfloat16
+            and self._states_on_device_fp32(u) and u.group_size > 1 and u.dtype == torch.bfloat16
             and u.shard_size % 8 == 0
         )
 
@@ -753,7 +809,7 @@ class TrainingEngine:
             return False
         if os.getenv("ATB200_SINGLE_PASS_UPDATE", "1") == "0" or u.n_train <= 0:
             return False
-        if getattr(u, "is_expert", False) or not self._states_on_device_fp32() or u.dtype != torch.bfloat16:
+        if getattr(u, "is_expert", False) or not self._states_on_device_fp32(u) or u.dtype != torch.bfloat16 or u.host_params:
             return False
         if self.cfg.bf16_optimizer_states:
             return False
@@ -764,11 +820,22 @@ class TrainingEngine:
     def _accumulate(self, u: ZeroUnit, piece: torch.Tensor, scale: float) -> None:
         acc = u.grad_acc[: piece.numel()]
         if acc.device != piece.device:
-            tmp = piece.float() * scale
+            # offloaded optimizer states: the reduced shard leaves for pinned host memory on the current (communication)
+            # stream while backward goes on; its squared norm is taken on the device first
+            tmp = piece.float() * scale if (piece.dtype != torch.float32 or scale != 1.0) else piece
             if u.grad_acc_valid:
-                acc.add_(tmp.to("cpu", non_blocking=False).to(acc.dtype))
+                if u.grad_event is not None:
+                    u.grad_event.synchronize()
+                host = torch.empty(tmp.shape, dtype=tmp.dtype, device="cpu", pin_memory=self.on_gpu)
+                host.copy_(tmp)  # accumulation steps: add on the host (synchronous)
+                acc.add_(host.to(acc.dtype))
+                u.grad_sumsq = None
             else:
-                acc.copy_(tmp.to(acc.dtype))
+                u.grad_sumsq = ops.sumsq(tmp) if acc.dtype == torch.float32 else None
+                acc.copy_(tmp.to(acc.dtype), non_blocking=True)
+                if self.on_gpu:
+                    u.grad_event = torch.cuda.Event()
+                    u.grad_event.record()
         elif acc.dtype == torch.float32 and piece.dtype == torch.bfloat16:
             ops.accumulate_lp_grad(piece, acc, scale, overwrite=not u.grad_acc_valid)
         else:
@@ -857,9 +924,7 @@ class TrainingEngine:
         """Raise if a kernel of this device gave up a bounded wait since the last check (a barrier a peer never
         reached, a staging or tensor-core wait, an expert-parallel buffer overflow).  Runs before every optimizer
         step and before every checkpoint: gradients reduced from stale peer buffers or a partial GEMM output must
-        not reach the weights or the disk.  Costs one device synchronisation."""
-        if not self.on_gpu:
-            return
+        not reach the weights or the disk.  Costs one device synchronisation (nothing on a CPU engine)."""
         from ..comm.errors import raise_for_error_words
 
         kernel_code, comm_code = self._read_error_words()
@@ -875,7 +940,12 @@ class TrainingEngine:
         for u in self.units:
             if u.grad_acc is None or not u.grad_acc_valid:
                 continue
-            sq = ops.sumsq(u.grad_acc)  # fp32 or bf16 on the kernel; other cases fall back inside
+            if u.grad_sumsq is not None:
+                sq = u.grad_sumsq  # taken on the device before the shard was copied to the host
+            else:
+                if u.grad_event is not None:
+                    u.grad_event.synchronize()
+                sq = ops.sumsq(u.grad_acc)  # fp32 or bf16 on the kernel; other cases fall back inside
             sq = sq.to(self.device)
             if getattr(u, "is_expert", False) and self.expert_dp_group is not None:
                 expert_total += sq
@@ -924,6 +994,7 @@ class TrainingEngine:
                 if view.grad.dtype != view.dtype:
                     view.grad = view.grad.to(view.dtype)
         if fused:
+            self._step_host_units(opt, coef)
             opt.step_flat(coef)
             opt._opt_called = True  # keeps torch's scheduler-order check quiet
         else:
@@ -935,15 +1006,41 @@ class TrainingEngine:
             if u.master is None:
                 continue
             tl = u.train_len
-            if not (fused and getattr(opt, "writes_lp", False) and u.master.device == self.device
-                    and u.master.dtype == torch.float32 and u.dtype == torch.bfloat16):
-                u.shard[:tl].copy_(u.master[:tl].to(self.device, non_blocking=True).to(u.dtype))
+            if not (fused and getattr(u, "lp_in_step", False)):
+                # the optimizer did not write the rounded weights itself: round the master copy
+                u.shard[:tl].copy_(u.master[:tl].to(u.dtype))
             u.grad_acc_valid = False
+            u.grad_sumsq = None
+            u.grad_event = None
             u.stepped_in_backward = False
         self._sync_full_params()
         if self.symm is not None:
             self.symm.barrier(slot=0)  # shards are final on every rank before anyone pulls them again
         self._update_keep_state()
+
+    def _step_host_units(self, opt, coef: Optional[torch.Tensor]) -> None:
+        """Units whose optimizer states live in host memory, one after the other: wait for the unit's gradient shard
+        to have arrived, run the host AdamW over its views (which also writes the rounded bf16 weights into a pinned
+        buffer), and queue the copy of those weights back to the device on the communication stream, so that the
+        copy of one unit runs under the host arithmetic of the next."""
+        host_units = [u for u in self.units if u.host_states and u.master is not None and getattr(u, "view_list", None)]
+        if not host_units:
+            return
+        scale = None if coef is None else float(coef)  # one synchronisation: the clip factor is needed on the host
+        for u in host_units:
+            if u.grad_event is not None:
+                u.grad_event.synchronize()
+            for s, e, gi, view in u.view_list:
+                if view._atb_skip:
+                    continue
+                opt.step_one(view, opt.param_groups[gi], scale)
+                view._atb_skip = True  # type: ignore[attr-defined]
+            if u.lp_stage is not None and self.on_gpu:
+                tl = u.train_len
+                with torch.cuda.stream(self.comm_stream):
+                    u.shard[:tl].copy_(u.lp_stage[:tl], non_blocking=True)
+        if self.on_gpu:
+            torch.cuda.current_stream().wait_stream(self.comm_stream)
 
     def _sync_full_params(self) -> None:
         """After an update every persistent unit re-assembles its full buffer from the shards."""

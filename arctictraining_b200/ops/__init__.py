@@ -1,5 +1,6 @@
 from . import reference
 from .functional import IGNORE_INDEX
+from .functional import COMM_COUNTER
 from .functional import LAUNCH_COUNTER
 from .functional import accumulate_lp_grad
 from .functional import adamw_step
@@ -18,7 +19,7 @@ from .functional import sumsq
 from .functional import swiglu_interleaved
 
 __all__ = [
-    "reference", "IGNORE_INDEX", "LAUNCH_COUNTER", "accumulate_lp_grad", "adamw_step", "attention",
+    "reference", "IGNORE_INDEX", "LAUNCH_COUNTER", "COMM_COUNTER", "accumulate_lp_grad", "adamw_step", "attention",
     "fused_linear_cross_entropy", "fused_linear_logprobs", "gemm", "linear", "linear_swiglu", "mlp_swiglu", "rms_norm", "rope", "rope_qkv", "set_gemm_backend",
     "sumsq", "swiglu_interleaved",
 ]

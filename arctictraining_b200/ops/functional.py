@@ -22,6 +22,8 @@ IGNORE_INDEX = ref.IGNORE_INDEX
 # which GEMM serves nn.Linear-shaped work on the GPU: "tcgen05" (this library's kernel) or "cublas"
 _GEMM_BACKEND = os.getenv("ATB200_GEMM", "tcgen05")
 LAUNCH_COUNTER = {"native": 0}
+# launches of this package's communication kernels by kind (peer barrier, pull all-gather, reduce-scatter ...)
+COMM_COUNTER: dict = {}
 
 
 def set_gemm_backend(name: str) -> None:
@@ -38,8 +40,10 @@ def _use_kernels(t: torch.Tensor) -> bool:
     return t.is_cuda and _ext.available()
 
 
-def _count(n: int = 1) -> None:
+def _count(n: int = 1, comm: str = "") -> None:
     LAUNCH_COUNTER["native"] += n
+    if comm:
+        COMM_COUNTER[comm] = COMM_COUNTER.get(comm, 0) + n
 
 
 # ------------------------------------------------------------------------------------------------ RMSNorm

@@ -32,32 +32,40 @@ class FusedAdamW(torch.optim.Optimizer):
         if not st:
             sdt = getattr(p, "_atb_state_dtype", torch.float32)
             st["step"] = 0
-            st["exp_avg"] = torch.zeros(p.numel(), dtype=sdt, device=p.device)
-            st["exp_avg_sq"] = torch.zeros(p.numel(), dtype=sdt, device=p.device)
+            pin = p.device.type == "cpu" and p.is_pinned()
+            st["exp_avg"] = torch.zeros(p.numel(), dtype=sdt, device=p.device, pin_memory=pin)
+            st["exp_avg_sq"] = torch.zeros(p.numel(), dtype=sdt, device=p.device, pin_memory=pin)
         return st
+
+    @torch.no_grad()
+    def step_one(self, p: torch.Tensor, group: Dict[str, Any], grad_scale: Optional[torch.Tensor] = None) -> None:
+        """Update one flat view (gradient in ``_atb_grad``, optional low-precision copy written to ``_atb_lp``).
+        The view, its states and its gradient may live on the device (fused CUDA kernel) or in host memory
+        (vectorised multi-threaded C++)."""
+        g = getattr(p, "_atb_grad", None)
+        if g is None:
+            g = p.grad
+        if g is None:
+            return
+        b1, b2 = group["betas"]
+        st = self._state_for(p)
+        st["step"] += 1
+        gs = grad_scale
+        if gs is not None and torch.is_tensor(gs) and gs.device != p.device:
+            gs = float(gs)
+        ops.adamw_step(
+            p.data, g, st["exp_avg"], st["exp_avg_sq"], float(group["lr"]), b1, b2, group["eps"],
+            group["weight_decay"], st["step"], gs, getattr(p, "_atb_lp", None),
+        )
 
     @torch.no_grad()
     def step_flat(self, grad_scale: Optional[torch.Tensor] = None) -> None:
         """Update every flat view handed over by the engine (gradient in ``_atb_grad``)."""
         for group in self.param_groups:
-            b1, b2 = group["betas"]
             for p in group["params"]:
                 if getattr(p, "_atb_skip", False):
-                    continue  # updated during the backward pass by the fused reduce-scatter + AdamW kernel
-                g = getattr(p, "_atb_grad", None)
-                if g is None:
-                    g = p.grad
-                if g is None:
-                    continue
-                st = self._state_for(p)
-                st["step"] += 1
-                gs = grad_scale
-                if gs is not None and gs.device != p.device:
-                    gs = float(gs)
-                ops.adamw_step(
-                    p.data, g, st["exp_avg"], st["exp_avg_sq"], float(group["lr"]), b1, b2, group["eps"],
-                    group["weight_decay"], st["step"], gs, getattr(p, "_atb_lp", None),
-                )
+                    continue  # already updated (during the backward pass, or view by view by the engine)
+                self.step_one(p, group, grad_scale)
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -67,9 +75,9 @@ class FusedAdamW(torch.optim.Optimizer):
 
 
 class CPUAdamW(FusedAdamW):
-    """Same update rule with master weights and moments in (pinned) host memory."""
-
-    writes_lp = False
+    """Same update rule; the recipe name ``cpu_adam`` of the reference.  Where the states live is decided by the
+    engine (``zero_optimization.offload_optimizer``): views in host memory are updated by the host kernel, views on
+    the device by the CUDA kernel, so a partial offload (``ratio``) runs both."""
 
 
 def _make(cls, groups: List[Dict[str, Any]], cfg: OptimizerConfig):

@@ -167,7 +167,7 @@ class _PeerExchange:
         self._reserve("do", S * Hl * D)
         buf.tensor[off : off + S * Hl * D].view(S, Hl, D).copy_(y)
         self.symm.barrier(self.OP_SLOT)
-        ops.functional._count()
+        ops.functional._count(comm="gemm_bf16_peer_a")
         return ops._ext.ops().gemm_bf16_peer_a(
             buf.ptrs, off * 2, S, Hl * D, self.rank * (S // P), S // P, weight, residual, stage_ctas
         )
@@ -218,7 +218,7 @@ class _QKVProjectPushPeer(torch.autograd.Function):
         Wl = (Hlq + 2 * Hlkv) * D
         buf, off = ex._buffer("qkv", P * S_loc * Wl)
         ex._reserve("dqkv", P * S_loc * Wl)
-        ops.functional._count()
+        ops.functional._count(comm="gemm_bf16_push_heads")
         ops._ext.ops().gemm_bf16_push_heads(x2, w, buf.ptrs, off * 2, ex.rank, Hq, Hkv, D)
         ex.symm.barrier(ex.Q_SLOT)
         ctx.save_for_backward(x2, w)

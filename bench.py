@@ -36,7 +36,13 @@ def parse_args():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=5)
     p.add_argument("--warmup", type=int, default=3)
-    p.add_argument("--impl", type=str, default="native", choices=["native", "reference"])
+    p.add_argument("--impl", type=str, default="native", choices=["native", "reference", "library_stack"],
+                   help="native: this framework; reference: the unmodified reference (unavailable offline); library_stack: "
+                        "a stand-in built from stock libraries (transformers + flash-attn + Liger + FSDP2), never "
+                        "labelled as the reference")
+    p.add_argument("--library-attn", type=str, default="flash_attention_2", help="attn_implementation of the library stack")
+    p.add_argument("--no-liger", action="store_true", help="library stack without the Liger kernels")
+    p.add_argument("--no-grad-ckpt", action="store_true", help="library stack without gradient checkpointing")
     p.add_argument("--model", type=str, default="llama-3.1-8b")
     p.add_argument("--seq-len", type=int, default=8192)
     p.add_argument("--zero-stage", type=int, default=3)
@@ -185,9 +191,8 @@ def main() -> None:
         "logger": {"level": "WARNING"},
     }
     config = get_config(recipe)
-    trainer = get_registered_trainer(config.type)(config)
-    engine = trainer.model
-    engine.train()
+    library = args.impl == "library_stack"
+    trainer = get_registered_trainer(config.type)(config, mode="process-data" if library else "train")
 
     batches = []
     it = iter(trainer.train_dataloader)
@@ -197,6 +202,14 @@ def main() -> None:
         batches.append(b)
     tokens_per_step = batches[0]["input_ids"].numel() * world
     h2d_bytes = sum(v.numel() * v.element_size() for v in batches[0].values() if torch.is_tensor(v))
+    if library:
+        sys.path.insert(0, str(ROOT / "benchmarks"))
+        import library_stack
+
+        library_stack.run(args, batches, tokens_per_step, h2d_bytes, ClockSampler)
+        return
+    engine = trainer.model
+    engine.train()
 
     def barrier():
         if world > 1:
@@ -218,6 +231,7 @@ def main() -> None:
     if rank == 0:
         sampler.start()
     launches0 = ops.LAUNCH_COUNTER["native"]
+    comm0 = dict(ops.COMM_COUNTER)
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     prof = None
     if args.torch_profile and rank == 0:
@@ -237,6 +251,7 @@ def main() -> None:
     barrier()
     ms = start.elapsed_time(end)
     launches = ops.LAUNCH_COUNTER["native"] - launches0
+    comm_launches = {k: int(v - comm0.get(k, 0)) for k, v in ops.COMM_COUNTER.items() if v - comm0.get(k, 0)}
     clocks = sampler.stop(set(range(world))) if rank == 0 else {}
     final_loss = float(loss)
     err = int(torch.ops.atb200.read_and_clear_error_flag(dev_batches[0]["input_ids"]))
@@ -246,12 +261,12 @@ def main() -> None:
     e2e_ms = None
     if not args.skip_e2e:
         e2e_batches = batches[total_steps : 2 * total_steps]
-        for b in e2e_batches[: min(1, args.warmup)]:
+        for b in e2e_batches[: args.warmup]:  # the same warm-up as the device-timed loop
             trainer.metrics.values.clear() if trainer.metrics.enabled else None
             trainer.step(dict(b))
         barrier()
         t0 = time.perf_counter()
-        for b in e2e_batches[min(1, args.warmup) : min(1, args.warmup) + args.steps]:
+        for b in e2e_batches[args.warmup : args.warmup + args.steps]:
             if trainer.metrics.enabled:
                 trainer.metrics.values.clear()
             trainer.step(dict(b))  # H2D of the pinned batch, fwd, bwd, optimizer step, loss.item()
@@ -292,12 +307,16 @@ def main() -> None:
                 "layers_keeping_activations": (engine._keep_state.get("kept_layers", 0) if args.keep == "auto"
                                                else min(int(args.keep), cfg["num_hidden_layers"])),
                 "attention": args.attn,
+                "attention_backward": ("own tcgen05 kernel" if args.attn == "native" and os.getenv("ATB200_ATTN_BWD", "native") == "native"
+                                       else os.getenv("ATB200_ATTN_BWD", "library")),
+                "fused_comm": bool(getattr(engine, "symm", None) is not None),
                 "gemm": args.gemm + ("" if args.gemm != "tcgen05" else ("-1cta" if args.no_cta_pairs else "-2cta")),
                 "l2_policy": "inputs larger than L2 (16 GB of weights streamed every step)",
                 "valid": not args.layers,
             },
             "clocks": clocks,
             "gpu_launches": int(launches),
+            "comm_kernel_launches": comm_launches,
             "final_loss": round(final_loss, 4),
             "kernel_error_flag": err,
             "keep_state": {k: (round(v / 2**30, 2) if isinstance(v, (int, float)) and v > 1e6 else v)

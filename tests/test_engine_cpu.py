@@ -217,3 +217,91 @@ def test_auto_keep_policy_follows_measured_memory(monkeypatch):
     kept = one_step(4 * GiB)
     assert kept == [100 + 4 * (i + 1) + 10 <= st["limit"] / GiB for i in range(len(units))] and all(kept)
     engine.on_gpu = False
+
+
+def test_fused_reduce_decision_is_the_same_for_every_rank_of_a_partly_frozen_unit():
+    """A unit whose trainable prefix is shorter than one shard (LoRA, SwiftKV-style partial freezing): the ranks
+    behind the frozen tail hold no trainable element, yet they must take the same communication path."""
+    from types import SimpleNamespace
+
+    m = make_model()
+    layer = m.model.layers[1]
+    for n, p in layer.named_parameters():
+        p.requires_grad_("input_layernorm" in n)  # only a 64-element vector trains in this layer
+    e = make_engine(m, 2)
+    u = next(u for u in e.units if u.name.endswith("1") and u.checkpointed)
+    assert 0 < u.n_train < 256
+    # pretend to be each rank of a 4-way group with the peer-memory path available
+    decisions, single, lengths = [], [], []
+    for r in range(4):
+        u.group_size, u.group_rank, u.shard_size, u.dtype = 4, r, u.numel // 4, torch.bfloat16
+        e.symm, e._grad_symm = SimpleNamespace(), [object()]
+        lengths.append(u.train_len)
+        decisions.append(e._fused_reduce_ok(u))
+        e.cfg.gradient_clipping = 0.0
+        single.append(e._single_pass_update_ok(u))
+        e.cfg.gradient_clipping = 1.0
+    assert lengths[0] > 0 and lengths[-1] == 0  # the premise: the local trainable length differs between ranks
+    assert len(set(decisions)) == 1 and decisions[0] is True
+    assert len(set(single)) == 1
+    # the runs that any rank computes for a peer are that peer's own runs
+    u.group_rank = 0
+    assert e._runs_of_rank(u, 0) and not e._runs_of_rank(u, 3)
+
+
+def test_step_raises_on_a_recorded_kernel_error_and_applies_no_update():
+    from arctictraining_b200.exceptions import CommTimeoutError
+    from arctictraining_b200.exceptions import KernelWaitError
+
+    m = make_model()
+    e = make_engine(m, 1)
+    b = batches(1)[0]
+    for words, exc in (((0, 0x102), CommTimeoutError), ((0x2801, 0), KernelWaitError), ((0, 0x3102), RuntimeError)):
+        e._read_error_words = lambda w=words: w
+        before = full_params(e)
+        masters = [u.master.clone() for u in e.units if u.master is not None]
+        out = e(**b)
+        e.backward(out.loss)
+        with pytest.raises(exc):
+            e.step()
+        assert e.global_steps == 0
+        after = full_params(e)
+        assert all(torch.equal(before[n], after[n]) for n in before)
+        assert all(torch.equal(a, u.master) for a, u in zip(masters, [u for u in e.units if u.master is not None]))
+        e.micro_steps = 0
+        for u in e.units:
+            u.grad_acc_valid = False
+
+
+def _engine_with(model, zero_cfg, opt_cls=FusedAdamW, **extra):
+    model.activation_checkpointing = True
+    groups = OptimizerFactory.get_optimizer_grouped_params(model, 0.1)
+    opt = opt_cls(groups, lr=1e-2, betas=(0.9, 0.95))
+    return TrainingEngine(model, opt, None, {"zero_optimization": zero_cfg, "gradient_clipping": 1.0, **extra})
+
+
+@pytest.mark.parametrize("ratio", [1.0, 0.5])
+def test_optimizer_offload_places_units_by_ratio_and_matches_the_plain_engine(ratio):
+    """``offload_optimizer`` (with ``ratio``) changes where states live, not what is computed."""
+    from arctictraining_b200.optimizer.adam import CPUAdamW
+
+    data = batches(3)
+    base = _engine_with(make_model(), {"stage": 3})
+    off = _engine_with(make_model(), {"stage": 3, "offload_optimizer": {"device": "cpu", "ratio": ratio}}, CPUAdamW)
+    hosted = [u for u in off.units if u.host_states]
+    trainable = [u for u in off.units if u.n_train > 0]
+    assert hosted and (len(hosted) == len(trainable)) == (ratio == 1.0)
+    frac = sum(u.n_train for u in hosted) / sum(u.n_train for u in trainable)
+    assert frac >= ratio - 1e-9 and (ratio == 1.0 or frac < 1.0)
+    assert not any(u.host_states for u in base.units)
+    assert run(base, data) == run(off, data)
+    a, b = full_params(base), full_params(off)
+    assert all(torch.equal(a[n], b[n]) for n in a)
+
+
+def test_offload_keys_are_read_from_the_recipe_spelling():
+    from arctictraining_b200.engine.config import EngineConfig
+
+    c = EngineConfig.from_dict({"zero_optimization": {"stage": 3, "offload_optimizer": {"device": "cpu", "ratio": 0.7},
+                                                      "offload_param": {"device": "cpu"}}})
+    assert c.offload_optimizer and c.offload_param and c.offload_optimizer_ratio == 0.7
