@@ -30,6 +30,10 @@ def main() -> None:
     ap.add_argument("--act-offload", action="store_true", help="checkpointed activations go to pinned host memory")
     ap.add_argument("--keep", default="auto")
     ap.add_argument("--fused-comm", default="auto", choices=["auto", "off"])
+    ap.add_argument("--optimizer", default="fused_adam", choices=["fused_adam", "cpu_adam"],
+                    help="cpu_adam: optimizer states in pinned host memory (zero_optimization.offload_optimizer)")
+    ap.add_argument("--offload-ratio", type=float, default=1.0, help="fraction of the optimizer states kept on the host")
+    ap.add_argument("--offload-param", action="store_true", help="parameter shards in pinned host memory too")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
 
@@ -58,6 +62,11 @@ def main() -> None:
     assert S % (world * 128) == 0, "sequence length must be a multiple of 128 x ranks"
 
     workdir = Path(tempfile.gettempdir()) / f"atb200_alst_{os.getuid()}"
+    zero = {"stage": 3}
+    if args.optimizer == "cpu_adam":
+        zero["offload_optimizer"] = {"device": "cpu", "ratio": args.offload_ratio}
+    if args.offload_param:
+        zero["offload_param"] = {"device": "cpu"}
     recipe = {
         "type": "sft",
         "micro_batch_size": 1,
@@ -70,9 +79,9 @@ def main() -> None:
                   "hf_config_kwargs": {"num_hidden_layers": args.layers} if args.layers else {}},
         "data": {"sources": [{"type": "synthetic", "num_samples": 8 * world, "min_length": 64, "max_length": 128}],
                  "cache_dir": str(workdir / "cache"), "max_length": 128, "dl_num_workers": 0, "num_proc": 1},
-        "optimizer": {"lr": 1e-5, "weight_decay": 0.1},
+        "optimizer": {"type": args.optimizer, "lr": 1e-5, "weight_decay": 0.1},
         "scheduler": {"name": "constant"},
-        "deepspeed": {"zero_optimization": {"stage": 3}, "gradient_clipping": 1.0, "activation_checkpoint_keep": args.keep},
+        "deepspeed": {"zero_optimization": zero, "gradient_clipping": 1.0, "activation_checkpoint_keep": args.keep},
         "train_log_iter_interval": 0,
         "train_log_metrics_path": str(workdir / f"metrics_{rank}.jsonl"),
         "logger": {"level": "WARNING"},
@@ -130,7 +139,10 @@ def main() -> None:
                        "tiled_cross_entropy": True, "activation_offload": args.act_offload, "attention": args.attn,
                        "peer_memory_exchange": bool(world > 1 and trainer.sp_context.fused),
                        "attention_blocks_with_exchange_in_gemm": trainer.sp_context.fused_block_calls if world > 1 else 0,
-                       "layers_keeping_activations": eng._keep_state.get("kept_layers", 0)},
+                       "layers_keeping_activations": eng._keep_state.get("kept_layers", 0),
+                       "optimizer": args.optimizer, "offload_optimizer_ratio": args.offload_ratio if args.optimizer == "cpu_adam" else 0.0,
+                       "offload_param": args.offload_param,
+                       "attention_backward": os.getenv("ATB200_ATTN_BWD", "native")},
             "max_memory_gib_per_gpu": round(float(mem), 2), "gpu_launches": ops.LAUNCH_COUNTER["native"] - launches0,
             "kernel_error_flag": err,
         }

@@ -95,3 +95,41 @@ def test_native_attention_in_the_model_matches_sdpa():
     a = run(make_engine(make_model("cuda", torch.bfloat16, "sdpa")), data)
     b = run(make_engine(make_model("cuda", torch.bfloat16, "native")), data)
     assert b == pytest.approx(a, rel=2e-2)
+
+
+@pytest.mark.parametrize("zero", [
+    {"stage": 3, "offload_optimizer": {"device": "cpu"}},
+    {"stage": 3, "offload_optimizer": {"device": "cpu", "ratio": 0.5}},
+    {"stage": 3, "offload_optimizer": {"device": "cpu"}, "offload_param": {"device": "cpu"}},
+    {"stage": 2, "offload_optimizer": {"device": "cpu"}},
+])
+def test_host_offload_of_optimizer_states_and_parameters_matches_the_device_engine(zero, monkeypatch):
+    """Optimizer states (all, or a fraction) and parameter shards in pinned host memory: same losses and the same
+    weights as with everything on the device (the host AdamW and the CUDA AdamW follow the same update rule; the
+    comparison run keeps fp32 gradient shards so that both accumulate alike)."""
+    monkeypatch.setenv("ATB200_DIRECT_GRADS", "0")
+    data = batches(3, "cuda")
+    base = make_engine(make_model("cuda", torch.bfloat16), zero["stage"])
+    opt = FusedAdamW(OptimizerFactory.get_optimizer_grouped_params(m := make_model("cuda", torch.bfloat16), 0.1), lr=3e-3, betas=(0.9, 0.95))
+    off = TrainingEngine(m, opt, None, {"zero_optimization": zero, "gradient_clipping": 1.0, "bf16": {"enabled": True}})
+    hosted = [u for u in off.units if u.host_states]
+    assert hosted and all(u.master.device.type == "cpu" and u.master.is_pinned() for u in hosted if u.master is not None)
+    if "ratio" in zero["offload_optimizer"]:
+        assert any(u.master is not None and u.master.is_cuda for u in off.units)
+    if "offload_param" in zero:
+        held = [u for u in off.units if u.host_params]
+        assert held and all(u.shard.device.type == "cpu" and u.shard.is_pinned() and not u.persistent for u in held)
+    la, lb = run(base, data), run(off, data)
+    assert lb == pytest.approx(la, rel=2e-3)
+    pa = dict(base.iter_full_named_parameters())
+    for n, t in off.iter_full_named_parameters():
+        # AdamW turns gradients near its epsilon into full-size steps of either sign, and the host kernel (exact
+        # division and square root) and the CUDA kernel (fast-math) round differently there: allow a small fraction
+        # of elements to differ by a few learning-rate steps, and require the tensors to agree as a whole
+        a, b = t.float().cpu(), pa[n].float().cpu()
+        bad = ((a - b).abs() > 2e-3 + 2e-2 * b.abs()).float().mean().item()
+        assert bad < 0.01, (n, bad)
+        assert float((a - b).abs().max()) <= 4 * 3e-3 * len(data), n
+        assert float((a - b).norm() / (b.norm() + 1e-12)) < 2e-2, n
+    assert float(off.get_global_grad_norm()) == pytest.approx(float(base.get_global_grad_norm()), rel=1e-2)
+    assert int(torch.ops.atb200.read_and_clear_error_flag(torch.zeros(1, device="cuda"))) == 0
