@@ -75,6 +75,48 @@ def scenario_fused_vs_nccl(out_dir):
         (Path(out_dir) / "fused_vs_nccl.json").write_text(json.dumps(res))
 
 
+def scenario_partly_frozen(out_dir):
+    """Layers whose trainable prefix is shorter than one rank's shard (what LoRA or SwiftKV-style freezing produces):
+    the ranks behind the frozen tail hold no trainable element of those units and must still take the same
+    communication path as the others.  Also: two identical runs of the peer-memory path give bit-identical weights."""
+    def build(fused, clip):
+        e_cfg = load_arch_config("llama-3.1-8b", OVERRIDES)
+        with torch.device("cuda"):
+            m = CausalLM(e_cfg, dtype=torch.bfloat16)
+        m.init_weights(seed=0)
+        m.attn_impl = "sdpa"
+        for layer in m.model.layers[1:]:
+            for n, p in layer.named_parameters():
+                p.requires_grad_("input_layernorm" in n)
+        opt = FusedAdamW(OptimizerFactory.get_optimizer_grouped_params(m, 0.1), lr=1e-3, betas=(0.9, 0.95))
+        return TrainingEngine(m, opt, None, {"zero_optimization": {"stage": 3}, "gradient_clipping": clip,
+                                             "bfloat16": {"enabled": True}, "fused_comm": "auto" if fused else "off"})
+
+    res = {}
+    for clip in (1.0, 0.0):
+        a = build(False, clip)
+        la = run(a)
+        pa = {n: t.float().clone() for n, t in a.iter_full_named_parameters()}
+        runs = []
+        for _ in range(2):
+            b = build(True, clip)
+            assert b.symm is not None, "peer-memory path did not come up"
+            frozen_tail = [u for u in b.units if u.checkpointed and 0 < u.n_train < u.shard_size]
+            assert frozen_tail, "the scenario needs units whose trainable prefix is shorter than a shard"
+            assert all(b._fused_reduce_ok(u) for u in frozen_tail)
+            lb = run(b)
+            b.check_device_errors()
+            runs.append((lb, {n: t.clone() for n, t in b.iter_full_named_parameters()}))
+        diff = max(float((pa[n] - runs[0][1][n].float()).abs().max()) for n in pa)
+        same = all(torch.equal(runs[0][1][n], runs[1][1][n]) for n in pa) and runs[0][0] == runs[1][0]
+        res[f"clip{clip}"] = {"nccl": la, "fused": runs[0][0], "max_param_diff": diff, "bit_identical_reruns": bool(same),
+                              "local_train_len": [u.train_len for u in frozen_tail]}
+    allres = [None] * dist.get_world_size()
+    dist.all_gather_object(allres, res)
+    if dist.get_rank() == 0:
+        (Path(out_dir) / "partly_frozen.json").write_text(json.dumps(allres))
+
+
 def scenario_barrier_timeout(out_dir):
     """Rank 0 waits at a barrier that rank 1 joins only later: the wait runs out, the host sees an error status,
     and the context keeps working (plain peer loads, no multicast involved)."""
@@ -261,7 +303,7 @@ def main():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch._C._set_print_stack_traces_on_fatal_signal(True)  # a crash in native code reports where
     init_distributed(timeout_s=120)
-    {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout,
+    {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout, "partly_frozen": scenario_partly_frozen,
      "ulysses_peer": scenario_ulysses_peer, "moe_peer": scenario_moe_peer,
      "fused_attention_block": scenario_fused_attention_block}[scenario](out_dir)
     dist.barrier()

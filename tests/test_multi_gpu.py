@@ -33,6 +33,19 @@ def test_peer_memory_path_matches_nccl(tmp_path):
         assert r["max_param_diff"] < 2e-2, stage
 
 
+def test_partly_frozen_units_take_one_communication_path_on_every_rank(tmp_path):
+    launch(2, "partly_frozen", tmp_path)
+    per_rank = json.loads((tmp_path / "partly_frozen.json").read_text())
+    # the premise: the last rank holds no trainable element of the partly frozen units, the first one does
+    assert all(n > 0 for n in per_rank[0]["clip1.0"]["local_train_len"])
+    assert all(n == 0 for n in per_rank[-1]["clip1.0"]["local_train_len"])
+    for r in per_rank:
+        for name, v in r.items():
+            assert v["fused"] == pytest.approx(v["nccl"], rel=2e-3), name
+            assert v["max_param_diff"] < 2e-2, name
+            assert v["bit_identical_reruns"], name
+
+
 def test_bounded_barrier_reports_a_missing_peer(tmp_path):
     launch(2, "barrier_timeout", tmp_path)
     assert json.loads((tmp_path / "barrier_timeout.json").read_text())["ok"]
