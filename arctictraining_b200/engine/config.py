@@ -30,6 +30,17 @@ def _parse_keep(v: Any) -> Any:
     return int(v or 0)
 
 
+def _parse_comm_dtype(v: Any) -> Optional[torch.dtype]:
+    if v is None:
+        return None
+    name = str(v).replace("torch.", "").lower()
+    table = {"fp32": torch.float32, "float32": torch.float32, "bf16": torch.bfloat16, "bfloat16": torch.bfloat16,
+             "fp16": torch.float16, "float16": torch.float16}
+    if name not in table:
+        raise ValueError(f"communication_data_type: unknown dtype {v!r} (fp32, bf16 or fp16)")
+    return table[name]
+
+
 @dataclass
 class EngineConfig:
     zero_stage: int = 0
@@ -39,6 +50,11 @@ class EngineConfig:
     sequence_parallel_size: int = 1
     bf16: bool = False
     fp16: bool = False
+    initial_scale_power: int = 16
+    loss_scale_window: int = 1000
+    min_loss_scale: float = 1.0
+    loss_scale: float = 0.0  # 0: dynamic
+    communication_data_type: Optional[torch.dtype] = None  # dtype in which gradients cross the wire (None: as stored)
     bf16_master_weights_and_grads: bool = False
     bf16_optimizer_states: bool = False
     autocast: bool = False
@@ -71,6 +87,11 @@ class EngineConfig:
             sequence_parallel_size=int(d.get("sequence_parallel_size", 1)),
             bf16=bool(bf.get("enabled", False)),
             fp16=bool(fp.get("enabled", False)),
+            initial_scale_power=int(fp.get("initial_scale_power", 16)),
+            loss_scale_window=int(fp.get("loss_scale_window", 1000)),
+            min_loss_scale=float(fp.get("min_loss_scale", 1.0)),
+            loss_scale=float(fp.get("loss_scale", 0.0)),
+            communication_data_type=_parse_comm_dtype(d.get("communication_data_type")),
             bf16_master_weights_and_grads=bool(bf.get("bf16_master_weights_and_grads", False)),
             bf16_optimizer_states=bool(bf.get("bf16_optimizer_states", False)),
             autocast=bool(ac.get("enabled", False)),

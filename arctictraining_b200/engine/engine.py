@@ -116,6 +116,8 @@ class ZeroUnit:
         self.grad_event = None    # completion of the asynchronous device -> host copy of the gradient shard
         self.grad_sumsq = None    # sum of squares of that shard, computed on the device before it left
         self.lp_stage: Optional[torch.Tensor] = None  # pinned bf16 buffer the host optimizer writes updated weights to
+        self.grad_symm = None     # symmetric gradient buffer of a unit outside the pool (embedding, head)
+        self.grad_hook_left = 0   # parameters of such a unit whose gradients have not arrived yet in this backward
 
     @property
     def train_len(self) -> int:
@@ -160,6 +162,12 @@ class TrainingEngine:
         self.skipped_steps = 0
         self._grad_norm: Optional[torch.Tensor] = None
         self._single_pass_sumsq: Optional[torch.Tensor] = None
+        # fp16: gradients are computed on a scaled loss; the scale is divided out when they are accumulated, halved
+        # after a step whose gradient norm is not finite (that step is skipped) and doubled after a window of good steps
+        self.loss_scale = 1.0
+        self._good_steps = 0
+        if self.cfg.fp16:
+            self.loss_scale = self.cfg.loss_scale if self.cfg.loss_scale > 0 else float(2 ** self.cfg.initial_scale_power)
         self.timers = TimerGroup()
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.on_gpu else None
         self.sp_size = max(1, self.cfg.sequence_parallel_size)
@@ -291,6 +299,7 @@ class TrainingEngine:
             for p, o in zip(ordered, u.offsets):
                 flat[o : o + p.numel()].copy_(p.data.reshape(-1))
                 p.data = flat[o : o + p.numel()].view(p.shape)
+                p._atb_numel = p.numel()  # the logical size: ``p.data`` is empty while a stage-3 unit is released
             u.flat = flat
             lo = u.group_rank * u.shard_size
             # a group of one rank has nothing to gather: the shard is the whole unit and stays in place
@@ -332,6 +341,14 @@ class TrainingEngine:
                     # gradient buffers that peers read directly: same three slots on every rank
                     self._grad_symm = [self.symm.alloc(f"grad{i}", n, torch.bfloat16) for i in range(3)]
                     self._grad_pool.bufs = [b.tensor for b in self._grad_symm]
+            if self.symm is not None:
+                # the large units outside the pool (embedding, head) get symmetric gradient buffers of their own, so
+                # that they are reduced by the same peer-memory kernel, as soon as their gradients are complete
+                for u in self.units:
+                    if (not u.checkpointed and u.n_train > 0 and u.group_size > 1 and u.dtype == torch.bfloat16
+                            and not getattr(u, "is_expert", False) and u.numel >= (1 << 16)):
+                        u.grad_symm = self.symm.alloc(f"grad_{u.name}", u.numel, torch.bfloat16)
+                self._install_grad_ready_hooks()
 
     @staticmethod
     def _runs_of_rank(u: ZeroUnit, group_rank: int) -> List[Tuple[int, int, int]]:
@@ -387,9 +404,13 @@ class TrainingEngine:
             logger.warning(f"peer-memory communication unavailable ({exc}); using NCCL")
             self.symm = None
             return
-        if self.stage == 3 and max_pool_numel:
-            # all released units keep their bf16 shards in one symmetric slab so that peers can pull them
-            units = [u for u in self.units if not u.persistent and u.dtype == torch.bfloat16 and not u.host_params]
+        if self.stage >= 1:
+            # bf16 shards live in one symmetric slab so that peers can pull them: the released units of stage 3
+            # (gathered right before use) and the units that stay assembled (every unit below stage 3; embedding and
+            # head at stage 3), whose full buffers are re-assembled from the peers' shards after each update
+            units = [u for u in self.units
+                     if u.dtype == torch.bfloat16 and not u.host_params and u.group_size > 1 and not getattr(u, "is_expert", False)
+                     and (not u.persistent or (u.n_train > 0 and self.training_mode and self.optimizer is not None))]
             total = sum(u.shard_size for u in units)
             if total:
                 self._shard_symm = self.symm.alloc("shards", total, torch.bfloat16)
@@ -402,6 +423,27 @@ class TrainingEngine:
                     off += u.shard_size
                 torch.cuda.synchronize()
                 dist.barrier(group=self.dp_group, device_ids=[self.device.index])
+
+    def _install_grad_ready_hooks(self) -> None:
+        """Units that are not wrapped (embedding, final norm + head) are reduced as soon as every one of their
+        parameters has received its gradient in the running backward pass: the head's weight gradient exists right at
+        the start of backward, and reducing it then leaves the whole pass to hide the transfer.  A parameter that
+        gets no gradient in some pass simply leaves the unit to the sweep at the end of ``backward``."""
+        for u in self.units:
+            if u.grad_symm is None:
+                continue
+            trainable = [p for p in u.params[: u.n_trainable_params]]
+            u.grad_hook_params = len(trainable)
+
+            def hook(_p, __unit=u):
+                if __unit.grad_flat is None:
+                    return
+                __unit.grad_hook_left -= 1
+                if __unit.grad_hook_left == 0:
+                    self._reduce_unit(__unit)
+
+            for p in trainable:
+                p.register_post_accumulate_grad_hook(hook)
 
     def _persist_threshold(self) -> int:
         zo = self.cfg.raw.get("zero_optimization", {}) or {}
@@ -493,7 +535,7 @@ class TrainingEngine:
             # place), all on the communication stream so that the copy of the next unit runs under this one's compute
             lo = u.group_rank * u.shard_size
             self.comm_stream.wait_stream(torch.cuda.current_stream())
-            with torch.cuda.stream(self.comm_stream):
+            with torch.cuda.stream(self.comm_stream), self._timed("gather"):
                 flat[lo : lo + u.shard_size].copy_(u.shard, non_blocking=True)
                 if self.dist_on and u.group_size > 1:
                     self._all_gather(flat, flat[lo : lo + u.shard_size], u.group)
@@ -502,7 +544,7 @@ class TrainingEngine:
         elif self.dist_on and u.group_size > 1:
             if self.on_gpu:
                 self.comm_stream.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(self.comm_stream):
+                with torch.cuda.stream(self.comm_stream), self._timed("gather"):
                     if self._shard_symm is not None and hasattr(u, "symm_shard_offset"):
                         # shards only change in the optimizer step, which ends with a barrier: pull directly
                         self.symm.all_gather(self._shard_symm, u.symm_shard_offset, u.shard_size, flat)
@@ -687,6 +729,10 @@ class TrainingEngine:
             slot, buf = self._grad_pool.acquire()
             g = buf[: u.numel]
             g.zero_()
+        elif u.grad_symm is not None:
+            slot, g = None, u.grad_symm.tensor[: u.numel]
+            g.zero_()
+            u.grad_hook_left = u.grad_hook_params
         else:
             slot, g = None, torch.zeros(u.numel, dtype=u.dtype, device=self.device)
         u.grad_flat, u.grad_slot = g, slot
@@ -715,13 +761,16 @@ class TrainingEngine:
             u.grad_acc_valid = True
             return
         tl = u.train_len
-        scale = 1.0 / (u.grad_divisor * self.gas)
+        scale = 1.0 / (u.grad_divisor * self.gas * self.loss_scale)
         lo = u.group_rank * u.shard_size
 
         # Both decisions use values that are equal on every rank of the group: a rank whose shard holds no trainable
         # element (a partly frozen unit: LoRA, SwiftKV) still joins the barriers and skips the arithmetic.
         fused = self._fused_reduce_ok(u)
         single_pass = fused and self._single_pass_update_ok(u)
+
+        symm_buf = u.grad_symm if u.grad_symm is not None else (
+            self._grad_symm[u.grad_slot] if (self._grad_symm is not None and u.grad_slot is not None) else None)
 
         def work() -> None:
             if single_pass:
@@ -736,7 +785,7 @@ class TrainingEngine:
                     st["step"] += 1
                     b1, b2 = group["betas"]
                     ss = torch.ops.atb200.p2p_reduce_scatter_adamw(
-                        self._grad_symm[u.grad_slot].ptrs, lo + s, e - s, scale, view, st["exp_avg"], st["exp_avg_sq"],
+                        symm_buf.ptrs, lo + s, e - s, scale, view, st["exp_avg"], st["exp_avg_sq"],
                         view._atb_lp, float(group["lr"]), b1, b2, group["eps"], group["weight_decay"], st["step"],
                     )
                     self._single_pass_sumsq = ss if self._single_pass_sumsq is None else self._single_pass_sumsq + ss
@@ -751,19 +800,23 @@ class TrainingEngine:
                 if tl > 0:
                     n8 = (tl + 7) // 8 * 8
                     self.symm.reduce_scatter_accumulate(
-                        self._grad_symm[u.grad_slot], lo, min(n8, u.grad_acc.numel() // 8 * 8), u.grad_acc, scale,
+                        symm_buf, lo, min(n8, u.grad_acc.numel() // 8 * 8), u.grad_acc, scale,
                         overwrite=not u.grad_acc_valid,
                     )
                     u.grad_acc_valid = True
                 self.symm.barrier(slot=2)
                 return
             if self.dist_on and u.group_size > 1:
+                # ``communication_data_type``: the dtype in which the library collective sums (the peer-memory kernel
+                # always sums in fp32)
+                cdt = self.cfg.communication_data_type
+                src = g if cdt is None or cdt == g.dtype else g.to(cdt)
                 if self.stage >= 1:
-                    piece = torch.empty(u.shard_size, dtype=g.dtype, device=g.device)
-                    self._reduce_scatter(piece, g, u.group)
+                    piece = torch.empty(u.shard_size, dtype=src.dtype, device=src.device)
+                    self._reduce_scatter(piece, src, u.group)
                 else:
-                    dist.all_reduce(g, group=u.group)
-                    piece = g[lo : lo + u.shard_size]
+                    dist.all_reduce(src, group=u.group)
+                    piece = src[lo : lo + u.shard_size]
             else:
                 piece = g[lo : lo + u.shard_size]
             if tl > 0:
@@ -772,15 +825,17 @@ class TrainingEngine:
         if self.on_gpu:
             self.comm_stream.wait_stream(torch.cuda.current_stream())
             with torch.cuda.stream(self.comm_stream):
-                work()
+                with self._timed("reduce"):
+                    work()
                 ev = torch.cuda.Event()
                 ev.record()
             if u.grad_slot is not None:
                 self._grad_pool.release(u.grad_slot, ev)
-            else:
+            elif u.grad_symm is None:
                 g.record_stream(self.comm_stream)
         else:
-            work()
+            with self._timed("reduce"):
+                work()
             if u.grad_slot is not None:
                 self._grad_pool.release(u.grad_slot, None)
         u.grad_flat, u.grad_slot = None, None
@@ -794,8 +849,9 @@ class TrainingEngine:
         of NCCL.  Every input is the same on all ranks of the unit's group: taking the decision from rank-local
         values (for instance the length of the local trainable slice, which is zero on the ranks behind a frozen
         tail) would send some ranks into the barriers and the others into a collective nobody else joins."""
+        pooled = self._grad_symm is not None and u.checkpointed
         return bool(
-            self.symm is not None and self._grad_symm is not None and u.checkpointed and u.n_train > 0
+            self.symm is not None and (pooled or u.grad_symm is not None) and u.n_train > 0
             and self._states_on_device_fp32(u) and u.group_size > 1 and u.dtype == torch.bfloat16
             and u.shard_size % 8 == 0
         )
@@ -849,8 +905,23 @@ class TrainingEngine:
     def __call__(self, *args, **kwargs):
         return self.forward(*args, **kwargs)
 
+    @contextmanager
+    def _timed(self, name: str):
+        """``wall_clock_breakdown``: device-timed sections ``forward`` / ``backward`` / ``step`` on the compute stream and
+        ``gather`` / ``reduce`` on the communication stream (milliseconds, merged into the trainer's JSONL metrics as
+        the reference merges its engine's wall-clock timers, arctic_training/trainer/trainer.py:603-605)."""
+        if not self.cfg.wall_clock_breakdown:
+            yield
+            return
+        t = self.timers(name)
+        t.start()
+        try:
+            yield
+        finally:
+            t.stop()
+
     def forward(self, *args, **kwargs):
-        with self.autocast():
+        with self._timed("forward"), self.autocast():
             return self.module(*args, **kwargs)
 
     def autocast(self):
@@ -892,14 +963,15 @@ class TrainingEngine:
 
     def backward(self, loss: torch.Tensor) -> None:
         """Back-propagate one micro-batch; gradients end up reduced in the fp32 shards."""
-        for u in self.units:
-            if not u.checkpointed and u.n_train > 0:
-                self._ensure_resident(u)
-                self._prepare_grad_buffer(u)
-        loss.backward()
-        for u in self.units:
-            if u.grad_flat is not None:
-                self._reduce_unit(u)
+        with self._timed("backward"):
+            for u in self.units:
+                if not u.checkpointed and u.n_train > 0:
+                    self._ensure_resident(u)
+                    self._prepare_grad_buffer(u)
+            (loss * self.loss_scale if self.cfg.fp16 else loss).backward()
+            for u in self.units:
+                if u.grad_flat is not None:
+                    self._reduce_unit(u)
 
     def step(self) -> None:
         boundary = self.is_gradient_accumulation_boundary()
@@ -910,7 +982,8 @@ class TrainingEngine:
         if self.on_gpu:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
         self.check_device_errors()
-        self._optimizer_step()
+        with self._timed("step"):
+            self._optimizer_step()
         self.global_steps += 1
         if self.lr_scheduler is not None:
             self.lr_scheduler.step()
@@ -953,7 +1026,7 @@ class TrainingEngine:
                 total += sq
         if self.dist_on:
             if self.stage >= 1:
-                dist.all_reduce(total, group=self.dp_group)
+                total = self._sum_over_ranks(total)
             if self.expert_dp_group is not None:
                 if self.stage >= 1:
                     dist.all_reduce(expert_total, group=self.expert_dp_group)
@@ -962,6 +1035,26 @@ class TrainingEngine:
                 if ep_world > 1:
                     dist.all_reduce(expert_total, group=self._ep_group_for_norm())
         return (total + expert_total).sqrt()
+
+    def _sum_over_ranks(self, value: torch.Tensor) -> torch.Tensor:
+        """Sum of a scalar over the data-parallel group.  With the peer-memory path every rank writes its part into a
+        symmetric slot, a device barrier follows, and each rank reads and adds all parts in rank order (the same
+        bits everywhere); otherwise a library all-reduce."""
+        if self.symm is None:
+            dist.all_reduce(value, group=self.dp_group)
+            return value
+        if getattr(self, "_scalar_symm", None) is None:
+            self._scalar_symm = self.symm.alloc("scalars", 2 * 4, torch.float32)  # two turns of one 16-byte slot
+            self._scalar_turn = 0
+            self._scalar_gathered = torch.zeros(self.world * 4, dtype=torch.float32, device=self.device)
+        turn = self._scalar_turn
+        self._scalar_turn ^= 1
+        slot = self._scalar_symm.tensor[turn * 4 : turn * 4 + 4]
+        slot.zero_()
+        slot[0:1].copy_(value.reshape(1))
+        self.symm.barrier(slot=3)
+        self.symm.all_gather(self._scalar_symm, turn * 4, 4, self._scalar_gathered)
+        return self._scalar_gathered.view(self.world, 4)[:, 0].sum()
 
     def _ep_group_for_norm(self):
         return getattr(self, "ep_group", None)
@@ -972,6 +1065,8 @@ class TrainingEngine:
             return
         norm = self._compute_grad_norm()
         self._grad_norm = norm
+        if self.cfg.fp16 and self._fp16_overflow(norm):
+            return
         clip = self.cfg.gradient_clipping
         coef: Optional[torch.Tensor] = None
         if clip and clip > 0:
@@ -1014,9 +1109,29 @@ class TrainingEngine:
             u.grad_event = None
             u.stepped_in_backward = False
         self._sync_full_params()
-        if self.symm is not None:
-            self.symm.barrier(slot=0)  # shards are final on every rank before anyone pulls them again
         self._update_keep_state()
+
+    def _fp16_overflow(self, norm: torch.Tensor) -> bool:
+        """Dynamic loss scaling: a gradient norm that is not finite means the scaled loss overflowed somewhere.  The
+        step is skipped (gradients dropped, ``skipped_steps`` counted) and the scale halved; after
+        ``loss_scale_window`` good steps in a row the scale doubles.  One host read of the norm per step."""
+        finite = bool(torch.isfinite(norm))
+        dynamic = self.cfg.loss_scale <= 0
+        if finite:
+            self._good_steps += 1
+            if dynamic and self._good_steps % self.cfg.loss_scale_window == 0:
+                self.loss_scale *= 2.0
+            return False
+        self.skipped_steps += 1
+        self._good_steps = 0
+        if dynamic:
+            self.loss_scale = max(self.cfg.min_loss_scale, self.loss_scale / 2.0)
+        for u in self.units:
+            u.grad_acc_valid = False
+            u.grad_sumsq = None
+            u.grad_event = None
+        logger.warning(f"fp16: gradient overflow, step skipped, loss scale now {self.loss_scale:g}")
+        return True
 
     def _step_host_units(self, opt, coef: Optional[torch.Tensor]) -> None:
         """Units whose optimizer states live in host memory, one after the other: wait for the unit's gradient shard
@@ -1043,15 +1158,22 @@ class TrainingEngine:
             torch.cuda.current_stream().wait_stream(self.comm_stream)
 
     def _sync_full_params(self) -> None:
-        """After an update every persistent unit re-assembles its full buffer from the shards."""
+        """After an update every unit that stays assembled rebuilds its full buffer from the shards: pulled from the
+        peers' symmetric shard slabs where the peer-memory path is up (after a device barrier: shards are final on
+        every rank before anyone reads them), through the library all-gather otherwise."""
         if self.stage == 0 or not self.dist_on:
             return
+        if self.symm is not None:
+            self.symm.barrier(slot=0)
         for u in self.units:
             if u.group_size <= 1 or u.master is None and u.n_train == 0:
                 continue
             if u.persistent:
-                # shard is a view of flat: in-place all-gather
-                self._all_gather(u.flat, u.shard.clone() if self.on_gpu is False else u.shard, u.group)
+                if self._shard_symm is not None and hasattr(u, "symm_shard_offset"):
+                    self.symm.all_gather(self._shard_symm, u.symm_shard_offset, u.shard_size, u.flat)
+                else:
+                    # shard is a view of flat: in-place all-gather
+                    self._all_gather(u.flat, u.shard.clone() if self.on_gpu is False else u.shard, u.group)
 
     # ================================================================== gathered access (checkpoint export etc.)
     @contextmanager

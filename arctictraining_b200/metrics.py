@@ -53,7 +53,7 @@ class Metrics:
         self.losses: List[float] = []
         module = trainer.model_unwrapped
         self.model_size = module.num_parameters() if hasattr(module, "num_parameters") else sum(
-            p.numel() for p in module.parameters()
+            getattr(p, "_atb_numel", p.numel()) for p in module.parameters()
         )
         self.model_config = getattr(module, "config", {})
         horizon = trainer.training_horizon

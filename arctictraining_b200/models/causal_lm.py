@@ -208,5 +208,5 @@ class CausalLM(nn.Module):
         for p in self.parameters():
             if id(p) not in seen:
                 seen.add(id(p))
-                n += p.numel()
+                n += getattr(p, "_atb_numel", p.numel())
         return n

@@ -236,9 +236,10 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
             if id(p) in seen:
                 continue
             seen.add(id(p))
-            sizes["total"] += p.numel()
+            n = getattr(p, "_atb_numel", p.numel())  # released ZeRO-3 parameters are empty views: use the logical size
+            sizes["total"] += n
             if p.requires_grad:
-                sizes["trainable"] += p.numel()
+                sizes["trainable"] += n
         return dict(sizes)
 
     # ================================================================== accessors

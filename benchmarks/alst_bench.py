@@ -34,6 +34,8 @@ def main() -> None:
                     help="cpu_adam: optimizer states in pinned host memory (zero_optimization.offload_optimizer)")
     ap.add_argument("--offload-ratio", type=float, default=1.0, help="fraction of the optimizer states kept on the host")
     ap.add_argument("--offload-param", action="store_true", help="parameter shards in pinned host memory too")
+    ap.add_argument("--bf16-optimizer", action="store_true",
+                    help="bf16 master weights, gradients and AdamW moments (6 bytes per parameter instead of 16)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
 
@@ -81,7 +83,9 @@ def main() -> None:
                  "cache_dir": str(workdir / "cache"), "max_length": 128, "dl_num_workers": 0, "num_proc": 1},
         "optimizer": {"type": args.optimizer, "lr": 1e-5, "weight_decay": 0.1},
         "scheduler": {"name": "constant"},
-        "deepspeed": {"zero_optimization": zero, "gradient_clipping": 1.0, "activation_checkpoint_keep": args.keep},
+        "deepspeed": {"zero_optimization": zero, "gradient_clipping": 1.0, "activation_checkpoint_keep": args.keep,
+                      **({"bf16": {"enabled": True, "bf16_master_weights_and_grads": True, "bf16_optimizer_states": True}}
+                         if args.bf16_optimizer else {})},
         "train_log_iter_interval": 0,
         "train_log_metrics_path": str(workdir / f"metrics_{rank}.jsonl"),
         "logger": {"level": "WARNING"},
@@ -141,7 +145,7 @@ def main() -> None:
                        "attention_blocks_with_exchange_in_gemm": trainer.sp_context.fused_block_calls if world > 1 else 0,
                        "layers_keeping_activations": eng._keep_state.get("kept_layers", 0),
                        "optimizer": args.optimizer, "offload_optimizer_ratio": args.offload_ratio if args.optimizer == "cpu_adam" else 0.0,
-                       "offload_param": args.offload_param,
+                       "offload_param": args.offload_param, "bf16_optimizer_states": args.bf16_optimizer,
                        "attention_backward": os.getenv("ATB200_ATTN_BWD", "native")},
             "max_memory_gib_per_gpu": round(float(mem), 2), "gpu_launches": ops.LAUNCH_COUNTER["native"] - launches0,
             "kernel_error_flag": err,

@@ -305,3 +305,72 @@ def test_offload_keys_are_read_from_the_recipe_spelling():
     c = EngineConfig.from_dict({"zero_optimization": {"stage": 3, "offload_optimizer": {"device": "cpu", "ratio": 0.7},
                                                       "offload_param": {"device": "cpu"}}})
     assert c.offload_optimizer and c.offload_param and c.offload_optimizer_ratio == 0.7
+
+
+def test_fp16_loss_scaling_skips_an_overflowing_step_and_halves_the_scale():
+    m = make_model()
+    m.activation_checkpointing = True
+    groups = OptimizerFactory.get_optimizer_grouped_params(m, 0.1)
+    e = TrainingEngine(m, FusedAdamW(groups, lr=1e-2), None, {
+        "zero_optimization": {"stage": 1}, "gradient_clipping": 1.0,
+        "fp16": {"enabled": True, "initial_scale_power": 4, "loss_scale_window": 2},
+    })
+    assert e.loss_scale == 16.0
+    b = batches(1)[0]
+    ref = make_engine(make_model(), 1)
+    # good steps: same results as without scaling (the scale is divided out), scale doubles after the window
+    for _ in range(2):
+        la = run(e, [b])
+        lb = run(ref, [b])
+        assert la == pytest.approx(lb, rel=1e-5)
+    assert e.loss_scale == 32.0 and e.skipped_steps == 0
+    a, r = full_params(e), full_params(ref)
+    assert all(torch.allclose(a[n], r[n], atol=2e-3) for n in a)  # Adam amplifies rounding of near-zero gradients
+    # an overflow: the step is skipped, nothing moves, the scale halves
+    out = e(**b)
+    e.backward(out.loss * float("inf"))
+    before = full_params(e)
+    e.step()
+    after = full_params(e)
+    assert e.skipped_steps == 1 and e.loss_scale == 16.0
+    assert all(torch.equal(before[n], after[n]) for n in before)
+
+
+def test_communication_data_type_is_parsed_and_rejects_unknown_names():
+    from arctictraining_b200.engine.config import EngineConfig
+
+    assert EngineConfig.from_dict({"communication_data_type": "fp32"}).communication_data_type == torch.float32
+    assert EngineConfig.from_dict({}).communication_data_type is None
+    with pytest.raises(ValueError):
+        EngineConfig.from_dict({"communication_data_type": "int8"})
+
+
+def test_parameter_count_survives_the_release_of_stage3_units():
+    m = make_model()
+    want = sum(p.numel() for p in m.parameters())
+    e = make_engine(m, 3)
+    for u in e.units:  # what stage 3 does to a released unit on more than one rank
+        if u.checkpointed:
+            for p in u.params:
+                p.data = torch.empty(0)
+    from arctictraining_b200.trainer.trainer import Trainer
+
+    assert Trainer._count_params(m)["total"] == want and m.num_parameters() == want
+
+
+def test_bf16_master_weights_and_optimizer_states_train():
+    """``bf16.bf16_master_weights_and_grads`` + ``bf16.bf16_optimizer_states``: 6 bytes per parameter of optimizer
+    state instead of 16; the loss still goes down on a repeated batch."""
+    cfg = load_arch_config("tiny-llama", {})
+    m = CausalLM(cfg, dtype=torch.bfloat16)
+    m.init_weights(seed=0)
+    m.activation_checkpointing = True
+    opt = FusedAdamW(OptimizerFactory.get_optimizer_grouped_params(m, 0.0), lr=3e-3, betas=(0.9, 0.95))
+    e = TrainingEngine(m, opt, None, {"zero_optimization": {"stage": 3}, "gradient_clipping": 1.0,
+                                      "bf16": {"enabled": True, "bf16_master_weights_and_grads": True, "bf16_optimizer_states": True}})
+    assert all(u.master.dtype == torch.bfloat16 and u.grad_acc.dtype == torch.bfloat16 for u in e.units if u.master is not None)
+    b = batches(1)[0]
+    losses = run(e, [b] * 8)
+    st = next(iter(opt.state.values()))
+    assert st["exp_avg"].dtype == torch.bfloat16 and st["exp_avg_sq"].dtype == torch.bfloat16
+    assert losses[-1] < losses[0] - 0.05
