@@ -4,7 +4,8 @@ Writes ``output_dir/global_step_<N>/{config.json, model.safetensors | model-0000
 model.safetensors.index.json, tokenizer files}``.  Parity: arctic_training/checkpoint/hf_engine.py:28-161.
 Under ZeRO-3 the parameters are gathered one unit (decoder layer) at a time — every rank takes part in the
 gathers, rank 0 streams tensors into shards of bounded size — so the full model is never resident on one
-GPU.  With PEFT only trainable tensors are written.  Loading is not supported (resume uses the sharded
+GPU.  Under expert parallelism the expert stacks of all expert-parallel ranks are gathered into the Hugging Face
+per-expert names.  With PEFT only trainable tensors are written.  Loading is not supported (resume uses the sharded
 engine), as in the reference.
 """
 
@@ -43,11 +44,19 @@ class HFCheckpointEngine(CheckpointEngine):
         keep = self._export_filter(module)
         writer = ShardedSafetensorsWriter(out_dir, self.max_shard_bytes) if is_main else None
         arch = cfg if isinstance(cfg, dict) else None
+        from ..moe.convert import expert_parallel_of
+        from ..moe.convert import gather_expert_tensor
+
+        ep_size, ep_group = expert_parallel_of(module)
         if hasattr(model, "iter_full_named_parameters"):
             named = model.iter_full_named_parameters()
         else:
             named = ((n, p.data) for n, p in module.named_parameters())
         for name, tensor in named:
+            if ep_size > 1 and name.endswith(("mlp.expert_gate_up", "mlp.expert_down")):
+                # every expert-parallel rank holds a slice of the expert stack: all ranks of the group join the
+                # gather, the writing rank receives the experts in global order
+                tensor = gather_expert_tensor(tensor, ep_size, ep_group, keep=is_main)
             if not keep(name) or writer is None:
                 continue
             items = native_to_hf(name, tensor, arch) if arch is not None else [(name, tensor)]

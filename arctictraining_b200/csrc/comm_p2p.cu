@@ -18,6 +18,8 @@
 // (arctic_training/trainer/trainer.py:195-202,315-322; arctic_training/model/moe/alltoall.py:20-46).
 
 #include "common.cuh"
+
+#include <cstdlib>
 #include "ptx_sm100.cuh"
 
 namespace atb {
@@ -395,6 +397,18 @@ static int grid_for_bytes(int64_t nvec, int threads, int max_waves = 8) {
     return (int)std::max<int64_t>(1, std::min<int64_t>(ceil_div(nvec, threads), (int64_t)kNumSMs * max_waves));
 }
 
+// CTAs of the bulk copy / reduction kernels that run beside the compute stream (parameter gathers, gradient
+// reductions).  They share the SMs with persistent GEMM CTAs: enough of them to fill the NVLink ports, few enough to
+// leave the issue slots and memory pipes to the math.  ATB200_COMM_CTAS overrides the default.
+static int comm_cta_cap() {
+    static const int cap = [] {
+        const char* e = std::getenv("ATB200_COMM_CTAS");
+        const int v = e ? std::atoi(e) : 0;
+        return v > 0 ? v : kNumSMs * 4;
+    }();
+    return cap;
+}
+
 void p2p_barrier(const at::Tensor& flag_ptrs, int64_t rank, int64_t slot, int64_t epoch, double timeout_s,
                  const at::Tensor& like) {
     const int P = (int)flag_ptrs.numel();
@@ -424,7 +438,7 @@ void p2p_all_gather(const at::Tensor& shard_ptrs, int64_t shard_byte_offset, at:
     c10::cuda::CUDAGuard guard(full.device());
     PeerTable t = make_table(shard_ptrs, shard_byte_offset);
     const int64_t vec = bytes / 16;
-    dim3 grid(std::max(1, grid_for_bytes(vec, 512, 4) / P), P);
+    dim3 grid(std::max(1, std::min(grid_for_bytes(vec, 512, 4), comm_cta_cap()) / P), P);
     p2p_all_gather_kernel<<<grid, 512, 0, current_stream()>>>(t, reinterpret_cast<uint4*>(full.data_ptr()), vec, (int)rank, P);
     ATB_LAUNCH_CHECK();
 }
@@ -436,7 +450,7 @@ at::Tensor p2p_reduce_scatter_accum(const at::Tensor& grad_ptrs, int64_t elem_of
     TORCH_CHECK(n % 8 == 0 && elem_offset % 8 == 0 && acc.numel() >= n, "reduce_scatter: n and offset must be multiples of 8");
     c10::cuda::CUDAGuard guard(acc.device());
     PeerTable t = make_table(grad_ptrs, elem_offset * 2);
-    const int grid = grid_for_bytes(n / 8, 256, 4);
+    const int grid = std::min(grid_for_bytes(n / 8, 256, 4), comm_cta_cap());
     at::Tensor partial = want_sumsq ? at::empty({grid}, acc.options()) : at::Tensor();
     p2p_reduce_scatter_kernel<false><<<grid, 256, 0, current_stream()>>>(
         t, (int)grad_ptrs.numel(), n, (float)scale, acc.data_ptr<float>(), overwrite ? 1 : 0,

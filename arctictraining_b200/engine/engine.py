@@ -1188,6 +1188,18 @@ class TrainingEngine:
             if was_released:
                 self._release_params(u)
 
+    def refresh_unit_from_full(self, u: ZeroUnit) -> None:
+        """After the gathered parameters of a unit were overwritten in place (weights read from files): copy this
+        rank's slice back into the resident shard and into the master weights."""
+        if u.flat is None:
+            return
+        lo = u.group_rank * u.shard_size
+        if u.shard.data_ptr() != u.flat[lo : lo + 1].data_ptr():
+            u.shard.copy_(u.flat[lo : lo + u.shard_size])
+        if u.master is not None:
+            tl = u.train_len
+            u.master[:tl].copy_(u.shard[:tl].to(u.master.dtype))
+
     def iter_full_named_parameters(self) -> Iterable[Tuple[str, torch.Tensor]]:
         """Yield ``(name, full tensor)`` for every parameter, gathering stage-3 units one at a time.
         Every rank must iterate (the gathers are collectives)."""
@@ -1241,6 +1253,9 @@ class TrainingEngine:
                 },
                 d / "mp_rank_00_model_states.pt",
             )
+        from ..moe.convert import save_moe_states
+
+        save_moe_states(self, d)  # ep_rank_<r>_moe_layer_<l>_model_states.pt (nothing for dense models)
         if self.dist_on:
             dist.barrier()
         if self.global_rank == 0:

@@ -130,6 +130,13 @@ class CausalLM(nn.Module):
                 p.fill_(1.0)
             elif name.endswith("bias"):
                 p.zero_()
+            elif getattr(p, "_num_experts", 0) and p.shape[0] != p._num_experts:
+                # expert-parallel shard: draw the whole stack (one layer at a time) and keep this rank's experts, so
+                # that the weights do not depend on the expert-parallel degree
+                full = torch.empty((p._num_experts,) + tuple(p.shape[1:]), dtype=p.dtype, device=p.device)
+                full.normal_(0.0, std, generator=gen)
+                p.copy_(full[p._first_expert : p._first_expert + p.shape[0]])
+                del full
             else:
                 p.normal_(0.0, std, generator=gen)
 

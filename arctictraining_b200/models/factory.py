@@ -109,7 +109,12 @@ class HFModelFactory(ModelFactory):
         if model_config.get("model_type") not in NATIVE_MODEL_TYPES:
             return self._create_transformers_model(model_config, dtype)
         device = self.device
-        with torch.device(device):
+        from ..moe.layer import expert_parallel_layout
+
+        groups = getattr(self.trainer, "groups", None)
+        use_ep = groups is not None and groups.ep_size > 1 and getattr(self.trainer.config, "arctic_moe", False) not in (False, None)
+        layout = expert_parallel_layout(groups.ep_size, groups.ep_rank, groups.ep_group) if use_ep else expert_parallel_layout(1, 0, None)
+        with torch.device(device), layout:
             model = self._native_class()(model_config, dtype=dtype)
         model.attn_impl = self.config.attn_implementation
         if self.using_random_model:

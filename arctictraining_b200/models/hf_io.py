@@ -182,4 +182,7 @@ def load_pretrained_into(model: torch.nn.Module, path: Path, cfg: ArchConfig, st
     with torch.no_grad():
         for k, t in native.items():
             if k in own:
-                own[k].copy_(t.to(own[k].dtype))
+                dst = own[k]
+                if getattr(dst, "_num_experts", 0) and t.shape[0] == dst._num_experts != dst.shape[0]:
+                    t = t[dst._first_expert : dst._first_expert + dst.shape[0]]  # this rank's experts only
+                dst.copy_(t.to(dst.dtype))

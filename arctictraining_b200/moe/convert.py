@@ -4,11 +4,12 @@ Behaviour parity: arctic_training/model/moe/utils.py:75-666.
 * HF Qwen3-MoE keeps one ``nn.Linear`` triple per expert (``mlp.experts.<i>.{gate,up,down}_proj.weight``) and
   ``mlp.gate.weight`` for the router.  ArcticMoE stacks this rank's experts into ``expert_gate_up
   [E_local, 2I, H]`` (gate/up rows block-interleaved) and ``expert_down [E_local, H, I]``.
-* ``convert_to_arctic_moe`` re-creates every MoE block of a native model for the run's expert-parallel layout
-  (each rank keeps only its own experts) — skipped weights are never materialised twice.
-* export gathers the experts of all expert-parallel ranks back into HF names.
-* expert state is checkpointed per (expert-parallel rank, layer) in
-  ``ep_rank_<r>_moe_layer_<l>_model_states.pt`` files, the dense remainder only by expert-parallel rank 0.
+* The model factory builds MoE blocks inside ``expert_parallel_layout`` so that a rank only ever allocates its own
+  experts; ``convert_to_arctic_moe`` sets the run-time switches and re-shards blocks that were built unsharded.
+* export (``checkpoint/hf.py``) gathers the experts of all expert-parallel ranks back into HF names
+  (``gather_expert_tensor``).
+* expert state is also written per (expert-parallel rank, layer) in ``ep_rank_<r>_moe_layer_<l>_model_states.pt``
+  files beside the engine's own shard files (``save_moe_states`` / ``load_moe_states``).
 """
 
 from __future__ import annotations
@@ -138,46 +139,91 @@ def convert_to_arctic_moe(model: nn.Module, groups: Any, is_resume: bool = False
     return n
 
 
-def gather_experts_for_export(moe: ArcticMoE) -> Tuple[Optional[torch.Tensor], Optional[torch.Tensor]]:
-    """All experts of a block on expert-parallel rank 0 (``None`` elsewhere)."""
-    if moe.ep_size == 1:
-        return moe.expert_gate_up.data, moe.expert_down.data
-    outs = []
-    for p in (moe.expert_gate_up.data, moe.expert_down.data):
-        parts = [torch.empty_like(p) for _ in range(moe.ep_size)]
-        dist.all_gather(parts, p.contiguous(), group=moe.ep_group)
-        outs.append(torch.cat(parts, dim=0) if moe.ep_rank == 0 else None)
-    return outs[0], outs[1]
+def gather_expert_tensor(local: torch.Tensor, ep_size: int, ep_group: Any, keep: bool) -> Optional[torch.Tensor]:
+    """Stack of all experts ``[E, ...]`` from the ``[E / ep_size, ...]`` stacks of an expert-parallel group, in expert
+    order (expert-parallel rank r holds experts ``[r E / ep, (r + 1) E / ep)``).  A collective of the group; the result
+    is kept only where ``keep`` is true (the rank that writes the export).  Reference: the expert gather before an
+    export, arctic_training/model/moe/utils.py:331-422."""
+    if ep_size == 1:
+        return local
+    parts = [torch.empty_like(local) for _ in range(ep_size)]
+    dist.all_gather(parts, local.contiguous(), group=ep_group)
+    return torch.cat(parts, dim=0) if keep else None
+
+
+def expert_parallel_of(model: nn.Module) -> Tuple[int, Any]:
+    """``(ep_size, ep_group)`` of the model's MoE blocks (``(1, None)`` for dense models)."""
+    for _, _, moe in moe_layers(model):
+        return moe.ep_size, moe.ep_group
+    return 1, None
 
 
 # ------------------------------------------------------------------ expert checkpoint files
+_LAYER_RE = re.compile(r"layers\.(\d+)\.mlp\.(expert_gate_up|expert_down)$")
+
+
 def moe_state_file(directory: Path, ep_rank: int, layer_idx: int) -> Path:
     return Path(directory) / f"ep_rank_{ep_rank}_moe_layer_{layer_idx}_model_states.pt"
 
 
-def save_moe_states(model: nn.Module, directory: Path, expert_dp_rank: int = 0) -> List[Path]:
-    """Every expert-parallel rank (first expert-data-parallel replica only) writes its experts, one file per layer."""
+def save_moe_states(engine: Any, directory: Path) -> List[Path]:
+    """One file per (expert-parallel rank, MoE layer) with that rank's expert stacks, next to the engine's own
+    shard files (naming of the reference, arctic_training/model/moe/utils.py:541-666).  Expert units that are
+    ZeRO-sharded over the expert-data-parallel group are gathered first (every rank takes part); the first replica of
+    each expert-parallel rank writes."""
+    module = engine.module
+    blocks = {idx: moe for idx, _, moe in moe_layers(module)}
+    if not blocks:
+        return []
+    writer = engine.expert_dp_group is None or dist.get_rank(engine.expert_dp_group) == 0
+    if engine.expert_dp_group is None and dist.is_initialized():
+        ep_size = next(iter(blocks.values())).ep_size
+        writer = ep_size > 1 or dist.get_rank() == 0  # without expert parallelism every rank holds the same experts
+    per_layer: Dict[int, Dict[str, torch.Tensor]] = {}
+    for u in engine.units:
+        names = [n for n in u.param_names if _LAYER_RE.search(n)]
+        if not names:
+            continue
+        with engine.gathered_unit(u):
+            for n, p in zip(u.param_names, u.params):
+                m = _LAYER_RE.search(n)
+                if m and writer:
+                    per_layer.setdefault(int(m.group(1)), {})[m.group(2)] = p.data.detach().cpu().clone()
     written = []
-    if expert_dp_rank != 0:
-        return written
-    for idx, _, moe in moe_layers(model):
+    for idx, tensors in sorted(per_layer.items()):
+        moe = blocks[idx]
         f = moe_state_file(directory, moe.ep_rank, idx)
-        torch.save({"expert_gate_up": moe.expert_gate_up.detach().cpu(), "expert_down": moe.expert_down.detach().cpu(),
-                    "num_experts": moe.num_experts, "ep_size": moe.ep_size}, f)
+        torch.save({**tensors, "num_experts": moe.num_experts, "ep_size": moe.ep_size, "ep_rank": moe.ep_rank}, f)
         written.append(f)
     return written
 
 
-def load_moe_states(model: nn.Module, directory: Path) -> int:
+def load_moe_states(engine: Any, directory: Path) -> int:
+    """Fill the expert stacks of this rank from the per-(rank, layer) files (e.g. into a run whose expert-data-parallel
+    replication differs from the run that wrote them; the expert-parallel degree must be the same).  Returns the number
+    of layers loaded."""
+    module = engine.module
+    blocks = {idx: moe for idx, _, moe in moe_layers(module)}
     n = 0
-    for idx, _, moe in moe_layers(model):
-        f = moe_state_file(directory, moe.ep_rank, idx)
-        if not f.exists():
+    for u in engine.units:
+        if not any(_LAYER_RE.search(x) for x in u.param_names):
             continue
-        st = torch.load(f, map_location="cpu", weights_only=True)
-        assert st["ep_size"] == moe.ep_size, "expert checkpoint was written with another expert-parallel degree"
-        with torch.no_grad():
-            moe.expert_gate_up.copy_(st["expert_gate_up"])
-            moe.expert_down.copy_(st["expert_down"])
-        n += 1
+        with engine.gathered_unit(u):
+            touched = False
+            for name, p in zip(u.param_names, u.params):
+                m = _LAYER_RE.search(name)
+                if not m:
+                    continue
+                idx = int(m.group(1))
+                f = moe_state_file(directory, blocks[idx].ep_rank, idx)
+                if not f.exists():
+                    continue
+                st = torch.load(f, map_location="cpu", weights_only=True)
+                assert st["ep_size"] == blocks[idx].ep_size, "expert files were written with another expert-parallel degree"
+                with torch.no_grad():
+                    p.data.copy_(st[m.group(2)].to(p.dtype))
+                touched = True
+                n += m.group(2) == "expert_down"
+            if touched:
+                engine.refresh_unit_from_full(u)
     return n

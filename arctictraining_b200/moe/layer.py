@@ -32,6 +32,28 @@ from .grouped import grouped_mlp
 
 SEGMENT_ALIGN = 128
 
+# Expert-parallel layout with which MoE blocks are built while a model is being constructed (set by the model factory
+# from the trainer's process groups), so that every rank allocates only its own experts from the start.
+_BUILD_LAYOUT = {"ep_size": 1, "ep_rank": 0, "ep_group": None}
+
+
+class expert_parallel_layout:
+    """``with expert_parallel_layout(size, rank, group): model = CausalLM(cfg)`` builds every MoE block of the model
+    with ``num_experts / size`` local experts (the reference creates its blocks on the meta device and fills in the
+    local experts only, arctic_training/model/moe/utils.py:76-200)."""
+
+    def __init__(self, ep_size: int, ep_rank: int, ep_group: Any) -> None:
+        self.new = {"ep_size": int(ep_size), "ep_rank": int(ep_rank), "ep_group": ep_group}
+
+    def __enter__(self):
+        self.old = dict(_BUILD_LAYOUT)
+        _BUILD_LAYOUT.update(self.new)
+        return self
+
+    def __exit__(self, *exc):
+        _BUILD_LAYOUT.update(self.old)
+        return False
+
 
 @dataclass
 class MoEConfig:
@@ -68,6 +90,8 @@ class ArcticMoE(nn.Module):
         self.expert_down = nn.Parameter(torch.empty(El, H, I, dtype=dtype, device=device))
         for p in (self.expert_gate_up, self.expert_down):
             p.is_expert_param = True
+            p._first_expert = c.ep_rank * El     # global index of this rank's first expert
+            p._num_experts = c.num_experts
         if c.use_shared_expert:
             Is = c.shared_intermediate_dim or I
             self.shared_expert_gate_up = nn.Parameter(torch.empty(2 * Is, H, dtype=dtype, device=device))
@@ -173,8 +197,12 @@ class ArcticMoE(nn.Module):
         return mops.gather_rows(returned, slots, scores)
 
 
-def build_moe_block(cfg: ArchConfig, dtype=None, device=None, ep_size: int = 1, ep_rank: int = 0, ep_group=None) -> ArcticMoE:
-    """ArcticMoE configured from a Hugging Face style architecture dict (Qwen3-MoE naming)."""
+def build_moe_block(cfg: ArchConfig, dtype=None, device=None, ep_size: Optional[int] = None, ep_rank: Optional[int] = None,
+                    ep_group=None) -> ArcticMoE:
+    """ArcticMoE configured from a Hugging Face style architecture dict (Qwen3-MoE naming).  Without explicit
+    arguments the expert-parallel layout is the one of the enclosing :class:`expert_parallel_layout` block."""
+    if ep_size is None:
+        ep_size, ep_rank, ep_group = _BUILD_LAYOUT["ep_size"], _BUILD_LAYOUT["ep_rank"], _BUILD_LAYOUT["ep_group"]
     mc = MoEConfig(
         model_dim=cfg["hidden_size"],
         intermediate_dim=cfg.get("moe_intermediate_size") or cfg["intermediate_size"],
