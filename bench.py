@@ -55,6 +55,7 @@ def parse_args():
     p.add_argument("--torch-profile", type=str, default=None,
                    help="write a torch.profiler kernel table of the timed steps of rank 0 to this file (the number "
                         "printed by such a run is not a benchmark value)")
+    p.add_argument("--torch-trace", type=str, default=None, help="with --torch-profile: also write a Chrome trace of rank 0")
     p.add_argument("--ep", type=int, default=1, help="expert-parallel size (mixture-of-experts models)")
     p.add_argument("--sample-max", type=int, default=4096, help="longest synthetic sample that is packed")
     p.add_argument("--no-cta-pairs", action="store_true", help="use the single-CTA 128x256 GEMM tile instead of the CTA-pair kernel")
@@ -248,6 +249,8 @@ def main() -> None:
         torch.cuda.synchronize()
         prof.__exit__(None, None, None)
         Path(args.torch_profile).write_text(prof.key_averages().table(sort_by="cuda_time_total", row_limit=60, max_name_column_width=90))
+        if args.torch_trace:
+            prof.export_chrome_trace(args.torch_trace)
     barrier()
     ms = start.elapsed_time(end)
     launches = ops.LAUNCH_COUNTER["native"] - launches0
