@@ -42,6 +42,8 @@ class HFCheckpointEngine(CheckpointEngine):
         cfg = getattr(module, "config", None)
         is_main = self.global_rank == 0
         keep = self._export_filter(module)
+        if getattr(self.trainer.config.model, "peft_config", None):
+            return self._save_adapter(model, module, out_dir, is_main)
         writer = ShardedSafetensorsWriter(out_dir, self.max_shard_bytes) if is_main else None
         arch = cfg if isinstance(cfg, dict) else None
         from ..moe.convert import expert_parallel_of
@@ -72,6 +74,26 @@ class HFCheckpointEngine(CheckpointEngine):
             if tok is not None and hasattr(tok, "save_pretrained"):
                 tok.save_pretrained(out_dir)
             logger.info(f"saved Hugging Face checkpoint to {out_dir}")
+        from ..comm import dist as cdist
+
+        cdist.barrier()
+
+    def _save_adapter(self, model, module, out_dir, is_main: bool) -> None:
+        """PEFT runs export the adapter only, in the layout of the ``peft`` package (``adapter_model.safetensors`` +
+        ``adapter_config.json``), as the reference does through ``save_pretrained(state_dict=trainable)``."""
+        from ..models.peft import save_adapter
+
+        if hasattr(model, "iter_full_named_parameters"):
+            named = model.iter_full_named_parameters()  # every rank takes part in the gathers
+        else:
+            named = ((n, p.data) for n, p in module.named_parameters())
+        pairs = [(n, t.detach().to("cpu").clone()) for n, t in named if ".lora_A." in n or ".lora_B." in n]
+        if is_main:
+            n = save_adapter(out_dir, pairs, module, str(self.trainer.config.model.name_or_path))
+            tok = getattr(self.trainer, "tokenizer", None)
+            if tok is not None and hasattr(tok, "save_pretrained"):
+                tok.save_pretrained(out_dir)
+            logger.info(f"saved {n} adapter tensors to {out_dir}")
         from ..comm import dist as cdist
 
         cdist.barrier()

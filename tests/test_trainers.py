@@ -129,16 +129,61 @@ def test_hf_checkpoint_reloads_into_an_identical_model(tiny_recipe, tmp_path):
 
 
 def test_lora_trains_only_adapters_and_exports_them(tiny_recipe, tmp_path):
-    ck = [{"type": "huggingface", "output_dir": str(tmp_path / "hf"), "save_end_of_training": True}]
-    tr = build(tiny_recipe(model={"peft_config": {"peft_type": "LORA", "r": 4, "target_modules": ["q_proj", "down_proj"]}},
-                           checkpoint=ck, exit_iteration=2))
-    trainable = [n for n, p in tr.model_unwrapped.named_parameters() if p.requires_grad]
-    assert trainable and all("lora_" in n for n in trainable)
-    tr.train()
+    """Adapters of the requested Hugging Face modules only (k_proj shares a fused weight with q_proj and v_proj and must
+    stay untouched), exported as ``adapter_model.safetensors`` + ``adapter_config.json`` in the PEFT key layout; the
+    exported A / B pairs reproduce the update the model applies."""
+    import json
+
     from safetensors.torch import load_file
 
-    saved = load_file(str(tmp_path / "hf" / "global_step_2" / "model.safetensors"))
-    assert saved and all("lora_" in n for n in saved)
+    from arctictraining_b200.models.peft import merged_weight_delta
+
+    ck = [{"type": "huggingface", "output_dir": str(tmp_path / "hf"), "save_end_of_training": True}]
+    tr = build(tiny_recipe(model={"peft_config": {"peft_type": "LORA", "r": 4, "lora_alpha": 8,
+                                                  "target_modules": ["q_proj", "v_proj", "down_proj", "up_proj"]}},
+                           checkpoint=ck, exit_iteration=2, optimizer={"lr": 1e-2}))
+    trainable = [n for n, p in tr.model_unwrapped.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    assert not any(n.endswith(("lora_A.k_proj", "lora_A.gate_proj")) for n in trainable)
+    tr.train()
+    out = tmp_path / "hf" / "global_step_2"
+    saved = load_file(str(out / "adapter_model.safetensors"))
+    cfg = json.loads((out / "adapter_config.json").read_text())
+    assert cfg["peft_type"] == "LORA" and cfg["r"] == 4 and sorted(cfg["target_modules"]) == ["down_proj", "q_proj", "up_proj", "v_proj"]
+    assert not (out / "model.safetensors").exists()
+    key = "base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight"
+    assert key in saved and saved[key].shape[0] == 4
+    assert "base_model.model.model.layers.0.mlp.up_proj.lora_B.weight" in saved
+    assert not any(".k_proj." in k or ".gate_proj." in k or "qkv_proj" in k for k in saved)
+    # B A * alpha / r from the file equals the update of the live model, module by module
+    want = merged_weight_delta(tr.model_unwrapped)
+    assert want
+    for mod, delta in want.items():
+        a = saved[f"base_model.model.{mod}.lora_A.weight"].float()
+        b = saved[f"base_model.model.{mod}.lora_B.weight"].float()
+        if delta.numel():
+            torch.testing.assert_close(b @ a * (8 / 4), delta.cpu(), atol=1e-6, rtol=1e-5)
+    assert any(float(saved[k].abs().max()) > 0 for k in saved if ".lora_B." in k), "the adapters did not train"
+
+
+def test_lora_update_touches_only_the_rows_of_the_requested_projections():
+    from arctictraining_b200.models.arch import load_arch_config
+    from arctictraining_b200.models.causal_lm import CausalLM
+    from arctictraining_b200.models.peft import apply_lora
+
+    m = CausalLM(load_arch_config("tiny-llama", {}), dtype=torch.float32)
+    m.init_weights(seed=0)
+    attn = m.model.layers[0].self_attn
+    x = torch.randn(2, 8, attn.qkv_proj.weight.shape[1])
+    before = attn.qkv_proj(x)
+    apply_lora(m, {"r": 2, "target_modules": ["v_proj"]})
+    lora = m.model.layers[0].self_attn.qkv_proj
+    with torch.no_grad():
+        lora.lora_B["v_proj"].normal_()
+    after = lora(x)
+    hq, hkv, d = attn.hq, attn.hkv, attn.d
+    changed = (after - before).abs().amax(dim=(0, 1)) > 0
+    assert not changed[: (hq + hkv) * d].any() and changed[(hq + hkv) * d :].all()
 
 
 def test_callbacks_declared_on_a_custom_trainer_fire(tiny_recipe):
