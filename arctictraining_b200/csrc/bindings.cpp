@@ -39,6 +39,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, 
                                                          const at::Tensor& v, const at::Tensor& out, const at::Tensor& lse,
                                                          const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
 at::Tensor fmha_bwd_read_profile(const at::Tensor& like);
+at::Tensor gemm_bf16_gather_b(const at::Tensor& x, const at::Tensor& shard_ptrs, int64_t shard_byte_offset, int64_t shard_elems,
+                              at::Tensor flat, int64_t w_elem_offset, int64_t N, int64_t stage_ctas);
 bool set_gemm_cta_pairs(bool on);
 at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at::Tensor& offsets, int64_t mode, bool b_mn,
                              int64_t epilogue, const c10::optional<at::Tensor>& out);
@@ -104,6 +106,8 @@ TORCH_LIBRARY(atb200, m) {
     m.def("fmha_read_profile() -> Tensor", &atb::fmha_read_profile);
 #endif
     m.def("fmha_fwd(Tensor q, Tensor k, Tensor v, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor)", &atb::fmha_fwd);
+    m.def("gemm_bf16_gather_b(Tensor x, Tensor shard_ptrs, int shard_byte_offset, int shard_elems, Tensor(a!) flat, "
+          "int w_elem_offset, int N, int stage_ctas) -> Tensor", &atb::gemm_bf16_gather_b);
     m.def("fmha_bwd_read_profile(Tensor like) -> Tensor", &atb::fmha_bwd_read_profile);
     m.def("fmha_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor, Tensor)", &atb::fmha_bwd);
     m.def("set_gemm_cta_pairs(bool on) -> bool", &atb::set_gemm_cta_pairs);

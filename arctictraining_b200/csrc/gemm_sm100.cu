@@ -68,6 +68,14 @@ struct GemmParams {
     // segments per 256-row tile in `stage_flags`; a computing pair starts a tile once its rows have all arrived.
     int stage_ctas;
     int stage_segs;
+    // stage_mode 0: gather of A as described above.  stage_mode 1: gather of B (a weight [N, K] stored K-major inside a
+    // flat parameter buffer that is sharded contiguously over the ranks, `stage_shard_elems` elements each): the
+    // staging CTAs copy the element range [stage_flat_off + 256 n K, +256 K) of N tile n from the shards that hold it
+    // (stage_src[p] = rank p's shard) into the local full buffer `stage_dst` and then count the tile in
+    // stage_flags[n]; a computing pair starts a tile once the rows of its B tile have arrived.
+    int stage_mode;
+    int64_t stage_flat_off;
+    int64_t stage_shard_elems;
     const bf16* stage_src[8];
     int64_t stage_src_ld;
     bf16* stage_dst;
@@ -460,7 +468,61 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         // One thread streams the segments through this CTA's (otherwise idle) tile buffers with bulk copies: a chunk of
         // rows is contiguous at the owner, lands in shared memory, and is written row by row into the local matrix.
         // Several chunks are in flight; the only waits are on this CTA's own copies (bounded).
-        if (threadIdx.x == 0) {
+        if (threadIdx.x == 0 && p.stage_mode == 1) {
+            // ---- gather of B: contiguous element ranges of the sharded flat buffer, 32 KB chunks through shared memory
+            constexpr int NBUF = STAGES < 6 ? STAGES : 6;
+            constexpr int LEAD = NBUF / 2;
+            constexpr int64_t CHUNK = 16384;  // elements (32 KB)
+            const int sidx = (int)blockIdx.x - 2 * num_clusters;
+            uint32_t ph[NBUF];
+            for (int i = 0; i < NBUF; ++i) ph[i] = 0;
+            bool ok = true;
+            const int64_t w_end = p.stage_flat_off + (int64_t)p.N * p.K;
+            for (int nt = sidx; nt < tiles_n && ok; nt += p.stage_ctas) {
+                const int64_t e0 = p.stage_flat_off + (int64_t)nt * TN * p.K;
+                const int64_t e1 = min(e0 + (int64_t)TN * p.K, w_end);
+                // a chunk never crosses a shard boundary: count the chunks of this tile first
+                int n_chunks = 0;
+                for (int64_t e = e0; e < e1; ++n_chunks) {
+                    const int64_t off = e % p.stage_shard_elems;
+                    e += min(min(CHUNK, e1 - e), p.stage_shard_elems - off);
+                }
+                int64_t load_e = e0, store_e = e0;
+                int64_t lens[NBUF];
+                // software pipeline: loads run LEAD chunks ahead of the stores; one bulk group is committed per step
+                for (int c = 0; c < n_chunks + LEAD && ok; ++c) {
+                    if (c < n_chunks) {
+                        const int b = c % NBUF;
+                        ptx::bulk_wait_read<NBUF - LEAD - 1>();  // the stores that last read buffer b have drained it
+                        const int64_t owner = load_e / p.stage_shard_elems;
+                        const int64_t off = load_e - owner * p.stage_shard_elems;
+                        const int64_t len = min(min(CHUNK, e1 - load_e), p.stage_shard_elems - off);
+                        lens[b] = len;
+                        ptx::mbar_expect_tx(&empty_bar[b], (uint32_t)(len * 2));
+                        ptx::bulk_load(smem + b * 32768, p.stage_src[owner] + off, (uint32_t)(len * 2), &empty_bar[b]);
+                        load_e += len;
+                    }
+                    const int d = c - LEAD;
+                    if (d >= 0) {
+                        const int b = d % NBUF;
+                        if (!ptx::mbar_wait_bounded(&empty_bar[b], ph[b], abort_flag, kWaitLimitNs)) {
+                            atomicCAS(p.error_flag, 0, (0x16 << 8) | 1);
+                            ok = false;
+                            break;
+                        }
+                        ph[b] ^= 1u;
+                        ptx::bulk_store(p.stage_dst + store_e, smem + b * 32768, (uint32_t)(lens[b] * 2));
+                        store_e += lens[b];
+                    }
+                    ptx::bulk_commit();
+                }
+                ptx::bulk_wait<0>();  // the rows of this tile are written
+                ptx::fence_proxy_async_all();
+                __threadfence();
+                if (ok) atomicAdd(&p.stage_flags[nt], 1);
+            }
+            ptx::bulk_wait<0>();
+        } else if (threadIdx.x == 0) {
             constexpr int NBUF = STAGES < 6 ? STAGES : 6;
             constexpr uint32_t BUF_BYTES = 32768;
             const int sidx = (int)blockIdx.x - 2 * num_clusters;
@@ -526,9 +588,11 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                 tile_coords(t, tm, tn);
                 const int a_m0 = tm * TM + (int)cta * 128, b_n0 = tn * TN + (int)cta * 128;
                 if (p.stage_ctas > 0) {
-                    // rows of this tile are being gathered by the staging CTAs: wait (bounded) until all segments landed
+                    // rows of this tile (of A, or of B in mode 1) are being gathered by the staging CTAs: wait (bounded)
+                    // until they have all landed
                     const uint64_t t0 = ptx::globaltimer_ns();
-                    while (ptx::ld_acquire_gpu(reinterpret_cast<const uint32_t*>(p.stage_flags) + tm) < (uint32_t)p.stage_segs) {
+                    const int fidx = p.stage_mode == 1 ? tn : tm;
+                    while (ptx::ld_acquire_gpu(reinterpret_cast<const uint32_t*>(p.stage_flags) + fidx) < (uint32_t)p.stage_segs) {
                         if (*abort_flag || ptx::globaltimer_ns() - t0 > kWaitLimitNs) {
                             *abort_flag = 1;
                             atomicCAS(p.error_flag, 0, (0x14 << 8) | 1);
@@ -1112,6 +1176,7 @@ std::tuple<at::Tensor, at::Tensor> gemm_bf16_peer_a(const at::Tensor& a_ptrs, in
     p.a_seg_row0 = (int)row0;
     p.stage_ctas = (int)stage_ctas;
     p.stage_segs = P;
+    p.stage_mode = 0;
     CUtensorMap ta;
     if (stage_ctas > 0) {
         flags = at::zeros({(int64_t)ceil_div(M, 256)}, b.options().dtype(at::kInt));
@@ -1151,6 +1216,58 @@ std::tuple<at::Tensor, at::Tensor> gemm_bf16_peer_a(const at::Tensor& a_ptrs, in
     if (epi == EPI_STORE) launch_gemm_pair<6, false, false, EPI_STORE>(ta, tb, p, kNumSMs, segs);
     else launch_gemm_pair<6, false, false, EPI_ACCUM>(ta, tb, p, kNumSMs, segs);
     return {out, a_local};
+}
+
+// out [M, N] = x [M, K] * W^T where W [N, K] lives at element offset `w_elem_offset` of a flat parameter buffer that is
+// sharded contiguously over the ranks (ZeRO-3): rank p holds elements [p * shard_elems, (p + 1) * shard_elems) at
+// shard_ptrs[p] + shard_byte_offset.  Staging CTAs of the same launch copy W's element range from the owners' shards
+// (peer memory: plain bulk copies, no multicast) into `flat` (this rank's full buffer of the unit) while the CTA pairs
+// multiply the row tiles of W that have arrived.  When the call returns (in stream order) `flat` holds all of W.
+at::Tensor gemm_bf16_gather_b(const at::Tensor& x, const at::Tensor& shard_ptrs, int64_t shard_byte_offset, int64_t shard_elems,
+                              at::Tensor flat, int64_t w_elem_offset, int64_t N, int64_t stage_ctas) {
+    ATB_CHECK_CUDA(x); ATB_CHECK_DTYPE(x, at::kBFloat16); ATB_CHECK_CUDA(flat); ATB_CHECK_DTYPE(flat, at::kBFloat16);
+    ATB_CHECK_CONTIG(flat); ATB_CHECK_ALIGNED16(flat); ATB_CHECK_ALIGNED16(x);
+    TORCH_CHECK(shard_ptrs.device().is_cpu() && shard_ptrs.scalar_type() == at::kLong, "peer pointers: int64 CPU tensor");
+    const int P = (int)shard_ptrs.numel();
+    TORCH_CHECK(P >= 1 && P <= kMaxSegs, "gemm_gather_b: 1..8 ranks");
+    TORCH_CHECK(x.dim() == 2 && x.stride(1) == 1 && x.stride(0) % 8 == 0, "gemm_gather_b: x must be [M, K], K contiguous");
+    const int64_t M = x.size(0), K = x.size(1);
+    TORCH_CHECK(M > 0 && M < (1ll << 31) && N % 8 == 0 && K % 64 == 0, "gemm_gather_b: N % 8 == 0 and K % 64 == 0 expected");
+    TORCH_CHECK(shard_elems % 8 == 0 && w_elem_offset % 8 == 0 && shard_byte_offset % 16 == 0,
+                "gemm_gather_b: shard size and offsets must be multiples of 16 bytes");
+    TORCH_CHECK(w_elem_offset >= 0 && w_elem_offset + N * K <= std::min<int64_t>(flat.numel(), shard_elems * P),
+                "gemm_gather_b: the weight lies outside the flat buffer");
+    TORCH_CHECK(stage_ctas >= 2 && stage_ctas % 2 == 0 && stage_ctas <= 64, "gemm_gather_b: staging CTAs: even, 2..64");
+    c10::cuda::CUDAGuard guard(x.device());
+    auto out = at::empty({M, N}, x.options());
+    auto flags = at::zeros({(int64_t)ceil_div(N, 256)}, x.options().dtype(at::kInt));
+    SegMaps segs = {};
+    GemmParams p;
+    p.a_seg_len = 0; p.a_seg_row0 = 0;
+    p.stage_ctas = (int)stage_ctas;
+    p.stage_segs = 1;
+    p.stage_mode = 1;
+    p.stage_flat_off = w_elem_offset;
+    p.stage_shard_elems = shard_elems;
+    for (int j = 0; j < P; ++j)
+        p.stage_src[j] = reinterpret_cast<const bf16*>(shard_ptrs.data_ptr<int64_t>()[j] + shard_byte_offset);
+    p.stage_src_ld = 0;
+    p.stage_dst = (bf16*)flat.data_ptr();
+    p.stage_dst_ld = 0;
+    p.stage_flags = flags.data_ptr<int>();
+    const CUtensorMap ta = make_tmap_bf16(x.data_ptr(), M, K, x.stride(0), 128);
+    const CUtensorMap tb = make_tmap_bf16((bf16*)flat.data_ptr() + w_elem_offset, N, K, K, 128);
+    p.C = (bf16*)out.data_ptr();
+    p.M = (int)M; p.N = (int)N; p.K = (int)K;
+    p.ldc = out.stride(0);
+    p.R = p.C;
+    p.ldr = p.ldc;
+    p.error_flag = error_flag_for(x.device()).data_ptr<int>();
+    p.group_offsets = nullptr;
+    p.num_groups = 0;
+    p.group_mode = GROUP_NONE;
+    launch_gemm_pair<6, false, false, EPI_STORE>(ta, tb, p, kNumSMs, segs);
+    return out;
 }
 
 bool set_gemm_cta_pairs(bool on) {

@@ -50,6 +50,18 @@ int fail_cuda(cudaError_t e, const char* what, char* err, unsigned long err_len)
 
 bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
+// A pointer the kernels may dereference on device `dev`: device (or managed) memory that belongs to that device.
+// Queries the driver's address map; allocates nothing.
+bool on_device(const void* p, int dev) {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    if (a.type == cudaMemoryTypeManaged) return true;
+    return a.type == cudaMemoryTypeDevice && a.device == dev;
+}
+
 }  // namespace
 
 extern "C" int atb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void* w, const float* rstd, void* dx, float* dw,
@@ -71,6 +83,12 @@ extern "C" int atb_rmsnorm_bwd_noalloc(const void* dy, const void* x, const void
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess) return fail_cuda(e, "cudaGetDevice", err, err_len);
     if (dev < 0 || dev >= kMaxDevices) return fail(1, err, err_len, "rmsnorm_bwd_noalloc: device index out of range");
+    // the scratch array that is used is the current device's: operands that live elsewhere (another GPU, host memory)
+    // would fault in the kernel or, where the GPU can reach them, silently mix devices
+    const void* ptrs[6] = {dy, x, w, rstd, dx, dw};
+    for (const void* p : ptrs)
+        if (!on_device(p, dev))
+            return fail(1, err, err_len, "rmsnorm_bwd_noalloc: every operand must be device memory of the current device");
     float* partials = nullptr;
     {
         // set-up, once per device, with that device current: resolve the device address of the scratch array

@@ -13,7 +13,9 @@
  *     dx[t, :] = rstd[t] * (dy[t, :] * w - x[t, :] * rstd[t]^2 * mean(dy[t, :] * w * x[t, :]))
  *     dw[:]    = sum_t dy[t, :] * x[t, :] * rstd[t]
  * dy, x, dx are bf16 [rows, hidden] (row-major, 16-byte aligned), w is bf16 [hidden], rstd is fp32 [rows] as
- * produced by the forward pass, dw is fp32 [hidden].  All pointers are device pointers owned by the caller.
+ * produced by the forward pass, dw is fp32 [hidden].  All pointers are device pointers owned by the caller and
+ * must belong to the device that is current at the call (the scratch array that is used is that device's); the
+ * function looks each one up in the driver's address map and refuses host memory or another GPU's memory.
  *
  * Scratch: the per-block partial sums of dw live in a fixed array inside the library image
  * (148 x 8192 floats = 4.6 MiB), which every GPU that loads the library holds until the process exits.
@@ -29,7 +31,8 @@
  *
  * Returns 0 on success.  On failure returns a non-zero code and, when `err` is not NULL, writes a
  * NUL-terminated message of at most `err_len` bytes:  1 = bad argument (null pointer, misalignment, size beyond
- * the limit), 2 = the CUDA runtime reported an error (message carries its text).
+ * the limit, memory that is not the current device's), 2 = the CUDA runtime reported an error (message carries
+ * its text).
  */
 #pragma once
 

@@ -35,6 +35,8 @@ class ForwardContext:
     extras: Dict[str, Any] = field(default_factory=dict)
     # rotary tables for arbitrary positions (used for the whole sequence when rotation happens after the Ulysses exchange)
     rope_fn: Optional[Any] = None
+    # generation: one (keys, values) pair per layer, [B, S_past, Hkv, D], grown by every call (None: training / scoring)
+    kv_cache: Optional[list] = None
 
 
 class RMSNorm(nn.Module):
@@ -104,8 +106,31 @@ class Attention(nn.Module):
             return ctx.sp.attention(q, k, v, ctx)
         return ops.attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
 
+    def _forward_cached(self, x: torch.Tensor, ctx: ForwardContext, residual: Optional[torch.Tensor]) -> torch.Tensor:
+        """Generation step: the new tokens' keys and values are appended to the layer's cache and the queries attend to
+        everything cached so far (causally among the new tokens when a whole prompt is processed at once)."""
+        import torch.nn.functional as F
+
+        B, S, _ = x.shape
+        q, k, v = self.project_qkv(x, ctx)
+        past = ctx.kv_cache[self.layer_idx]
+        if past is not None:
+            k = torch.cat([past[0], k], dim=1)
+            v = torch.cat([past[1], v], dim=1)
+        ctx.kv_cache[self.layer_idx] = (k, v)
+        Sk = k.shape[1]
+        mask = None
+        if S > 1:
+            qpos = torch.arange(Sk - S, Sk, device=x.device).view(S, 1)
+            mask = torch.arange(Sk, device=x.device).view(1, Sk) <= qpos
+        o = F.scaled_dot_product_attention(q.transpose(1, 2), k.transpose(1, 2), v.transpose(1, 2), attn_mask=mask,
+                                           enable_gqa=(self.hq != self.hkv))
+        return _project_with_residual(self.o_proj, o.transpose(1, 2).reshape(B, S, self.hq * self.d), residual)
+
     def forward(self, x: torch.Tensor, ctx: ForwardContext, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
         B, S, _ = x.shape
+        if ctx.kv_cache is not None:
+            return self._forward_cached(x, ctx, residual)
         if (
             ctx.sp is not None and hasattr(ctx.sp, "fused_attention_block") and not self.qk_norm
             and type(self.qkv_proj) is Linear and self.qkv_proj.bias is None

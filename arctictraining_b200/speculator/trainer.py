@@ -187,6 +187,8 @@ class MLPSpeculatorTrainerConfig(TrainerConfig):
     gen_train: bool = False
     """ Train on continuations generated on the fly by the base model instead of the dataset's own tokens. """
     gen_train_simple: bool = False
+    """ With ``gen_train``: one speculator update per generated batch.  Without it, a batch of ``gen_micro_batch_size``
+    prompts is generated at once and the speculator is updated once per ``gen_train_micro_batch_size`` of them. """
     gen_micro_batch_size: int = 384
     gen_train_global_batch_size: int = 2048
     gen_train_micro_batch_size: int = 32
@@ -199,11 +201,29 @@ class MLPSpeculatorTrainerConfig(TrainerConfig):
             assert self.gen_micro_batch_size % self.gen_train_micro_batch_size == 0, (
                 "gen_micro_batch_size must be divisible by gen_train_micro_batch_size"
             )
+            assert self.gen_micro_batch_size % self.micro_batch_size == 0, (
+                "gen_micro_batch_size must be a multiple of micro_batch_size"
+            )
         elif self.gen_train:
             assert self.gen_train_micro_batch_size == self.gen_micro_batch_size, (
                 "gen_train_micro_batch_size must equal gen_micro_batch_size"
             )
         return self
+
+
+def speculator_loss_on_generated(module: torch.nn.Module, hidden: torch.Tensor, tokens: torch.Tensor) -> torch.Tensor:
+    """Loss on sequences the base model generated itself: ``hidden[:, t]`` is the state that produced ``tokens[:, t + 1]``
+    and head ``i`` at position ``t`` is scored against ``tokens[:, t + i + 1]`` (the reference's generation losses,
+    projects/mlp_speculator/train.py:329-416)."""
+    spec = module.speculator
+    states = spec.head_states(hidden, tokens[:, :-1])
+    N = states[0].size(1)
+    total = hidden.new_zeros((), dtype=torch.float32)
+    for i, st in enumerate(states):
+        targ = tokens[:, i + 1 : N + i + 1]
+        loss_sum, cnt = ops.fused_linear_cross_entropy(st[:, : targ.shape[1]], spec.head[i].weight, targ)
+        total = total + loss_sum / cnt.clamp(min=1).to(loss_sum.dtype)
+    return total
 
 
 class MLPSpeculatorTrainer(ArcticLSTMSpeculatorTrainer):
@@ -214,20 +234,60 @@ class MLPSpeculatorTrainer(ArcticLSTMSpeculatorTrainer):
 
     @torch.no_grad()
     def generate_continuations(self, prompt_ids: torch.Tensor, new_tokens: int) -> torch.Tensor:
-        """Greedy continuation by the frozen base model (full re-forward per token; a training-data helper)."""
+        """Greedy continuation by the frozen base model that re-runs the whole sequence for every token (the oracle of
+        the cached generation)."""
         ids = prompt_ids
         for _ in range(new_tokens):
             out = self.model(input_ids=ids, return_logits=True, use_cache=False)
             ids = torch.cat([ids, out.logits[:, -1:].argmax(-1)], dim=1)
         return ids
 
+    @torch.no_grad()
+    def generate(self, prompts: torch.Tensor, new_tokens: int, do_sample: bool = True):
+        """Sampled (top-k 10) continuation with a key/value cache; returns ``(tokens, hidden states)``."""
+        from ..models.generation import generate
+
+        self.model.eval()
+        try:
+            return generate(self.model_unwrapped, prompts, new_tokens, do_sample=do_sample)
+        finally:
+            self.model.train()
+
+    def _generated_batch(self, batch, rows: int):
+        """Cut the batch's token rows into ``rows`` prompts of ``gen_prompt_length`` tokens, generate ``gen_seq_length``
+        tokens after each and keep the generated part with the states that produced it."""
+        c = self.config
+        inputs = to_device(batch, self.device)
+        ids = inputs["input_ids"]
+        grow = max(1, rows // ids.shape[0])
+        assert c.gen_prompt_length * grow <= ids.shape[1], "the batch is too short for gen_prompt_length x gen_micro_batch_size"
+        prompts = ids[:, : c.gen_prompt_length * grow].reshape(ids.shape[0] * grow, c.gen_prompt_length)
+        tokens, hidden = self.generate(prompts, c.gen_seq_length)
+        n = self.model_unwrapped.speculator.n_predict
+        tokens = tokens[:, -c.gen_seq_length :]
+        # hidden[:, t] belongs to input position t and predicts token t + 1: the state before the first generated token
+        # comes first; the last n states have no complete set of targets
+        hidden = hidden[:, -c.gen_seq_length : hidden.shape[1] - n]
+        return tokens, hidden.detach()
+
     def loss(self, batch) -> torch.Tensor:
+        if isinstance(batch, dict) and "speculator_input" in batch:
+            # speculator-only update on states and tokens that were generated earlier (see step)
+            return speculator_loss_on_generated(self.model_unwrapped, batch["speculator_input"], batch["speculator_label"])
         if not self.config.gen_train:
             return super().loss(batch)
-        inputs = to_device(batch, self.device)
-        inputs.pop("packed_sample_seqlens", None)
+        tokens, hidden = self._generated_batch(batch, batch["input_ids"].shape[0])
+        return speculator_loss_on_generated(self.model_unwrapped, hidden, tokens)
+
+    def step(self, batch) -> None:
         c = self.config
-        prompts = inputs["input_ids"][:, : c.gen_prompt_length]
-        seq = self.generate_continuations(prompts, max(0, c.gen_seq_length - prompts.shape[1]))
-        hidden = self.base_hidden_states({"input_ids": seq})
-        return speculator_loss(self.model_unwrapped, hidden, seq, seq)
+        if not c.gen_train or c.gen_train_simple:
+            return super().step(batch)
+        # one generation of gen_micro_batch_size sequences feeds several speculator updates of gen_train_micro_batch_size
+        rows = batch["input_ids"].shape[0] * (c.gen_micro_batch_size // c.micro_batch_size)
+        tokens, hidden = self._generated_batch(batch, rows)
+        mb = min(c.gen_train_micro_batch_size, tokens.shape[0])
+        for s in range(0, tokens.shape[0] - mb + 1, mb):
+            if self.metrics.enabled:
+                self.metrics.values.pop("loss", None)
+            super().step({"speculator_input": hidden[s : s + mb], "speculator_label": tokens[s : s + mb]})

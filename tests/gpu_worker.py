@@ -117,6 +117,51 @@ def scenario_partly_frozen(out_dir):
         (Path(out_dir) / "partly_frozen.json").write_text(json.dumps(allres))
 
 
+def scenario_gather_gemm(out_dir):
+    """ZeRO-3 gather inside the consuming GEMM: the weight that the staging CTAs assemble from the ranks' shards is
+    bit-identical to what the pull all-gather assembles, and so is the product (odd sizes: a weight that starts in
+    the middle of a shard, spans a shard boundary and ends in a partial tile)."""
+    from arctictraining_b200.comm.symm import SymmetricContext
+    from arctictraining_b200.ops import functional as Fn
+
+    rank, P = dist.get_rank(), dist.get_world_size()
+    ops = torch.ops.atb200
+    symm = SymmetricContext(None)
+    res = {}
+    for name, (M, K, N, w_off, shard) in {
+        "llama_qkv": (1024, 4096, 6144, 4096 * 8, ((4096 * 8 + 6144 * 4096 + 5000) // P + 255) // 256 * 256),
+        "ragged": (300, 512, 1000, 1304, ((1304 + 1000 * 512 + 77) // P + 255) // 256 * 256),
+    }.items():
+        slab = symm.alloc(f"shards_{name}", shard, torch.bfloat16)
+        g = torch.Generator(device="cuda").manual_seed(7 + rank)
+        slab.tensor.copy_((torch.randn(shard, device="cuda", generator=g) * 0.05).bfloat16())
+        x = torch.randn(M, K, device="cuda", generator=g).bfloat16()
+        full_a = torch.zeros(shard * P, device="cuda", dtype=torch.bfloat16)
+        full_b = torch.zeros(shard * P, device="cuda", dtype=torch.bfloat16)
+        torch.cuda.synchronize()
+        dist.barrier()
+        symm.all_gather(slab, 0, shard, full_a)
+        ref = Fn.gemm(x, full_a[w_off : w_off + N * K].view(N, K))
+        for _ in range(2):  # a second call reuses the arrival counters' allocation pattern
+            full_b.zero_()
+            got = ops.gemm_bf16_gather_b(x, slab.ptrs, 0, shard, full_b, w_off, N, 4)
+        torch.cuda.synchronize()
+        assert int(ops.read_and_clear_error_flag(x)) == 0
+        symm.check()
+        want = ref.float()
+        res[name] = {
+            "weight_equal": bool(torch.equal(full_b[w_off : w_off + N * K], full_a[w_off : w_off + N * K])),
+            "outside_untouched": bool((full_b[:w_off] == 0).all() and (full_b[w_off + N * K :] == 0).all()),
+            "out_equal": bool(torch.equal(got, ref)),
+            "rel_err_vs_fp32": float((got.float() - x.float() @ full_a[w_off : w_off + N * K].view(N, K).float().t()).norm()
+                                     / (want.norm() + 1e-12)),
+        }
+    allres = [None] * P
+    dist.all_gather_object(allres, res)
+    if rank == 0:
+        (Path(out_dir) / "gather_gemm.json").write_text(json.dumps(allres))
+
+
 def scenario_barrier_timeout(out_dir):
     """Rank 0 waits at a barrier that rank 1 joins only later: the wait runs out, the host sees an error status,
     and the context keeps working (plain peer loads, no multicast involved)."""
@@ -303,7 +348,7 @@ def main():
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     torch._C._set_print_stack_traces_on_fatal_signal(True)  # a crash in native code reports where
     init_distributed(timeout_s=120)
-    {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout, "partly_frozen": scenario_partly_frozen,
+    {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout, "partly_frozen": scenario_partly_frozen, "gather_gemm": scenario_gather_gemm,
      "ulysses_peer": scenario_ulysses_peer, "moe_peer": scenario_moe_peer,
      "fused_attention_block": scenario_fused_attention_block}[scenario](out_dir)
     dist.barrier()

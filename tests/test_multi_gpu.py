@@ -46,6 +46,14 @@ def test_partly_frozen_units_take_one_communication_path_on_every_rank(tmp_path)
             assert v["bit_identical_reruns"], name
 
 
+def test_parameter_gather_inside_the_consuming_gemm_matches_the_pull_gather(tmp_path):
+    launch(2, "gather_gemm", tmp_path)
+    for per_rank in json.loads((tmp_path / "gather_gemm.json").read_text()):
+        for name, r in per_rank.items():
+            assert r["weight_equal"] and r["outside_untouched"] and r["out_equal"], (name, r)
+            assert r["rel_err_vs_fp32"] < 1e-2, (name, r)
+
+
 def test_bounded_barrier_reports_a_missing_peer(tmp_path):
     launch(2, "barrier_timeout", tmp_path)
     assert json.loads((tmp_path / "barrier_timeout.json").read_text())["ok"]

@@ -54,15 +54,23 @@ def test_matches_tensor_operator_on_two_calls_in_a_row(lib, shapes):
         dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
         _, rstd = k.rmsnorm_fwd(x, w, 1e-5)
         dx_ref, dw_ref = k.rmsnorm_bwd(dy, x, w, rstd)
+        # the same operation in plain fp32 PyTorch
+        xf = x.float().requires_grad_(True)
+        wf = w.float().requires_grad_(True)
+        (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf).backward(dy.float())
         dx = torch.empty_like(x)
         dw = torch.full((H,), float("nan"), device="cuda")
+        torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
+        free_before, _ = torch.cuda.mem_get_info()  # sees allocations made behind the framework's back as well
         rc, msg = call(lib, dy, x, w, rstd, dx, dw)
         assert rc == 0, msg
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before  # nothing was allocated through the framework either
-        assert rel(dx, dx_ref) < 1e-2
-        assert rel(dw, dw_ref) < 1e-2
+        free_after, _ = torch.cuda.mem_get_info()
+        assert torch.cuda.memory_allocated() == before
+        assert free_before - free_after < (1 << 20), "device memory was allocated during the call"
+        assert rel(dx, dx_ref) < 1e-2 and rel(dw, dw_ref) < 1e-2      # the tensor-based entry point
+        assert rel(dx, xf.grad) < 2e-2 and rel(dw, wf.grad) < 2e-2      # the fp32 reference
 
 
 def test_sizes_beyond_the_limit_are_refused_with_a_message(lib):
@@ -75,3 +83,14 @@ def test_sizes_beyond_the_limit_are_refused_with_a_message(lib):
     assert rc == 1 and "limit" in msg and str(MAX_HIDDEN) in msg
     rc, msg = call(lib, x[:, :12], x[:, :12], w, rstd, dx, dw)  # hidden = 12 is not a multiple of 8
     assert rc == 1 and "multiple of 8" in msg
+
+
+def test_operands_outside_the_current_device_are_refused(lib):
+    H = 1024
+    x = torch.zeros(4, H, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(4, device="cuda")
+    dx, dw = torch.empty_like(x), torch.empty(H, device="cuda")
+    host = torch.zeros(4, H, dtype=torch.bfloat16).pin_memory()  # reachable from the GPU, but not device memory
+    rc, msg = call(lib, host, x, w, rstd, dx, dw)
+    assert rc == 1 and "device memory of the current device" in msg
