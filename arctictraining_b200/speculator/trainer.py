@@ -288,6 +288,5 @@ class MLPSpeculatorTrainer(ArcticLSTMSpeculatorTrainer):
         tokens, hidden = self._generated_batch(batch, rows)
         mb = min(c.gen_train_micro_batch_size, tokens.shape[0])
         for s in range(0, tokens.shape[0] - mb + 1, mb):
-            if self.metrics.enabled:
-                self.metrics.values.pop("loss", None)
+            self.metrics.values.pop("loss", None)  # one loss per update; the last one is reported for the iteration
             super().step({"speculator_input": hidden[s : s + mb], "speculator_label": tokens[s : s + mb]})
