@@ -28,7 +28,9 @@ def _ray():
 
 def _post_step_ray_report(trainer) -> None:
     every = trainer.config.train_log_iter_interval
-    if trainer.gas_boundary and every and trainer.global_step % every == 0:
+    # the summary of an iteration is assembled after its step: what is reported here is the previous iteration's
+    # (nothing yet after the very first step)
+    if trainer.gas_boundary and every and trainer.global_step % every == 0 and trainer.metrics.summary_dict:
         _ray().train.report(dict(trainer.metrics.summary_dict))
 
 
