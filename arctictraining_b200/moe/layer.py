@@ -119,16 +119,12 @@ class ArcticMoE(nn.Module):
                 scores = scores / scores.sum(-1, keepdim=True)
             lb = None
         else:
-            # load-balancing term: d(sum_e mean_t(p_te) * freq_e)/dp = freq / T; freq needs the routing itself,
-            # so route once without gradient to count, then with the analytic term attached.
-            lb = None
+            # load-balancing term: d(sum_e mean_t(p_te) * freq_e)/dp = freq / T, with freq taken from this routing
+            # inside the gating op (one top-k pass)
+            coeff = 0.0
             if self.training and c.loss_coeff > 0 and torch.is_grad_enabled():
-                with torch.no_grad():
-                    _, ex0, _ = mops.topk_gating(logits.detach(), self.top_k, c.normalize_topk_scores)
-                    freq = torch.bincount(ex0.reshape(-1).long(), minlength=self.num_experts).float()
-                    freq = freq / freq.sum().clamp(min=1)
-                lb = freq * (c.loss_coeff / T / self.ep_size)
-            scores, experts, probs = mops.topk_gating(logits, self.top_k, c.normalize_topk_scores, lb)
+                coeff = c.loss_coeff / T / self.ep_size
+            scores, experts, probs = mops.topk_gating(logits, self.top_k, c.normalize_topk_scores, None, coeff)
         if c.enable_routing_replay:
             self.recorded_assignments = experts.detach()
         return scores, experts

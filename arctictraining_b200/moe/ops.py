@@ -17,11 +17,20 @@ from ..ops.functional import _count
 from ..ops.functional import _use_kernels
 
 
+def _load_balance_grad(experts: torch.Tensor, num_experts: int, coeff: float) -> torch.Tensor:
+    """``coeff * freq [E]`` with ``freq`` the fraction of (token, k) assignments every expert received: the analytic
+    gradient of the load-balancing loss with respect to each token's router probabilities."""
+    freq = torch.bincount(experts.reshape(-1).long(), minlength=num_experts).float()
+    return freq * (coeff / freq.sum().clamp(min=1))
+
+
 class _GatingFn(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, logits, top_k, normalize, lb_grad):
+    def forward(ctx, logits, top_k, normalize, lb_grad, lb_coeff):
         probs, scores, experts = _ext.ops().moe_topk_gating_fwd(logits.contiguous(), top_k, normalize)
         _count()
+        if lb_grad is None and lb_coeff:
+            lb_grad = _load_balance_grad(experts, logits.shape[1], lb_coeff)  # from this very routing: one top-k pass
         ctx.save_for_backward(probs, experts, lb_grad if lb_grad is not None else torch.empty(0, device=logits.device))
         ctx.normalize, ctx.has_lb, ctx.in_dtype = normalize, lb_grad is not None, logits.dtype
         ctx.mark_non_differentiable(experts)
@@ -32,21 +41,24 @@ class _GatingFn(torch.autograd.Function):
         probs, experts, lb = ctx.saved_tensors
         dlogits = _ext.ops().moe_topk_gating_bwd(dscores.contiguous().float(), probs, experts, lb if ctx.has_lb else None, ctx.normalize)
         _count()
-        return dlogits.to(ctx.in_dtype), None, None, None
+        return dlogits.to(ctx.in_dtype), None, None, None, None
 
 
 def topk_gating(
-    logits: torch.Tensor, top_k: int, normalize: bool, lb_grad: Optional[torch.Tensor] = None
+    logits: torch.Tensor, top_k: int, normalize: bool, lb_grad: Optional[torch.Tensor] = None, lb_coeff: float = 0.0
 ) -> Tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """Returns ``scores [T,K]`` (fp32, differentiable), ``experts [T,K]`` (int32) and ``probs [T,E]`` (fp32,
     detached).  ``lb_grad [E]`` is added to d(loss)/d(probs) of every token in the backward pass — the
-    analytic gradient of the load-balancing loss."""
+    analytic gradient of the load-balancing loss; with ``lb_coeff`` instead, that term is ``lb_coeff`` times the
+    assignment frequencies of this routing itself (no second routing pass to count them)."""
     if _use_kernels(logits) and logits.shape[1] <= 1024 and top_k <= 32:
-        return _GatingFn.apply(logits, top_k, normalize, lb_grad)
+        return _GatingFn.apply(logits, top_k, normalize, lb_grad, float(lb_coeff))
     probs = torch.softmax(logits.float(), dim=-1)
+    order = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, :top_k]
+    if lb_grad is None and lb_coeff:
+        lb_grad = _load_balance_grad(order, logits.shape[1], float(lb_coeff))
     if lb_grad is not None and probs.requires_grad:
         probs.register_hook(lambda g: g + lb_grad.unsqueeze(0))
-    order = torch.sort(probs, dim=-1, descending=True, stable=True).indices[:, :top_k]
     scores = torch.gather(probs, 1, order)
     if normalize:
         scores = scores / scores.sum(-1, keepdim=True)
