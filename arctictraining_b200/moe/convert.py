@@ -42,7 +42,26 @@ def detect_if_moe_model(model: nn.Module) -> bool:
 
 
 # ------------------------------------------------------------------ state-dict converters (registered in hf_io)
+def _stacked_expert_layout(cfg: Any) -> bool:
+    """gpt-oss keeps all experts of a block in two stacked tensors (``mlp.experts.gate_up_proj [E, H, 2I]`` with gate
+    and up interleaved element-wise on the last dimension, ``mlp.experts.down_proj [E, I, H]``) and names its router
+    ``mlp.router``; Qwen keeps one ``nn.Linear`` triple per expert.  Reference:
+    arctic_training/model/moe/utils.py:118-137,198-232."""
+    get = cfg.get if isinstance(cfg, dict) else (lambda k, d=None: getattr(cfg, k, d))
+    return get("model_type") == "gpt_oss"
+
+
 def _native_to_hf(name: str, tensor: torch.Tensor, cfg: ArchConfig):
+    if _stacked_expert_layout(cfg):
+        if name.endswith("mlp.router_gate"):
+            return [(name[: -len("router_gate")] + "router.weight", tensor)]
+        if name.endswith("mlp.expert_gate_up"):
+            E, two_i, H = tensor.shape
+            g, u = zip(*(ref.deinterleave_gate_up_rows(tensor[i]) for i in range(E)))  # [I, H] each
+            gu = torch.stack([torch.stack((gi.t(), ui.t()), dim=-1).reshape(H, two_i) for gi, ui in zip(g, u)])
+            return [(name[: -len("expert_gate_up")] + "experts.gate_up_proj", gu)]
+        if name.endswith("mlp.expert_down"):
+            return [(name[: -len("expert_down")] + "experts.down_proj", tensor.transpose(1, 2).contiguous())]
     if name.endswith("mlp.router_gate"):
         return [(name[: -len("router_gate")] + "gate.weight", tensor)]
     if name.endswith("mlp.expert_gate_up"):
@@ -80,6 +99,25 @@ def _hf_to_native(hf: Dict[str, torch.Tensor], out: Dict[str, torch.Tensor], cfg
             [ref.interleave_gate_up_rows(experts[i]["gate_proj"], experts[i]["up_proj"]) for i in idx]
         )
         out[f"{pre}expert_down"] = torch.stack([experts[i]["down_proj"] for i in idx])
+    for name in list(hf):
+        if name not in hf:
+            continue
+        if name.endswith("mlp.experts.gate_up_proj"):  # gpt-oss: [E, H, 2I], gate = [..., 0::2], up = [..., 1::2]
+            gu = hf.pop(name)
+            out[name[: -len("experts.gate_up_proj")] + "expert_gate_up"] = torch.stack(
+                [ref.interleave_gate_up_rows(gu[e][:, 0::2].t().contiguous(), gu[e][:, 1::2].t().contiguous())
+                 for e in range(gu.shape[0])]
+            )
+        elif name.endswith("mlp.experts.down_proj"):   # gpt-oss: [E, I, H]
+            out[name[: -len("experts.down_proj")] + "expert_down"] = hf.pop(name).transpose(1, 2).contiguous()
+        elif name.endswith("mlp.router.weight"):
+            out[name[: -len("router.weight")] + "router_gate"] = hf.pop(name)
+        elif name.endswith(("mlp.experts.gate_up_proj_bias", "mlp.experts.down_proj_bias", "mlp.router.bias")):
+            b = hf.pop(name)
+            if float(b.abs().max()) != 0.0:
+                import warnings
+
+                warnings.warn(f"{name}: expert / router biases are not carried by ArcticMoE and are dropped", stacklevel=2)
     for name in list(hf):
         if name.endswith("mlp.gate.weight"):
             out[name[: -len("gate.weight")] + "router_gate"] = hf.pop(name)

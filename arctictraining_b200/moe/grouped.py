@@ -16,21 +16,33 @@ from ..ops import reference as ref
 from ..ops.functional import _use_kernels
 
 
-def grouped_mlp_reference(x: torch.Tensor, offsets: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
+def _gated_act(gu: torch.Tensor, act_fn: str) -> torch.Tensor:
+    if act_fn == "silu":
+        return ref.swiglu_interleaved(gu)
+    if act_fn == "silu_alpha":  # gate * sigmoid(1.702 gate) * up
+        blocks = gu.reshape(*gu.shape[:-1], gu.shape[-1] // 128, 2, 64)
+        g, u = blocks[..., 0, :], blocks[..., 1, :]
+        return (g * torch.sigmoid(1.702 * g.float()).to(g.dtype) * u).reshape(*gu.shape[:-1], gu.shape[-1] // 2)
+    raise ValueError(f"unsupported expert activation {act_fn!r}")
+
+
+def grouped_mlp_reference(x: torch.Tensor, offsets: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                          act_fn: str = "silu") -> torch.Tensor:
     E = w_gate_up.shape[0]
     bounds = offsets.tolist()
     out = x.new_zeros(x.shape[0], w_down.shape[1])
     for e in range(E):
         s, t = bounds[e], bounds[e + 1]
         if t > s:
-            h = ref.swiglu_interleaved(F.linear(x[s:t], w_gate_up[e]))
+            h = _gated_act(F.linear(x[s:t], w_gate_up[e]), act_fn)
             out[s:t] = F.linear(h, w_down[e])
     return out
 
 
-def grouped_mlp(x: torch.Tensor, offsets: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor) -> torch.Tensor:
-    if _use_kernels(x) and x.dtype == torch.bfloat16:
+def grouped_mlp(x: torch.Tensor, offsets: torch.Tensor, w_gate_up: torch.Tensor, w_down: torch.Tensor,
+                act_fn: str = "silu") -> torch.Tensor:
+    if _use_kernels(x) and x.dtype == torch.bfloat16 and act_fn == "silu":  # the fused epilogue is the plain SwiGLU
         from .grouped_cuda import grouped_mlp_cuda
 
         return grouped_mlp_cuda(x, offsets, w_gate_up, w_down)
-    return grouped_mlp_reference(x, offsets, w_gate_up, w_down)
+    return grouped_mlp_reference(x, offsets, w_gate_up, w_down, act_fn)

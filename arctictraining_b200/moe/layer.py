@@ -63,7 +63,7 @@ class MoEConfig:
     top_k: int
     normalize_topk_scores: bool = True
     loss_coeff: float = 0.01
-    act_fn: str = "silu"
+    act_fn: str = "silu"  # "silu", or "silu_alpha" = x * sigmoid(1.702 x) (the gated activation of gpt-oss)
     is_gated: bool = True
     use_shared_expert: bool = False
     shared_intermediate_dim: int = 0
@@ -140,7 +140,7 @@ class ArcticMoE(nn.Module):
             rows = T * self.top_k + self.num_experts * (SEGMENT_ALIGN - 1)
             rows = (rows + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
             permuted = mops.scatter_rows(x, slots, rows)
-            y = grouped_mlp(permuted, offsets, self.expert_gate_up, self.expert_down)
+            y = grouped_mlp(permuted, offsets, self.expert_gate_up, self.expert_down, self._config.act_fn)
             out = mops.gather_rows(y, slots, scores)
         else:
             out = self._forward_ep(x, scores, experts)
@@ -164,7 +164,7 @@ class ArcticMoE(nn.Module):
             if ex is not None:
                 return peer_expert_forward(
                     x, scores, experts, self.num_experts, ex, SEGMENT_ALIGN,
-                    lambda tokens, seg: grouped_mlp(tokens, seg, self.expert_gate_up, self.expert_down),
+                    lambda tokens, seg: grouped_mlp(tokens, seg, self.expert_gate_up, self.expert_down, self._config.act_fn),
                 ).to(x.dtype)
         slots, counts, _ = mops.assign_slots(experts, self.num_experts, 1)
         send = mops.scatter_rows(x, slots, T * K)
@@ -206,6 +206,7 @@ def build_moe_block(cfg: ArchConfig, dtype=None, device=None, ep_size: Optional[
         top_k=cfg.get("num_experts_per_tok", 2),
         normalize_topk_scores=bool(cfg.get("norm_topk_prob", True)),
         loss_coeff=float(cfg.get("router_aux_loss_coef", 0.01) or 0.0),
+        act_fn="silu_alpha" if cfg.get("model_type") == "gpt_oss" else "silu",
         use_shared_expert=bool(cfg.get("shared_expert_intermediate_size")),
         shared_intermediate_dim=int(cfg.get("shared_expert_intermediate_size") or 0),
         ep_size=ep_size, ep_rank=ep_rank, ep_group=ep_group,

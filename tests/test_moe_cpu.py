@@ -137,3 +137,35 @@ def test_tiny_moe_model_trains(tiny_recipe):
     assert tr.use_arctic_moe
     tr.train()
     assert tr.global_step == 3
+
+
+def test_gpt_oss_stacked_expert_layout_round_trips_and_keeps_the_math():
+    """gpt-oss stores all experts of a block in two stacked tensors with gate / up interleaved element-wise; the remap
+    into ArcticMoE's stacks and back is lossless, and a block built from them computes gate * sigmoid(1.702 gate) * up."""
+    from arctictraining_b200.models import hf_io
+    from arctictraining_b200.moe.grouped import grouped_mlp_reference
+
+    cfg = load_arch_config("tiny-qwen3-moe")
+    cfg = type(cfg)({**cfg, "model_type": "gpt_oss"})
+    E, H, I = 4, 64, 128
+    g = torch.Generator().manual_seed(0)
+    gu = torch.randn(E, H, 2 * I, generator=g)
+    down = torch.randn(E, I, H, generator=g)
+    hf = {"model.layers.0.mlp.experts.gate_up_proj": gu, "model.layers.0.mlp.experts.down_proj": down,
+          "model.layers.0.mlp.router.weight": torch.randn(E, H, generator=g),
+          "model.layers.0.mlp.experts.gate_up_proj_bias": torch.zeros(E, 2 * I)}
+    native = hf_io.hf_to_native_state_dict(dict(hf), cfg)
+    assert native["model.layers.0.mlp.expert_gate_up"].shape == (E, 2 * I, H)
+    assert native["model.layers.0.mlp.expert_down"].shape == (E, H, I)
+    back = dict(hf_io.iter_hf_tensors(native.items(), cfg))
+    for k in ("model.layers.0.mlp.experts.gate_up_proj", "model.layers.0.mlp.experts.down_proj", "model.layers.0.mlp.router.weight"):
+        assert torch.equal(back[k], hf[k]), k
+    # the math of one expert, written out in the Hugging Face layout
+    x = torch.randn(128, H, generator=g)
+    offsets = torch.tensor([0, 128, 128, 128, 128], dtype=torch.int32)
+    y = grouped_mlp_reference(x, offsets, native["model.layers.0.mlp.expert_gate_up"], native["model.layers.0.mlp.expert_down"],
+                              act_fn="silu_alpha")
+    z = x @ gu[0]
+    gate, up = z[:, 0::2], z[:, 1::2]
+    want = (gate * torch.sigmoid(1.702 * gate) * up) @ down[0]
+    torch.testing.assert_close(y, want, atol=1e-3, rtol=1e-4)
