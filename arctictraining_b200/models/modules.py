@@ -82,6 +82,13 @@ class Attention(nn.Module):
         bias = bool(cfg.get("attention_bias", False))
         self.qkv_proj = Linear(hidden, (self.hq + 2 * self.hkv) * self.d, bias=bias, dtype=dtype, device=device)
         self.o_proj = Linear(self.hq * self.d, hidden, bias=False, dtype=dtype, device=device)
+        # sliding-window layers (Qwen2: layers from ``max_window_layers`` on when ``use_sliding_window`` is set; Mistral:
+        # every layer when ``sliding_window`` is given)
+        self.window: Optional[int] = None
+        sw = cfg.get("sliding_window")
+        if sw and cfg.get("use_sliding_window", cfg.get("model_type") == "mistral"):
+            if layer_idx >= int(cfg.get("max_window_layers", 0) or 0):
+                self.window = int(sw)
         self.qk_norm = bool(cfg.get("qk_norm", False))
         if self.qk_norm:
             self.q_norm = RMSNorm(self.d, cfg["rms_norm_eps"], dtype=dtype, device=device)
@@ -104,7 +111,7 @@ class Attention(nn.Module):
     def core(self, q, k, v, ctx: ForwardContext) -> torch.Tensor:
         if ctx.sp is not None:
             return ctx.sp.attention(q, k, v, ctx)
-        return ops.attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl)
+        return ops.attention(q, k, v, ctx.cu_seqlens, ctx.max_seqlen, True, ctx.attn_impl, window=self.window)
 
     def _forward_cached(self, x: torch.Tensor, ctx: ForwardContext, residual: Optional[torch.Tensor]) -> torch.Tensor:
         """Generation step: the new tokens' keys and values are appended to the layer's cache and the queries attend to

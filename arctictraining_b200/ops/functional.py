@@ -461,11 +461,16 @@ def attention(
     causal: bool = True,
     impl: str = "sdpa",
     scale: Optional[float] = None,
+    window: Optional[int] = None,
 ) -> torch.Tensor:
-    """Causal GQA attention over ``[B, S, H, D]`` tensors; ``cu_seqlens`` marks packed samples (B == 1).
+    """Causal GQA attention over ``[B, S, H, D]`` tensors; ``cu_seqlens`` marks packed samples (B == 1).  ``window``
+    restricts every query to the last ``window`` keys (sliding-window layers of Qwen2 / Mistral); windowed layers run
+    on PyTorch's attention with a band mask, sample by sample.
 
     ``impl == "native"`` runs this package's tcgen05 forward kernel (head_dim 128, causal, bf16) and falls
     back to the flash-attn library for shapes the kernel does not cover."""
+    if window is not None and window > 0 and window < q.shape[1]:
+        return _windowed_attention(q, k, v, cu_seqlens, scale, int(window))
     if (
         impl == "native" and q.is_cuda and causal and q.dtype == torch.bfloat16 and q.shape[-1] == 128
         and _ext.available()
@@ -502,6 +507,24 @@ def attention(
         o = F.scaled_dot_product_attention(
             q[:, s:e].transpose(1, 2), k[:, s:e].transpose(1, 2), v[:, s:e].transpose(1, 2), is_causal=causal,
             scale=scale, enable_gqa=(Hq != Hkv),
+        )
+        outs.append(o.transpose(1, 2))
+    return torch.cat(outs, dim=1)
+
+
+def _windowed_attention(q, k, v, cu_seqlens, scale, window: int) -> torch.Tensor:
+    """Causal attention in which query t sees keys ``(t - window, t]`` of its own sample."""
+    B, S, Hq, D = q.shape
+    Hkv = k.shape[2]
+    bounds = [0, S] if cu_seqlens is None or cu_seqlens.numel() <= 2 else [int(x) for x in cu_seqlens.tolist()]
+    outs = []
+    for s, e in zip(bounds[:-1], bounds[1:]):
+        n = e - s
+        pos = torch.arange(n, device=q.device)
+        band = (pos.view(1, n) <= pos.view(n, 1)) & (pos.view(1, n) > pos.view(n, 1) - window)
+        o = F.scaled_dot_product_attention(
+            q[:, s:e].transpose(1, 2), k[:, s:e].transpose(1, 2), v[:, s:e].transpose(1, 2), attn_mask=band, scale=scale,
+            enable_gqa=(Hq != Hkv),
         )
         outs.append(o.transpose(1, 2))
     return torch.cat(outs, dim=1)

@@ -66,3 +66,33 @@ def test_swiftkv_hf_names(swiftkv_recipe):
     assert set(native) == set(own)
     for n in own:
         assert torch.equal(native[n], own[n]), n
+
+
+def test_sliding_window_layers_limit_the_keys_a_query_sees():
+    """Qwen2-style configuration: layers from ``max_window_layers`` on attend to the last ``sliding_window`` keys only
+    (the SwiftKV Qwen2 variant of the reference inherits this from the Qwen2 attention,
+    projects/swiftkv/models/qwen2/modeling_qwen2_swiftkv.py)."""
+    import torch
+
+    from arctictraining_b200 import ops
+    from arctictraining_b200.models.arch import load_arch_config
+    from arctictraining_b200.models.causal_lm import CausalLM
+
+    cfg = load_arch_config("tiny-llama", {"sliding_window": 8, "use_sliding_window": True, "max_window_layers": 1,
+                                          "attention_bias": True})
+    m = CausalLM(cfg, dtype=torch.float32)
+    assert m.model.layers[0].self_attn.window is None and m.model.layers[1].self_attn.window == 8
+    assert m.model.layers[0].self_attn.qkv_proj.bias is not None
+    torch.manual_seed(0)
+    q, k, v = (torch.randn(1, 32, 4, 16) for _ in range(3))
+    full = ops.attention(q, k, v)
+    win = ops.attention(q, k, v, window=8)
+    assert torch.allclose(full[:, :8], win[:, :8], atol=1e-6)          # the first 8 queries see everything anyway
+    assert not torch.allclose(full[:, 20:], win[:, 20:], atol=1e-4)
+    # a far-away key has no influence inside the window
+    k2, v2 = k.clone(), v.clone()
+    k2[:, 0], v2[:, 0] = 5.0, -3.0
+    assert torch.allclose(ops.attention(q, k2, v2, window=8)[:, 16:], win[:, 16:], atol=1e-6)
+    cu = torch.tensor([0, 12, 32])
+    packed = ops.attention(q, k, v, cu_seqlens=cu, window=8)
+    assert torch.allclose(packed[:, 12:], ops.attention(q[:, 12:], k[:, 12:], v[:, 12:], window=8), atol=1e-6)
