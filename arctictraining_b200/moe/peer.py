@@ -24,7 +24,7 @@ _EXCHANGES: Dict[int, "PeerMoEExchange"] = {}
 
 
 class PeerMoEExchange:
-    D_SLOT, C_SLOT, BD_SLOT, BC_SLOT, BY_SLOT = 16, 17, 18, 19, 20
+    D_SLOT, C_SLOT, BD_SLOT, BC_SLOT, BY_SLOT, N_SLOT = 16, 17, 18, 19, 20, 21
 
     def __init__(self, group) -> None:
         from ..comm.symm import RotatingBuffers
@@ -45,9 +45,27 @@ class PeerMoEExchange:
         return (rows + align - 1) // align * align
 
     def all_counts(self, counts: torch.Tensor) -> torch.Tensor:
-        out = torch.empty(self.size, counts.numel(), dtype=counts.dtype, device=counts.device)
-        dist.all_gather_into_tensor(out, counts.contiguous(), group=self.group)
-        return out
+        """``[ranks, experts]``: every rank's per-expert pair counts.  Each rank publishes its counts in a symmetric
+        slot, a device barrier follows, and every rank reads all peers' slots with the pull kernel (two slots used
+        in turn, so that a slot is rewritten only after another barrier has passed): no library collective and no
+        host synchronisation on the routing path.  The reference exchanges the counts with an all-to-all
+        (arctic_training/model/moe/moe.py:389)."""
+        n = counts.numel()
+        npad = (n + 3) // 4 * 4  # 16-byte vectors of int32
+        if getattr(self, "_counts_buf", None) is None or self._counts_pad != npad:
+            torch.cuda.synchronize()
+            self._counts_buf = self.symm.alloc(f"moe_counts_{npad}", 2 * npad, torch.int32)
+            self._counts_buf.tensor.zero_()
+            torch.cuda.synchronize()
+            dist.barrier(group=self.group, device_ids=[self.symm.device.index])
+            self._counts_pad, self._counts_turn = npad, 0
+        turn = self._counts_turn
+        self._counts_turn ^= 1
+        self._counts_buf.tensor[turn * npad : turn * npad + n].copy_(counts.to(torch.int32).reshape(-1))
+        self.symm.barrier(self.N_SLOT)
+        out = torch.empty(self.size, npad, dtype=torch.int32, device=counts.device)
+        self.symm.all_gather(self._counts_buf, turn * npad, npad, out.view(-1))
+        return out[:, :n].to(counts.dtype).contiguous()
 
 
 def exchange_for(group) -> Optional[PeerMoEExchange]:
