@@ -4,7 +4,10 @@ key blocks whose mean key scores highest against the query.
 Behaviour parity: projects/moba_attention/moba/moba_naive.py:27-110 (oracle) and moba_efficient.py:31-417 (two varlen
 attention calls merged by their log-sum-exp).  ``moba_attn_naive`` materialises the full score matrix and is the test
 oracle; ``moba_attn_varlen`` computes block gating once and evaluates attention chunk by chunk with a block mask, which
-keeps memory at ``O(chunk x seqlen)`` per head.
+keeps memory at ``O(chunk x seqlen)`` per head; ``moba_attn_efficient`` is the sparse algorithm of the reference: causal
+attention inside the own key block, plus, for every earlier key block, attention of exactly the queries that selected it,
+the partial results merged by their log-sum-exp — work and memory ``O(seqlen x topk x chunk)`` instead of
+``O(seqlen^2)``.
 """
 
 from __future__ import annotations
@@ -81,6 +84,64 @@ def moba_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, moba_chunk_size: int,
     return out
 
 
+def _partial_attention(q, k, v, scale, mask=None):
+    """``(out [n, D] fp32, lse [n] fp32)`` of queries ``q [n, D]`` over keys ``k [m, D]``."""
+    s = (q.float() @ k.float().t()) * scale
+    if mask is not None:
+        s = s.masked_fill(~mask, float("-inf"))
+    lse = torch.logsumexp(s, dim=-1)
+    return torch.exp(s - lse.unsqueeze(-1)) @ v.float(), lse
+
+
+def moba_attn_efficient(q, k, v, cu_seqlens, max_seqlen: int, moba_chunk_size: int, moba_topk: int) -> torch.Tensor:
+    """Sparse MoBA (differentiable): same result as :func:`moba_attn_naive`.
+
+    Per sequence and head: (1) every query attends causally inside its own key block; (2) the gate picks ``topk - 1``
+    earlier blocks per query; for each key block the queries that picked it are gathered and attend to that block in
+    full; (3) the partial outputs of a query are merged with weights ``exp(lse_i - lse_total)``.  This is the
+    two-call-and-merge scheme of projects/moba_attention/moba/moba_efficient.py:88-417 in the reference, which runs the
+    two calls on a variable-length attention library."""
+    out = torch.empty_like(q)
+    D = q.shape[-1]
+    scale = D ** -0.5
+    C = moba_chunk_size
+    bounds = cu_seqlens.tolist()
+    for s0, e0 in zip(bounds[:-1], bounds[1:]):
+        n = e0 - s0
+        q_, k_, v_ = q[s0:e0], k[s0:e0], v[s0:e0]
+        nblk = math.ceil(n / C)
+        H = q_.shape[1]
+        with torch.no_grad():
+            allowed = _gate_mask(q_, k_, C, moba_topk)  # [H, n, nblk], own block included
+        pos = torch.arange(n, device=q.device)
+        own_blk = pos // C
+        acc = torch.zeros(n, H, D, dtype=torch.float32, device=q.device)
+        for h in range(H):
+            outs, lses, rows = [], [], []
+            for b in range(nblk):
+                lo, hi = b * C, min(n, (b + 1) * C)
+                kb, vb = k_[lo:hi, h], v_[lo:hi, h]
+                # (1) own block, causal
+                idx = pos[lo:hi]
+                o, l = _partial_attention(q_[lo:hi, h], kb, vb, scale, idx.view(1, -1) <= idx.view(-1, 1))
+                outs.append(o); lses.append(l); rows.append(idx)
+                # (2) queries of later blocks that selected block b
+                sel = torch.nonzero(allowed[h, :, b] & (own_blk > b), as_tuple=False).squeeze(-1)
+                if sel.numel():
+                    o, l = _partial_attention(q_[sel, h], kb, vb, scale)
+                    outs.append(o); lses.append(l); rows.append(sel)
+            rows_cat = torch.cat(rows)
+            lse_cat = torch.cat(lses)
+            out_cat = torch.cat(outs)
+            # (3) merge the partial results of every query by their log-sum-exp (max subtracted for stability)
+            mx = torch.full((n,), float("-inf"), device=q.device).scatter_reduce(0, rows_cat, lse_cat.detach(), "amax")
+            w = torch.exp(lse_cat - mx[rows_cat])
+            denom = torch.zeros(n, device=q.device).index_add(0, rows_cat, w)
+            acc[:, h] = torch.zeros(n, D, device=q.device).index_add(0, rows_cat, out_cat * w.unsqueeze(-1)) / denom.unsqueeze(-1)
+        out[s0:e0] = acc.to(q.dtype)
+    return out
+
+
 class MoBAContext:
     """Drop-in attention core for the native model: set ``model.sp_context``-style hook via ``install``."""
 
@@ -95,5 +156,5 @@ class MoBAContext:
             cu = ctx.cu_seqlens if (ctx.cu_seqlens is not None and B == 1) else torch.tensor([0, S], device=q.device)
             kb = k[b].repeat_interleave(rep, dim=1)
             vb = v[b].repeat_interleave(rep, dim=1)
-            outs.append(moba_attn_varlen(q[b], kb, vb, cu, S, self.chunk_size, self.topk))
+            outs.append(moba_attn_efficient(q[b], kb, vb, cu, S, self.chunk_size, self.topk))
         return torch.stack(outs, 0)
