@@ -6,7 +6,8 @@ with one sub-directory ``batch_XXXXXXXX`` per global batch holding ``queries.par
 ``relations.parquet`` (``BATCH_QUERY_ID``, ``BATCH_DOCUMENT_ID``, ``RELEVANCE``).  Every rank reads the same batch,
 keeps a contiguous slice of the queries and of the documents (optionally ``split_factor`` sub-batches), while the
 relevance matrix stays *global* (sparse COO) because the loss is taken over the gathered embeddings.
-A one-thread read-ahead overlaps parquet decoding with the training step.
+The root may live on any ``fsspec`` file system (local disk, S3, GCS, in-memory); a read-ahead pool overlaps fetching
+and parquet decoding with the training step, and padding is one vectorised scatter per column.
 """
 
 from __future__ import annotations
@@ -78,34 +79,93 @@ def slice_sparse_coo_tensor(t: Tensor, rows: slice, cols: slice) -> Tensor:
     return torch.sparse_coo_tensor(new_idx, val[keep], (r1 - r0, c1 - c0))
 
 
-def read_batch_dir(path: Path) -> Dict[str, Any]:
+def open_filesystem(protocol: str = "local", **options):
+    """An ``fsspec`` file system by protocol name (``local``, ``s3``, ``gs``, ``memory`` ...).  Object stores need their
+    ``fsspec`` driver installed; the error of a missing one names it."""
+    import fsspec
+
+    return fsspec.filesystem("file" if protocol == "local" else protocol, **options)
+
+
+def collate_token_column(column, pad_id: int, max_len: Optional[int], left_pad: bool = False):
+    """Pad an arrow list column of token ids into ``(ids [n, L], mask [n, L])`` without a Python loop over rows:
+    the flat value buffer is scattered with one fancy-index assignment."""
+    arr = column.combine_chunks() if hasattr(column, "combine_chunks") else column
+    offsets = arr.offsets.to_numpy().astype(np.int64)
+    flat = arr.values.to_numpy(zero_copy_only=False).astype(np.int64, copy=False)
+    lens = np.diff(offsets)
+    n = len(lens)
+    L = int(lens.max()) if n else 1
+    if max_len:
+        L = min(L, int(max_len))
+    kept = np.minimum(lens, L)
+    ids = np.full((n, max(L, 1)), pad_id, dtype=np.int64)
+    col = np.arange(max(L, 1))[None, :]
+    if left_pad:
+        mask = col >= (L - kept)[:, None]
+        src = offsets[:-1, None] + (col - (L - kept)[:, None])
+    else:
+        mask = col < kept[:, None]
+        src = offsets[:-1, None] + col
+    ids[mask] = flat[src[mask]]
+    return torch.from_numpy(ids), torch.from_numpy(mask.astype(np.int64))
+
+
+def read_batch_dir(path, filesystem=None) -> Dict[str, Any]:
+    """One ``batch_*`` directory -> un-padded arrow token columns in id order + the sparse relevance matrix.  The three
+    parquet files are fetched concurrently (on an object store the round trips dominate)."""
     import pyarrow.parquet as pq
 
-    q = pq.read_table(path / "queries.parquet").to_pydict()
-    d = pq.read_table(path / "documents.parquet").to_pydict()
-    r = pq.read_table(path / "relations.parquet").to_pydict()
-    q_order = np.argsort(q["BATCH_QUERY_ID"])
-    d_order = np.argsort(d["BATCH_DOCUMENT_ID"])
-    q_pos = {q["BATCH_QUERY_ID"][i]: n for n, i in enumerate(q_order)}
-    d_pos = {d["BATCH_DOCUMENT_ID"][i]: n for n, i in enumerate(d_order)}
-    rel_idx = torch.tensor([[q_pos[a] for a in r["BATCH_QUERY_ID"]], [d_pos[b] for b in r["BATCH_DOCUMENT_ID"]]],
-                           dtype=torch.long)
+    fs = filesystem or open_filesystem("local")
+    base = str(path).rstrip("/")
+    names = ("queries.parquet", "documents.parquet", "relations.parquet")
+    with ThreadPoolExecutor(max_workers=3) as pool:
+        q, d, r = pool.map(lambda n: pq.read_table(f"{base}/{n}", filesystem=fs), names)
+    qids = q.column("BATCH_QUERY_ID").to_numpy()
+    dids = d.column("BATCH_DOCUMENT_ID").to_numpy()
+    if len(np.unique(qids)) != len(qids) or len(np.unique(dids)) != len(dids):
+        raise ValueError(f"{base}: query / document ids must be unique inside a batch")
+    q_order, d_order = np.argsort(qids, kind="stable"), np.argsort(dids, kind="stable")
+    # position of every id after sorting: searchsorted on the sorted ids is the id -> row map
+    rq = np.searchsorted(qids[q_order], r.column("BATCH_QUERY_ID").to_numpy())
+    rd = np.searchsorted(dids[d_order], r.column("BATCH_DOCUMENT_ID").to_numpy())
+    rel = torch.sparse_coo_tensor(torch.from_numpy(np.vstack([rq, rd]).astype(np.int64)),
+                                  torch.from_numpy(r.column("RELEVANCE").to_numpy().astype(np.int64)),
+                                  (len(qids), len(dids))).coalesce()
     return {
-        "queries": [q["QUERY_TOKEN_ID_LIST"][i] for i in q_order],
-        "documents": [d["DOCUMENT_TOKEN_ID_LIST"][i] for i in d_order],
-        "relations": torch.sparse_coo_tensor(rel_idx, torch.tensor(r["RELEVANCE"], dtype=torch.long),
-                                             (len(q_order), len(d_order))),
+        "queries": q.column("QUERY_TOKEN_ID_LIST").take(q_order),
+        "documents": d.column("DOCUMENT_TOKEN_ID_LIST").take(d_order),
+        "relations": rel,
     }
 
 
-class PretokenizedBatchLoader:
-    """Iterates the ``batch_*`` directories of one dataset, yielding this rank's :class:`ContrastiveLearningBatch`."""
+def read_dataset_metadata(root: str, filesystem) -> Any:
+    """``metadata.json`` written by the pre-tokeniser one or two levels above the batch directories, if present."""
+    import json
+    import posixpath
 
-    def __init__(self, root: Path, rank: int, world: int, pad_id: int = 0, max_query_len: Optional[int] = None,
-                 max_doc_len: Optional[int] = None, split_factor: int = 1, left_pad: bool = False) -> None:
-        self.root, self.rank, self.world = Path(root), rank, world
+    parent = posixpath.dirname(str(root).rstrip("/"))
+    for cand in (parent, posixpath.dirname(parent)):
+        path = posixpath.join(cand, "metadata.json")
+        if cand and filesystem.exists(path):
+            return json.loads(filesystem.read_text(path))
+    return None
+
+
+class PretokenizedBatchLoader:
+    """Iterates the ``batch_*`` directories of one dataset on any ``fsspec`` file system, yielding this rank's
+    :class:`ContrastiveLearningBatch`.  ``read_ahead`` directories are fetched and decoded by background threads while
+    the training step runs; with ``device`` set, each batch is copied there (pinned, non-blocking) one step early."""
+
+    def __init__(self, root, rank: int, world: int, pad_id: int = 0, max_query_len: Optional[int] = None,
+                 max_doc_len: Optional[int] = None, split_factor: int = 1, left_pad: bool = False, filesystem=None,
+                 read_ahead: int = 2, device=None) -> None:
+        self.fs = filesystem or open_filesystem("local")
+        self.root, self.rank, self.world = str(root).rstrip("/"), rank, world
         self.pad_id, self.max_q, self.max_d, self.split, self.left_pad = pad_id, max_query_len, max_doc_len, split_factor, left_pad
-        self.dirs = sorted(p for p in self.root.iterdir() if p.is_dir() and p.name.startswith("batch_"))
+        self.read_ahead, self.device = max(1, read_ahead), device
+        listed = self.fs.ls(self.root, detail=False)
+        self.dirs = sorted(p for p in listed if str(p).rstrip("/").rsplit("/", 1)[-1].startswith("batch_"))
         if not self.dirs:
             raise FileNotFoundError(f"no batch_* directories under {self.root}")
 
@@ -115,27 +175,51 @@ class PretokenizedBatchLoader:
     def _make(self, raw: Dict[str, Any], part: int) -> ContrastiveLearningBatch:
         nq, nd = len(raw["queries"]), len(raw["documents"])
         pq_, pd_ = nq // self.split, nd // self.split
-        qs = slice(part * pq_, (part + 1) * pq_)
-        ds = slice(part * pd_, (part + 1) * pd_)
-        rel = slice_sparse_coo_tensor(raw["relations"], qs, ds) if self.split > 1 else raw["relations"]
-        queries, docs = raw["queries"][qs], raw["documents"][ds]
-        mq, md = shard_rows(len(queries), self.rank, self.world), shard_rows(len(docs), self.rank, self.world)
-        q_ids, q_mask = pad_token_lists(queries[mq], self.pad_id, self.max_q, self.left_pad)
-        d_ids, d_mask = pad_token_lists(docs[md], self.pad_id, self.max_d, self.left_pad)
+        rel = slice_sparse_coo_tensor(raw["relations"], slice(part * pq_, (part + 1) * pq_),
+                                      slice(part * pd_, (part + 1) * pd_)) if self.split > 1 else raw["relations"]
+        mq, md = shard_rows(pq_, self.rank, self.world), shard_rows(pd_, self.rank, self.world)
+        queries = raw["queries"].slice(part * pq_ + mq.start, mq.stop - mq.start)
+        docs = raw["documents"].slice(part * pd_ + md.start, md.stop - md.start)
+        q_ids, q_mask = collate_token_column(queries, self.pad_id, self.max_q, self.left_pad)
+        d_ids, d_mask = collate_token_column(docs, self.pad_id, self.max_d, self.left_pad)
         # rows that do not divide evenly over the ranks are dropped from the labels as well
-        used_q, used_d = (len(queries) // self.world) * self.world, (len(docs) // self.world) * self.world
+        used_q, used_d = (pq_ // self.world) * self.world, (pd_ // self.world) * self.world
         rel = slice_sparse_coo_tensor(rel, slice(0, used_q), slice(0, used_d))
         return ContrastiveLearningBatch(q_ids, q_mask, d_ids, d_mask, rel)
 
+    def _load(self, path) -> List[ContrastiveLearningBatch]:
+        raw = read_batch_dir(path, self.fs)
+        return [self._make(raw, part) for part in range(self.split)]
+
+    def _stage(self, batch: ContrastiveLearningBatch) -> ContrastiveLearningBatch:
+        if self.device is None:
+            return batch
+        pinned = ContrastiveLearningBatch(*(t.pin_memory() if not t.is_sparse and torch.cuda.is_available() else t
+                                            for t in (batch.query_tokens, batch.query_attention_mask, batch.document_tokens,
+                                                      batch.document_attention_mask, batch.relevance_labels)))
+        return pinned.to_device(self.device)
+
     def __iter__(self) -> Iterator[ContrastiveLearningBatch]:
-        with ThreadPoolExecutor(max_workers=1) as pool:
-            nxt = pool.submit(read_batch_dir, self.dirs[0])
-            for i in range(len(self.dirs)):
-                raw = nxt.result()
-                if i + 1 < len(self.dirs):
-                    nxt = pool.submit(read_batch_dir, self.dirs[i + 1])
-                for part in range(self.split):
-                    yield self._make(raw, part)
+        meta = read_dataset_metadata(self.root, self.fs)
+        from ..logging import logger
+
+        logger.info(f"iterating {self.root} ({len(self.dirs)} batch directories; tokenisation: {meta or 'no metadata'})")
+        with ThreadPoolExecutor(max_workers=self.read_ahead) as pool:
+            pending = [pool.submit(self._load, p) for p in self.dirs[: self.read_ahead]]
+            nxt = self.read_ahead
+            staged = None
+            while pending:
+                parts = pending.pop(0).result()
+                if nxt < len(self.dirs):
+                    pending.append(pool.submit(self._load, self.dirs[nxt]))
+                    nxt += 1
+                for b in parts:  # copy batch i+1 to the device before handing out batch i
+                    b = self._stage(b)
+                    if staged is not None:
+                        yield staged
+                    staged = b
+            if staged is not None:
+                yield staged
 
 
 class SyntheticContrastiveLoader:
@@ -167,6 +251,11 @@ class SyntheticContrastiveLoader:
 class ContrastivePretokenizedDataConfig(DataConfig):
     sources: List[Any] = Field(default_factory=list)
     filesystem: str = "local"
+    """ ``fsspec`` protocol of the data: ``local``, ``s3``, ``gs``, ``memory`` ... """
+    filesystem_options: Dict[str, Any] = Field(default_factory=dict)
+    """ Keyword arguments of the file system (credentials, endpoint, ...). """
+    read_ahead: int = 2
+    """ Batch directories fetched and decoded ahead of the training step. """
     root_directory: str = ""
     """ Directory with ``batch_*`` sub-directories (train). """
     eval_root_directories: List[str] = Field(default_factory=list)
@@ -193,11 +282,16 @@ class ContrastivePretokenizedDataFactory(DataFactory):
             train = SyntheticContrastiveLoader(c.synthetic_batches, c.synthetic_global_queries, c.synthetic_docs_per_query,
                                                c.synthetic_seq_len, c.synthetic_vocab, self.global_rank, self.world_size, c.seed)
         else:
-            train = PretokenizedBatchLoader(Path(c.root_directory), self.global_rank, self.world_size, c.pad_value,
-                                            c.max_seq_length_query, c.max_seq_length_doc, c.split_factor, c.left_pad)
-        evals = {Path(d).name: PretokenizedBatchLoader(Path(d), self.global_rank, self.world_size, c.pad_value,
-                                                        c.max_seq_length_query, c.max_seq_length_doc, 1, c.left_pad)
-                 for d in c.eval_root_directories}
+            fs = open_filesystem(c.filesystem, **c.filesystem_options)
+            train = PretokenizedBatchLoader(c.root_directory, self.global_rank, self.world_size, c.pad_value,
+                                            c.max_seq_length_query, c.max_seq_length_doc, c.split_factor, c.left_pad,
+                                            filesystem=fs, read_ahead=c.read_ahead)
+        evals = {}
+        for d in c.eval_root_directories:
+            fs = open_filesystem(c.filesystem, **c.filesystem_options)
+            evals[d.rstrip("/").rsplit("/", 1)[-1]] = PretokenizedBatchLoader(
+                d, self.global_rank, self.world_size, c.pad_value, c.max_seq_length_query, c.max_seq_length_doc, 1,
+                c.left_pad, filesystem=fs, read_ahead=c.read_ahead)
         return train, (evals or None)
 
     def load(self, data_sources):

@@ -1,5 +1,6 @@
 from pathlib import Path
 
+import numpy as np
 import pytest
 import torch
 import torch.nn.functional as F
@@ -95,3 +96,73 @@ def test_biencoder_trainer_learns_on_synthetic_batches(tiny_recipe, tmp_path):
     assert tr.global_step == 12 and last < first
     out = next((tmp_path / "ck").glob("global_step_*"))
     assert (out / "biencoder_config.json").exists() and (out / "model.safetensors").exists()
+
+
+def _write_memory_dataset(fs, root, n_batches=3, nq=8, dpq=2):
+    import io
+
+    import pyarrow as pa
+    import pyarrow.parquet as pq
+
+    rng = np.random.default_rng(0)
+    fs.pipe(f"{root}/metadata.json", b'{"tokenizer": "toy"}')
+    for b in range(n_batches):
+        base = f"{root}/data/batch_{b:08d}"
+        # ids deliberately out of order: the loader must sort by id and map relations through the ids
+        qid = rng.permutation(nq) + 100
+        did = rng.permutation(nq * dpq) + 500
+        tables = {
+            "queries.parquet": pa.table({"BATCH_QUERY_ID": qid,
+                                         "QUERY_TOKEN_ID_LIST": [list(range(1, 2 + int(i) % 5)) for i in qid]}),
+            "documents.parquet": pa.table({"BATCH_DOCUMENT_ID": did,
+                                           "DOCUMENT_TOKEN_ID_LIST": [[int(i)] * (1 + int(i) % 7) for i in did]}),
+            "relations.parquet": pa.table({"BATCH_QUERY_ID": np.repeat(np.sort(qid), dpq),
+                                           "BATCH_DOCUMENT_ID": np.sort(did),
+                                           "RELEVANCE": np.tile([1, -1], nq)}),
+        }
+        for name, t in tables.items():
+            buf = io.BytesIO()
+            pq.write_table(t, buf)
+            fs.pipe(f"{base}/{name}", buf.getvalue())
+    return f"{root}/data"
+
+
+def test_loader_streams_from_an_fsspec_object_store_and_shards_consistently():
+    from arctictraining_b200.embed.data import PretokenizedBatchLoader
+    from arctictraining_b200.embed.data import open_filesystem
+    from arctictraining_b200.embed.data import read_dataset_metadata
+
+    fs = open_filesystem("memory")
+    root = _write_memory_dataset(fs, "/embed_ds")
+    assert read_dataset_metadata(root, fs) == {"tokenizer": "toy"}
+    whole = list(PretokenizedBatchLoader(root, 0, 1, filesystem=fs))
+    assert len(whole) == 3
+    b = whole[0]
+    # rows come out sorted by id: query i has id 100 + i and 1 + (100 + i) % 5 tokens
+    lens = b.query_attention_mask.sum(1).tolist()
+    assert lens == [1 + (100 + i) % 5 for i in range(8)]
+    assert b.document_tokens[:, 0].tolist() == list(range(500, 516))
+    dense = b.relevance_labels.to_dense()
+    assert dense.shape == (8, 16) and all(dense[i, 2 * i] == 1 and dense[i, 2 * i + 1] == -1 for i in range(8))
+    # two ranks see disjoint contiguous slices of the same batch and the same (global) labels
+    r0 = list(PretokenizedBatchLoader(root, 0, 2, filesystem=fs, read_ahead=1))
+    r1 = list(PretokenizedBatchLoader(root, 1, 2, filesystem=fs, read_ahead=3))
+    assert torch.equal(torch.cat([r0[1].query_tokens[:, :1], r1[1].query_tokens[:, :1]]), whole[1].query_tokens[:, :1])
+    assert torch.equal(r0[1].relevance_labels.to_dense(), whole[1].relevance_labels.to_dense())
+    # split_factor=2 yields two sub-batches per directory with re-based labels
+    halves = list(PretokenizedBatchLoader(root, 0, 1, filesystem=fs, split_factor=2))
+    assert len(halves) == 6 and halves[0].relevance_labels.shape == (4, 8)
+    assert torch.equal(halves[1].relevance_labels.to_dense(), dense[4:, 8:])
+
+
+def test_collate_truncates_and_left_pads():
+    import pyarrow as pa
+
+    from arctictraining_b200.embed.data import collate_token_column
+
+    col = pa.chunked_array([pa.array([[1, 2, 3, 4, 5], [6], [7, 8]], type=pa.list_(pa.int64()))])
+    ids, mask = collate_token_column(col, pad_id=0, max_len=3)
+    assert ids.tolist() == [[1, 2, 3], [6, 0, 0], [7, 8, 0]] and mask.tolist() == [[1, 1, 1], [1, 0, 0], [1, 1, 0]]
+    ids, mask = collate_token_column(col, pad_id=9, max_len=None, left_pad=True)
+    assert ids.tolist() == [[1, 2, 3, 4, 5], [9, 9, 9, 9, 6], [9, 9, 9, 7, 8]]
+    assert mask.sum(1).tolist() == [5, 1, 2]
