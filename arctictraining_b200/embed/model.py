@@ -35,10 +35,13 @@ class BiencoderConfig:
 
 def pool(hidden: Tensor, attention_mask: Tensor, how: str) -> Tensor:
     """``hidden [B, S, H]``, ``attention_mask [B, S]`` (1 = token) -> ``[B, H]``."""
+    how = {"first_token": "first", "last_token": "last", "average": "mean"}.get(how, how)
     if how == "first":
         return hidden[:, 0]
     if how == "last":
-        last = attention_mask.long().sum(1).clamp(min=1) - 1
+        # index of the last real token, for right- and left-padded rows alike
+        S = attention_mask.shape[1]
+        last = S - 1 - attention_mask.long().flip(1).argmax(1)
         return hidden[torch.arange(hidden.size(0), device=hidden.device), last]
     if how == "mean":
         m = attention_mask.unsqueeze(-1).to(hidden.dtype)

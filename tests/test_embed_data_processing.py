@@ -1,0 +1,157 @@
+"""Offline data preparation of the embedding project: parquet collections, sharded pre-tokenisation jobs that write
+what the training loader reads, dense retrieval."""
+
+import json
+
+import numpy as np
+import pyarrow as pa
+import pyarrow.parquet as pq
+import pytest
+import torch
+
+from arctictraining_b200.embed.data import PretokenizedBatchLoader
+from arctictraining_b200.embed.data_processing import MinedDataJob
+from arctictraining_b200.embed.data_processing import PairsJob
+from arctictraining_b200.embed.data_processing import ParquetCollection
+from arctictraining_b200.embed.data_processing import dense_retrieval
+from arctictraining_b200.embed.data_processing import pretokenize_mined_data
+from arctictraining_b200.embed.data_processing import pretokenize_pairs
+from arctictraining_b200.embed.data_processing import shard_row_range
+from arctictraining_b200.embed.data_processing.embedders import read_embeddings
+from arctictraining_b200.embed.data_processing.embedders import write_embeddings
+
+
+def toy_tokenize(texts):
+    return [[1] + [2 + ord(c) % 40 for c in t] for t in texts]
+
+
+def write_pairs(root, n_files=3, rows_per_file=7):
+    root.mkdir(parents=True, exist_ok=True)
+    k = 0
+    for f in range(n_files):
+        rows = []
+        for _ in range(rows_per_file):
+            rows.append({"QUERY_ID": f"q{k}", "DOCUMENT_ID": f"d{k % 5}" if k % 4 else None, "QUERY_TEXT": f"query {k}",
+                         "DOCUMENT_TEXT": f"document {k % 5}"})
+            k += 1
+        pq.write_table(pa.Table.from_pylist(rows), root / f"part_{f}.parquet")
+    return k
+
+
+def test_parquet_collection_streams_row_ranges_across_files(tmp_path):
+    n = write_pairs(tmp_path / "pairs")
+    ds = ParquetCollection.from_location(str(tmp_path / "pairs"))
+    assert ds.num_files == 3 and ds.num_rows == n == 21 and ds.batches_per_epoch(4) == 5
+    got = pa.concat_tables(list(ds.stream_tables(["QUERY_ID"], (5, 16))))["QUERY_ID"].to_pylist()
+    assert got == [f"q{i}" for i in range(5, 16)]
+    sizes = [t.num_rows for t in ds.stream_chunks(8)]
+    assert sizes == [8, 8, 5]
+    one = ParquetCollection.from_location(str(tmp_path / "pairs" / "part_1.parquet"))
+    assert one.num_rows == 7
+
+
+def test_shard_row_range_hands_out_whole_chunks():
+    spans = [shard_row_range(103, 10, s, 4) for s in range(4)]
+    assert spans[0][0] == 0 and spans[-1][1] == 103
+    assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+    assert all(a % 10 == 0 for a, _ in spans)
+    assert sorted((b - a + 9) // 10 for a, b in spans) == [2, 3, 3, 3]
+    with pytest.raises(ValueError):
+        shard_row_range(10, 2, 4, 4)
+
+
+def test_pairs_job_sharded_output_is_what_the_loader_reads(tmp_path):
+    write_pairs(tmp_path / "pairs")
+    job = PairsJob(tokenizer_id="toy", query_doc_pair_dir=str(tmp_path / "pairs"), output_dir=str(tmp_path / "out"),
+                   batch_size=8, query_prefix="Q:", document_prefix="D:", max_seq_length=6)
+    shards = job.split_to_shards(2)
+    with pytest.raises(ValueError):
+        shards[0].split_to_shards(2)
+    assert sum(pretokenize_pairs(s, toy_tokenize) for s in shards) == 3
+    meta = json.loads((tmp_path / "out" / "metadata.json").read_text())
+    assert meta["batch_size"] == 8 and meta["query_prefix"] == "Q:"
+    batches = list(PretokenizedBatchLoader(tmp_path / "out", 0, 1))
+    assert len(batches) == 3
+    b = batches[0]
+    # 8 pairs; documents de-duplicated by id (d1..d4 + two rows without id that share text with d0 / d4)
+    assert b.query_tokens.shape == (8, 6)           # truncated to max_seq_length
+    assert b.relevance_labels.to_dense().sum() == 8  # every pair a positive
+    assert b.document_tokens.shape[0] < 8
+    assert b.query_tokens[0, :3].tolist() == toy_tokenize(["Q:"])[0]
+    ids = pq.read_table(tmp_path / "out" / "batch_00000000" / "did_map.parquet")["DOCUMENT_ID"].to_pylist()
+    assert any(i.startswith("__MISSING_ID__") for i in ids)
+
+
+def test_mined_job_reuses_queries_with_disjoint_negatives(tmp_path):
+    nq, nd = 8, 40
+    pq.write_table(pa.table({"QUERY_ID": np.arange(nq), "QUERY_TEXT": [f"q{i}" for i in range(nq)]}), tmp_path / "q.parquet")
+    pq.write_table(pa.table({"DOCUMENT_ID": np.arange(nd), "DOCUMENT_TEXT": [f"doc{i}" for i in range(nd)]}), tmp_path / "d.parquet")
+    rows = []
+    for q in range(nq):
+        rows.append((q, q, 1.0))
+        rows += [(q, (q + 1 + j) % nd + 0, -float(j)) for j in range(1, 7) if (q + 1 + j) % nd != q]
+    lq, ld, lr = zip(*rows)
+    pq.write_table(pa.table({"QUERY_ID": lq, "DOCUMENT_ID": ld, "RELEVANCE": lr}), tmp_path / "labels.parquet")
+    job = MinedDataJob(tokenizer_id="toy", query_loc=str(tmp_path / "q.parquet"), document_loc=str(tmp_path / "d.parquet"),
+                       labels_loc=str(tmp_path / "labels.parquet"), output_loc=str(tmp_path / "mined"), queries_per_batch=4,
+                       num_query_uses=2, num_negatives_per_query_per_batch=3)
+    assert pretokenize_mined_data(job, toy_tokenize) == 4
+    batches = list(PretokenizedBatchLoader(tmp_path / "mined" / "data", 0, 1))
+    assert len(batches) == 4
+    for b in batches:
+        dense = b.relevance_labels.to_dense()
+        assert dense.shape[0] == 4
+        assert ((dense == 1).sum(1) == 1).all() and ((dense == -1).sum(1) == 3).all()
+    # a query's negatives in its two uses do not overlap
+    seen = {}
+    for i in range(4):
+        d = tmp_path / "mined" / "data" / f"batch_{i:08d}"
+        q_tok = {r["BATCH_QUERY_ID"]: tuple(r["QUERY_TOKEN_ID_LIST"]) for r in pq.read_table(d / "queries.parquet").to_pylist()}
+        d_tok = {r["BATCH_DOCUMENT_ID"]: tuple(r["DOCUMENT_TOKEN_ID_LIST"]) for r in pq.read_table(d / "documents.parquet").to_pylist()}
+        for r in pq.read_table(d / "relations.parquet").to_pylist():
+            if r["RELEVANCE"] < 0:
+                seen.setdefault(q_tok[r["BATCH_QUERY_ID"]], []).append(d_tok[r["BATCH_DOCUMENT_ID"]])
+    assert len(seen) == 8 and all(len(v) == 6 and len(set(v)) == 6 for v in seen.values())
+    assert json.loads((tmp_path / "mined" / "metadata.json").read_text())["num_query_uses"] == 2
+
+
+def test_dense_retrieval_matches_brute_force_across_slices():
+    g = torch.Generator().manual_seed(0)
+    q = torch.nn.functional.normalize(torch.randn(37, 16, generator=g), dim=-1)
+    d = torch.nn.functional.normalize(torch.randn(211, 16, generator=g), dim=-1)
+    idx, val = dense_retrieval(q.numpy(), d.numpy(), retrieval_depth=10, item_slice_size=50, query_slice_size=16, device="cpu")
+    ref_val, ref_idx = torch.topk(q @ d.t(), 10, dim=1)
+    assert np.array_equal(idx, ref_idx.numpy().astype(np.int32))
+    assert np.allclose(val, ref_val.numpy(), atol=1e-6)
+    idx2, _ = dense_retrieval(q.numpy(), d.numpy(), retrieval_depth=500, device="cpu")
+    assert idx2.shape == (37, 211)
+
+
+def test_embedding_parquet_round_trip(tmp_path):
+    m = np.random.default_rng(0).standard_normal((5, 8)).astype(np.float32)
+    write_embeddings(str(tmp_path / "e.parquet"), [f"id{i}" for i in range(5)], m)
+    ids, back = read_embeddings(str(tmp_path / "e.parquet"))
+    assert list(ids) == [f"id{i}" for i in range(5)] and np.array_equal(back, m)
+
+
+def test_embed_all_keeps_input_order_and_config_cli_runs_a_shard(tmp_path):
+    from arctictraining_b200.embed.data_processing import Embedder
+    from arctictraining_b200.embed.data_processing import run_config_file_cli
+
+    class LengthEmbedder(Embedder):
+        def to_device(self, device):
+            pass
+
+        def embed_batch(self, texts, is_query, **kw):
+            return np.array([[len(t), float(is_query)] for t in texts], dtype=np.float32)
+
+    texts = ["aaa", "b", "cccccc", "dd", "eeee"]
+    out = LengthEmbedder().embed_all(texts, is_query=True, batch_size=2)
+    assert out[:, 0].tolist() == [3, 1, 6, 2, 4] and out[:, 1].tolist() == [1] * 5
+
+    write_pairs(tmp_path / "pairs")
+    cfg = tmp_path / "job.yaml"
+    cfg.write_text(f"tokenizer_id: toy\nquery_doc_pair_dir: {tmp_path / 'pairs'}\noutput_dir: {tmp_path / 'o'}\nbatch_size: 8\n")
+    ran = []
+    run_config_file_cli(PairsJob, lambda c: ran.append(pretokenize_pairs(c, toy_tokenize)), [str(cfg), "--num-shards", "3", "--shard", "2"])
+    assert ran == [1] and (tmp_path / "o" / "batch_00000002").is_dir() and not (tmp_path / "o" / "batch_00000000").exists()
