@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Import-name compatibility: ``import arctic_training`` resolves to :mod:`arctictraining_b200`, so user
 ``train.py`` files and recipes written against the reference's package name keep working."""
 

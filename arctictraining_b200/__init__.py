@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """arctictraining_b200 — a Blackwell-native LLM post-training framework with the public surface of
 ArcticTraining (arctic_training/__init__.py:20-57): YAML recipes, registry-driven trainers and factories,
 callbacks, Hugging Face and sharded checkpoints."""

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Mixture of Block Attention (MoBA): every query attends to its own key block (causally) plus the ``topk - 1`` earlier
 key blocks whose mean key scores highest against the query.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .callback import Callback
 from .mixin import CallbackMixin
 from .mixin import callback_wrapper

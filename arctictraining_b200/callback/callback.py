@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """One bound callback: an event name, the user function and the wrapped method it observes.
 
 Behaviour parity: arctic_training/callback/callback.py:26-156.  A *pre* callback receives ``self`` plus

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Built-in logging callbacks.  Parity: arctic_training/callback/logging.py:21-68."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Mixin giving a class ``pre-<event>`` / ``post-<event>`` hooks around selected methods.
 
 Behaviour parity: arctic_training/callback/mixin.py:35-162.  ``@callback_wrapper("step")`` marks a

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Checkpoint engine base class.  Parity: arctic_training/checkpoint/engine.py:36-128."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Hugging Face export checkpoints (recipe name ``huggingface``).
 
 Writes ``output_dir/global_step_<N>/{config.json, model.safetensors | model-0000i-of-0000N.safetensors +

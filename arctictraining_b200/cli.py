@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``arctic_training`` command line.  Parity: arctic_training_cli.py:24-125.
 
 ``arctic_training [train|process-data] recipe.yaml [--python_profile ...] [--launcher local|deepspeed|ray]

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .dist import all_gather_object
 from .dist import barrier
 from .dist import get_rank

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Process-group bootstrap and small helpers used all over the framework.
 
 One process drives one GPU.  ``torch.distributed`` (NCCL on GPUs, Gloo on CPU-only hosts) is the

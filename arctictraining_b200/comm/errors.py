@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Turns the per-device error words of the CUDA kernels into Python exceptions.
 
 Every device-side wait of this library is bounded: a kernel that gives up records a code and returns, so the CUDA

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Symmetric (peer-mapped) device memory and the kernels that communicate through it.
 
 Every rank of a node allocates buffers of identical size through ``torch.distributed._symmetric_memory`` and

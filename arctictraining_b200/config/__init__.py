@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .base import BaseConfig
 from .checkpoint import CheckpointConfig
 from .data import DataConfig

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Base class of every config object.  Parity: arctic_training/config/base.py:26-42."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """One entry of the ``checkpoint:`` list.  Parity: arctic_training/config/checkpoint.py:31-60."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``data:`` section and the per-source configs.  Parity: arctic_training/config/data.py:45-208."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Data-type enum accepted by ``model.dtype``.  Parity: arctic_training/config/enums.py:25-64."""
 
 from __future__ import annotations

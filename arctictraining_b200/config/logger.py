@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``logger:`` section.  Parity: arctic_training/config/logger.py:29-66."""
 
 from __future__ import annotations

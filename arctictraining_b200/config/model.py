@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``model:`` section of a recipe.  Parity: arctic_training/config/model.py:35-98."""
 
 from __future__ import annotations

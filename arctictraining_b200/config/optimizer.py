@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``optimizer:`` section.  Parity: arctic_training/config/optimizer.py:30-45."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``scheduler:`` section.  Parity: arctic_training/config/scheduler.py:30-46."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``tokenizer:`` section.  Parity: arctic_training/config/tokenizer.py:32-44."""
 
 from __future__ import annotations

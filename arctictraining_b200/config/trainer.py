@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Top-level recipe config (one YAML file == one ``TrainerConfig``) and ``get_config``.
 
 Behaviour parity: arctic_training/config/trainer.py:67-548 — same field names and defaults, sub-config

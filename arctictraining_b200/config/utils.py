@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Helpers shared by the config classes: rank look-ups, human-readable numbers, strict YAML loading.
 
 Behaviour parity: arctic_training/config/utils.py:25-92.

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``wandb:`` section.  Parity: arctic_training/config/wandb.py:21-32."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Causal flash-attention backward for sm_100a: packed (variable-length) sequences, grouped-query heads, head_dim 128.
 //
 // Given Q, K, V, the forward output O with its log-sum-exp L, and dO, it computes per packed sequence

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Causal flash-attention forward for sm_100a: packed (variable-length) sequences, grouped-query heads, head_dim 128.
 //
 //   O[t, h, :] = softmax_j<=t ( Q[t, h, :] . K[j, g(h), :] * scale ) V[j, g(h), :]     within each packed sequence

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Operator registration: every kernel of the library is reachable as torch.ops.atb200.<name>.
 #include <ATen/ATen.h>
 #include <torch/library.h>

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Cross-entropy over one chunk of logits, forward and backward in a single kernel.
 //
 // For every row: loss = logsumexp(logits) - logits[label]; the logits are then overwritten in place by

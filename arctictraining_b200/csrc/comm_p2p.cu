@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Collectives written as plain kernels over NVLink peer memory (symmetric buffers that every rank of the node has
 // mapped).  Kernels receive a device table of peer base pointers; data moves with 16-byte peer loads / stores issued
 // from the SMs, so the transfer is part of the same kernel as the arithmetic that consumes it:

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Shared device/host helpers for the sm_100a kernels of this library.
 #pragma once
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Device-side helpers shared by the kernels of this library: 16-byte bf16 vectors and warp / block reductions.
 // This header depends on the CUDA toolkit only (no framework headers).
 #pragma once

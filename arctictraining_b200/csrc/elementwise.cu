@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Bandwidth-bound fused kernels: RMSNorm (fwd/bwd), rotary embedding, SwiGLU (fwd/bwd),
 // fused AdamW on flat shards, squared-norm partials.  All kernels use 16-byte vector accesses and
 // 64-bit row offsets (sequences of millions of tokens).

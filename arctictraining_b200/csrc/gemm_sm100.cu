@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // bf16 GEMM for sm_100a: TMA-fed shared-memory pipeline, tcgen05.mma with fp32 accumulators in TMEM,
 // persistent warp-specialised CTAs (one per SM) and a double-buffered accumulator so that the epilogue
 // of tile i overlaps the main loop of tile i+1.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Mixture-of-experts routing and token permutation kernels.
 //
 //   moe_topk_gating_fwd / _bwd : softmax over all experts (fp32), top-k with ties resolved to the lower

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) features used by this library:
 // mbarrier, TMA bulk tensor copies (each CTA fetches its own tiles), tcgen05 MMA / TMEM, peer flags.
 // Every wait is bounded: it gives up after a wall-clock limit and reports failure to the caller.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Allocation-free RMSNorm backward: see rmsnorm_bwd_noalloc.h for the contract.
 //
 // The partial sums of the weight gradient go to a file-scope device array instead of a freshly allocated tensor.

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 /* RMSNorm backward for callers that must not allocate device memory.
  *
  * This entry point has no counterpart in the reference project; it exists for users of this library.

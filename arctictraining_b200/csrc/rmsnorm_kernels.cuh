@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // RMSNorm backward kernel, shared by the tensor-based operator and the allocation-free C entry point.
 #pragma once
 

@@ -1,3 +1,4 @@
+// SPDX-License-Identifier: Apache-2.0
 // Host-side AdamW for optimizer states that live in (pinned) host memory: one fused pass over master weights, moments
 // and gradient, spread over ATen's intra-op thread pool, with the bf16 copy of the updated weights written in the same pass.  The reference gets
 // this from its engine dependency's vectorised host optimizer (arctic_training/optimizer/adam_factory.py:100-126).

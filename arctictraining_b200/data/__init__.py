@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .causal import CausalDataFactory
 from .dpo import DPODataFactory
 from .factory import DataFactory

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Causal (pre-training style) data: BOS + text + EOS tokenisation, then a token stream cut into rows of
 exactly ``max_length`` tokens; documents shorter than a row are packed together and document boundaries
 are kept in ``position_ids`` / ``packed_sample_seqlens``.  Parity: arctic_training/data/causal_factory.py:55-228.

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Preference (DPO) data: prompt / chosen / rejected tokenisation and the paired collator.
 
 Behaviour parity: arctic_training/data/dpo_factory.py:36-308 — the prompt is tokenised as part of

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Data factory base class.  Parity: arctic_training/data/factory.py:50-239 — the main process (local
 rank 0 on a node-local cache, global rank 0 on a shared one) builds the concatenated and shuffled
 dataset, replicates it up to ``min_iterations``, publishes it atomically, everybody meets at a barrier,

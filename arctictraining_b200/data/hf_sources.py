@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Data sources backed by the ``datasets`` library: generic, instruction (SFT), causal text, and two
 named datasets.  Parity: arctic_training/data/hf_source.py:33-170, hf_instruct_source.py:32-224,
 hf_causal_source.py:21-48."""

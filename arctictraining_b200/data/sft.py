@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Supervised fine-tuning data: chat-template tokenisation with assistant-only labels, length filter,
 sample packing and the padding collator.
 

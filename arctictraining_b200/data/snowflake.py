@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Snowflake data source: SQL query, whole table, or versioned Snowflake Dataset.
 
 Behaviour parity: arctic_training/data/snowflake_source.py:33-233 (three mutually exclusive modes,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Data source base class.  Parity: arctic_training/data/source.py:41-168 — per-source cache keyed by an
 md5 of (factory config, source config, tokenizer config), optional random sub-sampling, tokenisation
 by the owning factory, atomic ``.incomplete`` -> rename publication, memory-mapped reload."""

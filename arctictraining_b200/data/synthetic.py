@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Synthetic data sources: seeded uniform token ids, no files and no network.
 
 ``synthetic`` yields already tokenised samples (``input_ids``/``labels``/``attention_mask``; set

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Small helpers of the data layer.  Parity: arctic_training/data/utils.py:32-97."""
 
 from __future__ import annotations

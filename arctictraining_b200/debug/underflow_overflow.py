@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Numeric tracers: find where activations or gradients first become inf / nan, or drift towards the limits of the
 training dtype.  Behaviour parity: arctic_training/debug/underflow_overflow.py:48-540 (forward-hook tracer that keeps
 the last frames with absolute min / max of inputs, outputs and weights and aborts on inf/nan; backward-hook tracer

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Memory and rank-aware printing helpers.  Parity: arctic_training/debug/utils.py:50-287."""
 
 from __future__ import annotations

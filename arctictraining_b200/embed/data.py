@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Contrastive training batches: pre-tokenised, pre-batched parquet data and a synthetic stand-in.
 
 On-disk format (projects/arctic_embed/src/arctic_embed/core/pretokenized_batch_loader.py:52-406): a root directory

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Offline data preparation for contrastive embedding training: parquet collections on any file system, dense
 retrieval for hard-negative mining, teacher embedders, and the two pre-tokenise-and-batch jobs that write the
 ``batch_*`` layout the training loader streams.  Parity: projects/arctic_embed/src/arctic_embed/data_processing/."""

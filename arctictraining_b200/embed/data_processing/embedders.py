@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Teacher / mining embedders and small helpers of the data-preparation jobs.
 
 Parity: projects/arctic_embed/src/arctic_embed/data_processing/teacher_models.py:40-95 (embedder interface and the

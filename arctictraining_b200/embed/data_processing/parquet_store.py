@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """A directory (or explicit list) of parquet files treated as one table, streamed file by file.
 
 Parity: projects/arctic_embed/src/arctic_embed/data_processing/many_parquet_dataset.py:36-196.  Row counts come from

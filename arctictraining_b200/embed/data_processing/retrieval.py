@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Exact dense retrieval (inner product top-k) for hard-negative mining.
 
 Parity: projects/arctic_embed/src/arctic_embed/data_processing/dense_retrieval.py:27-85.  Here the running top-k stays

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """The two pre-tokenise-and-batch jobs.  Both write ``<out>/metadata.json`` and ``batch_XXXXXXXX/{queries,documents,
 relations}.parquet`` with batch-local integer ids — the layout ``PretokenizedBatchLoader`` streams.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Contrastive losses for embedding models: InfoNCE with many-to-many relevance labels, and the one-size
 Matryoshka variant.  Behaviour parity: projects/arctic_embed/src/arctic_embed/core/losses.py:36-207.
 

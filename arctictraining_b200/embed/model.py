@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Bi-encoder: one shared text encoder for queries and documents, pooled and (at loss time) L2-normalised.
 Behaviour parity: projects/arctic_embed/src/arctic_embed/core/biencoder_model.py:37-134 (first / last / mean
 pooling; ``biencoder_config.json`` next to the encoder checkpoint).

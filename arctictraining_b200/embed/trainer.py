@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Bi-encoder (embedding model) trainer.  Behaviour parity: projects/arctic_embed/src/arctic_embed/trainer.py:52-279,
 biencoder_model_factory.py:33-77, checkpointing.py:24-39.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Storage for the inputs of checkpointed units, optionally in pinned host memory.
 
 With offload on, the hidden state that enters a layer is copied to a pinned host buffer on a dedicated

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Typed view of the engine section of a recipe (the ``deepspeed:`` dict of the reference's YAML).
 
 Keys understood (same spelling as the recipes of the reference, arctic_training/config/trainer.py:395-440

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """The training engine: flat-buffer ZeRO stages 0-3, mixed precision, gradient accumulation and
 clipping, per-layer activation checkpointing with optional host offload, and sharded checkpoints.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Named timers that measure on the device (CUDA events) when a GPU is present, else wall clock.
 
 Parity: the reference relies on a synchronising wall-clock timer from its engine dependency

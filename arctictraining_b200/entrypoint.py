@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Per-rank entry point (``arctic_training_run``).  Parity: arctic_training/entrypoint.py:27-83."""
 
 from __future__ import annotations

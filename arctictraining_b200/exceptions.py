@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Error types raised by the registry and the communication layer."""
 
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Floating-point operation estimates for decoder transformers (used for the tflops metrics).
 
 Convention as in the reference (arctic_training/trainer/flops_counter.py:58-377): a matmul with N

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Process launcher: one worker per GPU, torchrun-style environment, fail-fast supervision.
 
 It accepts the launcher flags that recipes and docs of the reference pass through to its engine's

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Ray Train launcher.  Behaviour parity: arctic_training/launcher/ray_launcher.py:40-209 — one Ray worker per GPU
 (``TorchTrainer`` + ``ScalingConfig``), per-instance ``post-step`` (metrics report) and ``post-checkpoint`` (upload the
 checkpoint directory) callbacks, Snowflake ML-job stage paths from ``MLRS_STAGE_MOUNT_PATH`` /

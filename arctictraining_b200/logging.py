@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Per-rank logging on top of loguru.
 
 Behaviour parity: arctic_training/logging.py:37-156 (rank-tagged format, optional per-rank file sink

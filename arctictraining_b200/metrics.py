@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Per-iteration metrics: loss, iteration / step time, tflops, sequence length, learning rate.
 
 Behaviour parity: arctic_training/metrics.py:35-201 — one value per key per iteration (writing a key

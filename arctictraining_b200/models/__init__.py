@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .arch import ArchConfig
 from .arch import load_arch_config
 from .causal_lm import CausalLM

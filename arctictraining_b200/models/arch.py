@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Architecture descriptions: built-in presets and ``config.json`` loading, without ``transformers``.
 
 A model is described by a plain dict with Hugging Face key names (``hidden_size``,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Native decoder-only language model (Llama / Qwen2 / Qwen3 / Qwen3-MoE families).
 
 The forward signature follows the Hugging Face causal-LM convention used by the trainers

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Model factories.  Parity: arctic_training/model/factory.py:36-97, hf_factory.py:25-89,
 liger_factory.py:24-69.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Token generation with a key/value cache for the native decoder models.
 
 Used where training needs samples from the model itself (the MLP speculator's generation modes).  The reference

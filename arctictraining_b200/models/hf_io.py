@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Hugging Face checkpoint layout: name mapping between the native fused parameters and HF tensors,
 and safetensors reading / sharded writing.
 

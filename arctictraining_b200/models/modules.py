@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Decoder building blocks shared by the native model families (Llama, Qwen2, Qwen3, Qwen3-MoE).
 
 Weights of projections that are consumed together are stored fused — ``qkv_proj`` (q, k, v rows stacked)

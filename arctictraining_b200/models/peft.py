@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Parameter-efficient fine-tuning: LoRA adapters on the native ``Linear`` modules, exported in the PEFT layout.
 
 The reference delegates to the ``peft`` package (arctic_training/config/model.py:62-82,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .convert import convert_to_arctic_moe
 from .convert import detect_if_moe_model
 from .layer import ArcticMoE

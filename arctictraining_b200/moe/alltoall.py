@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Variable-split all-to-all with autograd (NCCL / Gloo baseline path of the expert-parallel exchange).
 Parity: arctic_training/model/moe/alltoall.py:20-59."""
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Hugging Face <-> ArcticMoE parameter layouts, model conversion and expert checkpoint files.
 
 Behaviour parity: arctic_training/model/moe/utils.py:75-666.

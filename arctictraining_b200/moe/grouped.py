@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Grouped expert MLP over tile-aligned expert segments.
 
 ``x`` holds the tokens of all local experts, expert-major, every segment starting at a multiple of 128

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Grouped expert MLP on the tcgen05 grouped GEMM (``csrc/gemm_sm100.cu``, modes "ragged M" and "ragged K").
 
 The tile -> expert map is resolved on the device from the segment offsets, so neither the forward nor the

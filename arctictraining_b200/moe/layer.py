@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """ArcticMoE: a mixture-of-experts feed-forward block with expert parallelism.
 
 Behaviour parity: arctic_training/model/moe/moe.py:33-509 — softmax-then-top-k routing with optional

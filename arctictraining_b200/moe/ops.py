@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Differentiable MoE primitives: gating, deterministic slot assignment, scatter, gather.
 
 CUDA kernels (``csrc/moe.cu``) on the GPU, PyTorch reference on CPU.  All of them are deterministic: slots

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Expert-parallel token exchange over NVLink peer memory.
 
 The sender computes, from the all-gathered per-expert counts, the row that each of its (token, k) pairs occupies in

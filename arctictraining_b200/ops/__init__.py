@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from . import reference
 from .functional import IGNORE_INDEX
 from .functional import COMM_COUNTER

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Builds and loads the sm_100a CUDA extension that lives in ``arctictraining_b200/csrc``.
 
 The shared object is built *in the source tree* (``csrc/build/atb200_ops.so``) so that it travels with

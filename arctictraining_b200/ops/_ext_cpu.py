@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Builds and loads the host-side C++ extension (``csrc_cpu``: multi-threaded, vectorised AdamW for optimizer states kept
 in host memory).  Built in the source tree like the CUDA library; optional: without a compiler the PyTorch fallback is used.
 """

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Differentiable front ends of the fused ops.
 
 Each function has one signature and two implementations: the sm_100a kernel from ``csrc`` (used

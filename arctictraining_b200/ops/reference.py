@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Plain PyTorch implementations of every fused op.
 
 These are the oracle the CUDA kernels are tested against and the code path used on CPU (Gloo runs,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Sequence-tiled MLP: run a feed-forward block over tiles of the sequence so that the
 ``[tokens, intermediate]`` activations exist for one tile at a time; the backward pass recomputes each tile.
 

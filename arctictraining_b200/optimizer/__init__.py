@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .adam import CPUAdamMoEOptimizerFactory
 from .adam import CPUAdamOptimizerFactory
 from .adam import CPUAdamW

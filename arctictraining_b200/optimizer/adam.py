@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """AdamW optimizers and their factories.
 
 ``FusedAdamW`` runs this library's fused CUDA kernel (one launch per flat view: moment update, bias

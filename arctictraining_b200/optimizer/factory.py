@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Optimizer factory base class.  Parity: arctic_training/optimizer/factory.py:34-95."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Process groups for data / sequence / expert parallelism.
 
 Ranks are laid out as consecutive blocks: the ``sp`` ranks ``[k*sp, (k+1)*sp)`` form one sequence-parallel

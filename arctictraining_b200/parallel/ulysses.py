@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Ulysses sequence parallelism: every rank holds ``S / P`` tokens for everything except core attention,
 around which an all-to-all re-shards sequence -> heads (each rank then attends over the full sequence with
 ``Hq / P`` query heads) and back.

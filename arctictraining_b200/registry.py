@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Class registry: every concrete subclass of a framework base class registers itself by ``name``.
 
 Behaviour parity: arctic_training/registry.py:66-212 (auto-registration through a metaclass,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .factory import HFSchedulerConfig
 from .factory import HFSchedulerFactory
 from .factory import SchedulerFactory

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Scheduler factories.  Parity: arctic_training/scheduler/factory.py:34-94, hf_factory.py:26-46,
 wsd_factory.py:25-46 (the WSD factory keeps the reference's registered name ``wds``)."""
 

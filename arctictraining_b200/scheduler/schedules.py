@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Learning-rate schedules as ``LambdaLR`` multipliers (own implementations of the usual families)."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .modules import ArcticLSTMSpeculator
 from .modules import ArcticLSTMSpeculatorConfig
 from .modules import LayerNormParameterized

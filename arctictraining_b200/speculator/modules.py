@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Speculative-decoding draft heads trained on top of a frozen base model.
 
 Two families (behaviour parity: projects/mlp_speculator/mlp_speculator/speculator.py:29-300 and

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Trainers, model factories and checkpoint engines for speculative-decoding draft heads.
 
 Registered names match the reference projects: ``arctic-lstm-speculator``

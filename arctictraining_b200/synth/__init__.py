@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .base import BatchProcessor
 from .base import InMemoryBatchProcessor
 from .callers import CortexSynth

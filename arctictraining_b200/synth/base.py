@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Batch processors for synthetic-data generation: a task is a named list of chat requests that is executed as one
 batch and whose responses can be turned back into plain messages.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Snowflake Cortex and vLLM synthesizers.  Behaviour parity: arctic_training/synth/callers.py:62-133,
 vllm_callers.py:40-207, vllm_utils.py:26-152.  Heavy dependencies (snowflake connector, vllm, aiohttp) are imported
 when a client is created or used.

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """``arctic_synth`` command line: inspect, download or cancel batch tasks kept in a work directory.
 Parity: arctic_training/synth/cli.py:27-133."""
 

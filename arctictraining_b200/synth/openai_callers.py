@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """OpenAI / Azure OpenAI batch-API clients.  Behaviour parity: arctic_training/synth/openai_callers.py:43-428 — the
 save -> upload -> submit -> poll -> download life cycle of a batch task, kept in a work directory so that an
 interrupted run can be picked up again; credentials from a YAML file or the environment.  The ``openai`` package is

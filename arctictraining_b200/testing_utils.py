@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Helpers for writing tests against the framework.  Behaviour parity with the subset of
 arctic_training/testing_utils.py:67-1156 that the reference's own tests use: hardware requirement markers, unique
 rendezvous ports per pytest-xdist worker, temp-dir test case, stream capture, subprocess execution with live output,

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .factory import FakeTokenizerFactory
 from .factory import HFTokenizerFactory
 from .factory import TokenizerFactory

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Tokenizer factories.  Parity: arctic_training/tokenizer/factory.py:35-87, hf_factory.py:23-31; the
 ``fake`` factory corresponds to the test tokenizer of the embedding project
 (projects/arctic_embed/src/arctic_embed/trainer.py:67-71)."""

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """A dependency-free tokenizer for tests, benchmarks and synthetic data.
 
 Words are mapped to ids by a stable hash (so no vocabulary file is needed), special tokens occupy the

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 from .sft import CausalTrainer
 from .sft import SFTTrainer
 from .trainer import Trainer

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Direct Preference Optimisation trainer.
 
 Behaviour parity: arctic_training/trainer/dpo_trainer.py:50-271 — a policy model and a frozen reference

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Supervised fine-tuning and causal-LM trainers.
 
 Behaviour parity: arctic_training/trainer/sft_trainer.py:38-166 and causal_trainer.py:31-40.  The native

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Base trainer: owns the whole lifecycle of a run.
 
 Behaviour parity: arctic_training/trainer/trainer.py:68-771.  Construction order: seeds -> tokenizer ->

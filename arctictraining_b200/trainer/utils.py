@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Moves (nested) batches to a device.  Parity: arctic_training/trainer/utils.py:21-28."""
 
 from __future__ import annotations

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Accessors shared by all factory base classes (they all hold a reference to the trainer)."""
 
 from __future__ import annotations

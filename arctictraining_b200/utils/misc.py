@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """JSON-lines helpers and human-readable number formatting.  Parity: arctic_training/utils.py:22-90."""
 
 from __future__ import annotations

@@ -1,4 +1,5 @@
 #!/usr/bin/env python
+# SPDX-License-Identifier: Apache-2.0
 """Headline benchmark: Llama-3.1-8B supervised fine-tuning throughput (tokens/s) on N B200 GPUs.
 
 Config (the one the baseline names): Llama-3.1-8B architecture, random-init bf16 weights, ZeRO-3, AdamW with

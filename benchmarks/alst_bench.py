@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Long-sequence (ALST) SFT step time: one synthetic sequence of ``--seq-len`` tokens per step, Ulysses sequence
 parallelism over all ranks, tiled MLP, tiled fused cross-entropy, activation checkpointing (optionally with host
 offload), ZeRO-3 bf16.  Timed on the device (CUDA events, max over ranks) through the trainer's public ``step``.

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Times the package's sm_100a flash-attention forward and backward kernels against library kernels (flash-attn 2;
 cuDNN's fused backward for a single unpacked sequence) on packed causal GQA shapes (CUDA events, L2 flushed between
 iterations).  Backward FLOPs are counted as 2.5 x the forward's.

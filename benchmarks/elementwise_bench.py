@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Bandwidth of the memory-bound kernels (RMSNorm, RoPE, SwiGLU, AdamW, squared norm, cross-entropy) on inputs larger
 than L2, against the measured copy bandwidth.  CUDA events, median of `--iters`, a 256 MB L2 flush between iterations.
 

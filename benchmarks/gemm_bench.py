@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Micro-benchmark of the tcgen05 GEMM against cuBLAS (torch.matmul) on the shapes of a Llama-3.1-8B layer.
 
     python benchmarks/gemm_bench.py                 # all shapes, forward / dgrad / wgrad layouts

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Library-stack proxy for the headline benchmark (NOT the reference and none of this package's kernels or engine).
 
 What a user gets on this machine from stock libraries for the same job: Hugging Face ``LlamaForCausalLM`` built from a

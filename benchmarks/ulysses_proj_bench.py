@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Head -> sequence exchange + output projection: one tcgen05 GEMM launch in which a few CTAs gather the
 A operand from the peers' memory over NVLink while the others multiply the row tiles that have arrived (and the variant
 where every CTA pair fetches its A tiles from the owners with TMA) against the two-step version (exchange kernel, barrier,

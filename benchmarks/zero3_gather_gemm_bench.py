@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """ZeRO-3 parameter all-gather inside the first consuming GEMM: one tcgen05 launch in which a few staging CTAs copy the
 q|k|v weight from the ranks that own its pieces (contiguous shards of the layer's flat parameter buffer, peer memory)
 into this rank's full buffer, tile of 256 weight rows by tile, while the CTA pairs multiply the tiles that have

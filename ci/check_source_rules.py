@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Repository hygiene checks run by CI: every Python / CUDA source compiles or at least parses, no source names one of
 the driver API calls that are closed on the target hosts, no TMA / bulk load with cluster multicast, and recipes parse
 as YAML with unique keys.  Exits non-zero with one line per violation."""

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Hard-negative mining for contrastive training: embed queries and documents with a teacher model, retrieve the
 top-k documents per query by dense dot product, drop the positives and anything scoring above
 `max_negative_to_positive_ratio` x the positive's score (likely false negatives), keep the next `num_negatives`.

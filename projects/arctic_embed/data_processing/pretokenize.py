@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Turn (query, document, relevance) data into the pre-tokenised, pre-batched parquet layout that the biencoder
 trainer streams (`arctictraining_b200/embed/data.py`): one `batch_XXXXXXXX/` directory per global batch with
 `queries.parquet`, `documents.parquet` and `relations.parquet`.

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Run a pre-tokenise-and-batch job from a config file (JSON or YAML).
 
     python projects/arctic_embed/data_processing/run_pretokenize_job.py pairs job.yaml [--num-shards 8 --shard 3]

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Fine-tune a bi-encoder from Python instead of a YAML recipe: build the config dict, let `get_config` resolve it against
 the trainer class, construct the trainer and call `train()`.  Run under the launcher (one process per GPU):
 

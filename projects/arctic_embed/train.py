@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Arctic-Embed project: importing this file registers the ``biencoder`` trainer, model factory, checkpoint engine and
 the ``contrastive_pretokenized`` data factory (implementation: ``arctictraining_b200/embed``)."""
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Merge the per-shard outputs of `vllm_data_generation.py` into one dataset directory.
 
     python concat_generated_datasets.py --inputs gen/shard* --out gen/all

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Run a list of shell commands over the GPUs of one node, each command on its own group of GPUs, starting the next
 command as soon as a group becomes free.  Used to fan `vllm_data_generation.py` shards out over 8 GPUs.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Generate speculator training data: let the base model continue real prompts with vLLM and store prompt + continuation
 as pre-tokenised `input_ids` / `labels` (a Hugging Face dataset consumed with `process: false`, see
 projects/arctic_lstm_speculator/llama3.1-8b.yaml).  A speculator must imitate what the base model itself would write,

@@ -1,4 +1,5 @@
 #!/usr/bin/env bash
+# SPDX-License-Identifier: Apache-2.0
 # Data generation -> speculator training -> serving with speculative decoding, for one base model on one 8-GPU node.
 # Usage: bash datagen_train_serve.sh meta-llama/Llama-3.1-8B-Instruct
 set -euo pipefail

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Arctic LSTM speculator project: importing this file registers the ``arctic-lstm-speculator`` trainer, model factory
 and checkpoint engine (implementation: ``arctictraining_b200/speculator``)."""
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """BIRD evaluation for text-to-SQL models: sample n answers per question with vLLM, take the final SQL of each, vote by
 execution result (self-consistency) and report execution accuracy.  Training code for this project is not part of the
 reference either (projects/arctic_text2sql_r1/README.md:14); its bird_eval/ directory has the same three stages.

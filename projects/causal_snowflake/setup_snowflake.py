@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Creates the Snowflake objects the `run-causal-snowflake-*.yml` recipes read: a database / schema, a table with one
 TEXT column filled from a Hugging Face text dataset, and (optionally) a Snowflake Dataset version of that table.
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """ExCoT data pipeline: generate chain-of-thought answers, verify them by execution, sample SFT and DPO sets, evaluate.
 
     python -m excot.pipeline generate --questions dev.json --schemas schemas.json --out cand.jsonl --model <name> --n 8

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Prompt of the divide-and-conquer chain-of-thought text-to-SQL generation."""
 
 SYSTEM = "You are an expert data analyst who writes correct SQLite queries."

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Execution-based checking of generated SQL against SQLite databases (BIRD / Spider layout: one `<db_id>.sqlite` per
 database directory).  A query is run in a worker process with a time limit; results are compared as multisets of rows.
 Same role as projects/excot_dpo/utils/sql_exec.py in the reference."""

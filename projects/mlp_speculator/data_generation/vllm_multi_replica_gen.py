@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Generate base-model continuations with several `vllm serve` replicas (one per GPU group) and store them as a
 pre-tokenised Hugging Face dataset for speculator training.  Uses `MultiReplicaVllmSynth`, which starts the servers,
 waits until they answer, fans the requests out over them and stops them again.

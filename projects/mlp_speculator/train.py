@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """MLP speculator project: importing this file registers the ``spec-decode`` trainer, model factory and checkpoint
 engine (implementation: ``arctictraining_b200/speculator``)."""
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """MoBA project: the SwiftKV-free variant of the reference's trainer (projects/moba_attention/train.py:23-61) — an SFT
 trainer whose model factory swaps the attention core for Mixture-of-Block-Attention."""
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Evaluate a SwiftKV checkpoint with lm-evaluation-harness.  The harness builds models through
 `transformers.AutoModelForCausalLM`; a SwiftKV export is a plain checkpoint directory whose `config.json` carries the
 SwiftKV fields, so this wrapper loads it with this package's model class and hands the module to the harness.

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """SwiftKV self-distillation on the native decoder.
 
 Behaviour parity: projects/swiftkv/train.py:46-264 and projects/swiftkv/models/llama/modeling_llama_swiftkv.py:

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Worker run by the multi-process CPU tests (Gloo, world size 2..4).  Usage:
 ``python tests/dist_worker.py <scenario> <out_dir>`` under the framework's launcher."""
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Worker for the multi-GPU tests (NCCL, one process per GPU).  ``python tests/gpu_worker.py <scenario> <out_dir>``."""
 
 import json

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 import pytest
 
 from arctictraining_b200.callback.mixin import CallbackMixin

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Data-movement kernels of csrc/comm_p2p.cu on ONE GPU: the "peers" are separate local buffers, every
 emulated rank is launched in turn (none of these kernels waits on another rank)."""
 

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Data layer: SFT tokenisation and masking, packing, padding, causal slicing, DPO pairs, caches, sources."""
 
 from types import SimpleNamespace

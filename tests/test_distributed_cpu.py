@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Multi-process tests on CPU (Gloo): ZeRO sharding, resume, launcher supervision, trainer equivalence
 across parallel layouts.  Pattern of the reference's multi-GPU tests (tests/trainer/test_ulysses_alst.py):
 same data, two layouts, compare the losses."""

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Offline data preparation of the embedding project: parquet collections, sharded pre-tokenisation jobs that write
 what the training loader reads, dense retrieval."""
 

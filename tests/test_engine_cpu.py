@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Engine correctness on CPU: the flat-buffer engine must reproduce plain PyTorch training, and the ZeRO
 stages / checkpointing / accumulation variants must agree with each other."""
 

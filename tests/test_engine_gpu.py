@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Single-GPU engine tests: bf16 model on the CUDA kernels against the same model in fp32 on the CPU, and the
 engine's memory/speed options (direct bf16 gradients, layers that keep activations, native attention) against
 each other."""

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Launchers and data sources that talk to external services, exercised against fakes (no Ray, no Snowflake installed).
 
 Pattern of the reference's mocked Snowflake tests (tests/data/test_snowflake_source.py:28-372): configuration rules,

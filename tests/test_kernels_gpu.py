@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Numerics of every CUDA kernel against a plain PyTorch fp32 reference of the same op."""
 
 import math

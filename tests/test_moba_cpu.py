@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 import torch
 
 from arctictraining_b200.attention.moba import moba_attn_naive

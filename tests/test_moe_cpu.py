@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """ArcticMoE on CPU: routing semantics, permutation round trip, equivalence with a naive per-token MoE,
 HF name conversion and a tiny MoE training run."""
 

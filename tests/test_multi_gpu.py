@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Multi-GPU tests (child processes, one per GPU, NCCL + peer memory); skipped when fewer than 2 GPUs are visible."""
 
 import json

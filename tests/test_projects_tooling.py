@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Pure-Python project tooling: SQL extraction / execution-based verification and the SFT / DPO sampling of ExCoT."""
 
 import sqlite3
@@ -81,3 +82,34 @@ def test_embed_pretokenize_writes_the_layout_the_loader_reads(tmp_path):
     dense = b.relevance_labels.to_dense()
     assert (dense > 0).sum(1).min() >= 1  # every query has its positive
     assert (dense < 0).any()              # mined negatives are marked
+
+
+def test_ci_helpers_resolve_extras_upgrade_user_code_and_check_licences(tmp_path):
+    sys.path.insert(0, str(ROOT / "ci"))
+    import check_license
+    import install_extras
+    import prefetch_assets
+    import upgrade_user_code
+
+    groups = {"__name__": ["arctictraining-b200"], "dev": ["pytest", "arctictraining_b200[embed, dev]"], "embed": ["pyarrow"]}
+    assert install_extras.resolve(["dev"], groups) == ["pyarrow", "pytest"]
+    assert "dev" in install_extras.load_groups()
+    assert install_extras.main(["dev", "--dry-run"]) == 0
+
+    old = '"""doc."""\nfrom x import A, B\n\nclass T(Trainer):\n    config_type = MyConfig  # keep\n    data_factory_type = [A, B]\n    model_factory_type = [A]\n'
+    new, n = upgrade_user_code.upgrade_source(old)
+    assert n == 3 and "    config: MyConfig  # keep" in new and "    data_factory: Union[A, B]" in new and "    model_factory: A\n" in new
+    assert new.startswith('"""doc."""\nfrom typing import Union')
+    assert upgrade_user_code.upgrade_source(new)[1] == 0  # idempotent
+
+    f = tmp_path / "m.py"
+    f.write_text("#!/usr/bin/env python\nimport os\n")
+    assert not check_license.has_identifier(f)
+    check_license.insert_identifier(f)
+    assert f.read_text().split("\n")[1] == "# " + check_license.SPDX and check_license.has_identifier(f)
+    assert check_license.main([]) == 0  # the repository itself is clean
+
+    cfg = {"data": {"sources": ["org/ds", {"name_or_path": "org/other", "split": "train[:10]", "kwargs": {"name": "x"}}]},
+           "model": {"name_or_path": "org/model"}, "tokenizer": {"name_or_path": "org/model"}}
+    assert list(prefetch_assets.iter_sources(cfg)) == [("org/ds", None, {}), ("org/other", "train[:10]", {"name": "x"})]
+    assert prefetch_assets.model_ids(cfg) == ["org/model"]

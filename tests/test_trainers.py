@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Trainer smoke tests and checkpoint round trips on CPU (pattern of the reference's tests/trainer and
 tests/checkpoint: a few iterations on a tiny random model; rebuild and compare weights bit for bit)."""
 

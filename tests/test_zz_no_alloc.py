@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """The allocation-free RMSNorm backward (`atb_rmsnorm_bwd_noalloc`, an exported C symbol) must agree with the
 tensor-based operator.
 
