@@ -56,10 +56,47 @@ class FlopsCounter:
         attn_linear = hidden * (heads * head_dim + 2 * kv_heads * head_dim + heads * head_dim)
         full_every = _get(c, "full_attention_interval", 1)
         full_layers = layers // full_every
-        dense_n = (mlp + attn_linear) * layers + vocab * hidden
+        linear_layers = layers - full_layers
+        dense_n = mlp * layers + attn_linear * full_layers + self._gated_delta_net_weights() * linear_layers + vocab * hidden
         dense_flops = dense_m * dense_n * tokens
         attn_flops = attn_m * sum(s * s for s in seqlens) * head_dim * heads * full_layers
         return (dense_flops + attn_flops) / 1e12
+
+    def _gated_delta_net_weights(self) -> int:
+        """Per-token multiply-accumulates of one linear-attention (gated delta rule) layer, the hybrid layers of
+        Qwen3-Next: input projections, short convolution, the four ``d_v x d_v`` state products per value head, output
+        projection.  Zero for models without such layers."""
+        c = self.config
+        kd, vd = _get(c, "linear_key_head_dim", 0), _get(c, "linear_value_head_dim", 0)
+        if not kd:
+            return 0
+        kh, vh = _get(c, "linear_num_key_heads"), _get(c, "linear_num_value_heads")
+        hidden, conv = _get(c, "hidden_size"), _get(c, "linear_conv_kernel_dim", 4)
+        qk, v = kd * kh, vd * vh
+        return hidden * (2 * qk + 2 * v + 2 * vh) + conv * (2 * qk + v) + vh * vd * vd * 4 + hidden * v
+
+    def _mla_moe(self, seqlens: Sequence[int], forward_only: bool) -> float:
+        """DeepSeek-V2 / V3: multi-head latent attention (low-rank query and joint key/value projections, a shared
+        rotary key) and routed + shared experts after ``first_k_dense_replace`` dense layers."""
+        c = self.config
+        hidden, vocab, layers = _get(c, "hidden_size"), _get(c, "vocab_size"), _get(c, "num_hidden_layers")
+        heads = _get(c, "num_attention_heads")
+        nope, rope, v_dim = _get(c, "qk_nope_head_dim"), _get(c, "qk_rope_head_dim"), _get(c, "v_head_dim")
+        q_rank, kv_rank = _get(c, "q_lora_rank", 0), _get(c, "kv_lora_rank")
+        q_dim = nope + rope
+        attn = hidden * heads * q_dim if not q_rank else hidden * q_rank + q_rank * heads * q_dim
+        attn += hidden * (kv_rank + rope)             # down-projection to the latent + the shared rotary key
+        attn += heads * (nope + v_dim) * kv_rank      # up-projection of keys (non-rotary part) and values
+        attn += heads * v_dim * hidden                # output projection
+        routed = _get(c, "n_routed_experts", 0)
+        dense_first = _get(c, "first_k_dense_replace", 0) if routed else layers
+        moe_layer = hidden * routed + hidden * _get(c, "moe_intermediate_size", 0) * 3 * (
+            _get(c, "num_experts_per_tok", 0) + _get(c, "n_shared_experts", 0))
+        dense_layer = hidden * _get(c, "intermediate_size") * 3
+        n = (moe_layer + attn) * (layers - dense_first) + (dense_layer + attn) * dense_first + vocab * hidden
+        dense_m, attn_m = self._mults(forward_only)
+        flops = dense_m * n * sum(seqlens) + attn_m * sum(s * s for s in seqlens) * layers * q_dim * heads
+        return flops / 1e12
 
     def _generic(self, seqlens: Sequence[int], forward_only: bool) -> float:
         c = self.config
@@ -72,6 +109,8 @@ class FlopsCounter:
 
     def estimate_tflos(self, batch_seqlens: Sequence[int], delta_time: float = 1, forward_only: bool = False) -> float:
         c = self.config
+        if _get(c, "kv_lora_rank") and _get(c, "qk_rope_head_dim"):
+            return self._mla_moe(batch_seqlens, forward_only)
         if _get(c, "num_attention_heads") and _get(c, "intermediate_size", _get(c, "moe_intermediate_size")):
             return self._decoder(batch_seqlens, forward_only)
         return self._generic(batch_seqlens, forward_only)
