@@ -36,7 +36,7 @@ class ArchConfig(dict):
 
     @property
     def is_moe(self) -> bool:
-        return bool(self.get("num_experts") or self.get("num_local_experts"))
+        return bool(self.get("num_experts") or self.get("num_local_experts") or self.get("n_routed_experts"))
 
     def to_json_dict(self) -> Dict[str, Any]:
         return {k: v for k, v in self.items() if not k.startswith("_")}
@@ -119,6 +119,8 @@ def load_arch_config(
 ) -> ArchConfig:
     """Resolve a preset name or a model directory into an :class:`ArchConfig` and apply overrides."""
     key = str(name_or_path)
+    if key.lower().startswith(("deepseek", "tiny-deepseek")):
+        from . import deepseek  # noqa: F401  (registers the DeepSeek presets and converters)
     if key.lower() in PRESETS:
         cfg = ArchConfig(json.loads(json.dumps(PRESETS[key.lower()])))
         cfg["_source"] = "preset"
@@ -141,4 +143,8 @@ def load_arch_config(
         cfg[k] = v
     if cfg.get("rope_theta") is None and isinstance(cfg.get("rope_parameters"), dict):
         cfg["rope_theta"] = cfg["rope_parameters"].get("rope_theta", 10000.0)
+        if cfg.get("rope_scaling") is None and cfg["rope_parameters"].get("rope_type", "default") != "default":
+            cfg["rope_scaling"] = {k: v for k, v in cfg["rope_parameters"].items() if k != "rope_theta"}
+    if cfg.get("model_type") == "deepseek_v2":
+        from . import deepseek  # noqa: F401,F811
     return cfg

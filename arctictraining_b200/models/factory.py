@@ -3,7 +3,7 @@
 liger_factory.py:24-69.
 
 ``huggingface`` builds this framework's native decoder for the supported families (Llama, Qwen2, Qwen3,
-Qwen3-MoE) — weights come from an HF-layout directory, or are random when the recipe names a built-in
+Qwen3-MoE, DeepSeek-V2) — weights come from an HF-layout directory, or are random when the recipe names a built-in
 preset or overrides ``num_hidden_layers`` — and falls back to ``transformers.AutoModelForCausalLM`` for
 other architectures.  ``liger`` is kept as a recipe-compatible alias: the fused kernels it stands for
 (RMSNorm, RoPE, SwiGLU, fused linear cross-entropy) are always on in the native model.
@@ -34,7 +34,7 @@ from .arch import load_arch_config
 if TYPE_CHECKING:
     from ..trainer.trainer import Trainer
 
-NATIVE_MODEL_TYPES = ("llama", "qwen2", "qwen3", "qwen3_moe", "mistral")
+NATIVE_MODEL_TYPES = ("llama", "qwen2", "qwen3", "qwen3_moe", "mistral", "deepseek_v2")
 
 
 class ModelFactory(ABC, CallbackMixin, metaclass=RegistryMeta):
@@ -100,9 +100,13 @@ class HFModelFactory(ModelFactory):
         )
         return cfg
 
-    def _native_class(self):
+    def _native_class(self, model_config=None):
         from .causal_lm import CausalLM
 
+        if self.model_cls is None and model_config is not None and model_config.get("model_type") == "deepseek_v2":
+            from .deepseek import DeepseekV2ForCausalLM
+
+            return DeepseekV2ForCausalLM
         return self.model_cls or CausalLM
 
     def create_model(self, model_config) -> torch.nn.Module:
@@ -116,7 +120,7 @@ class HFModelFactory(ModelFactory):
         use_ep = groups is not None and groups.ep_size > 1 and getattr(self.trainer.config, "arctic_moe", False) not in (False, None)
         layout = expert_parallel_layout(groups.ep_size, groups.ep_rank, groups.ep_group) if use_ep else expert_parallel_layout(1, 0, None)
         with torch.device(device), layout:
-            model = self._native_class()(model_config, dtype=dtype)
+            model = self._native_class(model_config)(model_config, dtype=dtype)
         model.attn_impl = self.config.attn_implementation
         if self.using_random_model:
             model.init_weights(seed=getattr(self.trainer.config, "seed", 42) if self.trainer is not None else 42)

@@ -39,7 +39,7 @@ _EXPERT_RE = re.compile(r"^(.*mlp\.)experts\.(\d+)\.(gate_proj|up_proj|down_proj
 def detect_if_moe_model(model: nn.Module) -> bool:
     cfg = getattr(model, "config", {})
     get = cfg.get if isinstance(cfg, dict) else (lambda k, d=None: getattr(cfg, k, d))
-    return bool(get("num_experts") or get("num_local_experts"))
+    return bool(get("num_experts") or get("num_local_experts") or get("n_routed_experts"))
 
 
 # ------------------------------------------------------------------ state-dict converters (registered in hf_io)
@@ -77,12 +77,13 @@ def _native_to_hf(name: str, tensor: torch.Tensor, cfg: ArchConfig):
         pre = name[: -len("expert_down")]
         first = getattr(tensor, "_first_expert", 0)
         return [(f"{pre}experts.{first + i}.down_proj.weight", tensor[i]) for i in range(tensor.shape[0])]
+    shared = "shared_experts" if cfg.get("n_routed_experts") else "shared_expert"  # DeepSeek uses the plural
     if name.endswith("mlp.shared_expert_gate_up"):
         pre = name[: -len("shared_expert_gate_up")]
         g, u = ref.deinterleave_gate_up_rows(tensor)
-        return [(f"{pre}shared_expert.gate_proj.weight", g), (f"{pre}shared_expert.up_proj.weight", u)]
+        return [(f"{pre}{shared}.gate_proj.weight", g), (f"{pre}{shared}.up_proj.weight", u)]
     if name.endswith("mlp.shared_expert_down"):
-        return [(name[: -len("shared_expert_down")] + "shared_expert.down_proj.weight", tensor)]
+        return [(name[: -len("shared_expert_down")] + f"{shared}.down_proj.weight", tensor)]
     if name.endswith("mlp.shared_expert_output_gate"):
         return [(name[: -len("shared_expert_output_gate")] + "shared_expert_gate.weight", tensor)]
     return None
@@ -124,12 +125,11 @@ def _hf_to_native(hf: Dict[str, torch.Tensor], out: Dict[str, torch.Tensor], cfg
             out[name[: -len("gate.weight")] + "router_gate"] = hf.pop(name)
         elif name.endswith("mlp.shared_expert_gate.weight"):
             out[name[: -len("shared_expert_gate.weight")] + "shared_expert_output_gate"] = hf.pop(name)
-        elif name.endswith("mlp.shared_expert.down_proj.weight"):
-            out[name[: -len("shared_expert.down_proj.weight")] + "shared_expert_down"] = hf.pop(name)
-        elif name.endswith("mlp.shared_expert.gate_proj.weight"):
-            pre = name[: -len("shared_expert.gate_proj.weight")]
-            up = hf.pop(f"{pre}shared_expert.up_proj.weight")
-            out[f"{pre}shared_expert_gate_up"] = ref.interleave_gate_up_rows(hf.pop(name), up)
+        elif name.endswith(("mlp.shared_expert.down_proj.weight", "mlp.shared_experts.down_proj.weight")):
+            out[name.rsplit("shared_expert", 1)[0] + "shared_expert_down"] = hf.pop(name)
+        elif name.endswith(("mlp.shared_expert.gate_proj.weight", "mlp.shared_experts.gate_proj.weight")):
+            up = hf.pop(name.replace("gate_proj.weight", "up_proj.weight"))
+            out[name.rsplit("shared_expert", 1)[0] + "shared_expert_gate_up"] = ref.interleave_gate_up_rows(hf.pop(name), up)
 
 
 if _native_to_hf not in hf_io._EXTRA_NATIVE_TO_HF:

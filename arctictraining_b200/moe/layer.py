@@ -68,6 +68,14 @@ class MoEConfig:
     is_gated: bool = True
     use_shared_expert: bool = False
     shared_intermediate_dim: int = 0
+    shared_expert_gated: bool = True
+    """ Qwen2-MoE multiplies the shared expert by a sigmoid gate of the token; DeepSeek adds it as it is. """
+    routed_scaling_factor: float = 1.0
+    """ Factor on the routed experts' scores (DeepSeek). """
+    n_group: int = 1
+    topk_group: int = 1
+    """ Group-limited routing (DeepSeek): the experts form ``n_group`` groups, a token may only use experts of its
+    ``topk_group`` best groups (a group's score is its best expert's probability). """
     ep_size: int = 1
     ep_rank: int = 0
     ep_group: Any = None
@@ -97,7 +105,8 @@ class ArcticMoE(nn.Module):
             Is = c.shared_intermediate_dim or I
             self.shared_expert_gate_up = nn.Parameter(torch.empty(2 * Is, H, dtype=dtype, device=device))
             self.shared_expert_down = nn.Parameter(torch.empty(H, Is, dtype=dtype, device=device))
-            self.shared_expert_output_gate = nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+            if c.shared_expert_gated:
+                self.shared_expert_output_gate = nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
         self.replay_assignments: Optional[torch.Tensor] = None
         self.recorded_assignments: Optional[torch.Tensor] = None
         self.last_expert_counts: Optional[torch.Tensor] = None
@@ -125,10 +134,35 @@ class ArcticMoE(nn.Module):
             coeff = 0.0
             if self.training and c.loss_coeff > 0 and torch.is_grad_enabled():
                 coeff = c.loss_coeff / T / self.ep_size
-            scores, experts, probs = mops.topk_gating(logits, self.top_k, c.normalize_topk_scores, None, coeff)
+            if c.n_group > 1 and c.topk_group < c.n_group:
+                scores, experts = self._route_group_limited(logits, coeff)
+            else:
+                scores, experts, probs = mops.topk_gating(logits, self.top_k, c.normalize_topk_scores, None, coeff)
+        if c.routed_scaling_factor != 1.0:
+            scores = scores * c.routed_scaling_factor
         if c.enable_routing_replay:
             self.recorded_assignments = experts.detach()
         return scores, experts
+
+    def _route_group_limited(self, logits: torch.Tensor, lb_coeff: float):
+        """Softmax over all experts, keep the ``topk_group`` groups whose best expert scores highest, top-k among the
+        experts of those groups.  Scores stay the full-softmax probabilities (no renormalisation over the groups)."""
+        c = self._config
+        T, E = logits.shape
+        probs = torch.softmax(logits, dim=-1)
+        group_best = probs.detach().view(T, c.n_group, E // c.n_group).max(-1).values
+        keep = torch.zeros_like(group_best, dtype=torch.bool).scatter_(
+            1, torch.topk(group_best, c.topk_group, dim=-1, sorted=False).indices, True)
+        allowed = keep.unsqueeze(-1).expand(T, c.n_group, E // c.n_group).reshape(T, E)
+        masked = probs.detach().masked_fill(~allowed, 0.0)
+        experts = torch.sort(masked, dim=-1, descending=True, stable=True).indices[:, : self.top_k]
+        if lb_coeff and probs.requires_grad:
+            lb = mops._load_balance_grad(experts, E, lb_coeff)
+            probs.register_hook(lambda g: g + lb.unsqueeze(0))
+        scores = torch.gather(probs, 1, experts)
+        if c.normalize_topk_scores:
+            scores = scores / scores.sum(-1, keepdim=True)
+        return scores, experts.to(torch.int32)
 
     # ------------------------------------------------------------------ forward
     def forward(self, hidden_states: torch.Tensor, *_: Any) -> torch.Tensor:
@@ -148,8 +182,9 @@ class ArcticMoE(nn.Module):
         self.last_expert_counts = None
         if self._config.use_shared_expert:
             sh = F.linear(ops.swiglu_interleaved(F.linear(x, self.shared_expert_gate_up)), self.shared_expert_down)
-            gate = torch.sigmoid(F.linear(x, self.shared_expert_output_gate))
-            out = out + gate * sh
+            if self._config.shared_expert_gated:
+                sh = torch.sigmoid(F.linear(x, self.shared_expert_output_gate)) * sh
+            out = out + sh
         return out.view(shp)
 
     def _forward_ep(self, x: torch.Tensor, scores: torch.Tensor, experts: torch.Tensor) -> torch.Tensor:
@@ -200,6 +235,21 @@ def build_moe_block(cfg: ArchConfig, dtype=None, device=None, ep_size: Optional[
     arguments the expert-parallel layout is the one of the enclosing :class:`expert_parallel_layout` block."""
     if ep_size is None:
         ep_size, ep_rank, ep_group = _BUILD_LAYOUT["ep_size"], _BUILD_LAYOUT["ep_rank"], _BUILD_LAYOUT["ep_group"]
+    if cfg.get("n_routed_experts"):  # DeepSeek naming
+        moe_i = int(cfg["moe_intermediate_size"])
+        group_limited = cfg.get("topk_method") == "group_limited_greedy" and (cfg.get("n_group") or 1) > 1
+        mc = MoEConfig(
+            model_dim=cfg["hidden_size"], intermediate_dim=moe_i, num_experts=int(cfg["n_routed_experts"]),
+            top_k=int(cfg.get("num_experts_per_tok") or 1), normalize_topk_scores=bool(cfg.get("norm_topk_prob", False)),
+            loss_coeff=float(cfg.get("aux_loss_alpha", 0.001) or 0.0),
+            use_shared_expert=bool(cfg.get("n_shared_experts")), shared_expert_gated=False,
+            shared_intermediate_dim=moe_i * int(cfg.get("n_shared_experts") or 0),
+            routed_scaling_factor=float(cfg.get("routed_scaling_factor", 1.0) or 1.0),
+            n_group=int(cfg.get("n_group") or 1) if group_limited else 1,
+            topk_group=int(cfg.get("topk_group") or 1) if group_limited else 1,
+            ep_size=ep_size, ep_rank=ep_rank, ep_group=ep_group, input_dtype=dtype or torch.bfloat16,
+        )
+        return ArcticMoE(mc, dtype=dtype, device=device)
     mc = MoEConfig(
         model_dim=cfg["hidden_size"],
         intermediate_dim=cfg.get("moe_intermediate_size") or cfg["intermediate_size"],

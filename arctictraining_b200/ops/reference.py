@@ -38,8 +38,42 @@ def rope_cos_sin(
         mid = (1 - smooth) * inv_freq / factor + smooth * inv_freq
         is_mid = (wavelen <= old_len / low) & (wavelen >= old_len / high)
         inv_freq = torch.where(is_mid, mid, scaled)
+    amplitude = 1.0
+    if scaling and scaling.get("rope_type", scaling.get("type")) == "yarn":
+        inv_freq, amplitude = _yarn_inv_freq(inv_freq, head_dim, theta, scaling)
     ang = position_ids.float().unsqueeze(-1) * inv_freq
+    if amplitude != 1.0:
+        return ang.cos() * amplitude, ang.sin() * amplitude
     return ang.cos(), ang.sin()
+
+
+def yarn_mscale(factor: float, mscale: float = 1.0) -> float:
+    return 1.0 if factor <= 1 else 0.1 * mscale * math.log(factor) + 1.0
+
+
+def _yarn_inv_freq(inv_freq: torch.Tensor, dim: int, theta: float, scaling: dict):
+    """YaRN: frequencies whose wavelength fits ``beta_fast`` times into the original context keep their value, those
+    fitting fewer than ``beta_slow`` times are divided by ``factor``, a linear ramp in between; cos/sin are scaled by
+    ``mscale(factor, mscale) / mscale(factor, mscale_all_dim)``."""
+    factor = float(scaling["factor"])
+    orig = float(scaling.get("original_max_position_embeddings") or 4096)
+    fast, slow = float(scaling.get("beta_fast") or 32), float(scaling.get("beta_slow") or 1)
+
+    def correction_dim(rotations: float) -> float:
+        return dim * math.log(orig / (rotations * 2 * math.pi)) / (2 * math.log(theta))
+
+    low = max(math.floor(correction_dim(fast)), 0)
+    high = min(math.ceil(correction_dim(slow)), dim - 1)
+    if low == high:
+        high += 0.001
+    ramp = ((torch.arange(dim // 2, dtype=torch.float32, device=inv_freq.device) - low) / (high - low)).clamp(0, 1)
+    keep = 1.0 - ramp
+    blended = inv_freq / factor * (1 - keep) + inv_freq * keep
+    m, m_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+    amplitude = yarn_mscale(factor, m) / yarn_mscale(factor, m_all) if (m and m_all) else yarn_mscale(factor)
+    if scaling.get("attention_factor") is not None:
+        amplitude = float(scaling["attention_factor"])
+    return blended, float(amplitude)
 
 
 def rope_apply(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, inverse: bool = False) -> torch.Tensor:

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Every tracked source file must carry the project's licence identifier in its first lines.
 
     python ci/check_license.py            # exit 1 and list the files that lack it

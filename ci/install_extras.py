@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Install optional dependency groups declared in ``pyproject.toml`` without installing the package itself.
 
     python ci/install_extras.py dev embed [--dry-run] [--pip-args="--no-index --find-links /wheels"]

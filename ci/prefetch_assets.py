@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Fetch what a recipe needs from the Hugging Face hub ahead of a run (CI caches, air-gapped clusters).
 
     python ci/prefetch_assets.py -c recipe.yaml -d data  [-t /scratch/tmp]

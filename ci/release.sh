@@ -1,4 +1,5 @@
 #!/usr/bin/env bash
+# SPDX-License-Identifier: Apache-2.0
 # Build the wheel (CUDA extension compiled for sm_100a in-tree first) and upload it to the package index.
 #   ci/release.sh            build + upload (needs ~/.pypirc)
 #   ci/release.sh --no-upload   build only

@@ -1,3 +1,4 @@
+# SPDX-License-Identifier: Apache-2.0
 """Rewrite user trainer / factory code written against the old class-attribute style to annotations.
 
     python ci/upgrade_user_code.py my_trainer.py [more.py ...] [--check]

@@ -2,6 +2,7 @@
 """SwiftKV self-distillation on the native decoder.
 
 Behaviour parity: projects/swiftkv/train.py:46-264 and projects/swiftkv/models/llama/modeling_llama_swiftkv.py:
+(Llama / Qwen2 / Mistral families; the DeepSeek-V2 variant with latent attention is further down)
 layers ``>= num_key_value_layers`` get an extra query projection (``q_proj_swiftkv``), every
 ``key_value_group_size``-th of them extra key/value projections (``k_proj_swiftkv`` / ``v_proj_swiftkv``); at layer
 ``num_key_value_layers`` the hidden state is normalised by ``norm_swiftkv`` and the keys/values of *all* later
@@ -37,6 +38,12 @@ from arctictraining_b200.config.trainer import TrainerConfig
 from arctictraining_b200.models import hf_io
 from arctictraining_b200.models.causal_lm import CausalLM
 from arctictraining_b200.models.causal_lm import DecoderModel
+from arctictraining_b200.models.deepseek import DeepseekDecoderLayer
+from arctictraining_b200.models.deepseek import DeepseekDecoderModel
+from arctictraining_b200.models.deepseek import MLAKeyValue
+from arctictraining_b200.models.deepseek import MLAQuery
+from arctictraining_b200.models.deepseek import MLAttention
+from arctictraining_b200.models.deepseek import permute_rotary_rows
 from arctictraining_b200.models.factory import HFModelFactory
 from arctictraining_b200.models.modules import Attention
 from arctictraining_b200.models.modules import DecoderLayer
@@ -113,9 +120,11 @@ class SwiftKVProjector(nn.Module):
 
 
 class SwiftKVDecoderModel(DecoderModel):
+    projector_cls = SwiftKVProjector
+
     def __init__(self, cfg, dtype=None, device=None) -> None:
         super().__init__(cfg, dtype=dtype, device=device)
-        self.swiftkv_kv = SwiftKVProjector(cfg, dtype=dtype, device=device)
+        self.swiftkv_kv = self.projector_cls(cfg, dtype=dtype, device=device)
         self.swiftkv_enabled = False
 
     def build_layer(self, cfg, idx: int, dtype, device) -> nn.Module:
@@ -150,6 +159,61 @@ class SwiftKVDecoderModel(DecoderModel):
         return (h, collect) if output_hidden_states else h
 
 
+# ------------------------------------------------------------------------------------------------ DeepSeek-V2 (MLA)
+class MLASwiftKVAttention(MLAttention):
+    """Parity: projects/swiftkv/models/deepseek_v2/modeling_deepseek_swiftkv.py:55-188 — SwiftKV layers get a second
+    query branch (``q_proj_swiftkv`` or ``q_a_proj_swiftkv / q_a_layernorm_swiftkv / q_b_proj_swiftkv``)."""
+
+    def __init__(self, cfg, layer_idx: int, dtype=None, device=None) -> None:
+        super().__init__(cfg, layer_idx, dtype=dtype, device=device)
+        nkv = cfg.get("num_key_value_layers") or cfg["num_hidden_layers"]
+        self.is_swiftkv_layer = layer_idx >= nkv
+        if self.is_swiftkv_layer:
+            self.q_swiftkv = MLAQuery(cfg, dtype=dtype, device=device)
+
+    def forward(self, x, ctx: ForwardContext, residual=None, k_shared=None, v_shared=None):
+        if k_shared is None:
+            return super().forward(x, ctx, residual)
+        return super().forward(x, ctx, residual, shared_kv=(k_shared, v_shared), query=self.q_swiftkv)
+
+
+class MLASwiftKVDecoderLayer(DeepseekDecoderLayer):
+    attention_cls = MLASwiftKVAttention
+
+    def forward(self, x, ctx: ForwardContext, k_shared=None, v_shared=None):
+        return super().forward(x, ctx, k_shared=k_shared, v_shared=v_shared)
+
+
+class MLASwiftKVProjector(nn.Module):
+    """``norm_swiftkv`` and one latent key/value branch (``kv_a_proj_with_mqa_swiftkv``, ``kv_a_layernorm_swiftkv``,
+    ``kv_b_proj_swiftkv``) per KV group, applied to the hidden state that enters layer ``num_key_value_layers``."""
+
+    def __init__(self, cfg, dtype=None, device=None) -> None:
+        super().__init__()
+        self.nkv = cfg.get("num_key_value_layers") or cfg["num_hidden_layers"]
+        self.group = max(1, int(cfg.get("key_value_group_size", 1)))
+        self.owner_layers = list(range(self.nkv, cfg["num_hidden_layers"], self.group))
+        self.norm_swiftkv = RMSNorm(cfg["hidden_size"], cfg["rms_norm_eps"], dtype=dtype, device=device)
+        self.kv_proj = nn.ModuleList([MLAKeyValue(cfg, dtype=dtype, device=device) for _ in self.owner_layers])
+
+    def forward(self, hidden: torch.Tensor, ctx: ForwardContext) -> Dict[int, Any]:
+        h = self.norm_swiftkv(hidden)
+        out: Dict[int, Any] = {}
+        for branch, first in zip(self.kv_proj, self.owner_layers):
+            kv = branch(h, ctx)
+            for layer_idx in range(first, first + self.group):
+                out[layer_idx] = kv
+        return out
+
+
+class MLASwiftKVDecoderModel(SwiftKVDecoderModel):
+    projector_cls = MLASwiftKVProjector
+    make_context = DeepseekDecoderModel.make_context
+
+    def build_layer(self, cfg, idx: int, dtype, device) -> nn.Module:
+        return MLASwiftKVDecoderLayer(cfg, idx, dtype=dtype, device=device)
+
+
 class SwiftKVForCausalLM(CausalLM):
     decoder_cls = SwiftKVDecoderModel
 
@@ -162,8 +226,62 @@ class SwiftKVForCausalLM(CausalLM):
         return units
 
 
+class MLASwiftKVForCausalLM(SwiftKVForCausalLM):
+    decoder_cls = MLASwiftKVDecoderModel
+
+
 # -- HF names: model.layers.N.self_attn.{k,v}_proj_swiftkv.weight <-> model.swiftkv_kv.kv_proj.<g>.weight -------------
+_MLA_Q = ("q_proj", "q_a_proj", "q_a_layernorm", "q_b_proj")
+_MLA_KV = ("kv_a_proj_with_mqa", "kv_a_layernorm", "kv_b_proj")
+
+
+def _mla_native_to_hf(name: str, tensor: torch.Tensor, cfg):
+    """``self_attn.q_swiftkv.<m>`` -> ``self_attn.<m>_swiftkv``; ``swiftkv_kv.kv_proj.<g>.<m>`` ->
+    ``layers.<first layer of group g>.self_attn.<m>_swiftkv``; rotary rows back to the interleaved order."""
+    if ".self_attn.q_swiftkv." in name:
+        pre, rest = name.split("q_swiftkv.")
+        mod, kind = rest.rsplit(".", 1)
+        if mod in ("q_proj", "q_b_proj"):
+            tensor = permute_rotary_rows(tensor, cfg, "q", inverse=True)
+        return [(f"{pre}{mod}_swiftkv.{kind}", tensor)]
+    if ".swiftkv_kv.kv_proj." in name:
+        g, mod, kind = name.split(".swiftkv_kv.kv_proj.")[1].split(".")
+        nkv = cfg.get("num_key_value_layers") or cfg["num_hidden_layers"]
+        layer = nkv + int(g) * max(1, int(cfg.get("key_value_group_size", 1)))
+        if mod == "kv_a_proj_with_mqa":
+            tensor = permute_rotary_rows(tensor, cfg, "kv_a", inverse=True)
+        return [(f"model.layers.{layer}.self_attn.{mod}_swiftkv.{kind}", tensor)]
+    if name == "model.swiftkv_kv.norm_swiftkv.weight":
+        return [("model.norm_swiftkv.weight", tensor)]
+    return None
+
+
+def _mla_hf_to_native(hf: Dict[str, torch.Tensor], out: Dict[str, torch.Tensor], cfg) -> None:
+    nkv = cfg.get("num_key_value_layers")
+    group = max(1, int(cfg.get("key_value_group_size", 1)))
+    for name in list(hf):
+        if "_swiftkv." not in name or ".self_attn." not in name:
+            continue
+        pre, rest = name.split("self_attn.")
+        mod, kind = rest.rsplit(".", 1)
+        mod = mod[: -len("_swiftkv")]
+        t = hf.pop(name)
+        if mod in _MLA_Q:
+            if mod in ("q_proj", "q_b_proj"):
+                t = permute_rotary_rows(t, cfg, "q")
+            out[f"{pre}self_attn.q_swiftkv.{mod}.{kind}"] = t
+        elif mod in _MLA_KV:
+            layer = int(name.split("model.layers.")[1].split(".")[0])
+            if mod == "kv_a_proj_with_mqa":
+                t = permute_rotary_rows(t, cfg, "kv_a")
+            out[f"model.swiftkv_kv.kv_proj.{(layer - nkv) // group}.{mod}.{kind}"] = t
+    if "model.norm_swiftkv.weight" in hf:
+        out["model.swiftkv_kv.norm_swiftkv.weight"] = hf.pop("model.norm_swiftkv.weight")
+
+
 def _native_to_hf(name: str, tensor: torch.Tensor, cfg):
+    if cfg.get("kv_lora_rank"):
+        return _mla_native_to_hf(name, tensor, cfg)
     if ".swiftkv_kv.kv_proj." in name:
         g = int(name.split(".swiftkv_kv.kv_proj.")[1].split(".")[0])
         kind = name.rsplit(".", 1)[1]
@@ -181,6 +299,8 @@ def _hf_to_native(hf: Dict[str, torch.Tensor], out: Dict[str, torch.Tensor], cfg
     nkv = cfg.get("num_key_value_layers")
     if nkv is None:
         return
+    if cfg.get("kv_lora_rank"):
+        return _mla_hf_to_native(hf, out, cfg)
     group = max(1, int(cfg.get("key_value_group_size", 1)))
     for name in list(hf):
         if name.endswith("k_proj_swiftkv.weight") or name.endswith("k_proj_swiftkv.bias"):
@@ -193,8 +313,9 @@ def _hf_to_native(hf: Dict[str, torch.Tensor], out: Dict[str, torch.Tensor], cfg
 
 
 if _native_to_hf not in hf_io._EXTRA_NATIVE_TO_HF:
-    hf_io._EXTRA_NATIVE_TO_HF.append(_native_to_hf)
-    hf_io._EXTRA_HF_TO_NATIVE.append(_hf_to_native)
+    # ahead of the family converters: the SwiftKV names are a superset of theirs
+    hf_io._EXTRA_NATIVE_TO_HF.insert(0, _native_to_hf)
+    hf_io._EXTRA_HF_TO_NATIVE.insert(0, _hf_to_native)
 
 
 # ------------------------------------------------------------------------------------------------ configs / factory
@@ -224,21 +345,51 @@ class SwiftKVModelFactory(HFModelFactory):
     model_cls = SwiftKVForCausalLM
 
     def post_create_config_callback(self, hf_config):
-        if hf_config.get("model_type") not in ("llama", "qwen2", "qwen3", "mistral"):
+        if hf_config.get("model_type") not in ("llama", "qwen2", "qwen3", "mistral", "deepseek_v2"):
             raise ValueError(f"Unsupported model type for SwiftKV: {hf_config.get('model_type')}")
         hf_config["num_key_value_layers"] = self.config.num_key_value_layers
         hf_config["key_value_group_size"] = self.config.key_value_group_size
         return hf_config
 
-    def create_model(self, model_config):
-        model = super().create_model(model_config)
-        return model
+    def _native_class(self, model_config=None):
+        if model_config is not None and model_config.get("model_type") == "deepseek_v2":
+            return MLASwiftKVForCausalLM
+        return SwiftKVForCausalLM
+
+    @staticmethod
+    def _init_mla(model) -> None:
+        """Queries copied from the teacher branch, every shared latent key/value branch = mean of the teacher
+        branches of its group (projections and the latent norm alike), ``norm_swiftkv`` from the first SwiftKV layer."""
+        cfg = model.config
+        nkv, group = cfg["num_key_value_layers"], max(1, int(cfg.get("key_value_group_size", 1)))
+        proj = model.model.swiftkv_kv
+        with torch.no_grad():
+            proj.norm_swiftkv.weight.copy_(model.model.layers[nkv].input_layernorm.weight)
+            proj.norm_swiftkv.weight.requires_grad_(True)
+            for layer in model.model.layers[nkv:]:
+                attn = layer.self_attn
+                for dst, src in zip(attn.q_swiftkv.parameters(), attn.q.parameters()):
+                    dst.copy_(src)
+                    dst.requires_grad_(True)
+            for g, first in enumerate(proj.owner_layers):
+                members = model.model.layers[first : first + group]
+                for dst in proj.kv_proj[g].parameters():
+                    dst.zero_()
+                for layer in members:
+                    for dst, src in zip(proj.kv_proj[g].parameters(), layer.self_attn.kv.parameters()):
+                        dst.add_(src / len(members))
+                for dst in proj.kv_proj[g].parameters():
+                    dst.requires_grad_(True)
 
     def post_create_model_callback(self, model):
         cfg = model.config
         nkv, group = cfg["num_key_value_layers"], max(1, int(cfg.get("key_value_group_size", 1)))
         for p in model.parameters():
             p.requires_grad_(False)
+        if cfg.get("kv_lora_rank"):
+            self._init_mla(model)
+            model.activation_checkpointing = not self.config.disable_activation_checkpoint
+            return model
         proj = model.model.swiftkv_kv
         hq, hkv, d = cfg["num_attention_heads"], cfg.get("num_key_value_heads") or cfg["num_attention_heads"], cfg.head_dim_
         with torch.no_grad():
@@ -275,7 +426,7 @@ def build_swiftkv_model(checkpoint_dir: str, dtype=torch.bfloat16, device: str =
 
     cfg = load_arch_config(checkpoint_dir)
     with torch.device(device):
-        model = SwiftKVForCausalLM(cfg, dtype=dtype)
+        model = (MLASwiftKVForCausalLM if cfg.get("kv_lora_rank") else SwiftKVForCausalLM)(cfg, dtype=dtype)
     load_pretrained_into(model, checkpoint_dir, cfg)
     model.swiftkv(True)
     return model
