@@ -67,8 +67,9 @@ constexpr uint32_t TM_S = 0, TM_DP = 128, TM_DV = 256, TM_DK = 384;
 struct BwdParams {
     const float* lse2;  // [Hq, T]  log-sum-exp in log2 units
     const float* dsum;  // [Hq, T]  rowsum(dO o O)
-    bf16* dk;           // [T, Hkv, 128]
+    bf16* dk;           // [T, Hkv, 128], dkv_row_stride elements between tokens
     bf16* dv;
+    int64_t dkv_row_stride;
     const int* cu_seqlens;
     int nseq, T, Hq, Hkv;
     float scale, scale_log2;
@@ -453,7 +454,7 @@ fmha_bwd_tcgen05_kernel(const __grid_constant__ CUtensorMap tmap_q, const __grid
         } else {
             // group 0 stores dV, group 1 dK (times the softmax scale)
             ptx::tc_fence_after();
-            bf16* dst = (cg == 0 ? p.dv : p.dk) + ((int64_t)(tok0 + kr) * p.Hkv + g) * HD;
+            bf16* dst = (cg == 0 ? p.dv : p.dk) + (int64_t)(tok0 + kr) * p.dkv_row_stride + (int64_t)g * HD;
             const float mul = cg == 0 ? 1.f : p.scale;
 #pragma unroll 1
             for (int c = 0; c < 4; ++c) {
@@ -566,14 +567,17 @@ __global__ void fmha_bwd_prep_kernel(const bf16* __restrict__ o, const bf16* __r
     }
 }
 
-// dQ: fp32 accumulator -> bf16, times the softmax scale.
-__global__ void fmha_bwd_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8, float scale) {
+// dQ: fp32 accumulator [T, row8 * 8] -> bf16 rows of ``dq_row_stride`` elements, times the softmax scale.
+__global__ void fmha_bwd_dq_convert_kernel(const float* __restrict__ acc, bf16* __restrict__ dq, int64_t n8, int64_t row8,
+                                           int64_t dq_row_stride, float scale) {
     const int64_t stride = (int64_t)gridDim.x * blockDim.x;
     for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < n8; i += stride) {
         const float4 x = reinterpret_cast<const float4*>(acc)[2 * i];
         const float4 y = reinterpret_cast<const float4*>(acc)[2 * i + 1];
         const float f8[8] = {x.x * scale, x.y * scale, x.z * scale, x.w * scale, y.x * scale, y.y * scale, y.z * scale, y.w * scale};
-        reinterpret_cast<bf16x8*>(dq)[i] = pack8(f8);
+        const int64_t t = i / row8;
+        const int64_t c8 = i - t * row8;
+        *reinterpret_cast<bf16x8*>(dq + t * dq_row_stride + c8 * 8) = pack8(f8);
     }
 }
 
@@ -595,10 +599,13 @@ at::Tensor fmha_bwd_read_profile(const at::Tensor& like) {
 }
 
 // dout / out [T, Hq, 128], q [T, Hq, 128], k / v [T, Hkv, 128] bf16 (q, k, v may be views of a fused projection),
-// lse [Hq, T] fp32 as written by fmha_fwd, cu_seqlens int32 [nseq + 1].  Returns (dq, dk, dv), contiguous.
+// lse [Hq, T] fp32 as written by fmha_fwd, cu_seqlens int32 [nseq + 1].  Returns (dq, dk, dv): contiguous tensors, or,
+// when ``packed`` is set, views of one new [T, (Hq + 2 Hkv) * 128] tensor laid out like a fused q|k|v projection (its
+// gradient then needs no concatenation).
 std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
                                                          const at::Tensor& v, const at::Tensor& out, const at::Tensor& lse,
-                                                         const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale) {
+                                                         const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale,
+                                                         bool packed) {
     ATB_CHECK_CUDA(q);
     for (const at::Tensor* t : {&dout, &q, &k, &v, &out}) {
         TORCH_CHECK(t->scalar_type() == at::kBFloat16 && t->dim() == 3 && t->size(2) == HD, "fmha_bwd: bf16 [tokens, heads, 128] expected");
@@ -615,9 +622,17 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, 
     const int nseq = (int)cu_seqlens.numel() - 1;
     TORCH_CHECK(nseq >= 1 && max_blocks >= 1 && max_blocks <= 65535, "fmha_bwd: need 1 .. 65535 key blocks");
     c10::cuda::CUDAGuard guard(q.device());
-    auto dq = at::empty({T, Hq, HD}, q.options());
-    auto dk = at::empty({T, Hkv, HD}, q.options());
-    auto dv = at::empty({T, Hkv, HD}, q.options());
+    at::Tensor dq, dk, dv;
+    if (packed) {
+        auto all = at::empty({T, (int64_t)(Hq + 2 * Hkv), HD}, q.options());
+        dq = all.narrow(1, 0, Hq);
+        dk = all.narrow(1, Hq, Hkv);
+        dv = all.narrow(1, Hq + Hkv, Hkv);
+    } else {
+        dq = at::empty({T, Hq, HD}, q.options());
+        dk = at::empty({T, Hkv, HD}, q.options());
+        dv = at::empty({T, Hkv, HD}, q.options());
+    }
     if (T == 0) return {dq, dk, dv};
     auto fopt = q.options().dtype(at::kFloat);
     auto dq_acc = at::zeros({T, Hq, HD}, fopt);
@@ -641,6 +656,7 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, 
     p.dsum = dsum.data_ptr<float>();
     p.dk = (bf16*)dk.data_ptr();
     p.dv = (bf16*)dv.data_ptr();
+    p.dkv_row_stride = dk.stride(0);
     p.cu_seqlens = cu_seqlens.data_ptr<int>();
     p.nseq = nseq; p.T = (int)T; p.Hq = Hq; p.Hkv = Hkv;
     p.scale = (float)softmax_scale;
@@ -661,7 +677,8 @@ std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, 
     {
         const int64_t n8 = T * Hq * HD / 8;
         const unsigned blocks = (unsigned)std::min<int64_t>(ceil_div(n8, 256), 148 * 16);
-        fmha_bwd_dq_convert_kernel<<<blocks, 256, 0, stream>>>(dq_acc.data_ptr<float>(), (bf16*)dq.data_ptr(), n8, (float)softmax_scale);
+        fmha_bwd_dq_convert_kernel<<<blocks, 256, 0, stream>>>(dq_acc.data_ptr<float>(), (bf16*)dq.data_ptr(), n8,
+                                                               (int64_t)Hq * HD / 8, dq.stride(0), (float)softmax_scale);
         ATB_LAUNCH_CHECK();
     }
     return {dq, dk, dv};

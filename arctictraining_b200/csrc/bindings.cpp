@@ -38,7 +38,8 @@ std::tuple<at::Tensor, at::Tensor> fmha_fwd(const at::Tensor& q, const at::Tenso
                                             const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
 std::tuple<at::Tensor, at::Tensor, at::Tensor> fmha_bwd(const at::Tensor& dout, const at::Tensor& q, const at::Tensor& k,
                                                          const at::Tensor& v, const at::Tensor& out, const at::Tensor& lse,
-                                                         const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale);
+                                                         const at::Tensor& cu_seqlens, int64_t max_blocks, double softmax_scale,
+                                                         bool packed);
 at::Tensor fmha_bwd_read_profile(const at::Tensor& like);
 at::Tensor gemm_bf16_gather_b(const at::Tensor& x, const at::Tensor& shard_ptrs, int64_t shard_byte_offset, int64_t shard_elems,
                               at::Tensor flat, int64_t w_elem_offset, int64_t N, int64_t stage_ctas);
@@ -110,7 +111,7 @@ TORCH_LIBRARY(atb200, m) {
     m.def("gemm_bf16_gather_b(Tensor x, Tensor shard_ptrs, int shard_byte_offset, int shard_elems, Tensor(a!) flat, "
           "int w_elem_offset, int N, int stage_ctas) -> Tensor", &atb::gemm_bf16_gather_b);
     m.def("fmha_bwd_read_profile(Tensor like) -> Tensor", &atb::fmha_bwd_read_profile);
-    m.def("fmha_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor cu_seqlens, int max_blocks, float softmax_scale) -> (Tensor, Tensor, Tensor)", &atb::fmha_bwd);
+    m.def("fmha_bwd(Tensor dout, Tensor q, Tensor k, Tensor v, Tensor out, Tensor lse, Tensor cu_seqlens, int max_blocks, float softmax_scale, bool packed=False) -> (Tensor, Tensor, Tensor)", &atb::fmha_bwd);
     m.def("set_gemm_cta_pairs(bool on) -> bool", &atb::set_gemm_cta_pairs);
     m.def("p2p_barrier(Tensor flag_ptrs, int rank, int slot, int epoch, float timeout_s, Tensor like) -> ()", &atb::p2p_barrier);
     m.def("comm_read_and_clear_error(Tensor like) -> int", &atb::comm_read_and_clear_error);

@@ -141,29 +141,48 @@ __global__ void __launch_bounds__(256) swiglu_fwd_kernel(const bf16* __restrict_
 __global__ void __launch_bounds__(256) swiglu_bwd_kernel(const bf16* __restrict__ dout, const bf16* __restrict__ gu,
                                                          bf16* __restrict__ dgu, bf16* __restrict__ h_out, int64_t T,
                                                          int I) {
+    // Two 8-element pieces per thread and iteration, all six loads issued before the arithmetic: the kernel moves
+    // six streams (three in, three out) and is bound by the number of loads in flight per SM.
     const int vec_per_row = I >> 3;
     const int64_t total = T * vec_per_row;
-    for (int64_t idx = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx < total;
-         idx += (int64_t)gridDim.x * blockDim.x) {
-        const int64_t t = idx / vec_per_row;
-        const int j = (int)(idx % vec_per_row) * 8;
-        const int blk = j >> 6, jj = j & 63;
-        const int64_t off = t * (2 * (int64_t)I) + blk * 128;
-        float g[8], u[8], d[8], dg[8], du[8], hh[8];
-        unpack8(*reinterpret_cast<const bf16x8*>(gu + off + jj), g);
-        unpack8(*reinterpret_cast<const bf16x8*>(gu + off + 64 + jj), u);
-        unpack8(*reinterpret_cast<const bf16x8*>(dout + t * (int64_t)I + j), d);
+    const int64_t step = (int64_t)gridDim.x * blockDim.x;
+    for (int64_t idx0 = blockIdx.x * (int64_t)blockDim.x + threadIdx.x; idx0 < total; idx0 += 2 * step) {
+        int64_t off[2], hoff[2];
+        bool live[2];
+        bf16x8 rg[2], ru[2], rd[2];
 #pragma unroll
-        for (int k = 0; k < 8; ++k) {
-            const float sig = 1.f / (1.f + __expf(-g[k]));
-            const float silu = g[k] * sig;
-            dg[k] = d[k] * u[k] * (sig * (1.f + g[k] * (1.f - sig)));
-            du[k] = d[k] * silu;
-            hh[k] = silu * u[k];
+        for (int q = 0; q < 2; ++q) {
+            const int64_t idx = idx0 + q * step;
+            live[q] = idx < total;
+            const int64_t t = live[q] ? idx / vec_per_row : 0;
+            const int j = live[q] ? (int)(idx - t * vec_per_row) * 8 : 0;
+            off[q] = t * (2 * (int64_t)I) + (j >> 6) * 128 + (j & 63);
+            hoff[q] = t * (int64_t)I + j;
+            if (live[q]) {
+                rg[q] = *reinterpret_cast<const bf16x8*>(gu + off[q]);
+                ru[q] = *reinterpret_cast<const bf16x8*>(gu + off[q] + 64);
+                rd[q] = *reinterpret_cast<const bf16x8*>(dout + hoff[q]);
+            }
         }
-        *reinterpret_cast<bf16x8*>(dgu + off + jj) = pack8(dg);
-        *reinterpret_cast<bf16x8*>(dgu + off + 64 + jj) = pack8(du);
-        if (h_out) *reinterpret_cast<bf16x8*>(h_out + t * (int64_t)I + j) = pack8(hh);
+#pragma unroll
+        for (int q = 0; q < 2; ++q) {
+            if (!live[q]) continue;
+            float g[8], u[8], d[8], dg[8], du[8], hh[8];
+            unpack8(rg[q], g);
+            unpack8(ru[q], u);
+            unpack8(rd[q], d);
+#pragma unroll
+            for (int k = 0; k < 8; ++k) {
+                const float sig = 1.f / (1.f + __expf(-g[k]));
+                const float silu = g[k] * sig;
+                dg[k] = d[k] * u[k] * (sig * (1.f + g[k] * (1.f - sig)));
+                du[k] = d[k] * silu;
+                hh[k] = silu * u[k];
+            }
+            *reinterpret_cast<bf16x8*>(dgu + off[q]) = pack8(dg);
+            *reinterpret_cast<bf16x8*>(dgu + off[q] + 64) = pack8(du);
+            if (h_out) *reinterpret_cast<bf16x8*>(h_out + hoff[q]) = pack8(hh);
+        }
     }
 }
 

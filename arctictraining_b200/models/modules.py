@@ -147,6 +147,11 @@ class Attention(nn.Module):
             fused = ctx.sp.fused_attention_block(x, self.qkv_proj.weight, self.o_proj.weight, ctx, self.hq, self.hkv, self.d, residual)
             if fused is not None:
                 return fused
+        if ctx.sp is None and not self.qk_norm and self.window is None and ctx.attn_impl == "native":
+            # rotary embedding + attention as one autograd node on the fused projection output
+            o = ops.rope_attention(self.qkv_proj(x), ctx.cos, ctx.sin, self.hq, self.hkv, self.d, ctx.cu_seqlens, ctx.max_seqlen)
+            if o is not None:
+                return _project_with_residual(self.o_proj, o.reshape(B, S, self.hq * self.d), residual)
         q, k, v = self.project_qkv(x, ctx)
         if ctx.sp is not None and type(self.o_proj) is Linear and self.o_proj.bias is None and hasattr(ctx.sp, "attention_project"):
             fused = ctx.sp.attention_project(q, k, v, ctx, self.o_proj.weight, residual)

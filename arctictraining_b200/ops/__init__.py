@@ -14,6 +14,7 @@ from .functional import linear_swiglu
 from .functional import mlp_swiglu
 from .functional import rms_norm
 from .functional import rope
+from .functional import rope_attention
 from .functional import rope_qkv
 from .functional import set_gemm_backend
 from .functional import sumsq
@@ -21,6 +22,6 @@ from .functional import swiglu_interleaved
 
 __all__ = [
     "reference", "IGNORE_INDEX", "LAUNCH_COUNTER", "COMM_COUNTER", "accumulate_lp_grad", "adamw_step", "attention",
-    "fused_linear_cross_entropy", "fused_linear_logprobs", "gemm", "linear", "linear_swiglu", "mlp_swiglu", "rms_norm", "rope", "rope_qkv", "set_gemm_backend",
+    "fused_linear_cross_entropy", "fused_linear_logprobs", "gemm", "linear", "linear_swiglu", "mlp_swiglu", "rms_norm", "rope", "rope_attention", "rope_qkv", "set_gemm_backend",
     "sumsq", "swiglu_interleaved",
 ]

@@ -407,6 +407,73 @@ class _NativeAttentionFn(torch.autograd.Function):
         return dq, dk, dv, None, None, None, None
 
 
+class _RopeAttentionFn(torch.autograd.Function):
+    """Rotary embedding + causal attention on a fused projection output ``qkv [T, (Hq + 2 Hkv) * 128]`` in one
+    autograd node.  Forward: q and k heads are rotated in place, the attention kernel reads q, k, v as strided views.
+    Backward: the attention backward writes dq, dk, dv straight into one tensor laid out like ``qkv`` and the inverse
+    rotation runs in place on it, so the gradient of the projection needs no split/concatenate/clone passes."""
+
+    @staticmethod
+    def forward(ctx, qkv, cos, sin, cu, max_seqlen, scale, hq, hkv, d, dense_rows):
+        T = qkv.shape[0]
+        ops = _ext.ops()
+        q = qkv[:, : hq * d].unflatten(1, (hq, d))
+        k = qkv[:, hq * d : (hq + hkv) * d].unflatten(1, (hkv, d))
+        v = qkv[:, (hq + hkv) * d :].unflatten(1, (hkv, d))
+        ops.rope_inplace(q, cos, sin, False)
+        ops.rope_inplace(k, cos, sin, False)
+        out, lse = ops.fmha_fwd(q, k, v, cu, T // 128 + cu.numel() - 1, scale)
+        _count(3)
+        ctx.save_for_backward(qkv, out, lse, cu, cos, sin)
+        ctx.dims, ctx.scale = (hq, hkv, d), scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        qkv, out, lse, cu, cos, sin = ctx.saved_tensors
+        hq, hkv, d = ctx.dims
+        T = qkv.shape[0]
+        ops = _ext.ops()
+        q = qkv[:, : hq * d].unflatten(1, (hq, d))
+        k = qkv[:, hq * d : (hq + hkv) * d].unflatten(1, (hkv, d))
+        v = qkv[:, (hq + hkv) * d :].unflatten(1, (hkv, d))
+        if dout.stride(-1) != 1 or dout.stride(1) != dout.shape[2] or dout.stride(0) % 8 != 0 or dout.data_ptr() % 16:
+            dout = dout.contiguous()
+        dq, dk, dv = ops.fmha_bwd(dout, q, k, v, out, lse, cu, T // 128 + cu.numel() - 1, ctx.scale, True)
+        ops.rope_inplace(dq, cos, sin, True)
+        ops.rope_inplace(dk, cos, sin, True)
+        _count(5)
+        # dq, dk, dv are views of one [T, Hq + 2 Hkv, d] tensor: hand that tensor on as the projection's gradient
+        width = (hq + 2 * hkv) * d
+        assert dq.stride(0) == width and dq.storage_offset() == 0, "fmha_bwd(packed=True) must return views of one buffer"
+        dqkv = dq.as_strided((T, width), (width, 1), 0)
+        return dqkv, None, None, None, None, None, None, None, None, None
+
+
+def rope_attention(qkv: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, hq: int, hkv: int, d: int,
+                   cu_seqlens: Optional[torch.Tensor], max_seqlen: Optional[int], scale: Optional[float] = None
+                   ) -> Optional[torch.Tensor]:
+    """``attention(rope(q), rope(k), v)`` for a fused projection output ``[B, S, (Hq + 2 Hkv) D]`` on the package's own
+    kernels; ``None`` when they do not cover the case (the caller then takes the unfused route).  The projection
+    output is overwritten with its rotated version."""
+    if not (_use_kernels(qkv) and qkv.dtype == torch.bfloat16 and d == 128 and qkv.is_contiguous() and _ext.available()):
+        return None
+    if os.getenv("ATB200_ATTN_BWD", "native") != "native" or os.getenv("ATB200_FUSED_ROPE_ATTN", "1") == "0":
+        return None
+    if qkv.requires_grad and qkv.is_leaf:
+        return None
+    B, S, _ = qkv.shape
+    if cu_seqlens is None or B > 1 or cu_seqlens.numel() <= 2:
+        cu = torch.arange(0, (B + 1) * S, S, device=qkv.device, dtype=torch.int32)
+        max_seqlen, dense_rows = S, B
+    else:
+        cu, max_seqlen, dense_rows = cu_seqlens.to(torch.int32), int(max_seqlen or S), 0
+    scale = float(scale if scale is not None else d ** -0.5)
+    o = _RopeAttentionFn.apply(qkv.view(B * S, -1), cos.reshape(B * S, d // 2).contiguous(), sin.reshape(B * S, d // 2).contiguous(),
+                               cu, max_seqlen, scale, hq, hkv, d, dense_rows)
+    return o.view(B, S, hq, d)
+
+
 def _cudnn_dense_backward_applicable(q, k, v) -> bool:
     """Explicit preconditions of the cuDNN comparison path: the operator exists and the [T, H, D] operands can be
     viewed as [rows, S, H, D] (dense heads).  Errors raised by the operator itself are not caught."""

@@ -624,6 +624,54 @@ def test_native_flash_attention_backward(k, lens, Hq, Hkv):
     torch.testing.assert_close(dq2.float(), dq.float(), atol=1e-2, rtol=1e-2)
 
 
+@pytest.mark.parametrize("lens,Hq,Hkv", [([384], 4, 2), ([200, 56, 512], 8, 2)])
+def test_rope_attention_fused_node_matches_fp32_reference(k, lens, Hq, Hkv):
+    """Rotary embedding + attention on a fused projection output as one autograd node: output and the gradient of the
+    projection (one tensor, written by the backward kernel without concatenation) against fp32 autograd of
+    rope -> attention; the packed form of the backward kernel equals its three-tensor form bit for bit."""
+    from arctictraining_b200 import ops
+    from arctictraining_b200.ops import reference as ref
+
+    torch.manual_seed(11)
+    T, D = sum(lens), 128
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), device="cuda", dtype=torch.int32)
+    pos = torch.cat([torch.arange(n) for n in lens]).cuda()[None]
+    cos, sin = ref.rope_cos_sin(pos, D, 10000.0)
+    base = torch.randn(1, T, (Hq + 2 * Hkv) * D, device="cuda", dtype=torch.bfloat16)
+    g = torch.randn(1, T, Hq, D, device="cuda", dtype=torch.bfloat16)
+
+    src = base.clone().requires_grad_(True)
+    out = ops.rope_attention(src * 1, cos, sin, Hq, Hkv, D, cu, max(lens))  # "* 1": a non-leaf, as a projection output is
+    assert out is not None
+    out.backward(g)
+    torch.cuda.synchronize()
+    _check_flag(out)
+
+    x = base.float().detach().requires_grad_(True)
+    q, kk, v = x.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    qr = ref.rope_apply(q.view(1, T, Hq, D), cos, sin)
+    kr = ref.rope_apply(kk.view(1, T, Hkv, D), cos, sin)
+    o2 = ref.attention(qr, kr, v.view(1, T, Hkv, D), cu_seqlens=cu.long())
+    o2.backward(g.float())
+    assert _rel(out, o2) < 1e-2
+    assert _rel(src.grad, x.grad) < 2e-2, _rel(src.grad, x.grad)
+    for lo, hi, name in ((0, Hq * D, "dq"), (Hq * D, (Hq + Hkv) * D, "dk"), ((Hq + Hkv) * D, (Hq + 2 * Hkv) * D, "dv")):
+        assert _rel(src.grad[..., lo:hi], x.grad[..., lo:hi]) < 2e-2, name
+
+    # packed and three-tensor forms of the backward kernel agree exactly (dk, dv) / to fp32 summation order (dq)
+    qkv = base[0].clone()
+    qv = qkv[:, : Hq * D].view(T, Hq, D)
+    kv_ = qkv[:, Hq * D : (Hq + Hkv) * D].view(T, Hkv, D)
+    vv = qkv[:, (Hq + Hkv) * D :].view(T, Hkv, D)
+    nblk = T // 128 + len(lens)
+    o, lse = k.fmha_fwd(qv, kv_, vv, cu, nblk, D ** -0.5)
+    a = k.fmha_bwd(g[0], qv, kv_, vv, o, lse, cu, nblk, D ** -0.5)
+    b = k.fmha_bwd(g[0], qv, kv_, vv, o, lse, cu, nblk, D ** -0.5, True)
+    assert b[0].stride(0) == (Hq + 2 * Hkv) * D and b[1].data_ptr() == b[0].data_ptr() + Hq * D * 2
+    assert torch.equal(a[1], b[1]) and torch.equal(a[2], b[2])
+    torch.testing.assert_close(a[0].float(), b[0].float(), atol=1e-2, rtol=1e-2)
+
+
 def test_native_flash_attention_long_sequence_forward_and_backward(k):
     """65 536 tokens (64-bit offsets, log-sum-exp layout, 512 key blocks) against a chunked fp32 reference."""
     torch.manual_seed(4)
