@@ -119,3 +119,28 @@ def test_moe_dispatch_and_combine_through_peer_buffers(k):
     assert int(k.comm_read_and_clear_error(xs[0])) == 0
     k.p2p_moe_dispatch(xs[0], experts[0], dests[0], ptrs(bufs), 0, El, 8, None)  # capacity far too small: rows are skipped
     assert int(k.comm_read_and_clear_error(xs[0])) >> 8 == 0x31
+
+
+def test_reduce_scatter_is_bit_identical_on_a_second_run_and_writes_only_its_slice(k):
+    """The reduction adds the peers' pieces in rank order, so two runs give the same bits; the accumulator lives inside a
+    larger buffer filled with a canary value, which must survive around the written slice (odd length: tail path)."""
+    torch.manual_seed(1)
+    P, n, pad = 4, 8 * 1000 + 8, 64
+    grads = [torch.randn(P * n, device="cuda").bfloat16() for _ in range(P)]
+    outs = []
+    for _ in range(2):
+        buf = torch.full((n + 2 * pad,), -123.25, device="cuda")
+        acc = buf[pad : pad + n]
+        ss = k.p2p_reduce_scatter_accum(ptrs(grads), 2 * n, n, acc, 0.5, True, True)
+        outs.append((acc.clone(), ss.clone()))
+        assert bool((buf[:pad] == -123.25).all()) and bool((buf[pad + n :] == -123.25).all())
+    assert torch.equal(outs[0][0], outs[1][0]) and torch.equal(outs[0][1], outs[1][1])
+
+
+def test_all_gather_writes_only_the_requested_range(k):
+    P, n, pad = 3, 8 * 500, 32
+    shards = [torch.randn(n, device="cuda").bfloat16() for _ in range(P)]
+    buf = torch.full((P * n + 2 * pad,), 7.5, device="cuda", dtype=torch.bfloat16)
+    k.p2p_all_gather(ptrs(shards), 0, buf[pad : pad + P * n], n, 0)
+    assert torch.equal(buf[pad : pad + P * n], torch.cat(shards))
+    assert bool((buf[:pad] == 7.5).all()) and bool((buf[pad + P * n :] == 7.5).all())

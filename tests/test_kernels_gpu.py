@@ -305,6 +305,32 @@ def test_moe_slots_scatter_gather_kernels(k):
     assert _rel(k.moe_scatter_bwd(dy, slots), dout.float() * scores.sum(-1, keepdim=True)) < 1e-2
 
 
+def test_moe_slot_assignment_and_scatter_are_bit_identical_on_a_second_run(k):
+    """Slots inside an expert follow the (token, k) order — no atomics decide them — so slot maps, permuted rows, the
+    combine and its gradients repeat bit for bit; rows of the permuted buffer that belong to no token stay zero."""
+    torch.manual_seed(2)
+    T, K, E, H = 3001, 4, 64, 128
+    experts = torch.randint(0, E, (T, K), device="cuda", dtype=torch.int32)
+    x = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    scores = torch.rand(T, K, device="cuda")
+    dout = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    runs = []
+    for _ in range(2):
+        slots, counts, offsets = k.moe_assign_slots(experts, E, 128)
+        rows = int(offsets[-1])
+        perm = k.moe_scatter_fwd(x, slots, rows)
+        out = k.moe_gather_fwd(perm, slots, scores)
+        dy, dscores = k.moe_gather_bwd(dout, perm, slots, scores)
+        dx = k.moe_scatter_bwd(dy, slots)
+        runs.append((slots, counts, offsets, perm, out, dy, dscores, dx))
+    for a, b in zip(*runs):
+        assert torch.equal(a, b)
+    slots, _, offsets, perm = runs[0][:4]
+    used = torch.zeros(int(offsets[-1]), dtype=torch.bool, device="cuda")
+    used[slots.reshape(-1).long()] = True
+    assert int(used.sum()) == T * K and not bool(perm[~used].any())
+
+
 def test_grouped_mlp_matches_reference_forward_and_backward(k):
     from arctictraining_b200.moe import ops as mops
     from arctictraining_b200.moe.grouped import grouped_mlp_reference
