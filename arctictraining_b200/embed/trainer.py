@@ -149,6 +149,35 @@ def gather_embeddings(embeddings: Tensor, rank: int, world_size: int) -> Tensor:
     return torch.cat(parts, dim=0)
 
 
+class PeerEmbeddingGather:
+    """Query and document embeddings of all ranks in ONE exchange over peer memory: every rank writes its ``q | d`` rows
+    into its half of a symmetric buffer, a device-side barrier follows, and one pull kernel reads all peers' rows over
+    NVLink — no library collective, no host synchronisation.  The local rows of the result keep their autograd
+    history, as in :func:`gather_embeddings`."""
+
+    def __init__(self, symm) -> None:
+        from ..comm.symm import RotatingBuffers
+
+        self.symm = symm
+        self.buffers = RotatingBuffers(symm)
+
+    def __call__(self, q: Tensor, d: Tensor, rank: int, world_size: int) -> Tuple[Tensor, Tensor]:
+        nq, nd = q.numel(), d.numel()
+        n = (nq + nd + 7) // 8 * 8
+        buf, off = self.buffers.take("embeddings", n, q.dtype)
+        mine = buf.tensor[off : off + n]
+        mine[:nq].copy_(q.detach().reshape(-1))
+        mine[nq : nq + nd].copy_(d.detach().reshape(-1))
+        self.symm.barrier(slot=5)
+        full = torch.empty(world_size * n, dtype=q.dtype, device=q.device)
+        self.symm.all_gather(buf, off, n, full)
+        rows = full.view(world_size, n)
+        qs = [rows[r, :nq].view_as(q) for r in range(world_size)]
+        ds = [rows[r, nq : nq + nd].view_as(d) for r in range(world_size)]
+        qs[rank], ds[rank] = q, d
+        return torch.cat(qs, dim=0), torch.cat(ds, dim=0)
+
+
 def sum_gradients_cb(self: "BiencoderTrainer") -> None:
     """The loss is global on every rank: data-parallel gradients are summed, not averaged."""
     for u in self.model.units:
@@ -197,8 +226,14 @@ class BiencoderTrainer(Trainer):
         relations = batch.relevance_labels.to_dense()
         q, d = self.model(query_input_ids=batch.query_tokens, query_attention_mask=batch.query_attention_mask,
                           document_input_ids=batch.document_tokens, document_attention_mask=batch.document_attention_mask)
-        q = gather_embeddings(q, self.global_rank, self.world_size)
-        d = gather_embeddings(d, self.global_rank, self.world_size)
+        symm = getattr(self.model, "symm", None)
+        if symm is not None and self.world_size > 1 and q.is_cuda and q.dtype == d.dtype == torch.bfloat16:
+            if getattr(self, "_peer_gather", None) is None:
+                self._peer_gather = PeerEmbeddingGather(symm)
+            q, d = self._peer_gather(q.contiguous(), d.contiguous(), self.global_rank, self.world_size)
+        else:
+            q = gather_embeddings(q, self.global_rank, self.world_size)
+            d = gather_embeddings(d, self.global_rank, self.world_size)
         return q, d, relations
 
     @torch.no_grad()

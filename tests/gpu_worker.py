@@ -344,6 +344,32 @@ def scenario_moe_peer(out_dir):
         (Path(out_dir) / "moe_peer.json").write_text(json.dumps(allres))
 
 
+def scenario_embed_gather(out_dir):
+    """Peer-memory gather of query | document embeddings against the NCCL gather: same values, twice in a row (both
+    halves of the rotating buffer), and the local rows carry gradients."""
+    from arctictraining_b200.comm.symm import SymmetricContext
+    from arctictraining_b200.embed.trainer import PeerEmbeddingGather
+    from arctictraining_b200.embed.trainer import gather_embeddings
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    gather = PeerEmbeddingGather(SymmetricContext(dist.group.WORLD, timeout_s=10.0))
+    ok = True
+    for step in range(3):
+        torch.manual_seed(100 * step + rank)
+        q = torch.randn(6, 72, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        d = torch.randn(13, 72, device="cuda", dtype=torch.bfloat16, requires_grad=True)
+        fq, fd = gather(q, d, rank, world)
+        rq, rd = gather_embeddings(q, rank, world), gather_embeddings(d, rank, world)
+        ok &= torch.equal(fq, rq) and torch.equal(fd, rd)
+        (fq.float().sum() * 2 + fd.float().sum() * 3).backward()
+        ok &= bool((q.grad == 2).all()) and bool((d.grad == 3).all())
+    gather.symm.check()
+    allok = [None] * world
+    dist.all_gather_object(allok, bool(ok))
+    if rank == 0:
+        (Path(out_dir) / "embed_gather.json").write_text(json.dumps({"ok": all(allok)}))
+
+
 def main():
     scenario, out_dir = sys.argv[1], sys.argv[2]
     os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
@@ -351,7 +377,7 @@ def main():
     init_distributed(timeout_s=120)
     {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout, "partly_frozen": scenario_partly_frozen, "gather_gemm": scenario_gather_gemm,
      "ulysses_peer": scenario_ulysses_peer, "moe_peer": scenario_moe_peer,
-     "fused_attention_block": scenario_fused_attention_block}[scenario](out_dir)
+     "fused_attention_block": scenario_fused_attention_block, "embed_gather": scenario_embed_gather}[scenario](out_dir)
     dist.barrier()
     dist.destroy_process_group()
 

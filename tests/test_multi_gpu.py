@@ -83,6 +83,11 @@ def test_attention_block_with_exchanges_inside_the_gemms(tmp_path):
             assert err < 1e-2, (name, err)
 
 
+def test_embedding_gather_through_peer_memory_matches_nccl(tmp_path):
+    launch(2, "embed_gather", tmp_path)
+    assert json.loads((tmp_path / "embed_gather.json").read_text())["ok"]
+
+
 @pytest.mark.parametrize("attn", ["native", "sdpa"])
 def test_cli_ulysses_alst_first_step_loss_equals_data_parallel(tmp_path, attn):
     """The reference's end-to-end pattern (tests/trainer/test_ulysses_alst.py:34-166) through the real command line on
