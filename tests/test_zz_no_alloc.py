@@ -30,6 +30,17 @@ def lib():
     fn = handle.atb_rmsnorm_bwd_noalloc
     fn.restype = ctypes.c_int
     fn.argtypes = [ctypes.c_void_p] * 6 + [ctypes.c_longlong, ctypes.c_int, ctypes.c_void_p, ctypes.c_char_p, ctypes.c_ulong]
+    # One call before any measurement: the CUDA runtime loads a kernel's code when it is first launched, which takes
+    # device memory once per process and has nothing to do with the entry point's own behaviour.
+    x = torch.randn(8, 1024, device="cuda", dtype=torch.bfloat16)
+    w = torch.ones(1024, device="cuda", dtype=torch.bfloat16)
+    rstd = torch.ones(8, device="cuda")
+    dx, dw = torch.empty_like(x), torch.empty(1024, device="cuda")
+    err = ctypes.create_string_buffer(256)
+    rc = fn(x.data_ptr(), x.data_ptr(), w.data_ptr(), rstd.data_ptr(), dx.data_ptr(), dw.data_ptr(), 8, 1024,
+            ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), err, 256)
+    assert rc == 0, err.value.decode()
+    torch.cuda.synchronize()
     return fn
 
 
@@ -55,10 +66,6 @@ def test_matches_tensor_operator_on_two_calls_in_a_row(lib, shapes):
         dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
         _, rstd = k.rmsnorm_fwd(x, w, 1e-5)
         dx_ref, dw_ref = k.rmsnorm_bwd(dy, x, w, rstd)
-        # the same operation in plain fp32 PyTorch
-        xf = x.float().requires_grad_(True)
-        wf = w.float().requires_grad_(True)
-        (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf).backward(dy.float())
         dx = torch.empty_like(x)
         dw = torch.full((H,), float("nan"), device="cuda")
         torch.cuda.synchronize()
@@ -70,6 +77,11 @@ def test_matches_tensor_operator_on_two_calls_in_a_row(lib, shapes):
         free_after, _ = torch.cuda.mem_get_info()
         assert torch.cuda.memory_allocated() == before
         assert free_before - free_after < (1 << 20), "device memory was allocated during the call"
+        # the same operation in plain fp32 PyTorch (after the memory checks: autograd's worker thread releases its
+        # temporaries on its own schedule, which would move the framework's allocation counter)
+        xf = x.float().requires_grad_(True)
+        wf = w.float().requires_grad_(True)
+        (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + 1e-5) * wf).backward(dy.float())
         assert rel(dx, dx_ref) < 1e-2 and rel(dw, dw_ref) < 1e-2      # the tensor-based entry point
         assert rel(dx, xf.grad) < 2e-2 and rel(dw, wf.grad) < 2e-2      # the fp32 reference
 
