@@ -729,13 +729,29 @@ class TrainingEngine:
             return
         if getattr(u, "direct_grad", False):
             g = u.grad_acc
+            store_first = self._store_first_params(u) if not u.grad_acc_valid else frozenset()
             if not u.grad_acc_valid:
-                g.zero_()
+                if store_first:
+                    # weights of plain linear layers get their first gradient by a storing GEMM epilogue: only the
+                    # other (small) slices need zeroing
+                    for p, o, n in zip(u.params, u.offsets, u.numels):
+                        if p.requires_grad and id(p) not in store_first:
+                            g[o : o + n].zero_()
+                else:
+                    g.zero_()
             u.grad_flat, u.grad_slot = g, None
             for p, o, n, shp in zip(u.params, u.offsets, u.numels, u.shapes):
                 if p.requires_grad:
-                    p.grad = g[o : o + n].view(shp)
-                    p._atb_main_grad = p.grad
+                    view = g[o : o + n].view(shp)
+                    p._atb_main_grad = view
+                    if id(p) in store_first:
+                        # autograd must not add into the uninitialised slice: a gradient that does not come from the
+                        # GEMM epilogue arrives as a tensor of its own and is folded in by _finish_store_first
+                        p.grad = None
+                        p._atb_grad_fresh = True
+                    else:
+                        p.grad = view
+            u.store_first = store_first
             return
         if u.checkpointed:
             slot, buf = self._grad_pool.acquire()
@@ -753,6 +769,44 @@ class TrainingEngine:
                 p.grad = g[o : o + n].view(shp)
                 p._atb_main_grad = p.grad
 
+    def _store_first_params(self, u: ZeroUnit) -> frozenset:
+        """Parameters of ``u`` whose gradient buffer slice is not zeroed before the backward pass: trainable 2-D bf16
+        weights of this package's plain ``Linear`` modules, whose weight gradient is written by a GEMM epilogue (store
+        on the first write of a step, accumulate afterwards).  Off unless ``ATB200_STORE_FIRST_WGRAD=1``."""
+        cached = getattr(u, "_store_first_cache", None)
+        if cached is not None:
+            return cached
+        found = set()
+        if os.getenv("ATB200_STORE_FIRST_WGRAD", "0") == "1" and self.on_gpu:
+            from ..models.modules import Linear
+
+            for mod in u.modules:
+                for m in mod.modules():
+                    if type(m) is Linear and m.weight.requires_grad and m.weight.dim() == 2 and m.weight.dtype == torch.bfloat16:
+                        found.add(id(m.weight))
+            found &= {id(p) for p in u.params}
+        u._store_first_cache = frozenset(found)
+        return u._store_first_cache
+
+    def _finish_store_first(self, u: ZeroUnit) -> None:
+        """After the unit's backward pass: a store-first parameter that the GEMM epilogue never wrote gets its
+        autograd gradient copied in (or zeros when it received none); one that was written and also received an
+        autograd gradient (a weight used by two code paths) gets that added."""
+        for p in u.params:
+            if id(p) not in u.store_first:
+                continue
+            main = p._atb_main_grad
+            extra = p.grad
+            if getattr(p, "_atb_grad_fresh", False):
+                if extra is not None:
+                    main.copy_(extra)
+                else:
+                    main.zero_()
+                p._atb_grad_fresh = False
+            elif extra is not None:
+                main.add_(extra)
+        u.store_first = None
+
     def _end_unit_backward(self, u: ZeroUnit) -> None:
         self._reduce_unit(u)
         exp = getattr(u, "expert_unit", None)
@@ -765,6 +819,8 @@ class TrainingEngine:
         if u.grad_flat is None:
             return
         g = u.grad_flat
+        if getattr(u, "store_first", None):
+            self._finish_store_first(u)
         for p in u.params:
             p.grad = None
             p._atb_main_grad = None

@@ -272,7 +272,13 @@ def _wgrad(dy: torch.Tensor, x2: torch.Tensor, w: torch.Tensor) -> Optional[torc
     temporary and a read-modify-write pass over the buffer)."""
     main = getattr(w, "_atb_main_grad", None)
     if main is not None and main.dtype == torch.bfloat16 and main.shape == w.shape and main.is_contiguous():
-        gemm(dy, x2, True, True, epilogue=1, out=main)
+        if getattr(w, "_atb_grad_fresh", False):
+            # first gradient of this step for a buffer the engine did not zero: store instead of accumulate (no fill
+            # pass before, no read of the old contents here)
+            gemm(dy, x2, True, True, epilogue=0, out=main)
+            w._atb_grad_fresh = False
+        else:
+            gemm(dy, x2, True, True, epilogue=1, out=main)
         return None
     return gemm(dy, x2, True, True)
 

@@ -80,6 +80,30 @@ def test_direct_bf16_gradients_equal_fp32_accumulation(monkeypatch):
     assert float(a.get_global_grad_norm()) == pytest.approx(float(b.get_global_grad_norm()), rel=1e-4)
 
 
+@pytest.mark.parametrize("keep", [0, 4])
+def test_first_weight_gradient_stored_without_zeroing_equals_zero_then_accumulate(monkeypatch, keep):
+    """Linear-layer weight gradients written by a storing GEMM epilogue into a gradient buffer that was not zeroed
+    (``ATB200_STORE_FIRST_WGRAD=1``) against the zero-fill + accumulate path: bf16(0 + x) == bf16(x), so losses,
+    gradient norm and parameters agree bit for bit, with and without recomputation of the layers."""
+    data = batches(3, "cuda")
+    extra = {"activation_checkpoint_keep": keep}
+    a = make_engine(make_model("cuda", torch.bfloat16), **extra)
+    la = run(a, data)
+    monkeypatch.setenv("ATB200_STORE_FIRST_WGRAD", "1")
+    b = make_engine(make_model("cuda", torch.bfloat16), **extra)
+    # poison the gradient buffers: whatever they hold must not reach the update
+    for u in b.units:
+        if u.grad_acc is not None:
+            u.grad_acc.fill_(float("nan"))
+    lb = run(b, data)
+    assert any(len(getattr(u, "_store_first_cache", ())) > 0 for u in b.units), "the store-first path did not engage"
+    assert la == lb
+    pa = dict(a.iter_full_named_parameters())
+    for n, t in b.iter_full_named_parameters():
+        assert torch.equal(pa[n], t), n
+    assert float(a.get_global_grad_norm()) == float(b.get_global_grad_norm())
+
+
 @pytest.mark.parametrize("keep", [2, "auto"])
 def test_layers_keeping_activations_on_gpu(keep):
     data = batches(5, "cuda")

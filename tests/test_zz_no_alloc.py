@@ -68,6 +68,9 @@ def test_matches_tensor_operator_on_two_calls_in_a_row(lib, shapes):
         dx_ref, dw_ref = k.rmsnorm_bwd(dy, x, w, rstd)
         dx = torch.empty_like(x)
         dw = torch.full((H,), float("nan"), device="cuda")
+        # unmeasured first call for this width: every kernel variant is loaded by the runtime at its first launch
+        rc, msg = call(lib, dy, x, w, rstd, torch.empty_like(x), torch.empty(H, device="cuda"))
+        assert rc == 0, msg
         torch.cuda.synchronize()
         before = torch.cuda.memory_allocated()
         free_before, _ = torch.cuda.mem_get_info()  # sees allocations made behind the framework's back as well
