@@ -88,6 +88,9 @@ struct GemmParams {
     // done by the epilogue stores).  KV heads are replicated when there are fewer of them than ranks.
     bf16* push_dst[8];
     int push_ranks, push_rank, push_hq, push_hkv, push_d, push_rows;
+    // Cache behaviour of the CTA-pair kernel (bit 0: the epilogue writes the output with streaming stores and reads
+    // the accumulate operand with streaming loads; bit 1: operand tiles are loaded with an evict-last L2 policy).
+    int cache_flags;
 };
 
 constexpr int kMaxSegs = 8;
@@ -581,6 +584,12 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
         if (lane == 0) {
             ptx::tma_prefetch_desc(&tmap_a);
             ptx::tma_prefetch_desc(&tmap_b);
+            const bool keep_operands = (p.cache_flags & 2) != 0;
+            const uint64_t keep_policy = keep_operands ? ptx::make_l2_policy_evict_last() : 0;
+            auto load = [&](void* dst, const CUtensorMap* tm_, int x, int y, uint64_t* bar) {
+                if (keep_operands) ptx::tma_load_2d_pair_hint(dst, tm_, x, y, bar, keep_policy);
+                else ptx::tma_load_2d_pair(dst, tm_, x, y, bar);
+            };
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -619,19 +628,19 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                             ptx::tma_load_2d_pair(sa, &segs.m[seg], kb * BK - seg * p.a_seg_len, p.a_seg_row0 + a_m0,
                                                   &full_bar[stage]);
                         } else {
-                            ptx::tma_load_2d_pair(sa, &tmap_a, kb * BK, a_m0, &full_bar[stage]);
+                            load(sa, &tmap_a, kb * BK, a_m0, &full_bar[stage]);
                         }
                     } else {
 #pragma unroll
                         for (int c = 0; c < 2; ++c)
-                            ptx::tma_load_2d_pair(sa + c * (BK * 128), &tmap_a, a_m0 + c * 64, kb * BK, &full_bar[stage]);
+                            load(sa + c * (BK * 128), &tmap_a, a_m0 + c * 64, kb * BK, &full_bar[stage]);
                     }
                     if constexpr (!B_MN) {
-                        ptx::tma_load_2d_pair(sb, &tmap_b, kb * BK, b_n0, &full_bar[stage]);
+                        load(sb, &tmap_b, kb * BK, b_n0, &full_bar[stage]);
                     } else {
 #pragma unroll
                         for (int c = 0; c < 2; ++c)
-                            ptx::tma_load_2d_pair(sb + c * (BK * 128), &tmap_b, b_n0 + c * 64, kb * BK, &full_bar[stage]);
+                            load(sb + c * (BK * 128), &tmap_b, b_n0 + c * 64, kb * BK, &full_bar[stage]);
                     }
                     if (++stage == STAGES) { stage = 0; phase ^= 1u; }
                 }
@@ -774,6 +783,7 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
             } else {
                 bf16* crow = p.C + (int64_t)row * p.ldc + (int64_t)tn * TN;
                 const bf16* rrow = p.R + (int64_t)row * p.ldr + (int64_t)tn * TN;
+                const bool streaming = (p.cache_flags & 1) != 0;
 #pragma unroll 1
                 for (int c = 0; c < TN / 32; ++c) {
                     uint32_t r[32];
@@ -787,14 +797,18 @@ gemm_bf16_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap tmap_a, const 
                                 float o[8];
 #pragma unroll
                                 for (int j = 0; j < 8; ++j) o[j] = __uint_as_float(r[v * 8 + j]);
-                                bf16x8* dst = reinterpret_cast<bf16x8*>(crow + c * 32 + v * 8);
+                                uint4* dst = reinterpret_cast<uint4*>(crow + c * 32 + v * 8);
                                 if constexpr (EPI == EPI_ACCUM) {
                                     float old[8];
-                                    unpack8(*reinterpret_cast<const bf16x8*>(rrow + c * 32 + v * 8), old);
+                                    const uint4* src = reinterpret_cast<const uint4*>(rrow + c * 32 + v * 8);
+                                    const uint4 raw = streaming ? __ldcs(src) : *src;
+                                    unpack8(*reinterpret_cast<const bf16x8*>(&raw), old);
 #pragma unroll
                                     for (int j = 0; j < 8; ++j) o[j] += old[j];
                                 }
-                                *dst = pack8(o);
+                                const bf16x8 packed = pack8(o);
+                                if (streaming) __stcs(dst, *reinterpret_cast<const uint4*>(&packed));
+                                else *dst = *reinterpret_cast<const uint4*>(&packed);
                             }
                         }
                     }
@@ -933,6 +947,15 @@ void dispatch_epi_pair(int epi, const CUtensorMap& ta, const CUtensorMap& tb, co
 
 static bool g_use_cta_pairs = true;  // dense GEMMs run on the CTA-pair kernel unless switched off
 
+// ATB200_GEMM_CACHE: bit 0 streaming output stores / accumulate loads, bit 1 evict-last operand loads (read once)
+static int gemm_cache_flags() {
+    static const int flags = [] {
+        const char* e = std::getenv("ATB200_GEMM_CACHE");
+        return e ? std::atoi(e) : 0;
+    }();
+    return flags;
+}
+
 template <bool A_MN, bool B_MN>
 void dispatch_epi(int epi, const CUtensorMap& ta, const CUtensorMap& tb, const GemmParams& p, int max_ctas) {
     switch (epi) {
@@ -996,6 +1019,7 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     if (a_mn) TORCH_CHECK(M % 8 == 0, "gemm: MN-major A needs M to be a multiple of 8");
 
     GemmParams p;
+    p.cache_flags = 0;
     p.C = (bf16*)out.data_ptr();
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.ldc = out.stride(0);
@@ -1009,6 +1033,7 @@ at::Tensor gemm_bf16(const at::Tensor& a, const at::Tensor& b, bool a_mn, bool b
     p.group_offsets = nullptr;
     p.num_groups = 0;
     p.group_mode = GROUP_NONE;
+    p.cache_flags = gemm_cache_flags();
     const int ctas = max_ctas > 0 ? (int)max_ctas : kNumSMs;
     if (pairs) {
         if (!a_mn && !b_mn) dispatch_epi_pair<false, false>(epi, ta, tb, p, ctas);
@@ -1043,6 +1068,7 @@ at::Tensor gemm_bf16_grouped(const at::Tensor& a, const at::Tensor& b, const at:
     const int epi = (int)epilogue;
     c10::cuda::CUDAGuard guard(a.device());
     GemmParams p;
+    p.cache_flags = 0;
     p.error_flag = error_flag_for(a.device()).data_ptr<int>();
     p.group_offsets = offsets.data_ptr<int>();
     p.num_groups = (int)G;
@@ -1135,6 +1161,7 @@ void gemm_bf16_push_heads(const at::Tensor& x, const at::Tensor& w, const at::Te
     const CUtensorMap ta = make_tmap_bf16(x.data_ptr(), M, K, x.stride(0), 128);
     const CUtensorMap tb = make_tmap_bf16(w.data_ptr(), N, K, w.stride(0), 128);
     GemmParams p;
+    p.cache_flags = 0;
     p.C = nullptr; p.R = nullptr; p.ldc = 0; p.ldr = 0;
     p.M = (int)M; p.N = (int)N; p.K = (int)K;
     p.error_flag = error_flag_for(x.device()).data_ptr<int>();
@@ -1173,6 +1200,7 @@ std::tuple<at::Tensor, at::Tensor> gemm_bf16_peer_a(const at::Tensor& a_ptrs, in
     at::Tensor flags;
     SegMaps segs = {};
     GemmParams p;
+    p.cache_flags = 0;
     p.a_seg_len = (int)seg_cols;
     p.a_seg_row0 = (int)row0;
     p.stage_ctas = (int)stage_ctas;
@@ -1244,6 +1272,7 @@ at::Tensor gemm_bf16_gather_b(const at::Tensor& x, const at::Tensor& shard_ptrs,
     auto flags = at::zeros({(int64_t)ceil_div(N, 256)}, x.options().dtype(at::kInt));
     SegMaps segs = {};
     GemmParams p;
+    p.cache_flags = 0;
     p.a_seg_len = 0; p.a_seg_row0 = 0;
     p.stage_ctas = (int)stage_ctas;
     p.stage_segs = 1;

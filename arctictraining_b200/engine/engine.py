@@ -772,12 +772,12 @@ class TrainingEngine:
     def _store_first_params(self, u: ZeroUnit) -> frozenset:
         """Parameters of ``u`` whose gradient buffer slice is not zeroed before the backward pass: trainable 2-D bf16
         weights of this package's plain ``Linear`` modules, whose weight gradient is written by a GEMM epilogue (store
-        on the first write of a step, accumulate afterwards).  Off unless ``ATB200_STORE_FIRST_WGRAD=1``."""
+        on the first write of a step, accumulate afterwards).  ``ATB200_STORE_FIRST_WGRAD=0`` switches it off."""
         cached = getattr(u, "_store_first_cache", None)
         if cached is not None:
             return cached
         found = set()
-        if os.getenv("ATB200_STORE_FIRST_WGRAD", "0") == "1" and self.on_gpu:
+        if os.getenv("ATB200_STORE_FIRST_WGRAD", "1") != "0" and self.on_gpu:
             from ..models.modules import Linear
 
             for mod in u.modules:

@@ -83,10 +83,11 @@ def test_direct_bf16_gradients_equal_fp32_accumulation(monkeypatch):
 @pytest.mark.parametrize("keep", [0, 4])
 def test_first_weight_gradient_stored_without_zeroing_equals_zero_then_accumulate(monkeypatch, keep):
     """Linear-layer weight gradients written by a storing GEMM epilogue into a gradient buffer that was not zeroed
-    (``ATB200_STORE_FIRST_WGRAD=1``) against the zero-fill + accumulate path: bf16(0 + x) == bf16(x), so losses,
+    (the default at world size 1) against the zero-fill + accumulate path (``ATB200_STORE_FIRST_WGRAD=0``): bf16(0 + x) == bf16(x), so losses,
     gradient norm and parameters agree bit for bit, with and without recomputation of the layers."""
     data = batches(3, "cuda")
     extra = {"activation_checkpoint_keep": keep}
+    monkeypatch.setenv("ATB200_STORE_FIRST_WGRAD", "0")
     a = make_engine(make_model("cuda", torch.bfloat16), **extra)
     la = run(a, data)
     monkeypatch.setenv("ATB200_STORE_FIRST_WGRAD", "1")

@@ -78,7 +78,9 @@ def test_matches_tensor_operator_on_two_calls_in_a_row(lib, shapes):
         assert rc == 0, msg
         torch.cuda.synchronize()
         free_after, _ = torch.cuda.mem_get_info()
-        assert torch.cuda.memory_allocated() == before
+        # "<=": the framework may hand a block that an earlier operator released on its own schedule back to its pool
+        # meanwhile; what matters is that nothing new was taken, from the pool or (next line) from the device
+        assert torch.cuda.memory_allocated() <= before
         assert free_before - free_after < (1 << 20), "device memory was allocated during the call"
         # the same operation in plain fp32 PyTorch (after the memory checks: autograd's worker thread releases its
         # temporaries on its own schedule, which would move the framework's allocation counter)
