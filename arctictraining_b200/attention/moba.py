@@ -85,21 +85,13 @@ def moba_attn_varlen(q, k, v, cu_seqlens, max_seqlen: int, moba_chunk_size: int,
     return out
 
 
-def _partial_attention(q, k, v, scale, mask=None):
-    """``(out [n, D] fp32, lse [n] fp32)`` of queries ``q [n, D]`` over keys ``k [m, D]``."""
-    s = (q.float() @ k.float().t()) * scale
-    if mask is not None:
-        s = s.masked_fill(~mask, float("-inf"))
-    lse = torch.logsumexp(s, dim=-1)
-    return torch.exp(s - lse.unsqueeze(-1)) @ v.float(), lse
-
-
 def moba_attn_efficient(q, k, v, cu_seqlens, max_seqlen: int, moba_chunk_size: int, moba_topk: int) -> torch.Tensor:
     """Sparse MoBA (differentiable): same result as :func:`moba_attn_naive`.
 
-    Per sequence and head: (1) every query attends causally inside its own key block; (2) the gate picks ``topk - 1``
-    earlier blocks per query; for each key block the queries that picked it are gathered and attend to that block in
-    full; (3) the partial outputs of a query are merged with weights ``exp(lse_i - lse_total)``.  This is the
+    Per sequence: (1) every query attends causally inside its own key block — one batched product over (block, head);
+    (2) the gate picks ``topk - 1`` earlier blocks per query and head; per head, the queries that picked a block are
+    gathered (padded to the largest group) and attend to that block in full — one batched product over the blocks;
+    (3) the partial outputs of a query are merged with weights ``exp(lse_i - lse_total)``.  This is the
     two-call-and-merge scheme of projects/moba_attention/moba/moba_efficient.py:88-417 in the reference, which runs the
     two calls on a variable-length attention library."""
     out = torch.empty_like(q)
@@ -107,39 +99,64 @@ def moba_attn_efficient(q, k, v, cu_seqlens, max_seqlen: int, moba_chunk_size: i
     scale = D ** -0.5
     C = moba_chunk_size
     bounds = cu_seqlens.tolist()
+    neg = float("-inf")
     for s0, e0 in zip(bounds[:-1], bounds[1:]):
         n = e0 - s0
-        q_, k_, v_ = q[s0:e0], k[s0:e0], v[s0:e0]
+        H = q.shape[1]
         nblk = math.ceil(n / C)
-        H = q_.shape[1]
+        pad = nblk * C - n
+        q_, k_, v_ = q[s0:e0].float(), k[s0:e0].float(), v[s0:e0].float()
         with torch.no_grad():
-            allowed = _gate_mask(q_, k_, C, moba_topk)  # [H, n, nblk], own block included
-        pos = torch.arange(n, device=q.device)
-        own_blk = pos // C
-        acc = torch.zeros(n, H, D, dtype=torch.float32, device=q.device)
+            allowed = _gate_mask(q[s0:e0], k[s0:e0], C, moba_topk)  # [H, n, nblk], own block included
+        if pad:
+            zeros = q_.new_zeros(pad, H, D)
+            qp, kp, vp = torch.cat([q_, zeros]), torch.cat([k_, zeros]), torch.cat([v_, zeros])
+        else:
+            qp, kp, vp = q_, k_, v_
+        kb = kp.view(nblk, C, H, D).permute(2, 0, 1, 3)  # [H, nblk, C, D]
+        vb = vp.view(nblk, C, H, D).permute(2, 0, 1, 3)
+        key_ok = (torch.arange(nblk * C, device=q.device) < n).view(nblk, C)  # padding keys of the last block
+
+        # (1) own block, causal: [H, nblk, C, C]
+        qb = qp.view(nblk, C, H, D).permute(2, 0, 1, 3)
+        s_own = torch.matmul(qb, kb.transpose(-1, -2)) * scale
+        tri = torch.ones(C, C, dtype=torch.bool, device=q.device).tril()
+        s_own = s_own.masked_fill(~(tri & key_ok.view(1, nblk, 1, C)), neg)
+        lse_own = torch.logsumexp(s_own, dim=-1)                       # [H, nblk, C]
+        o_own = torch.matmul(torch.exp(s_own - lse_own.unsqueeze(-1)), vb)  # [H, nblk, C, D]
+        lse_own = lse_own.reshape(H, nblk * C)[:, :n]
+        o_own = o_own.reshape(H, nblk * C, D)[:, :n]
+
+        # (2) + (3) per head: queries grouped by the earlier block they selected, merged with the own-block part
+        own_blk = torch.arange(n, device=q.device) // C
+        res = torch.empty(n, H, D, dtype=torch.float32, device=q.device)
         for h in range(H):
-            outs, lses, rows = [], [], []
-            for b in range(nblk):
-                lo, hi = b * C, min(n, (b + 1) * C)
-                kb, vb = k_[lo:hi, h], v_[lo:hi, h]
-                # (1) own block, causal
-                idx = pos[lo:hi]
-                o, l = _partial_attention(q_[lo:hi, h], kb, vb, scale, idx.view(1, -1) <= idx.view(-1, 1))
-                outs.append(o); lses.append(l); rows.append(idx)
-                # (2) queries of later blocks that selected block b
-                sel = torch.nonzero(allowed[h, :, b] & (own_blk > b), as_tuple=False).squeeze(-1)
-                if sel.numel():
-                    o, l = _partial_attention(q_[sel, h], kb, vb, scale)
-                    outs.append(o); lses.append(l); rows.append(sel)
-            rows_cat = torch.cat(rows)
-            lse_cat = torch.cat(lses)
-            out_cat = torch.cat(outs)
-            # (3) merge the partial results of every query by their log-sum-exp (max subtracted for stability)
-            mx = torch.full((n,), float("-inf"), device=q.device).scatter_reduce(0, rows_cat, lse_cat.detach(), "amax")
-            w = torch.exp(lse_cat - mx[rows_cat])
-            denom = torch.zeros(n, device=q.device).index_add(0, rows_cat, w)
-            acc[:, h] = torch.zeros(n, D, device=q.device).index_add(0, rows_cat, out_cat * w.unsqueeze(-1)) / denom.unsqueeze(-1)
-        out[s0:e0] = acc.to(q.dtype)
+            picks = allowed[h] & (own_blk.view(-1, 1) > torch.arange(nblk, device=q.device).view(1, -1))  # [n, nblk]
+            qi, bi = torch.nonzero(picks, as_tuple=True)     # pairs (query, selected block), sorted by query
+            if qi.numel() == 0:
+                res[:, h] = o_own[h]
+                continue
+            order = torch.sort(bi, stable=True).indices
+            qi, bi = qi[order], bi[order]
+            counts = torch.bincount(bi, minlength=nblk)
+            width = int(counts.max())
+            starts = torch.cumsum(counts, 0) - counts
+            col = torch.arange(qi.numel(), device=q.device) - starts[bi]   # position of every pair inside its block group
+            grid = torch.full((nblk, width), n, dtype=torch.long, device=q.device)  # n = "no query" (a zero row)
+            grid[bi, col] = qi
+            q_h = torch.cat([q_[:, h], q_.new_zeros(1, D)])[grid]          # [nblk, width, D]
+            s_sel = torch.matmul(q_h, kb[h].transpose(-1, -2)) * scale     # [nblk, width, C]
+            s_sel = s_sel.masked_fill(~key_ok.view(nblk, 1, C), neg)
+            lse_sel = torch.logsumexp(s_sel, dim=-1)                       # [nblk, width]
+            o_sel = torch.matmul(torch.exp(s_sel - lse_sel.unsqueeze(-1)), vb[h])  # [nblk, width, D]
+            lse_pairs, o_pairs = lse_sel[bi, col], o_sel[bi, col]          # back to the pair list
+            mx = lse_own[h].detach().clone().scatter_reduce(0, qi, lse_pairs.detach(), "amax")
+            w_own = torch.exp(lse_own[h] - mx)
+            w_pairs = torch.exp(lse_pairs - mx[qi])
+            denom = w_own.index_add(0, qi, w_pairs)
+            num = (o_own[h] * w_own.unsqueeze(-1)).index_add(0, qi, o_pairs * w_pairs.unsqueeze(-1))
+            res[:, h] = num / denom.unsqueeze(-1)
+        out[s0:e0] = res.to(q.dtype)
     return out
 
 
