@@ -61,6 +61,11 @@ class SymmetricBuffer:
         self.rank = self.handle.rank
         self.world = self.handle.world_size
 
+    def peer_view(self, rank: int, numel: int, elem_offset: int = 0) -> torch.Tensor:
+        """``numel`` elements of rank ``rank``'s part of this allocation as a tensor on the local device (the peer's
+        memory is mapped into this process)."""
+        return self.handle.get_buffer(rank, (numel,), self.tensor.dtype, elem_offset)
+
 
 class SymmetricContext:
     """Address tables, flags and barrier epochs of one process group."""
@@ -105,6 +110,18 @@ class SymmetricContext:
         """``out[p * n : (p + 1) * n] = peer p's shards[offset : offset + n]`` (pull over NVLink)."""
         _ext.ops().p2p_all_gather(shards.ptrs, shard_elem_offset * out.element_size(), out, shard_numel, self.rank)
         _count(comm="p2p_all_gather")
+
+    def all_gather_copy_engine(self, shards: SymmetricBuffer, shard_elem_offset: int, shard_numel: int, out: torch.Tensor) -> None:
+        """The same gather as :meth:`all_gather`, issued as one asynchronous device-to-device copy per peer: the copies
+        run on the copy engines over NVLink and take no SM from the kernels of the compute stream.  Peers are visited
+        in a rank-dependent order so that no rank is read by everybody at once."""
+        n = shard_numel
+        for step in range(self.world):
+            r = (self.rank + step) % self.world
+            out[r * n : (r + 1) * n].copy_(shards.peer_view(r, n, shard_elem_offset), non_blocking=True)
+        from ..ops.functional import COMM_COUNTER  # copies by the driver: counted as communication, not as kernel launches
+
+        COMM_COUNTER["copy_engine_all_gather"] = COMM_COUNTER.get("copy_engine_all_gather", 0) + self.world
 
     def reduce_scatter_accumulate(self, grads: SymmetricBuffer, elem_offset: int, n: int, acc: torch.Tensor,
                                   scale: float, overwrite: bool, want_sumsq: bool = False) -> torch.Tensor:

@@ -400,12 +400,13 @@ static int grid_for_bytes(int64_t nvec, int threads, int max_waves = 8) {
 
 // CTAs of the bulk copy / reduction kernels that run beside the compute stream (parameter gathers, gradient
 // reductions).  They share the SMs with persistent GEMM CTAs: enough of them to fill the NVLink ports, few enough to
-// leave the issue slots and memory pipes to the math.  ATB200_COMM_CTAS overrides the default.
+// leave the issue slots and memory pipes to the math.  ATB200_COMM_CTAS lowers the default (4 per SM, the largest value
+// these kernels have been run with; larger requests are clamped to it).
 static int comm_cta_cap() {
     static const int cap = [] {
         const char* e = std::getenv("ATB200_COMM_CTAS");
         const int v = e ? std::atoi(e) : 0;
-        return v > 0 ? v : kNumSMs * 4;
+        return v > 0 ? std::min(v, kNumSMs * 4) : kNumSMs * 4;
     }();
     return cap;
 }

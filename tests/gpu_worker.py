@@ -76,6 +76,61 @@ def scenario_fused_vs_nccl(out_dir):
         (Path(out_dir) / "fused_vs_nccl.json").write_text(json.dumps(res))
 
 
+def scenario_copy_engine_gather(out_dir):
+    """ZeRO-3 parameter gathers as peer copies on the copy engines against the pull kernel: the same bytes arrive, so
+    losses and weights agree bit for bit."""
+    os.environ["ATB200_GATHER"] = "kernel"
+    a = make_engine(3, fused=True)
+    assert not a._gather_on_copy_engines
+    la = run(a)
+    pa = {n: t.clone() for n, t in a.iter_full_named_parameters()}
+    os.environ.pop("ATB200_GATHER")
+    b = make_engine(3, fused=True)
+    assert b._gather_on_copy_engines and b.symm is not None
+    lb = run(b)
+    b.symm.check()
+    from arctictraining_b200.ops import COMM_COUNTER
+
+    same = la == lb and all(torch.equal(pa[n], t) for n, t in b.iter_full_named_parameters())
+    allsame = [None] * dist.get_world_size()
+    dist.all_gather_object(allsame, bool(same))
+    if dist.get_rank() == 0:
+        (Path(out_dir) / "copy_engine_gather.json").write_text(json.dumps(
+            {"same": all(allsame), "copies": int(COMM_COUNTER.get("copy_engine_all_gather", 0))}))
+
+
+def scenario_nvls_reduce_scatter(out_dir):
+    """Gradient reduce-scatter with the reduction done inside the NVSwitch (``multimem.ld_reduce`` on the multicast
+    mapping of a symmetric buffer) against the peer-load kernel; reported as unavailable when the fabric offers no
+    multicast mapping."""
+    from arctictraining_b200.comm.symm import SymmetricContext
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    ctx = SymmetricContext(dist.group.WORLD, timeout_s=10.0)
+    n = 8 * 4096
+    buf = ctx.alloc("nvls_test", world * n, torch.bfloat16)
+    res = {"multicast": bool(buf.multicast_ptr)}
+    if buf.multicast_ptr:
+        torch.manual_seed(rank)
+        buf.tensor.copy_(torch.randn(world * n, device="cuda").bfloat16())
+        ctx.barrier(slot=6)
+        k = torch.ops.atb200
+        a = torch.ones(n, device="cuda")
+        sa = k.p2p_reduce_scatter_accum(buf.ptrs, rank * n, n, a, 0.5, False, True)
+        b = torch.ones(n, device="cuda")
+        sb = k.nvls_reduce_scatter_accum(buf.multicast_ptr, rank * n, n, b, 0.5, False, True)
+        ctx.barrier(slot=6)
+        ctx.check()
+        # the switch adds the ranks' bf16 values in its own order and precision: equal up to bf16 rounding of the sum
+        res["max_diff"] = float((a - b).abs().max())
+        res["scale"] = float(a.abs().max())
+        res["sumsq_rel"] = abs(float(sa) - float(sb)) / float(sa)
+    allres = [None] * world
+    dist.all_gather_object(allres, res)
+    if rank == 0:
+        (Path(out_dir) / "nvls_reduce_scatter.json").write_text(json.dumps(allres))
+
+
 def scenario_partly_frozen(out_dir):
     """Layers whose trainable prefix is shorter than one rank's shard (what LoRA or SwiftKV-style freezing produces):
     the ranks behind the frozen tail hold no trainable element of those units and must still take the same
@@ -377,7 +432,8 @@ def main():
     init_distributed(timeout_s=120)
     {"fused_vs_nccl": scenario_fused_vs_nccl, "barrier_timeout": scenario_barrier_timeout, "partly_frozen": scenario_partly_frozen, "gather_gemm": scenario_gather_gemm,
      "ulysses_peer": scenario_ulysses_peer, "moe_peer": scenario_moe_peer,
-     "fused_attention_block": scenario_fused_attention_block, "embed_gather": scenario_embed_gather}[scenario](out_dir)
+     "fused_attention_block": scenario_fused_attention_block, "embed_gather": scenario_embed_gather,
+     "copy_engine_gather": scenario_copy_engine_gather, "nvls_reduce_scatter": scenario_nvls_reduce_scatter}[scenario](out_dir)
     dist.barrier()
     dist.destroy_process_group()
 

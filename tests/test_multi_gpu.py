@@ -83,6 +83,21 @@ def test_attention_block_with_exchanges_inside_the_gemms(tmp_path):
             assert err < 1e-2, (name, err)
 
 
+def test_parameter_gather_on_copy_engines_matches_the_pull_kernel(tmp_path):
+    launch(2, "copy_engine_gather", tmp_path)
+    res = json.loads((tmp_path / "copy_engine_gather.json").read_text())
+    assert res["same"] and res["copies"] > 0
+
+
+def test_in_switch_reduce_scatter_matches_the_peer_load_kernel(tmp_path):
+    launch(2, "nvls_reduce_scatter", tmp_path)
+    per_rank = json.loads((tmp_path / "nvls_reduce_scatter.json").read_text())
+    if not all(r["multicast"] for r in per_rank):
+        pytest.skip("the fabric offers no multicast mapping for symmetric buffers")
+    for r in per_rank:
+        assert r["max_diff"] <= 2e-2 * max(1.0, r["scale"]) and r["sumsq_rel"] < 1e-2, r
+
+
 def test_embedding_gather_through_peer_memory_matches_nccl(tmp_path):
     launch(2, "embed_gather", tmp_path)
     assert json.loads((tmp_path / "embed_gather.json").read_text())["ok"]
