@@ -209,6 +209,15 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
             return bool(cfg.get("num_experts") if isinstance(cfg, dict) else getattr(cfg, "num_experts", 0))
         return bool(flag)
 
+    def _config_for_logging(self) -> dict:
+        """The recipe as plain JSON types (enum members with non-JSON values, e.g. ``torch.dtype``, become strings)."""
+        try:
+            return self.config.model_dump(mode="json", fallback=str)
+        except TypeError:  # pydantic without the ``fallback`` argument
+            import json
+
+            return json.loads(json.dumps(self.config.model_dump(), default=str))
+
     def _init_wandb(self) -> None:
         if self.global_rank != 0 or not self.config.wandb.enable:
             return
@@ -218,7 +227,7 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
             self.wandb_run_id = wandb.util.generate_id()
         self.wandb_experiment = wandb.init(
             id=self.wandb_run_id, entity=self.config.wandb.entity, project=self.config.wandb.project,
-            name=self.config.wandb.name, config=self.config.model_dump(mode="json"),
+            name=self.config.wandb.name, config=self._config_for_logging(),
             dir=f"{self.config.logger.output_dir}/wandb", resume="allow",
         )
 

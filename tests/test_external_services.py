@@ -190,3 +190,45 @@ def test_ray_launcher_moves_relative_outputs_under_the_job_stage(monkeypatch):
     out = stage_paths_from_env(cfg)
     assert out["checkpoint"][0]["output_dir"] == "/mnt/stage/results/ckpts/run1"
     assert out["checkpoint"][1]["output_dir"] == "/abs/elsewhere"
+
+
+def test_wandb_run_receives_config_metrics_and_finish(tiny_recipe, monkeypatch, tmp_path):
+    """Weights & Biases logging against a fake ``wandb`` module: one run is opened with the recipe as its config, the
+    step metrics arrive with the step number, the run is finished, and its id survives in the checkpoint state so that
+    a resumed job continues the same run (the reference keeps this in arctic_training/trainer/trainer.py:305-330)."""
+    import sys
+    import types
+
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    calls = {"init": [], "log": [], "finish": 0}
+
+    class Run:
+        def log(self, data, step=None):
+            calls["log"].append((dict(data), step))
+
+        def finish(self):
+            calls["finish"] += 1
+
+    fake = types.ModuleType("wandb")
+    fake.util = types.SimpleNamespace(generate_id=lambda: "run123")
+    fake.init = lambda **kw: (calls["init"].append(kw), Run())[1]
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+
+    import yaml
+
+    r = tiny_recipe(exit_iteration=4, train_log_iter_interval=1, wandb={"enable": True, "project": "proj", "name": "unit"})
+    p = tmp_path / "wandb.yaml"
+    p.write_text(yaml.safe_dump(r))
+    cfg = get_config(p)
+    tr = get_registered_trainer(cfg.type)(cfg)
+    tr.train()
+    assert len(calls["init"]) == 1
+    init = calls["init"][0]
+    assert init["project"] == "proj" and init["name"] == "unit" and init["id"] == "run123" and init["resume"] == "allow"
+    assert init["config"]["type"] == "sft" and init["config"]["model"]["name_or_path"] == "tiny-llama"
+    steps = [s for _, s in calls["log"]]
+    assert steps and steps == sorted(steps) and all("loss" in d for d, _ in calls["log"])
+    assert calls["finish"] == 1
+    assert tr.wandb_run_id == "run123"

@@ -205,3 +205,32 @@ def test_callbacks_declared_on_a_custom_trainer_fire(tiny_recipe):
     tr = build(tiny_recipe(type="counting-sft-test", exit_iteration=2))
     tr.train()
     assert seen == ["loss", 1, "loss", 2]
+
+
+def test_cli_run_with_autocast_and_bf16_states(tiny_recipe, tmp_path):
+    """The reference's autocast test (tests/trainer/test_autocast.py:30-113) through the real command line: ZeRO-3,
+    bf16 master weights / gradients / optimizer states and ``torch_autocast``; both iterations are logged and the first
+    loss is sane."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    import yaml
+
+    root = Path(__file__).resolve().parent.parent
+    r = tiny_recipe(exit_iteration=2, train_log_iter_interval=1, micro_batch_size=1, logger={"level": "INFO"})
+    r["deepspeed"] = {"zero_optimization": {"stage": 3},
+                      "bf16": {"enabled": True, "bf16_master_weights_and_grads": True, "bf16_optimizer_states": True},
+                      "torch_autocast": {"enabled": True, "dtype": "torch.bfloat16"}}
+    r["model"]["dtype"] = "bf16"
+    path = tmp_path / "autocast.yaml"
+    path.write_text(yaml.safe_dump(r))
+    res = subprocess.run([sys.executable, "-m", "arctictraining_b200.cli", str(path), "--num_gpus", "1", "--master_port", "29733"],
+                         cwd=root, env={**os.environ, "PYTHONPATH": str(root)}, capture_output=True, text=True, timeout=600)
+    out = res.stdout + res.stderr
+    assert res.returncode == 0, out[-3000:]
+    assert "iter: 1/2" in out and "iter: 2/2" in out and "iter: 3/2" not in out
+    logs = [json.loads(x) for x in Path(r["train_log_metrics_path"]).read_text().splitlines() if x.strip()]
+    assert logs[0]["iter"] == 1 and 0 < logs[0]["loss"] < 20
