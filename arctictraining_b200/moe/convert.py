@@ -171,10 +171,70 @@ def convert_to_arctic_moe(model: nn.Module, groups: Any, is_resume: bool = False
             if cfg.use_shared_expert:
                 new.shared_expert_gate_up.copy_(moe.shared_expert_gate_up)
                 new.shared_expert_down.copy_(moe.shared_expert_down)
-                new.shared_expert_output_gate.copy_(moe.shared_expert_output_gate)
+                if cfg.shared_expert_gated:
+                    new.shared_expert_output_gate.copy_(moe.shared_expert_output_gate)
         layer.mlp = new
         del moe
         n += 1
+    return n
+
+
+# ------------------------------------------------------------------ Hugging Face sparse blocks -> ArcticMoE
+def _is_hf_sparse_block(m: nn.Module) -> bool:
+    experts, gate = getattr(m, "experts", None), getattr(m, "gate", None)
+    return (experts is not None and gate is not None and not isinstance(m, ArcticMoE)
+            and hasattr(experts, "gate_up_proj") and hasattr(experts, "down_proj") and hasattr(gate, "weight"))
+
+
+def arctic_moe_from_hf_block(block: nn.Module, ep_size: int = 1, ep_rank: int = 0, ep_group: Any = None,
+                             loss_coeff: float = 0.0) -> ArcticMoE:
+    """ArcticMoE with the weights of a ``transformers`` sparse MoE block of the Qwen family (Qwen2-MoE, Qwen3-MoE,
+    Qwen3-Next: ``gate.weight [E, H]``, ``experts.gate_up_proj [E, 2I, H]`` with the gate rows first,
+    ``experts.down_proj [E, H, I]``, optionally ``shared_expert`` + ``shared_expert_gate``).  With ``ep_size > 1`` the
+    new block holds this rank's experts only.  Reference: arctic_training/model/moe/utils.py:75-232."""
+    from .layer import MoEConfig
+
+    experts, gate = block.experts, block.gate
+    gu, down = experts.gate_up_proj.data, experts.down_proj.data
+    E, two_i, H = gu.shape
+    shared = getattr(block, "shared_expert", None)
+    cfg = MoEConfig(
+        model_dim=H, intermediate_dim=two_i // 2, num_experts=E, top_k=int(gate.top_k),
+        normalize_topk_scores=bool(getattr(gate, "norm_topk_prob", True)), loss_coeff=float(loss_coeff),
+        use_shared_expert=shared is not None,
+        shared_intermediate_dim=int(shared.gate_proj.weight.shape[0]) if shared is not None else 0,
+        shared_expert_gated=hasattr(block, "shared_expert_gate"),
+        ep_size=ep_size, ep_rank=ep_rank, ep_group=ep_group, input_dtype=gu.dtype,
+    )
+    moe = ArcticMoE(cfg, dtype=gu.dtype, device=gu.device)
+    lo, hi = moe.local_expert_indices.start, moe.local_expert_indices.stop
+    with torch.no_grad():
+        moe.router_gate.copy_(gate.weight.data)
+        for i, e in enumerate(range(lo, hi)):
+            g, u = gu[e].chunk(2, dim=0)
+            moe.expert_gate_up[i].copy_(ref.interleave_gate_up_rows(g, u))
+        moe.expert_down.copy_(down[lo:hi])
+        if shared is not None:
+            moe.shared_expert_gate_up.copy_(ref.interleave_gate_up_rows(shared.gate_proj.weight.data, shared.up_proj.weight.data))
+            moe.shared_expert_down.copy_(shared.down_proj.weight.data)
+            if cfg.shared_expert_gated:
+                moe.shared_expert_output_gate.copy_(block.shared_expert_gate.weight.data)
+    return moe
+
+
+def convert_hf_blocks_to_arctic_moe(model: nn.Module, groups: Any = None, loss_coeff: float = 0.0) -> int:
+    """Replace every ``transformers`` sparse MoE block of ``model`` (a model built by the ``transformers`` fallback of
+    the model factory, e.g. Qwen3-Next) by an :class:`ArcticMoE` with the same weights, sharded for the run's
+    expert-parallel degree.  Returns the number of blocks replaced."""
+    ep_size = getattr(groups, "ep_size", 1) if groups is not None else 1
+    ep_rank = getattr(groups, "ep_rank", 0) if groups is not None else 0
+    ep_group = getattr(groups, "ep_group", None) if groups is not None else None
+    n = 0
+    for parent in list(model.modules()):
+        for name, child in list(parent.named_children()):
+            if _is_hf_sparse_block(child):
+                setattr(parent, name, arctic_moe_from_hf_block(child, ep_size, ep_rank, ep_group, loss_coeff))
+                n += 1
     return n
 
 

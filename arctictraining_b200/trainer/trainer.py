@@ -148,8 +148,13 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
 
         self.use_arctic_moe = self._resolve_arctic_moe()
         if self.use_arctic_moe:
+            from ..moe.convert import convert_hf_blocks_to_arctic_moe
             from ..moe.convert import convert_to_arctic_moe
 
+            # a model of the ``transformers`` fallback (e.g. Qwen3-Next) still carries the library's sparse blocks
+            replaced = convert_hf_blocks_to_arctic_moe(self.model, self.groups)
+            if replaced:
+                logger.info(f"replaced {replaced} transformers sparse MoE blocks by ArcticMoE")
             convert_to_arctic_moe(
                 self.model, self.groups, is_resume=self.is_resume,
                 use_fused_kernels=config.enable_arctic_moe_custom_optimization,
@@ -206,7 +211,8 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
         flag = self.config.arctic_moe
         if flag == "auto":
             cfg = getattr(self.model, "config", {})
-            return bool(cfg.get("num_experts") if isinstance(cfg, dict) else getattr(cfg, "num_experts", 0))
+            get = cfg.get if isinstance(cfg, dict) else (lambda k, d=None: getattr(cfg, k, d))
+            return bool(get("num_experts") or get("num_local_experts") or get("n_routed_experts"))
         return bool(flag)
 
     def _config_for_logging(self) -> dict:

@@ -170,3 +170,36 @@ def test_gpt_oss_stacked_expert_layout_round_trips_and_keeps_the_math():
     gate, up = z[:, 0::2], z[:, 1::2]
     want = (gate * torch.sigmoid(1.702 * gate) * up) @ down[0]
     torch.testing.assert_close(y, want, atol=1e-3, rtol=1e-4)
+
+
+@pytest.mark.parametrize("family", ["qwen3_moe", "qwen2_moe"])
+def test_transformers_sparse_blocks_convert_to_arctic_moe_with_equal_logits(family):
+    """A ``transformers`` model of the Qwen MoE families (the path other architectures take through the model factory)
+    gives the same logits after its sparse blocks have been replaced by ArcticMoE blocks — router, experts, and for
+    Qwen2-MoE / Qwen3-Next the sigmoid-gated shared expert."""
+    transformers = pytest.importorskip("transformers")
+    from arctictraining_b200.moe.convert import convert_hf_blocks_to_arctic_moe
+    from arctictraining_b200.moe.layer import ArcticMoE
+
+    common = dict(hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                  vocab_size=256, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64, norm_topk_prob=True,
+                  decoder_sparse_step=1, mlp_only_layers=[], max_position_embeddings=128)
+    if family == "qwen3_moe":
+        cfg = transformers.Qwen3MoeConfig(**common, head_dim=16)
+        model = transformers.Qwen3MoeForCausalLM(cfg)
+    else:
+        cfg = transformers.Qwen2MoeConfig(**common, shared_expert_intermediate_size=64)
+        model = transformers.Qwen2MoeForCausalLM(cfg)
+    torch.manual_seed(0)
+    with torch.no_grad():
+        for p in model.parameters():
+            p.normal_(0, 0.05)
+    model = model.float().eval()
+    ids = torch.randint(0, 256, (2, 10))
+    with torch.no_grad():
+        want = model(input_ids=ids).logits
+        assert convert_hf_blocks_to_arctic_moe(model) == 2
+        assert all(isinstance(layer.mlp, ArcticMoE) for layer in model.model.layers)
+        model.eval()
+        got = model(input_ids=ids).logits
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-3), float((got - want).abs().max())
