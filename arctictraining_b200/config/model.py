@@ -61,11 +61,11 @@ class ModelConfig(BaseConfig):
             if "peft_type" not in value:
                 raise ValueError("No 'peft_type' specified in PEFT config.")
             from ..models.peft import SUPPORTED_PEFT_TYPES
+            from ..models.peft import library_peft_types
 
-            if str(value["peft_type"]).upper() not in SUPPORTED_PEFT_TYPES:
-                raise ValueError(
-                    f"PEFT type {value['peft_type']} config not found. Valid PEFT types are: {SUPPORTED_PEFT_TYPES}"
-                )
+            valid = list(SUPPORTED_PEFT_TYPES) + [t for t in library_peft_types() if t not in SUPPORTED_PEFT_TYPES]
+            if str(value["peft_type"]).upper() not in valid:
+                raise ValueError(f"PEFT type {value['peft_type']} config not found. Valid PEFT types are: {valid}")
         return value
 
     @field_validator("attn_implementation", mode="after")

@@ -148,9 +148,20 @@ class HFModelFactory(ModelFactory):
 
     def post_create_model_callback(self, model):
         if self.config.peft_config is not None:
+            from .causal_lm import CausalLM
+            from .peft import SUPPORTED_PEFT_TYPES
+            from .peft import apply_library_peft
             from .peft import apply_lora
 
-            trainable, total = apply_lora(model, self.config.peft_config)
+            kind = str(self.config.peft_config["peft_type"]).upper()
+            if isinstance(model, CausalLM) or getattr(model, "model", None).__class__.__module__.startswith("arctictraining_b200"):
+                if kind not in SUPPORTED_PEFT_TYPES:
+                    raise ValueError(f"PEFT type {kind} is not available on the native models (supported: {SUPPORTED_PEFT_TYPES})")
+                trainable, total = apply_lora(model, self.config.peft_config)
+            else:
+                model = apply_library_peft(model, self.config.peft_config)
+                trainable = sum(p.numel() for p in model.parameters() if p.requires_grad)
+                total = sum(p.numel() for p in model.parameters())
             logger.info(f"Applied PEFT config: total params {total}, trainable {trainable} ({100 * trainable / total:.2f}%)")
         model.activation_checkpointing = not self.config.disable_activation_checkpoint
         if hasattr(model, "gradient_checkpointing_enable") and not self.config.disable_activation_checkpoint:

@@ -28,7 +28,28 @@ from typing import Tuple
 import torch
 import torch.nn as nn
 
-SUPPORTED_PEFT_TYPES = ["LORA"]
+SUPPORTED_PEFT_TYPES = ["LORA"]  # on the native models; others only through the ``peft`` package on transformers models
+
+
+def library_peft_types() -> List[str]:
+    """Adapter types the installed ``peft`` package offers (empty without the package); usable on models that the
+    factory builds through ``transformers``."""
+    try:
+        import peft
+    except ImportError:
+        return []
+    mapping = getattr(peft, "PEFT_TYPE_TO_CONFIG_MAPPING", None) or getattr(getattr(peft, "mapping", None), "PEFT_TYPE_TO_CONFIG_MAPPING", {})
+    return [str(getattr(k, "value", k)).upper() for k in mapping]
+
+
+def apply_library_peft(model: nn.Module, cfg: Dict[str, Any]) -> nn.Module:
+    """Wrap a ``transformers`` model with the ``peft`` package (any adapter type it knows), as the reference does
+    (arctic_training/model/hf_factory.py:77-84)."""
+    import peft
+
+    conf = dict(cfg)
+    conf["peft_type"] = str(conf["peft_type"]).upper()
+    return peft.get_peft_model(model, peft.get_peft_config(conf))
 _FUSED = {
     "q_proj": "qkv_proj", "k_proj": "qkv_proj", "v_proj": "qkv_proj",
     "gate_proj": "gate_up_proj", "up_proj": "gate_up_proj",
