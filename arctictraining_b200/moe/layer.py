@@ -107,6 +107,9 @@ class ArcticMoE(nn.Module):
             self.shared_expert_down = nn.Parameter(torch.empty(H, Is, dtype=dtype, device=device))
             if c.shared_expert_gated:
                 self.shared_expert_output_gate = nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+        from .timers import StageTimers
+
+        self.timers = StageTimers()
         self.replay_assignments: Optional[torch.Tensor] = None
         self.recorded_assignments: Optional[torch.Tensor] = None
         self.last_expert_counts: Optional[torch.Tensor] = None
@@ -169,22 +172,35 @@ class ArcticMoE(nn.Module):
         shp = hidden_states.shape
         x = hidden_states.reshape(-1, shp[-1])
         T = x.shape[0]
+        tm, gpu = self.timers, x.is_cuda
+        tm.start("amoe e2e", gpu)
+        tm.start("router", gpu)
         scores, experts = self.route(x)
+        tm.stop("router", gpu)
         if self.ep_size == 1:
+            tm.start("dispatch", gpu)
             slots, counts, offsets = mops.assign_slots(experts, self.num_experts, SEGMENT_ALIGN)
             rows = T * self.top_k + self.num_experts * (SEGMENT_ALIGN - 1)
             rows = (rows + SEGMENT_ALIGN - 1) // SEGMENT_ALIGN * SEGMENT_ALIGN
             permuted = mops.scatter_rows(x, slots, rows)
+            tm.stop("dispatch", gpu)
+            tm.start("experts", gpu)
             y = grouped_mlp(permuted, offsets, self.expert_gate_up, self.expert_down, self._config.act_fn)
+            tm.stop("experts", gpu)
+            tm.start("combine", gpu)
             out = mops.gather_rows(y, slots, scores)
+            tm.stop("combine", gpu)
         else:
             out = self._forward_ep(x, scores, experts)
         self.last_expert_counts = None
         if self._config.use_shared_expert:
+            tm.start("shared-expert", gpu)
             sh = F.linear(ops.swiglu_interleaved(F.linear(x, self.shared_expert_gate_up)), self.shared_expert_down)
             if self._config.shared_expert_gated:
                 sh = torch.sigmoid(F.linear(x, self.shared_expert_output_gate)) * sh
             out = out + sh
+            tm.stop("shared-expert", gpu)
+        tm.stop("amoe e2e", gpu)
         return out.view(shp)
 
     def _forward_ep(self, x: torch.Tensor, scores: torch.Tensor, experts: torch.Tensor) -> torch.Tensor:
@@ -198,10 +214,21 @@ class ArcticMoE(nn.Module):
 
             ex = exchange_for(self.ep_group)
             if ex is not None:
-                return peer_expert_forward(
-                    x, scores, experts, self.num_experts, ex, SEGMENT_ALIGN,
-                    lambda tokens, seg: grouped_mlp(tokens, seg, self.expert_gate_up, self.expert_down, self._config.act_fn),
-                ).to(x.dtype)
+                tm = self.timers
+
+                def run_experts(tokens, seg):
+                    # the dispatch ends and the combine starts where the local experts run
+                    tm.stop("dispatch", True)
+                    tm.start("experts", True)
+                    y = grouped_mlp(tokens, seg, self.expert_gate_up, self.expert_down, self._config.act_fn)
+                    tm.stop("experts", True)
+                    tm.start("combine", True)
+                    return y
+
+                tm.start("dispatch", True)
+                out = peer_expert_forward(x, scores, experts, self.num_experts, ex, SEGMENT_ALIGN, run_experts).to(x.dtype)
+                tm.stop("combine", True)
+                return out
         slots, counts, _ = mops.assign_slots(experts, self.num_experts, 1)
         send = mops.scatter_rows(x, slots, T * K)
         # counts[src][e] for my local experts from every source rank
@@ -212,6 +239,7 @@ class ArcticMoE(nn.Module):
         send_splits = counts.view(P, El).sum(1)
         recv_splits = recv_counts.view(P, El).sum(1)
         splits = torch.stack([send_splits, recv_splits]).tolist()  # the one host sync of the baseline path
+        self.timers.record_token_counts(splits[1], splits[0])
         recv = all_to_all_v(send, splits[0], splits[1], self.ep_group)
         # regroup: received rows are ordered (src, expert); build expert-major aligned slots for them
         n_recv = recv.shape[0]

@@ -166,6 +166,10 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
         self.scheduler = config.scheduler.factory(self)()
         self.model = self._create_engine(self.model, self.optimizer, self.scheduler)
         self.ds_wall_clock_available = hasattr(self.model, "get_wall_clock_timers")
+        if self.use_arctic_moe and self.ds_wall_clock_available and self.model.wall_clock_breakdown():
+            from ..moe.timers import enable_moe_timers
+
+            enable_moe_timers(self.model_unwrapped)
 
         if config.sequence_parallel_size > 1:
             self.train_dataloader = UlyssesDataLoaderAdapter(
@@ -385,6 +389,14 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
                 record = dict(self.metrics.summary_dict)
                 if self.ds_wall_clock_available and self.model.wall_clock_breakdown():
                     record.update(self.model.get_wall_clock_timers().snapshot())
+                    if self.use_arctic_moe:
+                        from ..moe.timers import format_breakdown
+                        from ..moe.timers import forward_breakdown
+
+                        moe_times = forward_breakdown(self.model_unwrapped)
+                        if moe_times:
+                            logger.info(format_breakdown(moe_times))
+                            record.update({f"amoe/{k}": v for k, v in moe_times.items()})
                 append_json_file(self.config.train_log_metrics_path, record)
                 if self.wandb_experiment is not None and self.global_step > 1:
                     self.wandb_experiment.log({k: v for k, v in record.items() if k != "iter"}, step=self.global_step)

@@ -203,3 +203,34 @@ def test_transformers_sparse_blocks_convert_to_arctic_moe_with_equal_logits(fami
         model.eval()
         got = model(input_ids=ids).logits
     assert torch.allclose(got, want, atol=1e-4, rtol=1e-3), float((got - want).abs().max())
+
+
+def test_stage_timers_report_every_stage_once_enabled():
+    from arctictraining_b200.moe.layer import ArcticMoE
+    from arctictraining_b200.moe.layer import MoEConfig
+    from arctictraining_b200.moe.timers import enable_moe_timers
+    from arctictraining_b200.moe.timers import format_breakdown
+    from arctictraining_b200.moe.timers import forward_breakdown
+
+    torch.manual_seed(0)
+    model = torch.nn.Sequential(
+        ArcticMoE(MoEConfig(model_dim=32, intermediate_dim=64, num_experts=4, top_k=2, use_shared_expert=True,
+                            shared_intermediate_dim=64, input_dtype=torch.float32), dtype=torch.float32),
+        ArcticMoE(MoEConfig(model_dim=32, intermediate_dim=64, num_experts=4, top_k=2, input_dtype=torch.float32), dtype=torch.float32),
+    )
+    for p in model.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    x = torch.randn(2, 6, 32)
+    model(x)
+    assert forward_breakdown(model) == {}          # off by default: nothing recorded, nothing synchronised
+    assert enable_moe_timers(model) == 2
+    model(x)
+    model(x)
+    report = forward_breakdown(model)
+    assert set(report) == {"amoe e2e", "router", "dispatch", "experts", "combine", "shared-expert"}
+    assert report["amoe e2e"] >= report["experts"] > 0
+    assert model[0].timers.calls == {} and forward_breakdown(model) == {}   # the report resets the sums
+    line = format_breakdown(report)
+    assert line.startswith("AMoE time (ms) | amoe e2e: ") and "experts:" in line
+    model[0].timers.record_token_counts([5, 9, 2], [4, 4, 8])
+    assert forward_breakdown(model)["tokens/max_rcv_count_per_rank"] == 9
