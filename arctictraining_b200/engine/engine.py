@@ -146,6 +146,7 @@ class TrainingEngine:
         self.training_mode = training
         self.device = next(model.parameters()).device
         self.on_gpu = self.device.type == "cuda"
+        self._nvtx = self.on_gpu and os.getenv("ATB200_NVTX", "0") == "1"
         self.dist_on = dist.is_initialized() and dist.get_world_size() > 1
         self.dp_group = dp_group
         self.expert_dp_group = expert_dp_group
@@ -984,15 +985,22 @@ class TrainingEngine:
         """``wall_clock_breakdown``: device-timed sections ``forward`` / ``backward`` / ``step`` on the compute stream and
         ``gather`` / ``reduce`` on the communication stream (milliseconds, merged into the trainer's JSONL metrics as
         the reference merges its engine's wall-clock timers, arctic_training/trainer/trainer.py:603-605)."""
-        if not self.cfg.wall_clock_breakdown:
-            yield
-            return
-        t = self.timers(name)
-        t.start()
+        nvtx = self._nvtx
+        if nvtx:
+            torch.cuda.nvtx.range_push(f"atb200/{name}")  # ATB200_NVTX=1: phases show up as ranges in a system trace
         try:
-            yield
+            if not self.cfg.wall_clock_breakdown:
+                yield
+                return
+            t = self.timers(name)
+            t.start()
+            try:
+                yield
+            finally:
+                t.stop()
         finally:
-            t.stop()
+            if nvtx:
+                torch.cuda.nvtx.range_pop()
 
     def forward(self, *args, **kwargs):
         with self._timed("forward"), self.autocast():
