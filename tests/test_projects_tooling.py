@@ -113,3 +113,11 @@ def test_ci_helpers_resolve_extras_upgrade_user_code_and_check_licences(tmp_path
            "model": {"name_or_path": "org/model"}, "tokenizer": {"name_or_path": "org/model"}}
     assert list(prefetch_assets.iter_sources(cfg)) == [("org/ds", None, {}), ("org/other", "train[:10]", {"name": "x"})]
     assert prefetch_assets.model_ids(cfg) == ["org/model"]
+
+
+def test_recipe_reference_is_up_to_date():
+    """``docs/config.md`` is generated from the configuration classes; a field added without regenerating fails here."""
+    import subprocess
+
+    res = subprocess.run([sys.executable, str(ROOT / "docs" / "gen_config_reference.py"), "--check"], cwd=ROOT)
+    assert res.returncode == 0, "run `python docs/gen_config_reference.py`"
