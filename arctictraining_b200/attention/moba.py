@@ -14,7 +14,6 @@ the partial results merged by their log-sum-exp — work and memory ``O(seqlen x
 from __future__ import annotations
 
 import math
-from typing import Optional
 
 import torch
 

@@ -15,8 +15,6 @@ from __future__ import annotations
 
 import os
 from typing import Dict
-from typing import List
-from typing import Optional
 
 import torch
 import torch.distributed as dist

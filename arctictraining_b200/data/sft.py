@@ -25,7 +25,6 @@ from typing import Tuple
 import torch
 from pydantic import Field
 from pydantic import model_validator
-from torch.utils.data import DataLoader
 from typing_extensions import Self
 
 from ..config.data import DataConfig

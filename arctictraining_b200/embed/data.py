@@ -13,10 +13,8 @@ and parquet decoding with the training step, and padding is one vectorised scatt
 
 from __future__ import annotations
 
-import math
 from concurrent.futures import ThreadPoolExecutor
 from dataclasses import dataclass
-from pathlib import Path
 from typing import Any
 from typing import Dict
 from typing import Iterator

@@ -13,7 +13,6 @@ import json
 from dataclasses import asdict
 from dataclasses import dataclass
 from pathlib import Path
-from typing import Any
 from typing import Tuple
 
 import torch

@@ -26,7 +26,6 @@ Design
 
 from __future__ import annotations
 
-import math
 import os
 import time
 from contextlib import contextmanager

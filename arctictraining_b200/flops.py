@@ -13,7 +13,6 @@ from __future__ import annotations
 
 from typing import Any
 from typing import Iterable
-from typing import List
 from typing import Sequence
 from typing import Tuple
 

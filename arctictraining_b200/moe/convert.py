@@ -31,7 +31,6 @@ from ..models import hf_io
 from ..models.arch import ArchConfig
 from ..ops import reference as ref
 from .layer import ArcticMoE
-from .layer import build_moe_block
 
 _EXPERT_RE = re.compile(r"^(.*mlp\.)experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$")
 

@@ -7,7 +7,6 @@ whenever the tensors live on a GPU) and the PyTorch reference in :mod:`.referenc
 
 from __future__ import annotations
 
-import math
 import os
 from typing import Optional
 from typing import Tuple

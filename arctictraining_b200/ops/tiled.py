@@ -11,7 +11,6 @@ from __future__ import annotations
 
 import math
 import types
-from typing import List
 
 import torch
 import torch.nn as nn

@@ -25,7 +25,6 @@ from typing import Type
 from typing import Union
 from typing import get_args
 from typing import get_origin
-from typing import get_type_hints
 
 from .exceptions import RegistryError
 from .exceptions import RegistryValidationError

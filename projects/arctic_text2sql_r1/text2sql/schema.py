@@ -14,7 +14,6 @@ import random
 import re
 import sqlite3
 from typing import Dict
-from typing import Iterable
 from typing import List
 from typing import Optional
 from typing import Sequence

@@ -18,9 +18,7 @@ from collections import Counter
 from collections import defaultdict
 from pathlib import Path
 from typing import Dict
-from typing import Iterable
 from typing import List
-from typing import Sequence
 from typing import Tuple
 
 _TOKEN = re.compile(r"[A-Za-z0-9]+|[^\sA-Za-z0-9]")

@@ -19,7 +19,6 @@ as differentiable inputs of the checkpointed unit; and the student starts from t
 
 from __future__ import annotations
 
-import math
 from typing import Any
 from typing import Dict
 from typing import List
