@@ -1,24 +1,66 @@
 # SPDX-License-Identifier: Apache-2.0
-"""Import-name compatibility: ``import arctic_training`` resolves to :mod:`arctictraining_b200`, so user
-``train.py`` files and recipes written against the reference's package name keep working."""
+"""Import-name compatibility: ``import arctic_training`` resolves to :mod:`arctictraining_b200`, so user ``train.py``
+files, recipes and tests written against the reference's package name keep working — including the reference's module
+paths (``arctic_training.trainer.sft_trainer``, ``arctic_training.checkpoint.ds_engine``,
+``arctic_training.model.hf_factory`` ...).  An import hook hands out the module of this package that holds the same
+classes; nothing is executed twice, so classes register once."""
 
 import importlib
+import importlib.abc
+import importlib.machinery
 import sys
 
 import arctictraining_b200 as _impl
 from arctictraining_b200 import *  # noqa: F401,F403
 
-_ALIASES = {
-    "registry": "registry", "config": "config", "callback": "callback", "logging": "logging", "metrics": "metrics",
-    "trainer": "trainer", "data": "data", "tokenizer": "tokenizer", "optimizer": "optimizer", "scheduler": "scheduler",
-    "checkpoint": "checkpoint", "model": "models", "debug": "debug", "exceptions": "exceptions", "utils": "utils.misc",
-    "synth": "synth", "launcher": "launcher",
+_PREFIX = "arctic_training."
+# reference module path (below ``arctic_training.``) -> module of this package (below ``arctictraining_b200.``)
+_MODULES = {
+    "trainer.sft_trainer": "trainer.sft", "trainer.causal_trainer": "trainer.sft", "trainer.dpo_trainer": "trainer.dpo",
+    "checkpoint.ds_engine": "checkpoint.sharded", "checkpoint.hf_engine": "checkpoint.hf",
+    "data.sft_factory": "data.sft", "data.causal_factory": "data.causal", "data.dpo_factory": "data.dpo",
+    "data.hf_source": "data.hf_sources", "data.hf_instruct_source": "data.hf_sources", "data.hf_causal_source": "data.hf_sources",
+    "data.snowflake_source": "data.snowflake",
+    "model": "models", "model.factory": "models.factory", "model.hf_factory": "models.factory",
+    "model.liger_factory": "models.factory", "model.moe": "moe", "model.moe.moe": "moe.layer", "model.moe.utils": "moe.convert",
+    "model.moe.timers": "moe.timers", "model.tiled_compute": "ops.tiled",
+    "optimizer.adam_factory": "optimizer.adam",
+    "scheduler.hf_factory": "scheduler.factory", "scheduler.wsd_factory": "scheduler.factory",
+    "tokenizer.hf_factory": "tokenizer.factory",
+    "utils": "utils.misc", "trainer.flops_counter": "flops",
 }
-for _old, _new in _ALIASES.items():
-    try:
-        sys.modules[f"arctic_training.{_old}"] = importlib.import_module(f"arctictraining_b200.{_new}")
-    except ImportError:
+
+
+def _resolve(fullname: str):
+    rest = fullname[len(_PREFIX):]
+    for cand in (_MODULES.get(rest), rest):
+        if cand is None:
+            continue
+        try:
+            return importlib.import_module(f"arctictraining_b200.{cand}")
+        except ImportError:
+            continue
+    return None
+
+
+class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
+    def find_spec(self, fullname, path=None, target=None):
+        if not fullname.startswith(_PREFIX):
+            return None
+        module = _resolve(fullname)
+        if module is None:
+            return None
+        return importlib.machinery.ModuleSpec(fullname, self, is_package=hasattr(module, "__path__"))
+
+    def create_module(self, spec):
+        return _resolve(spec.name)  # the very module object of this package: its classes are the registered ones
+
+    def exec_module(self, module):
         pass
+
+
+if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
+    sys.meta_path.insert(0, _AliasFinder())
 for _name in dir(_impl):
     if not _name.startswith("__"):
         globals().setdefault(_name, getattr(_impl, _name))

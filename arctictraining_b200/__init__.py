@@ -4,6 +4,7 @@ ArcticTraining (arctic_training/__init__.py:20-57): YAML recipes, registry-drive
 callbacks, Hugging Face and sharded checkpoints."""
 
 from .callback.callback import Callback
+from .checkpoint.engine import CheckpointEngine
 from .checkpoint.hf import HFCheckpointEngine
 from .checkpoint.sharded import DSCheckpointEngine
 from .config.checkpoint import CheckpointConfig

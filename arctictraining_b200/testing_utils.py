@@ -28,6 +28,27 @@ import torch
 DEFAULT_MASTER_PORT = 10999
 
 
+def write_file(path, content: str, mode: str = "w") -> None:
+    """Write ``content`` to ``path``, creating the parent directories."""
+    from pathlib import Path
+
+    Path(path).parent.mkdir(parents=True, exist_ok=True)
+    with open(path, mode, encoding="utf-8") as f:
+        f.write(content)
+
+
+def read_json_file(path):
+    from .utils.misc import read_json_file as _read
+
+    return _read(path)
+
+
+def is_flash_attn_2_available() -> bool:
+    import importlib.util
+
+    return importlib.util.find_spec("flash_attn") is not None and torch.cuda.is_available()
+
+
 def get_xdist_worker_id() -> int:
     return int(os.environ.get("PYTEST_XDIST_WORKER", "gw0").replace("gw", "") or 0)
 

@@ -165,3 +165,40 @@ def test_builtin_names_are_registered():
         r.get_registered_scheduler_factory(n)
     for n in ("huggingface", "fake"):
         r.get_registered_tokenizer_factory(n)
+
+
+def test_module_paths_of_the_reference_resolve_to_this_package():
+    """User code imports the reference by its module paths; every one of them yields the (once registered) class of
+    this package."""
+    import importlib
+
+    import arctic_training
+    import arctictraining_b200 as impl
+
+    pairs = [
+        ("arctic_training.trainer.sft_trainer", "SFTTrainer", impl.SFTTrainer),
+        ("arctic_training.trainer.causal_trainer", "CausalTrainer", impl.CausalTrainer),
+        ("arctic_training.trainer.dpo_trainer", "DPOTrainer", impl.DPOTrainer),
+        ("arctic_training.trainer.trainer", "Trainer", impl.Trainer),
+        ("arctic_training.checkpoint.ds_engine", "DSCheckpointEngine", impl.DSCheckpointEngine),
+        ("arctic_training.checkpoint.hf_engine", "HFCheckpointEngine", impl.HFCheckpointEngine),
+        ("arctic_training.checkpoint.engine", "CheckpointEngine", impl.CheckpointEngine),
+        ("arctic_training.model.hf_factory", "HFModelFactory", impl.HFModelFactory),
+        ("arctic_training.model.liger_factory", "LigerModelFactory", impl.LigerModelFactory),
+        ("arctic_training.model.factory", "ModelFactory", impl.ModelFactory),
+        ("arctic_training.data.sft_factory", "SFTDataFactory", impl.SFTDataFactory),
+        ("arctic_training.data.hf_instruct_source", "HFDataSourceInstruct", impl.HFDataSourceInstruct),
+        ("arctic_training.data.snowflake_source", "SnowflakeDataSource", impl.SnowflakeDataSource),
+        ("arctic_training.optimizer.adam_factory", "FusedAdamOptimizerFactory", impl.FusedAdamOptimizerFactory),
+        ("arctic_training.scheduler.wsd_factory", "WSDSchedulerFactory", None),
+        ("arctic_training.tokenizer.hf_factory", "HFTokenizerFactory", impl.HFTokenizerFactory),
+        ("arctic_training.config.trainer", "TrainerConfig", impl.TrainerConfig),
+        ("arctic_training.testing_utils", "TestCasePlus", None),
+        ("arctic_training.model.moe.moe", "ArcticMoE", None),
+    ]
+    for mod, name, expect in pairs:
+        obj = getattr(importlib.import_module(mod), name)
+        assert expect is None or obj is expect, (mod, name)
+    assert arctic_training.CheckpointEngine is impl.CheckpointEngine
+    with pytest.raises(ImportError):
+        importlib.import_module("arctic_training.no_such_module")
