@@ -68,7 +68,7 @@ def register(cls: Optional[type] = None, force: bool = False) -> Union[Callable,
     """Deprecated no-op kept so that older user code ``@register`` still imports and runs."""
     from .logging import logger
 
-    logger.warning("@register is deprecated: subclasses register themselves when they are declared.")
+    logger.warning("The @register decorator is deprecated and does nothing: subclasses register themselves when they are declared.")
     if isinstance(cls, type):
         return cls
     return lambda klass: klass
