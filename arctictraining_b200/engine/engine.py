@@ -1293,6 +1293,25 @@ class TrainingEngine:
     def _ckpt_rank_file(self, d: Path) -> Path:
         return d / f"zero_pp_rank_{self.global_rank}_mp_rank_00_optim_states.pt"
 
+    @staticmethod
+    def _save_atomically(obj: Any, path: Path) -> None:
+        """Write to a temporary name and rename: a job killed in the middle of a save leaves no half-written file under
+        the final name (and ``latest`` is only moved once every rank has finished)."""
+        tmp = path.with_name(path.name + ".tmp")
+        torch.save(obj, tmp)
+        os.replace(tmp, path)
+
+    @staticmethod
+    def _load_checked(path: Path) -> Any:
+        from ..exceptions import CheckpointError
+
+        if not path.exists():
+            raise CheckpointError(f"checkpoint file {path} is missing")
+        try:
+            return torch.load(path, map_location="cpu", weights_only=False)
+        except Exception as e:  # noqa: BLE001 - whatever the unpickler raises on a damaged file
+            raise CheckpointError(f"checkpoint file {path} cannot be read ({type(e).__name__}: {e}); it may be truncated") from e
+
     def save_checkpoint(self, save_dir: Any, tag: Optional[str] = None, client_state: Optional[Dict[str, Any]] = None) -> None:
         save_dir = Path(save_dir)
         tag = tag or f"global_step{self.global_steps}"
@@ -1315,7 +1334,7 @@ class TrainingEngine:
         opt_state = None
         if self.optimizer is not None:
             opt_state = self._optimizer_state_for_save()
-        torch.save(
+        self._save_atomically(
             {
                 "units": units_state, "optimizer": opt_state, "stage": self.stage, "world": self.world,
                 "group_rank": self.rank,
@@ -1323,7 +1342,7 @@ class TrainingEngine:
             self._ckpt_rank_file(d),
         )
         if self.global_rank == 0:
-            torch.save(
+            self._save_atomically(
                 {
                     "lr_scheduler": self.lr_scheduler.state_dict() if self.lr_scheduler is not None else None,
                     "global_steps": self.global_steps, "micro_steps": self.micro_steps,
@@ -1363,20 +1382,25 @@ class TrainingEngine:
             if not latest.exists():
                 return None, {}
             tag = latest.read_text().strip()
+        from ..exceptions import CheckpointError
+
         d = load_dir / tag
-        meta = torch.load(d / "mp_rank_00_model_states.pt", map_location="cpu", weights_only=False)
+        if not d.is_dir():
+            raise CheckpointError(f"{load_dir / 'latest'} names the checkpoint {tag!r}, but {d} does not exist")
+        meta = self._load_checked(d / "mp_rank_00_model_states.pt")
         rank_file = self._ckpt_rank_file(d)
         if not rank_file.exists():
-            raise FileNotFoundError(
+            raise CheckpointError(
                 f"{rank_file} is missing: the checkpoint was written with a different world size "
                 f"({meta.get('dp_world_size')}) than this run ({self.world})"
             )
-        mine = torch.load(rank_file, map_location="cpu", weights_only=False)
+        mine = self._load_checked(rank_file)
         if mine["stage"] != self.stage or mine["world"] != self.world:
-            raise RuntimeError("checkpoint was written with another ZeRO stage or world size")
+            raise CheckpointError("checkpoint was written with another ZeRO stage or world size")
         for u in self.units:
-            st = mine["units"][u.name]
-            assert st["numel"] == u.numel and st["param_names"] == u.param_names, f"layout of unit {u.name} changed"
+            st = mine["units"].get(u.name)
+            if st is None or st["numel"] != u.numel or st["param_names"] != u.param_names:
+                raise CheckpointError(f"layout of unit {u.name} differs between the checkpoint and this model")
             u.shard.copy_(st["shard"].to(u.shard.dtype))
             if u.master is not None and "master" in st:
                 u.master[: u.train_len].copy_(st["master"].to(u.master.dtype))

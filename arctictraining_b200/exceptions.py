@@ -20,3 +20,7 @@ class EngineConfigError(ValueError):
 
 class KernelWaitError(RuntimeError):
     """A bounded barrier wait inside a compute kernel (GEMM, attention) ran out; its output is incomplete."""
+
+
+class CheckpointError(RuntimeError):
+    """A checkpoint cannot be used: a file is missing, truncated or unreadable, or it does not fit this run's layout."""

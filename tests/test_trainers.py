@@ -234,3 +234,27 @@ def test_cli_run_with_autocast_and_bf16_states(tiny_recipe, tmp_path):
     assert "iter: 1/2" in out and "iter: 2/2" in out and "iter: 3/2" not in out
     logs = [json.loads(x) for x in Path(r["train_log_metrics_path"]).read_text().splitlines() if x.strip()]
     assert logs[0]["iter"] == 1 and 0 < logs[0]["loss"] < 20
+
+
+def test_damaged_checkpoints_are_refused_with_the_file_named(tiny_recipe, tmp_path):
+    """Host-side failure injection: a shard cut short by a job that died while copying it, and a ``latest`` tag that
+    names a directory which is gone.  Resuming must stop with the offending file in the message, not continue on
+    fresh weights; and a save leaves no temporary files behind."""
+    from arctictraining_b200.exceptions import CheckpointError
+
+    ck = [{"type": "deepspeed", "output_dir": str(tmp_path / "ck"), "auto_resume": True, "save_every_n_steps": 2}]
+    a = build(tiny_recipe(checkpoint=ck, exit_iteration=2))
+    a.train()
+    tag = (tmp_path / "ck" / "latest").read_text().strip()
+    d = tmp_path / "ck" / tag
+    assert not list(d.glob("*.tmp"))
+    shard = next(d.glob("zero_pp_rank_0_*optim_states.pt"))
+    whole = shard.read_bytes()
+    shard.write_bytes(whole[: len(whole) // 3])
+    with pytest.raises(CheckpointError, match="zero_pp_rank_0"):
+        build(tiny_recipe(checkpoint=ck, exit_iteration=4))
+    shard.write_bytes(whole)
+    build(tiny_recipe(checkpoint=ck, exit_iteration=4))        # intact again: resumes
+    (tmp_path / "ck" / "latest").write_text("epoch_9_global_step_99")
+    with pytest.raises(CheckpointError, match="epoch_9_global_step_99"):
+        build(tiny_recipe(checkpoint=ck, exit_iteration=4))
