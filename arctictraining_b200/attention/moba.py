@@ -165,6 +165,15 @@ class MoBAContext:
     def __init__(self, chunk_size: int, topk: int) -> None:
         self.chunk_size, self.topk = chunk_size, topk
 
+    def global_cu_seqlens(self, position_ids: torch.Tensor):
+        """Packed-sample boundaries of the batch (there is no sequence sharding here: the local sequence is the global
+        one)."""
+        from ..models.causal_lm import cu_seqlens_from_position_ids
+
+        cu = cu_seqlens_from_position_ids(position_ids)
+        max_len = int((cu[1:] - cu[:-1]).max()) if cu is not None else position_ids.shape[-1]
+        return cu, max_len
+
     def attention(self, q, k, v, ctx) -> torch.Tensor:
         B, S, Hq, D = q.shape
         rep = Hq // k.shape[2]

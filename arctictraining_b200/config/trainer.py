@@ -387,6 +387,13 @@ def load_user_module_from_path(script_path: Path) -> None:
     mod_name = f"{link_name}.{script_path.stem}"
     if mod_name in sys.modules:
         return
+    # the same file may already be loaded under another name (one project's script importing a sibling project's):
+    # executing it again would declare, and try to register, its classes a second time
+    for loaded in list(sys.modules.values()):
+        f = getattr(loaded, "__file__", None)
+        if f and Path(f).resolve() == script_path:
+            sys.modules[mod_name] = loaded
+            return
     spec = importlib.util.spec_from_file_location(mod_name, link / script_path.name)
     assert spec is not None and spec.loader is not None
     module = importlib.util.module_from_spec(spec)
