@@ -278,7 +278,8 @@ class TrainerConfig(BaseConfig):
 
     @model_validator(mode="after")
     def _check_eval_interval(self) -> Self:
-        has_eval = bool(self.data.eval_sources) or self.data.train_eval_split[1] > 0.0
+        has_eval = (bool(self.data.eval_sources) or self.data.train_eval_split[1] > 0.0
+                    or bool(getattr(self.data, "eval_root_directories", None)))  # pre-batched evaluation directories
         if has_eval:
             assert self.eval_interval > 0, "`eval_interval` must be set if eval dataset is provided."
         if self.eval_interval > 0:
@@ -303,10 +304,13 @@ class TrainerConfig(BaseConfig):
         cfg["gradient_accumulation_steps"] = self.gradient_accumulation_steps
         cfg["sequence_parallel_size"] = self.sequence_parallel_size
         cfg.setdefault("steps_per_print", 10)
-        arch = load_arch_config(self.model.name_or_path, self.model.hf_config_kwargs)
-        hidden = arch.get("hidden_size") or max(arch.get("hidden_sizes") or [0])
-        if not hidden:
-            raise ValueError(f"Cannot find `hidden_size` in the config of {self.model.name_or_path}")
+        if "zero_optimization" in cfg:
+            hidden = 0  # only the defaults below depend on the model's width
+        else:
+            arch = load_arch_config(self.model.name_or_path, self.model.hf_config_kwargs)
+            hidden = arch.get("hidden_size") or max(arch.get("hidden_sizes") or [0])
+            if not hidden:
+                raise ValueError(f"Cannot find `hidden_size` in the config of {self.model.name_or_path}")
         cfg.setdefault(
             "zero_optimization",
             {

@@ -6,6 +6,9 @@ retrieval for hard-negative mining, teacher embedders, and the two pre-tokenise-
 from .embedders import Embedder
 from .embedders import HFEmbedder
 from .embedders import run_config_file_cli
+from .mining import combine_datasets
+from .mining import mine_hard_negatives
+from .mining import scramble_ids
 from .parquet_store import ParquetCollection
 from .parquet_store import filesystem_for
 from .retrieval import dense_retrieval

@@ -93,7 +93,11 @@ def write_embeddings(location: str, ids: Sequence, matrix: np.ndarray, id_col: s
 
     from .parquet_store import filesystem_for
 
+    import posixpath
+
     fs, path = filesystem_for(location)
+    if posixpath.dirname(path):
+        fs.makedirs(posixpath.dirname(path), exist_ok=True)
     flat = pa.array(np.ascontiguousarray(matrix).reshape(-1))
     vecs = pa.FixedSizeListArray.from_arrays(flat, matrix.shape[1])
     pq.write_table(pa.table({id_col: pa.array(list(ids)), vec_col: vecs}), path, filesystem=fs)

@@ -3,6 +3,7 @@
 what the training loader reads, dense retrieval."""
 
 import json
+from pathlib import Path
 
 import numpy as np
 import pyarrow as pa
@@ -156,3 +157,115 @@ def test_embed_all_keeps_input_order_and_config_cli_runs_a_shard(tmp_path):
     ran = []
     run_config_file_cli(PairsJob, lambda c: ran.append(pretokenize_pairs(c, toy_tokenize)), [str(cfg), "--num-shards", "3", "--shard", "2"])
     assert ran == [1] and (tmp_path / "o" / "batch_00000002").is_dir() and not (tmp_path / "o" / "batch_00000000").exists()
+
+
+def test_hard_negative_mining_respects_the_false_negative_threshold():
+    from arctictraining_b200.embed.data_processing import mine_hard_negatives
+
+    # query 1: positive doc 10 scores 0.9; docs 11 (0.89: too close, unlabelled positive?), 12 (0.8), 13 (0.5), 14 (0.1)
+    # query 2: its positive (doc 20) was not retrieved -> dropped;  query 3: only one eligible negative -> dropped
+    sq = np.array([1, 1, 1, 1, 1, 2, 2, 3, 3, 3])
+    sd = np.array([10, 11, 12, 13, 14, 21, 22, 30, 31, 32])
+    sc = np.array([0.9, 0.89, 0.8, 0.5, 0.1, 0.7, 0.6, 0.9, 0.88, 0.3])
+    lq, ld = np.array([1, 2, 3]), np.array([10, 20, 30])
+    q, d, r, stats = mine_hard_negatives(sq, sd, sc, lq, ld, threshold=0.95, negatives_per_query=2, max_positives_per_query=1)
+    assert q.tolist() == [1, 1, 1] and d.tolist() == [10, 12, 13] and r.tolist() == [1, -1, -1]
+    assert stats["kept_queries"] == 1 and stats["dropped_no_positive_retrieved"] == 1 and stats["dropped_too_few_negatives"] == 1
+    # against a plain per-query loop on random data
+    rng = np.random.default_rng(0)
+    nq, depth = 40, 30
+    sq = np.repeat(np.arange(nq), depth)
+    sd = np.concatenate([rng.permutation(200)[:depth] for _ in range(nq)])
+    sc = rng.random(nq * depth).astype(np.float32)
+    lq = np.repeat(np.arange(nq), 3)
+    ld = rng.integers(0, 200, nq * 3)
+    q, d, r, _ = mine_hard_negatives(sq, sd, sc, lq, ld, threshold=0.9, negatives_per_query=5, max_positives_per_query=2)
+    want = []
+    for qi in range(nq):
+        m = sq == qi
+        docs, scores = sd[m], sc[m]
+        pos = np.isin(docs, ld[lq == qi])
+        if not pos.any():
+            continue
+        o = np.argsort(-scores[pos], kind="stable")
+        use_pos, pos_scores = docs[pos][o][:2], scores[pos][o][:2]
+        ok = (~pos) & (scores < 0.9 * pos_scores.min())
+        o2 = np.argsort(-scores[ok], kind="stable")
+        negs = docs[ok][o2][:5]
+        if len(negs) < 5:
+            continue
+        want += [(qi, int(x), 1) for x in use_pos] + [(qi, int(x), -1) for x in negs]
+    assert list(zip(q.tolist(), d.tolist(), r.tolist())) == want
+
+
+def test_combining_sources_keeps_ids_apart():
+    from arctictraining_b200.embed.data_processing import combine_datasets
+    from arctictraining_b200.embed.data_processing import scramble_ids
+
+    a = scramble_ids(np.arange(1000), 0)
+    b = scramble_ids(np.arange(1000), 1)
+    assert len(np.unique(a)) == 1000 and len(np.intersect1d(a, b)) == 0 and np.array_equal(a, scramble_ids(np.arange(1000), 0))
+
+    def source(n):
+        return {"queries": pa.table({"QUERY_ID": np.arange(n, dtype=np.uint64), "QUERY_TEXT": [f"q{i}" for i in range(n)]}),
+                "documents": pa.table({"DOCUMENT_ID": np.arange(n, dtype=np.uint64), "DOCUMENT_TEXT": [f"d{i}" for i in range(n)]}),
+                "labels": pa.table({"QUERY_ID": np.arange(n, dtype=np.uint64), "DOCUMENT_ID": np.arange(n, dtype=np.uint64),
+                                    "RELEVANCE": np.ones(n, dtype=np.int8)})}
+
+    out = combine_datasets([source(5), source(7)])
+    assert out["queries"].num_rows == 12 and out["labels"].num_rows == 12
+    # labels still point at rows of their own source: the scrambled (query, document) ids of a label exist in the tables
+    qid = set(out["queries"]["QUERY_ID"].to_pylist())
+    did = set(out["documents"]["DOCUMENT_ID"].to_pylist())
+    assert all(r["QUERY_ID"] in qid and r["DOCUMENT_ID"] in did for r in out["labels"].to_pylist())
+
+
+def test_staged_preparation_script_runs_end_to_end_on_a_toy_dataset(tmp_path):
+    """embed -> retrieve -> mine -> combine -> batch -> dev-split of the fine-tuning example, with a stand-in embedder
+    and tokenizer; the result is what the training loader reads."""
+    import argparse
+    import sys
+
+    from arctictraining_b200.embed.data_processing import Embedder
+
+    root = Path(__file__).resolve().parent.parent
+    sys.path.insert(0, str(root / "projects" / "arctic_embed" / "examples" / "finetune_models"))
+    import prepare_data as prep
+
+    class BagOfLetters(Embedder):  # texts that share letters are close
+        def to_device(self, device):
+            pass
+
+        def embed_batch(self, texts, is_query, **kw):
+            out = np.zeros((len(texts), 26), dtype=np.float32)
+            for i, t in enumerate(texts):
+                for ch in t.lower():
+                    if "a" <= ch <= "z":
+                        out[i, ord(ch) - 97] += 1
+            return out / np.maximum(np.linalg.norm(out, axis=1, keepdims=True), 1e-6)
+
+    words = ["alpha", "bravo", "charlie", "delta", "echo", "foxtrot", "golf", "hotel", "india", "juliet", "kilo", "lima"]
+    for name in ("a", "b"):
+        d = tmp_path / name
+        d.mkdir()
+        pq.write_table(pa.table({"QUERY_ID": np.arange(12, dtype=np.uint64), "QUERY_TEXT": [f"{w} {w}" for w in words]}), d / "queries.parquet")
+        pq.write_table(pa.table({"DOCUMENT_ID": np.arange(12, dtype=np.uint64), "DOCUMENT_TEXT": [f"about {w}" for w in words]}), d / "documents.parquet")
+        pq.write_table(pa.table({"QUERY_ID": np.arange(12, dtype=np.uint64), "DOCUMENT_ID": np.arange(12, dtype=np.uint64)}), d / "labels.parquet")
+        ns = argparse.Namespace(dataset=str(d), batch_size=5, device="", pooling="", query_prefix="", document_prefix="", max_seq_len=32, model="")
+        prep.stage_embed(ns, embedder=BagOfLetters())
+        prep.stage_retrieve(argparse.Namespace(dataset=str(d), depth=12, device="cpu"))
+        prep.stage_mine(argparse.Namespace(dataset=str(d), threshold=0.99, negatives=3, max_positives=1))
+        mined = pq.read_table(d / "mined_labels.parquet").to_pandas()
+        assert (mined.groupby("QUERY_ID")["RELEVANCE"].apply(lambda r: (r == 1).sum()) == 1).all()
+        assert (mined.groupby("QUERY_ID")["RELEVANCE"].apply(lambda r: (r == -1).sum()) == 3).all()
+    prep.stage_combine(argparse.Namespace(datasets=[str(tmp_path / "a"), str(tmp_path / "b")], out=str(tmp_path / "combined")))
+    for d in ("a", "b", "combined"):
+        prep.stage_batch(argparse.Namespace(dataset=str(tmp_path / d), tokenizer="toy", name="v1", query_prefix="q: ", document_prefix="d: ",
+                                            queries_per_batch=4, negatives=3, max_seq_len=16), tokenize=toy_tokenize)
+    prep.stage_dev_split(argparse.Namespace(datasets=[str(tmp_path / "a"), str(tmp_path / "b")], name="v1", out=str(tmp_path / "eval"), batches=1))
+    train = list(PretokenizedBatchLoader(tmp_path / "combined" / "pretokenized" / "v1" / "data", 0, 1))
+    assert len(train) >= 4 and train[0].query_tokens.shape[0] == 4
+    dense = train[0].relevance_labels.to_dense()
+    assert ((dense == 1).sum(1) == 1).all() and ((dense == -1).sum(1) == 3).all()
+    assert len(list(PretokenizedBatchLoader(tmp_path / "eval" / "a", 0, 1))) == 1
+    assert json.loads((tmp_path / "eval" / "metadata.json").read_text())["query_prefix"] == "q: "
