@@ -52,11 +52,21 @@ class _AliasFinder(importlib.abc.MetaPathFinder, importlib.abc.Loader):
             return None
         return importlib.machinery.ModuleSpec(fullname, self, is_package=hasattr(module, "__path__"))
 
+    def __init__(self):
+        self._specs = {}
+
     def create_module(self, spec):
-        return _resolve(spec.name)  # the very module object of this package: its classes are the registered ones
+        module = _resolve(spec.name)  # the very module object of this package: its classes are the registered ones
+        self._specs[id(module)] = (getattr(module, "__spec__", None), getattr(module, "__loader__", None))
+        return module
 
     def exec_module(self, module):
-        pass
+        # the import machinery stamped the alias' spec on the shared module object: put its own back, so that
+        # relative imports inside it and importlib.reload keep seeing the module's real identity
+        spec, loader = self._specs.pop(id(module), (None, None))
+        if spec is not None:
+            module.__spec__ = spec
+            module.__loader__ = loader
 
 
 if not any(isinstance(f, _AliasFinder) for f in sys.meta_path):
