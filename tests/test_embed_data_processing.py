@@ -269,3 +269,35 @@ def test_staged_preparation_script_runs_end_to_end_on_a_toy_dataset(tmp_path):
     assert ((dense == 1).sum(1) == 1).all() and ((dense == -1).sum(1) == 3).all()
     assert len(list(PretokenizedBatchLoader(tmp_path / "eval" / "a", 0, 1))) == 1
     assert json.loads((tmp_path / "eval" / "metadata.json").read_text())["query_prefix"] == "q: "
+
+
+def test_download_tables_are_deduplicated_and_stable(tmp_path):
+    import importlib.util
+
+    import pyarrow.parquet as pq
+
+    path = Path(__file__).resolve().parent.parent / "projects" / "arctic_embed" / "examples" / "finetune_models" / "download_data.py"
+    spec = importlib.util.spec_from_file_location("_embed_download", path)
+    dl = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(dl)
+
+    q = ["who", "what", "who", "who"]
+    d = ["doc a", "doc b", "doc a", "doc c"]
+    tables = dl.pairs_to_tables(q, d, extra_documents=["doc z", "doc b"])
+    assert len(tables["queries"]) == 2 and len(tables["documents"]) == 4 and len(tables["labels"]) == 3
+    ids = dict(zip(tables["queries"]["QUERY_TEXT"].to_pylist(), tables["queries"]["QUERY_ID"].to_pylist()))
+    assert ids["who"] == int(dl.text_ids(["who"])[0])  # the id depends on the text alone
+    doc_ids = set(tables["documents"]["DOCUMENT_ID"].to_pylist())
+    assert set(tables["labels"]["DOCUMENT_ID"].to_pylist()) <= doc_ids
+    assert set(tables["labels"]["QUERY_ID"].to_pylist()) == set(ids.values())
+    dl.write_tables(tables, tmp_path / "toy")
+    assert pq.read_table(tmp_path / "toy" / "labels.parquet").num_rows == 3
+    with pytest.raises(ValueError):
+        dl.pairs_to_tables(["a"], [])
+
+    assert dl.title_and_text(" T ", "x") == "T\nx" and dl.title_and_text("", "x") == "x"
+    index = dl.BodyIndex(["the body text that is long enough to fill the whole tail key", "short", "a short"])
+    assert index.split("My title the body text that is long enough to fill the whole tail key") == (
+        "My title", "the body text that is long enough to fill the whole tail key")
+    assert index.split("Title: a short") == ("Title:", "a short")  # the longest matching body wins
+    assert index.split("nothing known") is None
