@@ -129,9 +129,10 @@ class MultiReplicaVllmSynth(InMemoryBatchProcessor):
 
     def __init__(self, model: str, n_replicas: int, tensor_parallel: int = 1, sampling: Optional[Dict[str, Any]] = None,
                  work_dir: Optional[str] = None, max_concurrency_per_replica: int = 64, servers: Optional[List[Dict[str, Any]]] = None,
-                 **server_kwargs: Any) -> None:
+                 max_attempts: int = 3, **server_kwargs: Any) -> None:
         super().__init__(work_dir)
         self.model, self.sampling, self.concurrency = model, sampling or {}, max_concurrency_per_replica
+        self.max_attempts = max(1, max_attempts)
         self.owns_servers = servers is None
         self.servers = servers if servers is not None else launch_vllm_servers(model, n_replicas, tensor_parallel, **server_kwargs)
         if self.owns_servers:
@@ -147,10 +148,21 @@ class MultiReplicaVllmSynth(InMemoryBatchProcessor):
         results: List[Optional[Dict[str, Any]]] = [None] * len(reqs)
 
         async def one(i: int, r: Dict[str, Any], session: Any) -> None:
-            url = self.servers[i % len(self.servers)]["url"] + "/v1/chat/completions"
+            # a failed request moves on to the next replica; after ``max_attempts`` the error is the result, so that one
+            # bad replica or prompt cannot lose the answers of all the others
+            error = "no attempt"
             async with sem:
-                async with session.post(url, json={"model": self.model, "messages": r["messages"], **self.sampling}) as resp:
-                    results[i] = {"custom_id": r["custom_id"], "response": await resp.json()}
+                for attempt in range(self.max_attempts):
+                    url = self.servers[(i + attempt) % len(self.servers)]["url"] + "/v1/chat/completions"
+                    try:
+                        async with session.post(url, json={"model": self.model, "messages": r["messages"], **self.sampling}) as resp:
+                            if resp.status == 200:
+                                results[i] = {"custom_id": r["custom_id"], "response": await resp.json(content_type=None)}
+                                return
+                            error = f"HTTP {resp.status}: {(await resp.text())[:200]}"
+                    except (aiohttp.ClientError, asyncio.TimeoutError) as e:
+                        error = f"{type(e).__name__}: {e}"
+            results[i] = {"custom_id": r["custom_id"], "response": None, "error": error}
 
         async with aiohttp.ClientSession(timeout=aiohttp.ClientTimeout(total=None)) as session:
             await asyncio.gather(*(one(i, r, session) for i, r in enumerate(reqs)))

@@ -72,3 +72,74 @@ def test_cortex_synth_with_fake_connection():
     s.add_chat_to_batch_task("t", "model", [{"role": "user", "content": "hi"}])
     out = CortexSynth.extract_messages_from_responses(s.execute_batch_task("t"))
     assert out[0]["choices"][0]["content"] == "ok:hi"
+
+
+def _start_replica(fail_first: int):
+    """A local HTTP server that answers like an OpenAI-compatible replica; its first `fail_first` requests get a 500."""
+    import threading
+    from http.server import BaseHTTPRequestHandler
+    from http.server import ThreadingHTTPServer
+
+    state = {"seen": 0, "lock": threading.Lock()}
+
+    class Handler(BaseHTTPRequestHandler):
+        def log_message(self, *a):
+            pass
+
+        def do_GET(self):
+            self.send_response(200 if self.path == "/health" else 404)
+            self.end_headers()
+
+        def do_POST(self):
+            body = json.loads(self.rfile.read(int(self.headers["Content-Length"])))
+            with state["lock"]:
+                state["seen"] += 1
+                fail = state["seen"] <= fail_first
+            payload = b"boom" if fail else json.dumps(
+                {"choices": [{"message": {"content": body["messages"][-1]["content"][::-1]}}]}).encode()
+            self.send_response(500 if fail else 200)
+            self.send_header("Content-Length", str(len(payload)))
+            self.end_headers()
+            self.wfile.write(payload)
+
+    server = ThreadingHTTPServer(("127.0.0.1", 0), Handler)
+    threading.Thread(target=server.serve_forever, daemon=True).start()
+    return server, state
+
+
+def test_multi_replica_fan_out_retries_on_another_replica_and_reports_lost_requests(tmp_path):
+    import pytest
+
+    from arctictraining_b200.synth.callers import MultiReplicaVllmSynth
+    from arctictraining_b200.synth.callers import wait_until_healthy
+
+    good, good_state = _start_replica(0)
+    flaky, flaky_state = _start_replica(2)
+    try:
+        servers = [{"url": f"http://127.0.0.1:{s.server_address[1]}", "gpus": [i], "proc": SimpleNamespace(poll=lambda: None)}
+                   for i, s in enumerate((good, flaky))]
+        wait_until_healthy(servers, timeout_s=10, poll_s=0.1)
+        synth = MultiReplicaVllmSynth("m", 2, servers=servers, work_dir=str(tmp_path), sampling={"temperature": 0})
+        for i in range(6):
+            synth.add_chat_to_batch_task("t", [{"role": "user", "content": f"abc{i}"}])
+        out = synth.extract_messages_from_responses(synth.execute_batch_task("t"))
+        assert [o["choices"][0]["content"] for o in out] == [f"{i}cba" for i in range(6)]
+        assert flaky_state["seen"] >= 3 and good_state["seen"] >= 5  # the two refused requests went to the other replica
+        synth.teardown()  # servers it did not start are left alone
+
+        # a replica that always fails: its requests end as error records, the rest still answer
+        dead, _ = _start_replica(10**6)
+        only_dead = [{"url": f"http://127.0.0.1:{dead.server_address[1]}", "gpus": [0], "proc": SimpleNamespace(poll=lambda: None)}]
+        lost = MultiReplicaVllmSynth("m", 1, servers=only_dead, max_attempts=2).process_conversations_across_replicas(
+            [[{"role": "user", "content": "x"}]])
+        assert lost[0]["response"] is None and lost[0]["error"].startswith("HTTP 500")
+        assert synth.extract_messages_from_responses(lost)[0]["choices"] == []
+        dead.shutdown()
+
+        # a server process that died is an error at once, not a time-out
+        gone = [{"url": "http://127.0.0.1:9", "gpus": [3], "proc": SimpleNamespace(poll=lambda: 1, returncode=1)}]
+        with pytest.raises(RuntimeError, match="exited"):
+            wait_until_healthy(gone, timeout_s=5, poll_s=0.1)
+    finally:
+        good.shutdown()
+        flaky.shutdown()
