@@ -51,12 +51,16 @@ def main() -> None:
     finally:
         client.teardown()
     rows = []
+    lost = 0
     for o in outputs:
+        if not o["choices"]:  # the request failed on every replica it was tried on
+            lost += 1
+            continue
         prompt_ids = tok.apply_chat_template(prompts[o["custom_id"]], add_generation_prompt=True, tokenize=True)
         gen_ids = tok(o["choices"][0]["content"], add_special_tokens=False)["input_ids"]
         rows.append({"input_ids": prompt_ids + gen_ids, "labels": [-100] * len(prompt_ids) + gen_ids})
     Dataset.from_list(rows).save_to_disk(args.out)
-    print(f"{len(rows)} samples -> {args.out}")
+    print(f"{len(rows)} samples -> {args.out} ({lost} requests lost)")
 
 
 if __name__ == "__main__":
