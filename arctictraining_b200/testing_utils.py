@@ -1,16 +1,21 @@
 # SPDX-License-Identifier: Apache-2.0
 """Helpers for writing tests against the framework.  Behaviour parity with the subset of
 arctic_training/testing_utils.py:67-1156 that the reference's own tests use: hardware requirement markers, unique
-rendezvous ports per pytest-xdist worker, temp-dir test case, stream capture, subprocess execution with live output,
-tolerant tensor / safetensors comparison, environment patching.
+rendezvous ports per pytest-xdist worker, temp-dir test case with path accessors, stream and logger capture, subprocess
+execution with live output, tolerant tensor / safetensors comparison, environment and ``sys.path`` patching, seeding,
+and per-category pytest report files (``--make-reports``).
 """
 
 from __future__ import annotations
 
 import asyncio
 import contextlib
+import inspect
 import io
+import logging
 import os
+import random
+import re
 import shutil
 import sys
 import tempfile
@@ -49,6 +54,74 @@ def is_flash_attn_2_available() -> bool:
     return importlib.util.find_spec("flash_attn") is not None and torch.cuda.is_available()
 
 
+def is_torch_available() -> bool:
+    return True
+
+
+def is_deepspeed_available() -> bool:
+    """The engine of this package takes the place of the external one, so tests that ask for it can run."""
+    return True
+
+
+def is_flash_attn_3_available() -> bool:
+    import importlib.util
+
+    return importlib.util.find_spec("flash_attn_interface") is not None and torch.cuda.is_available()
+
+
+def parse_flag_from_env(key: str, default: bool = False) -> bool:
+    """Boolean value of an environment variable (yes/no, true/false, on/off, 1/0); ``default`` when unset."""
+    if key not in os.environ:
+        return default
+    value = os.environ[key].strip().lower()
+    if value in ("y", "yes", "t", "true", "on", "1"):
+        return True
+    if value in ("n", "no", "f", "false", "off", "0"):
+        return False
+    raise ValueError(f"If set, {key} must be yes or no.")
+
+
+def parse_int_from_env(key: str, default: Optional[int] = None) -> Optional[int]:
+    if key not in os.environ:
+        return default
+    try:
+        return int(os.environ[key])
+    except ValueError:
+        raise ValueError(f"If set, {key} must be an int.") from None
+
+
+def set_seed(seed: int = 42) -> None:
+    """Seed ``random``, numpy and torch (all devices)."""
+    import numpy as np
+
+    random.seed(seed)
+    np.random.seed(seed)
+    torch.manual_seed(seed)
+    torch.cuda.manual_seed_all(seed)  # a no-op without a GPU
+
+
+def get_gpu_count() -> int:
+    return torch.cuda.device_count()
+
+
+def get_tests_dir(append_path: Optional[str] = None) -> str:
+    """Directory of the file that calls this function, optionally joined with ``append_path``: lets a test find its data
+    whatever the working directory is."""
+    here = os.path.abspath(os.path.dirname(inspect.stack()[1].filename))
+    return os.path.join(here, append_path) if append_path else here
+
+
+def apply_print_resets(buf: str) -> str:
+    """What a terminal would show: on every line, everything up to the last carriage return is dropped (progress
+    bars overwrite themselves), so captured output compares equal with and without ``pytest -s``."""
+    return re.sub(r"^.*\r", "", buf, flags=re.M)
+
+
+def replace_str_in_file(file, text_to_search: str, replacement_text: str) -> None:
+    path = Path(file)
+    path.write_text(path.read_text().replace(text_to_search, replacement_text))
+
+
 def get_xdist_worker_id() -> int:
     return int(os.environ.get("PYTEST_XDIST_WORKER", "gw0").replace("gw", "") or 0)
 
@@ -64,8 +137,32 @@ def _require(cond: bool, reason: str):
     return pytest.mark.skipif(not cond, reason=reason)
 
 
+def require_torch(fn):
+    return fn
+
+
+def require_deepspeed(fn):
+    return fn
+
+
 def require_torch_gpu(fn):
     return _require(torch.cuda.is_available(), "test requires a GPU")(fn)
+
+
+def require_torch_no_gpus(fn):
+    return _require(torch.cuda.device_count() == 0, "test requires a machine without GPUs")(fn)
+
+
+def require_torch_up_to_2_gpus(fn):
+    return _require(torch.cuda.device_count() < 3, "test requires 0, 1 or 2 GPUs")(fn)
+
+
+def require_flash_attn(fn):
+    return _require(is_flash_attn_2_available(), "test requires flash-attn 2 and a GPU")(fn)
+
+
+def require_flash_attn_3(fn):
+    return _require(is_flash_attn_3_available(), "test requires flash-attn 3 and a GPU")(fn)
 
 
 def require_torch_multi_gpu(fn):
@@ -150,6 +247,39 @@ class CaptureStderr(CaptureStd):
         super().__init__(out=False, replay=replay)
 
 
+class CaptureLogger:
+    """Context manager that collects what a ``logging`` logger emits; the text is in ``.out`` afterwards."""
+
+    def __init__(self, logger: logging.Logger) -> None:
+        self.logger = logger
+        self.io = io.StringIO()
+        self.handler = logging.StreamHandler(self.io)
+        self.out = ""
+
+    def __enter__(self) -> "CaptureLogger":
+        self.logger.addHandler(self.handler)
+        return self
+
+    def __exit__(self, *exc: Any) -> None:
+        self.logger.removeHandler(self.handler)
+        self.out = self.io.getvalue()
+
+    def __repr__(self) -> str:
+        return f"captured: {self.out}\n"
+
+
+@contextlib.contextmanager
+def ExtendSysPath(path) -> Iterator[None]:  # noqa: N802 - the name user tests import
+    """Put ``path`` in front of ``sys.path`` for the duration of the block."""
+    path = os.fspath(path)
+    sys.path.insert(0, path)
+    try:
+        yield
+    finally:
+        with contextlib.suppress(ValueError):
+            sys.path.remove(path)
+
+
 class _RunOutput:
     def __init__(self, returncode: int, stdout: List[str], stderr: List[str]) -> None:
         self.returncode, self.stdout, self.stderr = returncode, stdout, stderr
@@ -191,9 +321,20 @@ class TestCasePlus(unittest.TestCase):
 
     def setUp(self) -> None:
         self._teardown_dirs: List[str] = []
-        here = Path(sys.modules[self.__class__.__module__].__file__).resolve()
+        here = Path(inspect.getfile(self.__class__)).resolve()
+        self.test_file_path = here
         self.test_file_dir = here.parent
         self.repo_root_dir = next((p for p in here.parents if (p / "arctictraining_b200").is_dir()), here.parent)
+        self.tests_dir = self.repo_root_dir / "tests"
+        self.data_dir = self.tests_dir / "data"
+        self.src_dir = self.repo_root_dir / "arctictraining_b200"
+
+    test_file_path_str = property(lambda self: str(self.test_file_path))
+    test_file_dir_str = property(lambda self: str(self.test_file_dir))
+    tests_dir_str = property(lambda self: str(self.tests_dir))
+    data_dir_str = property(lambda self: str(self.data_dir))
+    repo_root_dir_str = property(lambda self: str(self.repo_root_dir))
+    src_dir_str = property(lambda self: str(self.src_dir))
 
     def get_env(self) -> Dict[str, str]:
         env = dict(os.environ)
@@ -214,7 +355,102 @@ class TestCasePlus(unittest.TestCase):
             self._teardown_dirs.append(tmp_dir)
         return tmp_dir
 
+    def get_auto_remove_tmp_dir_str(self, *args: Any, **kwargs: Any) -> str:
+        return str(self.get_auto_remove_tmp_dir(*args, **kwargs))
+
     def tearDown(self) -> None:
         for d in self._teardown_dirs:
             shutil.rmtree(d, ignore_errors=True)
         self._teardown_dirs = []
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# pytest report files: `pytest --make-reports=<id>` writes one file per kind of result under reports/<id>/.
+# In conftest.py:
+#     def pytest_addoption(parser): pytest_addoption_shared(parser)
+#     def pytest_terminal_summary(terminalreporter):
+#         rid = terminalreporter.config.getoption("--make-reports")
+#         if rid: pytest_terminal_summary_main(terminalreporter, id=rid)
+
+_registered_pytest_options: set = set()
+
+
+def pytest_addoption_shared(parser) -> None:
+    """Register ``--make-reports`` once, however many conftest files call this."""
+    option = "--make-reports"
+    if option in _registered_pytest_options:
+        return
+    try:
+        parser.addoption(option, action="store", default=False,
+                         help="write report files; the value names the directory under reports/")
+    except ValueError:  # another conftest of the same session registered it through its own copy of this module
+        pass
+    _registered_pytest_options.add(option)
+
+
+def pytest_terminal_summary_main(tr, id: str, min_duration: float = 0.05) -> Dict[str, str]:  # noqa: A002
+    """Write ``durations``, ``failures_long``, ``failures_short``, ``failures_line``, ``errors``, ``warnings``,
+    ``summary_short`` and ``stats`` (``.txt`` each) under ``reports/<id>/`` from the reporter's collected results;
+    returns ``{kind: path}``."""
+    if not id:
+        id = "tests"  # noqa: A001
+    out_dir = Path("reports") / str(id)
+    out_dir.mkdir(parents=True, exist_ok=True)
+    files = {k: str(out_dir / f"{k}.txt") for k in ("durations", "errors", "failures_long", "failures_short",
+                                                    "failures_line", "stats", "summary_short", "warnings")}
+    stats = getattr(tr, "stats", {})
+
+    def reports(kind: str) -> list:
+        return [r for r in stats.get(kind, []) if hasattr(r, "nodeid")]
+
+    timed = sorted((r for rs in stats.values() for r in rs if hasattr(r, "duration")), key=lambda r: -r.duration)
+    with open(files["durations"], "w") as f:
+        f.write("slowest durations\n")
+        for r in timed:
+            if r.duration < min_duration:
+                f.write(f"durations < {min_duration} secs were omitted\n")
+                break
+            f.write(f"{r.duration:02.2f}s {getattr(r, 'when', '?'):<8} {r.nodeid}\n")
+
+    def crash_line(r) -> str:
+        crash = getattr(getattr(r, "longrepr", None), "reprcrash", None)
+        if crash is not None:
+            return f"{crash.path}:{crash.lineno}: {crash.message.splitlines()[0] if crash.message else ''}"
+        text = str(getattr(r, "longrepr", "")).strip().splitlines()
+        return text[-1] if text else ""
+
+    def short_trace(r) -> str:
+        # the innermost frame only: what failed and where, without the call chain above it
+        text = getattr(r, "longreprtext", None) or str(getattr(r, "longrepr", ""))
+        frames = re.split(r"\n_ _ _ [_ ]*\n", text)
+        return frames[-1].strip()
+
+    failed = reports("failed")
+    with open(files["failures_long"], "w") as f:
+        for r in failed:
+            f.write(f"{'_' * 20} {r.nodeid} {'_' * 20}\n{getattr(r, 'longreprtext', str(getattr(r, 'longrepr', '')))}\n\n")
+    with open(files["failures_short"], "w") as f:
+        for r in failed:
+            f.write(f"{'_' * 20} {r.nodeid} {'_' * 20}\n{short_trace(r)}\n\n")
+    with open(files["failures_line"], "w") as f:
+        for r in failed:
+            f.write(f"{crash_line(r)}\n")
+    with open(files["errors"], "w") as f:
+        for r in reports("error"):
+            f.write(f"{'_' * 20} ERROR at {getattr(r, 'when', '?')} of {r.nodeid} {'_' * 20}\n"
+                    f"{getattr(r, 'longreprtext', str(getattr(r, 'longrepr', '')))}\n\n")
+    with open(files["warnings"], "w") as f:
+        for w in stats.get("warnings", []):
+            where = getattr(w, "nodeid", "") or ""
+            f.write(f"{where}\n  {str(getattr(w, 'message', w)).strip()}\n")
+    with open(files["summary_short"], "w") as f:
+        for kind, label in (("failed", "FAILED"), ("error", "ERROR"), ("skipped", "SKIPPED"), ("xfailed", "XFAIL"),
+                            ("xpassed", "XPASS"), ("passed", "PASSED")):
+            for r in reports(kind):
+                extra = f" - {crash_line(r)}" if kind in ("failed", "error") else ""
+                f.write(f"{label} {r.nodeid}{extra}\n")
+    with open(files["stats"], "w") as f:
+        counts = {k: len(reports(k)) for k in ("passed", "failed", "error", "skipped", "xfailed", "xpassed")}
+        counts["warnings"] = len(stats.get("warnings", []))
+        f.write(", ".join(f"{n} {k}" for k, n in counts.items() if n) + "\n")
+    return files

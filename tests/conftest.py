@@ -18,6 +18,20 @@ os.environ.setdefault("WORLD_SIZE", "1")
 os.environ.setdefault("AT_LOG_LEVEL", "WARNING")
 
 
+def pytest_addoption(parser):
+    from arctictraining_b200.testing_utils import pytest_addoption_shared
+
+    pytest_addoption_shared(parser)
+
+
+def pytest_terminal_summary(terminalreporter):
+    from arctictraining_b200.testing_utils import pytest_terminal_summary_main
+
+    report_id = terminalreporter.config.getoption("--make-reports")
+    if report_id:
+        pytest_terminal_summary_main(terminalreporter, id=report_id)
+
+
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: test needs a CUDA GPU (run with -m gpu on a B200)")
 

@@ -1,4 +1,7 @@
 # SPDX-License-Identifier: Apache-2.0
+import os
+from pathlib import Path
+
 import pytest
 import torch
 import torch.nn as nn
@@ -79,3 +82,98 @@ def test_host_adamw_extension_matches_reference_update():
     assert torch.allclose(p, p2, atol=1e-6, rtol=1e-5)
     assert torch.allclose(m, m2, atol=1e-7, rtol=1e-5) and torch.allclose(v, v2, atol=1e-9, rtol=1e-5)
     assert (lp.float() - lp2.float()).abs().max() <= 2 ** -7 * p.abs().max()
+
+
+def test_testing_helpers_env_paths_logger_and_seed(tmp_path, monkeypatch):
+    import logging
+    import random
+    import sys
+
+    from arctictraining_b200 import testing_utils as tu
+
+    monkeypatch.setenv("ATB_FLAG", "Yes")
+    monkeypatch.setenv("ATB_INT", "12")
+    assert tu.parse_flag_from_env("ATB_FLAG") is True and tu.parse_flag_from_env("ATB_UNSET", True) is True
+    assert tu.parse_int_from_env("ATB_INT") == 12 and tu.parse_int_from_env("ATB_UNSET", 3) == 3
+    monkeypatch.setenv("ATB_FLAG", "maybe")
+    with pytest.raises(ValueError, match="yes or no"):
+        tu.parse_flag_from_env("ATB_FLAG")
+    monkeypatch.setenv("ATB_INT", "x")
+    with pytest.raises(ValueError, match="int"):
+        tu.parse_int_from_env("ATB_INT")
+
+    tu.set_seed(7)
+    a = (random.random(), torch.rand(1).item())
+    tu.set_seed(7)
+    assert a == (random.random(), torch.rand(1).item())
+    assert tu.get_gpu_count() == torch.cuda.device_count()
+    assert tu.get_tests_dir() == str(Path(__file__).resolve().parent)
+    assert tu.get_tests_dir("data").endswith("tests/data")
+    assert tu.apply_print_resets("10%\r50%\r done\nnext") == " done\nnext"
+
+    f = tmp_path / "a" / "b.txt"
+    tu.write_file(f, "alpha beta")
+    tu.replace_str_in_file(f, "beta", "gamma")
+    assert f.read_text() == "alpha gamma"
+
+    log = logging.getLogger("atb200-test-capture")
+    with tu.CaptureLogger(log) as cl:
+        log.warning("look here")
+    assert cl.out == "look here\n" and "look here" in repr(cl)
+    with tu.ExtendSysPath(tmp_path):
+        assert sys.path[0] == str(tmp_path)
+    assert str(tmp_path) not in sys.path
+
+    for mark in (tu.require_torch, tu.require_deepspeed, tu.require_torch_no_gpus, tu.require_torch_up_to_2_gpus,
+                 tu.require_flash_attn, tu.require_flash_attn_3):
+        assert callable(mark(lambda: None))
+
+    class Case(tu.TestCasePlus):
+        def runTest(self):
+            pass
+
+    case = Case()
+    case.setUp()
+    assert case.test_file_path == Path(__file__).resolve() and case.tests_dir_str.endswith("tests")
+    assert case.src_dir.name == "arctictraining_b200" and case.repo_root_dir_str == str(case.tests_dir.parent)
+    d = case.get_auto_remove_tmp_dir_str()
+    assert Path(d).is_dir()
+    case.tearDown()
+    assert not Path(d).exists()
+
+
+def test_make_reports_writes_one_file_per_kind(tmp_path):
+    """A small suite with a pass, a failure, a skip and a warning, run with ``--make-reports``."""
+    import subprocess
+    import sys
+
+    root = Path(__file__).resolve().parent.parent
+    (tmp_path / "conftest.py").write_text(
+        "import arctictraining_b200.testing_utils as tu\n"
+        "def pytest_addoption(parser):\n    tu.pytest_addoption_shared(parser)\n"
+        "def pytest_terminal_summary(terminalreporter):\n"
+        "    rid = terminalreporter.config.getoption('--make-reports')\n"
+        "    if rid:\n        tu.pytest_terminal_summary_main(terminalreporter, id=rid)\n")
+    (tmp_path / "test_toy.py").write_text(
+        "import time, warnings, pytest\n"
+        "def test_ok():\n    time.sleep(0.06)\n"
+        "def helper():\n    assert 1 == 2, 'numbers differ'\n"
+        "def test_bad():\n    helper()\n"
+        "def test_warn():\n    warnings.warn('careful', UserWarning)\n"
+        "@pytest.mark.skip(reason='not today')\ndef test_skip():\n    pass\n")
+    env = dict(os.environ, PYTHONPATH=str(root))
+    r = subprocess.run([sys.executable, "-m", "pytest", "-q", "-p", "no:cacheprovider", "--make-reports=toy", "test_toy.py"],
+                       cwd=tmp_path, env=env, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 1, r.stdout + r.stderr
+    rep = tmp_path / "reports" / "toy"
+    assert sorted(p.name for p in rep.iterdir()) == [
+        "durations.txt", "errors.txt", "failures_line.txt", "failures_long.txt", "failures_short.txt", "stats.txt",
+        "summary_short.txt", "warnings.txt"]
+    assert "test_toy.py::test_ok" in (rep / "durations.txt").read_text()
+    assert "numbers differ" in (rep / "failures_line.txt").read_text()
+    long, short = (rep / "failures_long.txt").read_text(), (rep / "failures_short.txt").read_text()
+    assert "def test_bad" in long and "numbers differ" in short and len(short) < len(long)
+    assert "careful" in (rep / "warnings.txt").read_text()
+    summary = (rep / "summary_short.txt").read_text()
+    assert "FAILED test_toy.py::test_bad" in summary and "SKIPPED test_toy.py::test_skip" in summary
+    assert (rep / "stats.txt").read_text().strip() == "2 passed, 1 failed, 1 skipped, 1 warnings"
