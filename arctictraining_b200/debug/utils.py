@@ -38,23 +38,62 @@ def print_rank(*msg: Any, skip: bool = True, ranks: Optional[List[int]] = None, 
         printflock(f"[{_rank()}]", *msg)
 
 
-def pr0(*msg: Any, skip: bool = True, force: bool = False) -> None:
+def print_rank0(*msg: Any, skip: bool = True, force: bool = False) -> None:
     print_rank(*msg, skip=skip, ranks=[0], force=force)
 
 
-def _nvml_used_gb() -> Optional[float]:
-    global _nvml_handle
-    if not torch.cuda.is_available():
+pr0 = print_rank0
+pr = print_rank
+
+
+def get_device_id(current_device: Optional[int] = None):
+    """Physical index (or UUID string) of the GPU this process computes on, as management tools number it:
+    ``CUDA_VISIBLE_DEVICES`` re-numbers devices inside the process, NVML does not.  ``None`` when no device is visible."""
+    visible = os.getenv("CUDA_VISIBLE_DEVICES")
+    if current_device is None:
+        current_device = torch.cuda.current_device() if torch.cuda.is_available() else int(os.getenv("LOCAL_RANK", 0))
+    if visible is None:
+        return current_device
+    entries = [e.strip() for e in visible.split(",") if e.strip()]
+    if not entries:
         return None
+    entry = entries[current_device] if current_device < len(entries) else entries[0]
+    return int(entry) if entry.lstrip("-").isdigit() else entry
+
+
+def get_nvml_mem() -> int:
+    """Bytes in use on this process' GPU as NVML reports them (all processes, allocator caches included); 0 when NVML
+    is not available or does not support the query on this machine."""
+    global _nvml_handle
     try:
         import pynvml
 
         if _nvml_handle is None:
+            device = get_device_id()
+            if device is None:
+                return 0
             pynvml.nvmlInit()
-            _nvml_handle = pynvml.nvmlDeviceGetHandleByIndex(torch.cuda.current_device())
-        return pynvml.nvmlDeviceGetMemoryInfo(_nvml_handle).used / 2**30
+            by_uuid = isinstance(device, str)
+            _nvml_handle = (pynvml.nvmlDeviceGetHandleByUUID(device) if by_uuid
+                            else pynvml.nvmlDeviceGetHandleByIndex(device))
+        return int(pynvml.nvmlDeviceGetMemoryInfo(_nvml_handle).used)
     except Exception:
+        return 0
+
+
+def _nvml_used_gb() -> Optional[float]:
+    if not torch.cuda.is_available():
         return None
+    used = get_nvml_mem()
+    return used / 2**30 if used else None
+
+
+def gc_empty_accelerator_cache() -> None:
+    """Collect garbage and return the allocator's cached blocks to the device: for reading real memory use while
+    debugging (expensive, not for the training loop)."""
+    gc.collect()
+    if torch.cuda.is_available():
+        torch.cuda.empty_cache()
 
 
 def get_mem_metrics() -> str:

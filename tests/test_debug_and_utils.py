@@ -177,3 +177,37 @@ def test_make_reports_writes_one_file_per_kind(tmp_path):
     summary = (rep / "summary_short.txt").read_text()
     assert "FAILED test_toy.py::test_bad" in summary and "SKIPPED test_toy.py::test_skip" in summary
     assert (rep / "stats.txt").read_text().strip() == "2 passed, 1 failed, 1 skipped, 1 warnings"
+
+
+def test_device_id_follows_visible_devices_and_nvml_reads_that_device(monkeypatch):
+    import sys
+    from types import SimpleNamespace
+
+    from arctictraining_b200.debug import utils as du
+
+    monkeypatch.delenv("CUDA_VISIBLE_DEVICES", raising=False)
+    assert du.get_device_id(2) == 2
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "4,6,7")
+    assert du.get_device_id(1) == 6
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "GPU-abc, GPU-def")
+    assert du.get_device_id(1) == "GPU-def"
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "")
+    assert du.get_device_id(0) is None
+
+    asked = []
+    fake = SimpleNamespace(
+        nvmlInit=lambda: None,
+        nvmlDeviceGetHandleByIndex=lambda i: asked.append(i) or ("idx", i),
+        nvmlDeviceGetHandleByUUID=lambda u: asked.append(u) or ("uuid", u),
+        nvmlDeviceGetMemoryInfo=lambda h: SimpleNamespace(used=3 * 2**30))
+    monkeypatch.setitem(sys.modules, "pynvml", fake)
+    monkeypatch.setattr(du, "_nvml_handle", None)
+    monkeypatch.setenv("CUDA_VISIBLE_DEVICES", "5")
+    monkeypatch.setenv("LOCAL_RANK", "0")
+    assert du.get_nvml_mem() == 3 * 2**30 and asked == [5]
+    assert du.get_nvml_mem() == 3 * 2**30 and asked == [5]  # the handle is kept
+    monkeypatch.setattr(du, "_nvml_handle", None)
+    fake.nvmlDeviceGetMemoryInfo = lambda h: (_ for _ in ()).throw(RuntimeError("not supported"))
+    assert du.get_nvml_mem() == 0
+    du.gc_empty_accelerator_cache()
+    assert du.pr0 is du.print_rank0 and du.pr is du.print_rank
