@@ -27,6 +27,9 @@ _MODULES = {
     "optimizer.adam_factory": "optimizer.adam",
     "scheduler.hf_factory": "scheduler.factory", "scheduler.wsd_factory": "scheduler.factory",
     "tokenizer.hf_factory": "tokenizer.factory",
+    "model.moe.moe_gemm": "moe.grouped",
+    "synth.base_caller": "synth.base", "synth.vllm_callers": "synth.callers", "synth.vllm_utils": "synth.callers",
+    "trainer.parallel_groups": "parallel.mesh",
     "utils": "utils.misc", "trainer.flops_counter": "flops",
 }
 

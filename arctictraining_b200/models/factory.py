@@ -166,6 +166,11 @@ class HFModelFactory(ModelFactory):
         model.activation_checkpointing = not self.config.disable_activation_checkpoint
         if hasattr(model, "gradient_checkpointing_enable") and not self.config.disable_activation_checkpoint:
             model.gradient_checkpointing_enable()
+            if getattr(self.trainer.config, "activation_checkpoint_cpu_offload", False):
+                # a library model checkpoints through torch.utils.checkpoint: keep each layer's input in host memory
+                from ..monkey_patches import enable_host_offload_on_hf_model
+
+                enable_host_offload_on_hf_model(model)
         return model
 
 

@@ -47,3 +47,18 @@ def grouped_mlp(x: torch.Tensor, offsets: torch.Tensor, w_gate_up: torch.Tensor,
 
         return grouped_mlp_cuda(x, offsets, w_gate_up, w_down)
     return grouped_mlp_reference(x, offsets, w_gate_up, w_down, act_fn)
+
+
+def group_gemm_fn(a: torch.Tensor, b: torch.Tensor, rows_cumsum: torch.Tensor) -> torch.Tensor:
+    """``C[rows of group g] = A[rows of group g] @ B[g]`` for ``B [G, K, N]`` and inclusive row counts ``rows_cumsum
+    [G]`` (group ``g`` owns rows ``rows_cumsum[g-1] : rows_cumsum[g]``).  The stand-alone grouped matmul of the
+    reference (arctic_training/model/moe/moe_gemm.py:151-166), differentiable, in the input dtype, ragged tiles
+    allowed; the expert MLP of this package does not go through it but through :func:`grouped_mlp`."""
+    ends = rows_cumsum.tolist()
+    out = a.new_zeros(ends[-1] if ends else 0, b.shape[-1])
+    start = 0
+    pieces = []
+    for g, end in enumerate(ends):
+        pieces.append(a[start:end] @ b[g])
+        start = end
+    return torch.cat(pieces, dim=0) if pieces else out

@@ -124,6 +124,30 @@ def wait_until_healthy(servers: List[Dict[str, Any]], timeout_s: float = 1800.0,
         raise TimeoutError(f"{len(pending)} vllm server(s) did not become healthy within {timeout_s}s")
 
 
+def check_vllm_servers_health(base_port: int, num_services: int, timeout_s: float = 1800.0, poll_s: float = 30.0,
+                              host: str = "127.0.0.1") -> None:
+    """Block until ``num_services`` servers on consecutive ports from ``base_port`` answer ``/health``."""
+    alive = type("_Alive", (), {"poll": staticmethod(lambda: None), "returncode": None})
+    servers = [{"url": f"http://{host}:{base_port + i}", "gpus": [i], "proc": alive} for i in range(num_services)]
+    wait_until_healthy(servers, timeout_s=timeout_s, poll_s=poll_s)
+
+
+def kill_processes(process_ids: List[int]) -> None:
+    """SIGTERM to each given process id; ids that no longer exist or cannot be signalled are logged and skipped."""
+    import signal
+
+    from ..logging import logger
+
+    for pid in process_ids:
+        try:
+            os.kill(pid, signal.SIGTERM)
+            logger.info(f"Process {pid} terminated.")
+        except ProcessLookupError:
+            logger.info(f"Process {pid} does not exist.")
+        except PermissionError:
+            logger.info(f"Permission denied to terminate process {pid}.")
+
+
 class MultiReplicaVllmSynth(InMemoryBatchProcessor):
     """Fans chat requests out over several ``vllm serve`` replicas (one per GPU group) with bounded concurrency."""
 

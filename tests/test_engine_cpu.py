@@ -375,3 +375,76 @@ def test_bf16_master_weights_and_optimizer_states_train():
     st = next(iter(opt.state.values()))
     assert st["exp_avg"].dtype == torch.bfloat16 and st["exp_avg_sq"].dtype == torch.bfloat16
     assert losses[-1] < losses[0] - 0.05
+
+
+def test_checkpoint_patch_parks_inputs_and_keeps_gradients():
+    """``torch.utils.checkpoint`` patched for host offload: same loss and gradients, the checkpointed regions' inputs
+    went through the store (on a CPU device the store keeps them where they are)."""
+    import torch.utils.checkpoint as ckpt
+
+    from arctictraining_b200 import monkey_patches as mp
+
+    torch.manual_seed(0)
+    layers = torch.nn.ModuleList([torch.nn.Sequential(torch.nn.Linear(64, 64), torch.nn.GELU()) for _ in range(3)])
+
+    def run():
+        for p in layers.parameters():
+            p.grad = None
+        x = torch.randn(8, 64, requires_grad=True, generator=torch.Generator().manual_seed(1))
+        h = x
+        for layer in layers:
+            h = ckpt.checkpoint(layer, h, use_reentrant=False)
+        h.square().mean().backward()
+        return h.detach().clone(), x.grad.clone(), [p.grad.clone() for p in layers.parameters()]
+
+    want = run()
+    mp.monkey_patch_checkpoint_function_with_cpu_offload(min_bytes=0)
+    try:
+        mp.monkey_patch_checkpoint_function_with_cpu_offload(min_bytes=0)  # a second call changes nothing
+        mp.stats.update(packed=0, restored=0)
+        got = run()
+    finally:
+        mp.undo_checkpoint_patch()
+    assert ckpt.checkpoint is not None and mp._original_checkpoint is None
+    torch.testing.assert_close(got[0], want[0])
+    torch.testing.assert_close(got[1], want[1])
+    for a, b in zip(got[2], want[2]):
+        torch.testing.assert_close(a, b)
+    assert mp.stats["packed"] == 3 and mp.stats["restored"] == 3
+    a, b = mp.noop_context_fn()
+    with a, b:
+        pass
+
+
+def test_library_model_checkpoints_with_host_offload():
+    """A Hugging Face model with gradient checkpointing pointed at the offloading checkpoint function: every decoder
+    layer's input goes through the store, and the gradients match plain checkpointing."""
+    from transformers import LlamaConfig
+    from transformers import LlamaForCausalLM
+
+    from arctictraining_b200 import monkey_patches as mp
+
+    cfg = LlamaConfig(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=3, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=64)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg).train()
+    ids = torch.randint(0, 128, (2, 16), generator=torch.Generator().manual_seed(2))
+
+    def grads():
+        model.zero_grad()
+        model(input_ids=ids, labels=ids).loss.backward()
+        return {n: p.grad.clone() for n, p in model.named_parameters()}
+
+    model.gradient_checkpointing_enable()
+    want = grads()
+    assert mp.enable_host_offload_on_hf_model(model)
+    mp.stats.update(packed=0, restored=0)
+    old, mp.DEFAULT_MIN_BYTES = mp.DEFAULT_MIN_BYTES, 0
+    try:
+        got = grads()
+    finally:
+        mp.DEFAULT_MIN_BYTES = old
+    assert mp.stats["packed"] >= 3 and mp.stats["packed"] == mp.stats["restored"]
+    for n in want:
+        torch.testing.assert_close(got[n], want[n], msg=lambda m, n=n: f"{n}: {m}")
+    assert mp.enable_host_offload_on_hf_model(torch.nn.Linear(2, 2)) is False

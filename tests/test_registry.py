@@ -195,6 +195,16 @@ def test_module_paths_of_the_reference_resolve_to_this_package():
         ("arctic_training.config.trainer", "TrainerConfig", impl.TrainerConfig),
         ("arctic_training.testing_utils", "TestCasePlus", None),
         ("arctic_training.model.moe.moe", "ArcticMoE", None),
+        ("arctic_training.model.moe.moe_gemm", "group_gemm_fn", None),
+        ("arctic_training.monkey_patches", "monkey_patch_checkpoint_function_with_cpu_offload", None),
+        ("arctic_training.trainer.parallel_groups", "ParallelGroups", None),
+        ("arctic_training.synth.base_caller", "BatchProcessor", impl.synth.BatchProcessor),
+        ("arctic_training.synth.vllm_callers", "MultiReplicaVllmSynth", impl.synth.MultiReplicaVllmSynth),
+        ("arctic_training.synth.vllm_utils", "launch_vllm_servers", None),
+        ("arctic_training.synth.vllm_utils", "check_vllm_servers_health", None),
+        ("arctic_training.synth.vllm_utils", "kill_processes", None),
+        ("arctic_training.synth.utils", "recursive_to_dict", None),
+        ("arctic_training.debug.utils", "print_rank0", None),
     ]
     for mod, name, expect in pairs:
         obj = getattr(importlib.import_module(mod), name)
