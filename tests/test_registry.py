@@ -174,6 +174,7 @@ def test_module_paths_of_the_reference_resolve_to_this_package():
 
     import arctic_training
     import arctictraining_b200 as impl
+    import arctictraining_b200.synth  # noqa: F401 - the sub-package is not loaded by the top-level import
 
     pairs = [
         ("arctic_training.trainer.sft_trainer", "SFTTrainer", impl.SFTTrainer),
