@@ -28,6 +28,7 @@ from __future__ import annotations
 
 import os
 import time
+import weakref
 from contextlib import contextmanager
 from contextlib import nullcontext
 from pathlib import Path
@@ -126,7 +127,17 @@ class ZeroUnit:
         return max(0, min(self.n_train - lo, self.shard_size))
 
 
+_LIVE_ENGINES: "weakref.WeakSet[TrainingEngine]" = weakref.WeakSet()
+
+
+def live_engines() -> List["TrainingEngine"]:
+    """Engines that currently exist in this process, oldest first (look-up of the engine that owns a parameter)."""
+    return sorted(_LIVE_ENGINES, key=lambda e: e._serial)
+
+
 class TrainingEngine:
+    _next_serial = 0
+
     def __init__(
         self,
         model: nn.Module,
@@ -142,6 +153,9 @@ class TrainingEngine:
         self.optimizer = optimizer
         self.lr_scheduler = lr_scheduler
         self.cfg = EngineConfig.from_dict(config)
+        self._serial = TrainingEngine._next_serial
+        TrainingEngine._next_serial += 1
+        _LIVE_ENGINES.add(self)
         self.training_mode = training
         self.device = next(model.parameters()).device
         self.on_gpu = self.device.type == "cuda"

@@ -94,3 +94,118 @@ def enable_tiled_mlp_compute(model: nn.Module) -> int:
             mod._atb_tiled = True
             count += 1
     return count
+
+
+# ---------------------------------------------------------------------------------------------------------------------
+# Generic sequence-tiled autograd functions for user code: any ``fn(module, x_tile, ...)`` evaluated tile by tile.
+# Call signatures follow the upstream functions the reference calls (arctic_training/model/tiled_compute.py:75-81,
+# arctic_training/trainer/sft_trainer.py:145-154, projects/swiftkv/train.py:197-224).
+
+def _seq_chunks(t: torch.Tensor, num_shards: int):
+    dim = t.dim() - 2 if t.dim() >= 2 else 0
+    return list(torch.chunk(t, num_shards, dim=dim)), dim
+
+
+class TiledMLP(torch.autograd.Function):
+    """``TiledMLP.apply(fn, module, x, num_shards, compute_params)``: ``fn(module, x)`` over ``num_shards`` tiles of
+    the sequence dimension (second to last) of ``x``.  Forward keeps no intermediate activation; backward recomputes
+    one tile at a time and accumulates the parameter gradients across tiles, handing each parameter its gradient
+    once."""
+
+    @staticmethod
+    def forward(ctx, fn, module, x, num_shards, compute_params=None):
+        ctx.fn, ctx.module, ctx.num_shards = fn, module, int(num_shards)
+        ctx.params = [p for p in (compute_params or []) if p.requires_grad]
+        ctx.save_for_backward(x)
+        tiles, dim = _seq_chunks(x, ctx.num_shards)
+        with torch.no_grad():
+            outs = [fn(module, t) for t in tiles]
+        return torch.cat(outs, dim=dim)
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        (x,) = ctx.saved_tensors
+        tiles, dim = _seq_chunks(x, ctx.num_shards)
+        grads, _ = _seq_chunks(grad_out, ctx.num_shards)
+        dx_parts = []
+        param_grads = [None] * len(ctx.params)
+        for t, g in zip(tiles, grads):
+            t = t.detach().requires_grad_(True)
+            with torch.enable_grad():
+                y = ctx.fn(ctx.module, t)
+            got = torch.autograd.grad(y, [t] + ctx.params, g, allow_unused=True)
+            dx_parts.append(got[0] if got[0] is not None else torch.zeros_like(t))
+            for i, pg in enumerate(got[1:]):
+                if pg is not None:
+                    param_grads[i] = pg if param_grads[i] is None else param_grads[i].add_(pg)
+        for p, pg in zip(ctx.params, param_grads):
+            if pg is not None:
+                p.grad = pg if p.grad is None else p.grad.add_(pg)
+        return None, None, torch.cat(dx_parts, dim=dim), None, None
+
+
+class TiledFusedLogitsLoss(torch.autograd.Function):
+    """``TiledFusedLogitsLoss.apply(fn, module, x, y, mask, num_shards, compute_params, output_reduction)``: a loss
+    ``fn(module, x_tile, y_tile, mask_tile)`` that goes through a large projection (logits), evaluated tile by tile
+    over the sequence.  The gradient of every tile is taken inside forward, so a tile's logits are freed before the
+    next tile starts and ``[sequence, vocabulary]`` never exists; backward only scales the stored gradients by the
+    incoming one.  ``output_reduction``: ``"sum"`` adds the tile losses, ``"mean"`` averages them weighted by tile
+    length.  ``y`` is split like ``x`` when it has a sequence dimension (labels ``[B, S]`` or teacher states
+    ``[B, S, H]``); ``mask`` may be ``None``; the last tile may be shorter."""
+
+    @staticmethod
+    def forward(ctx, fn, module, x, y, mask, num_shards, compute_params=None, output_reduction="mean"):
+        if output_reduction not in ("sum", "mean"):
+            raise ValueError(f"output_reduction must be 'sum' or 'mean', got {output_reduction!r}")
+        params = [p for p in (compute_params or []) if p.requires_grad]
+        num_shards = int(num_shards)
+        seq_dim = x.dim() - 2
+        seq_len = x.shape[seq_dim]
+
+        def split_like_x(t):
+            if t is None:
+                return [None] * num_shards
+            dim = next((d for d in range(t.dim()) if t.shape[d] == seq_len and d >= seq_dim - (x.dim() - t.dim())
+                        and d <= seq_dim), None)
+            if dim is None:
+                raise ValueError(f"cannot find the sequence dimension ({seq_len}) in a tensor of shape {tuple(t.shape)}")
+            return list(torch.chunk(t, num_shards, dim=dim))
+
+        x_tiles = list(torch.chunk(x, num_shards, dim=seq_dim))
+        y_tiles, m_tiles = split_like_x(y), split_like_x(mask)
+        need_dx = x.requires_grad
+        dx_parts = []
+        param_grads = [None] * len(params)
+        total = None
+        for xt, yt, mt in zip(x_tiles, y_tiles, m_tiles):
+            xt = xt.detach().requires_grad_(need_dx)
+            with torch.enable_grad():
+                loss = fn(module, xt, yt, mt)
+                if output_reduction == "mean":
+                    loss = loss * (xt.shape[seq_dim] / seq_len)
+            wanted = ([xt] if need_dx else []) + params
+            if wanted and loss.requires_grad:
+                got = list(torch.autograd.grad(loss, wanted, allow_unused=True))
+                if need_dx:
+                    g = got.pop(0)
+                    dx_parts.append(g if g is not None else torch.zeros_like(xt))
+                for i, pg in enumerate(got):
+                    if pg is not None:
+                        param_grads[i] = pg if param_grads[i] is None else param_grads[i].add_(pg)
+            elif need_dx:
+                dx_parts.append(torch.zeros_like(xt))
+            total = loss.detach() if total is None else total + loss.detach()
+        ctx.seq_dim, ctx.params, ctx.need_dx = seq_dim, params, need_dx
+        ctx.dx = torch.cat(dx_parts, dim=seq_dim) if need_dx else None
+        ctx.param_grads = param_grads
+        return total
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        for p, pg in zip(ctx.params, ctx.param_grads):
+            if pg is not None:
+                pg = pg * grad_out.to(pg.dtype)
+                p.grad = pg if p.grad is None else p.grad.add_(pg)
+        dx = ctx.dx * grad_out.to(ctx.dx.dtype) if ctx.need_dx else None
+        ctx.dx, ctx.param_grads = None, []
+        return None, None, dx, None, None, None, None, None

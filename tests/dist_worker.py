@@ -106,6 +106,40 @@ def scenario_rank_failure(out_dir):
     time.sleep(60)
 
 
+def scenario_shim(out_dir):
+    """User code written against the upstream engine package: its imports resolve to the stand-in modules.  Rank 0
+    overwrites a stage-3 parameter inside ``GatheredParameters(modifier_rank=0)``; every rank then sees the new value,
+    also after a training step (the master weights were refreshed)."""
+    from arctictraining_b200.compat import deepspeed_shim
+
+    assert deepspeed_shim.install()
+    import deepspeed.comm as ds_dist
+    from deepspeed.accelerator import get_accelerator
+    from deepspeed.runtime.zero import GatheredParameters
+
+    rank = ds_dist.get_rank()
+    assert get_accelerator().communication_backend_name() == "gloo"
+    engine = make_engine(3)
+    layer = engine.module.model.layers[1]
+    target = layer.mlp.down_proj.weight if hasattr(layer.mlp, "down_proj") else next(layer.parameters())
+    name = next(n for n, p in engine.module.named_parameters() if p is target)
+    assert target.numel() == 0  # released between steps under stage 3
+    with GatheredParameters([target], modifier_rank=0):
+        assert target.numel() > 0
+        if rank == 0:
+            target.data.fill_(0.125)
+    assert target.numel() == 0
+    seen = dict(engine.iter_full_named_parameters())[name].clone()
+    with GatheredParameters([target]):  # read-only access
+        inside = target.detach().clone()
+    b = global_batches(1, ds_dist.get_world_size())[0]
+    out = engine(**{k: v[rank::ds_dist.get_world_size()] for k, v in b.items()})
+    engine.backward(out.loss)
+    engine.step()
+    after = dict(engine.iter_full_named_parameters())[name].clone()
+    torch.save({"seen": seen, "inside": inside, "after": after}, Path(out_dir) / f"shim_rank{rank}.pt")
+
+
 def main():
     scenario, out_dir = sys.argv[1], sys.argv[2]
     init_distributed(timeout_s=60)
@@ -119,6 +153,8 @@ def main():
         scenario_trainer(out_dir, sys.argv[3])
     elif scenario == "rank_failure":
         scenario_rank_failure(out_dir)
+    elif scenario == "shim":
+        scenario_shim(out_dir)
     else:
         raise SystemExit(f"unknown scenario {scenario}")
     dist.barrier()

@@ -172,3 +172,14 @@ def test_expert_parallel_run_matches_unsharded_experts_and_exports_all_experts(t
             # tensor as a whole tightly and single elements within a few steps of the learning rate (1e-3)
             assert float((b[k] - a[k]).norm() / (a[k].norm() + 1e-12)) < 3e-2, (k, step)
             torch.testing.assert_close(b[k], a[k], atol=2e-3 * step + 1e-4, rtol=0, msg=lambda m: f"{k} at step {step}: {m}")
+
+
+def test_gathered_parameters_of_the_stand_in_engine_package_two_ranks(tmp_path):
+    launch(2, "shim", tmp_path)
+    r0, r1 = (torch.load(tmp_path / f"shim_rank{r}.pt", weights_only=True) for r in (0, 1))
+    for r in (r0, r1):
+        assert torch.all(r["seen"] == 0.125) and torch.all(r["inside"] == 0.125)
+        # one AdamW step at lr 1e-2 moves every element by at most about lr (+ weight decay): the update started from
+        # the value rank 0 wrote, not from the initial weights
+        assert (r["after"] - 0.125).abs().max() < 0.03
+    torch.testing.assert_close(r0["after"], r1["after"])
