@@ -60,13 +60,17 @@ class DataFactory(ABC, CallbackMixin, metaclass=RegistryMeta):
         self.config = config if config is not None else trainer.config.data
 
     # ------------------------------------------------------------------ orchestration
+    def _get_data_sources(self, data_source_configs: List[DataSourceConfig]) -> List["DataSource"]:
+        """One data-source object per configured source, bound to this factory."""
+        return [c.data_source(data_factory=self, config=c) for c in data_source_configs]
+
     def _load_sources(self, cfgs: List[DataSourceConfig]):
         from datasets import concatenate_datasets
         from datasets import load_from_disk
 
         if not cfgs:
             return None
-        sources = [c.data_source(data_factory=self, config=c) for c in cfgs]
+        sources = self._get_data_sources(cfgs)
         cache_path = self.cache_path(sources)
         if self.is_main_process_by_path and not cache_path.exists():
             if self.config.fail_on_missing_cache:

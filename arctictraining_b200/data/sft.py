@@ -172,8 +172,8 @@ class SFTDataConfig(DataConfig):
         if self.pad_to == "max_length" and "div_length" in self.model_fields_set and self.max_length % self.div_length:
             lo = self.max_length // self.div_length * self.div_length
             raise ValueError(
-                f"pad_to='max_length' needs max_length ({self.max_length}) divisible by div_length "
-                f"({self.div_length}); use {lo} or {lo + self.div_length}, or drop div_length."
+                f"You have requested padding sequences to 'max_length', which needs max_length ({self.max_length}) "
+                f"divisible by div_length ({self.div_length}); use {lo} or {lo + self.div_length}, or drop div_length."
             )
         return self
 
