@@ -64,3 +64,32 @@ def test_generated_data_is_reproducible(tmp_path):
         pad = factory.tokenizer.pad_token_id
         sums.append(sum(int(x) for b in train_dl for x in b["input_ids"].flatten() if x != pad))
     assert sums[0] == sums[1] > 0
+
+
+def _toy_conversations(n=20):
+    from datasets import Dataset
+
+    rows = [{"messages": [{"role": "user", "content": f"question number {i} about topic {i % 3}"},
+                          {"role": "assistant", "content": f"answer number {i} with some more words"}],
+             "prompt_id": str(i)} for i in range(n)]
+    return Dataset.from_list(rows)
+
+
+@pytest.mark.parametrize("with_split", [True, False])
+def test_local_dataset_through_the_instruct_source(tmp_path, with_split):
+    """A dataset saved to disk, with a ``train`` split or as a bare dataset, read through ``huggingface_instruct`` with a
+    ``messages.role.<value>`` role mapping (tests/data/test_hf_source.py of the reference)."""
+    from datasets import DatasetDict
+
+    path = tmp_path / "local_chat"
+    data = _toy_conversations()
+    (DatasetDict(dict(train=data)) if with_split else data).save_to_disk(path.as_posix())
+    factory = create_data_factory(dict(
+        type="sft", cache_dir=tmp_path / "cache", max_length=4096, pack_samples=False,
+        sources=[dict(type="huggingface_instruct", name_or_path=path.as_posix(),
+                      role_mapping={"user": "messages.role.user", "assistant": "messages.role.assistant"})]))
+    train_dl, _ = factory()
+    assert len(train_dl) == 20
+    batch = next(iter(train_dl))
+    labels = batch["labels"][0]
+    assert (labels == -100).any() and (labels != -100).any()  # the user turn is masked, the assistant turn is trained on
