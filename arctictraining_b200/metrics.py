@@ -163,7 +163,9 @@ class Metrics:
         if "loss" in s:
             line += f" | loss: {s['loss']:.4f}"
         if "loss/eval" in s:
-            line += f" | loss: {s['loss/eval']:.4f}"
+            # an evaluation loss that was recorded but not yet reported (eval_log_iter_interval > eval_interval) rides
+            # along on the next training line: name it
+            line += f" | {'eval loss' if 'loss' in s else 'loss'}: {s['loss/eval']:.4f}"
         if "iter_time" in s:
             line += f" | iter time: {human_format_secs(s['iter_time'])}"
         if "iter_tflops" in s:

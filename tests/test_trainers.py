@@ -258,3 +258,24 @@ def test_damaged_checkpoints_are_refused_with_the_file_named(tiny_recipe, tmp_pa
     (tmp_path / "ck" / "latest").write_text("epoch_9_global_step_99")
     with pytest.raises(CheckpointError, match="epoch_9_global_step_99"):
         build(tiny_recipe(checkpoint=ck, exit_iteration=4))
+
+
+def test_eval_loss_is_reported_or_kept_according_to_the_log_interval(tiny_recipe, tmp_path):
+    """``eval_interval: 1``: the evaluation loss of the last step is in the summary and no longer pending.  With
+    ``eval_log_iter_interval: 2`` and three steps the loss of step 3 was recorded but not reported (pattern of the
+    reference's tests/trainer/test_sft_trainer.py)."""
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    def run(**extra):
+        r = tiny_recipe(**{"exit_iteration": 2, "eval_interval": 1, **extra})
+        r["data"]["train_eval_split"] = [0.8, 0.2]
+        r["data"]["cache_dir"] = str(tmp_path / f"cache{len(extra)}")
+        trainer = get_registered_trainer("sft")(get_config(r))
+        trainer.train()
+        return trainer
+
+    t = run()
+    assert t.metrics.summary_dict["loss/eval"] > 0 and "loss/eval" not in t.metrics.values
+    t = run(exit_iteration=3, eval_log_iter_interval=2)
+    assert "loss/eval" in t.metrics.values and "loss/eval" not in t.metrics.summary_dict
