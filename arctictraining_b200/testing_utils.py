@@ -342,18 +342,19 @@ class TestCasePlus(unittest.TestCase):
         env["PYTHONPATH"] = ":".join(paths)
         return env
 
-    def get_auto_remove_tmp_dir(self, tmp_dir: Optional[str] = None, before: bool = True, after: bool = True) -> str:
+    def get_auto_remove_tmp_dir(self, tmp_dir: Optional[str] = None, before: bool = True, after: bool = True) -> Path:
+        """A directory (``pathlib.Path``) that is removed when the test ends (``after``); a given ``tmp_dir`` is
+        emptied first (``before``) - handy for looking at the files of a failing test in a known place."""
         if tmp_dir is None:
-            tmp_dir = tempfile.mkdtemp()
+            path = Path(tempfile.mkdtemp())
         else:
             path = Path(tmp_dir).resolve()
             if before and path.exists():
                 shutil.rmtree(path, ignore_errors=True)
             path.mkdir(parents=True, exist_ok=True)
-            tmp_dir = str(path)
         if after:
-            self._teardown_dirs.append(tmp_dir)
-        return tmp_dir
+            self._teardown_dirs.append(str(path))
+        return path
 
     def get_auto_remove_tmp_dir_str(self, *args: Any, **kwargs: Any) -> str:
         return str(self.get_auto_remove_tmp_dir(*args, **kwargs))
