@@ -324,10 +324,11 @@ class TestCasePlus(unittest.TestCase):
         here = Path(inspect.getfile(self.__class__)).resolve()
         self.test_file_path = here
         self.test_file_dir = here.parent
-        self.repo_root_dir = next((p for p in here.parents if (p / "arctictraining_b200").is_dir()), here.parent)
+        self.repo_root_dir = next((p for p in here.parents if (p / "tests").is_dir() and (
+            (p / "arctictraining_b200").is_dir() or (p / "arctic_training").is_dir())), here.parent)
         self.tests_dir = self.repo_root_dir / "tests"
         self.data_dir = self.tests_dir / "data"
-        self.src_dir = self.repo_root_dir / "arctictraining_b200"
+        self.src_dir = self.repo_root_dir  # the directory to put on PYTHONPATH so that the package imports
 
     test_file_path_str = property(lambda self: str(self.test_file_path))
     test_file_dir_str = property(lambda self: str(self.test_file_dir))

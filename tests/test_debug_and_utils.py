@@ -135,7 +135,8 @@ def test_testing_helpers_env_paths_logger_and_seed(tmp_path, monkeypatch):
     case = Case()
     case.setUp()
     assert case.test_file_path == Path(__file__).resolve() and case.tests_dir_str.endswith("tests")
-    assert case.src_dir.name == "arctictraining_b200" and case.repo_root_dir_str == str(case.tests_dir.parent)
+    assert (case.src_dir / "arctictraining_b200").is_dir() and case.repo_root_dir_str == str(case.tests_dir.parent)
+    assert case.get_env()["PYTHONPATH"].split(":")[0] == case.src_dir_str
     d = case.get_auto_remove_tmp_dir_str()
     assert Path(d).is_dir()
     case.tearDown()
