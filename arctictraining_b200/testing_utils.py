@@ -217,7 +217,7 @@ class CaptureStd:
 
     def __init__(self, out: bool = True, err: bool = True, replay: bool = True) -> None:
         self.want_out, self.want_err, self.replay = out, err, replay
-        self.out = self.err = ""
+        self.out = self.err = self.combined = ""
 
     def __enter__(self) -> "CaptureStd":
         if self.want_out:
@@ -235,6 +235,11 @@ class CaptureStd:
             self.err, sys.stderr = sys.stderr.getvalue(), self._old_err
             if self.replay:
                 sys.stderr.write(self.err)
+        self.out, self.err = apply_print_resets(self.out), apply_print_resets(self.err)
+        self.combined = self.out + self.err
+
+    def __repr__(self) -> str:
+        return (f"stdout: {self.out}\n" if self.want_out else "") + (f"stderr: {self.err}\n" if self.want_err else "")
 
 
 class CaptureStdout(CaptureStd):

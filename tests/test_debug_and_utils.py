@@ -1,5 +1,6 @@
 # SPDX-License-Identifier: Apache-2.0
 import os
+import sys
 from pathlib import Path
 
 import pytest
@@ -55,7 +56,9 @@ def test_small_helpers(capsys):
     assert "ATB_TEST_VAR" not in __import__("os").environ
     with CaptureStd(replay=False) as cs:
         print("hello")
+        print("10%\r100% done", file=sys.stderr)
     assert cs.out.strip() == "hello"
+    assert cs.err == "100% done\n" and cs.combined == "hello\n100% done\n" and "stderr: 100% done" in repr(cs)
     assert get_unique_port_number() >= 10999
 
 
