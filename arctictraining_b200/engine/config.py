@@ -23,6 +23,38 @@ from typing import Optional
 import torch
 
 
+# keys this engine acts on (top level / zero_optimization); everything else in the section is a tuning knob of the
+# engine the recipes were written for (bucket sizes, overlap switches, ...) and is reported once, not silently dropped
+_ACTED_TOP = {"zero_optimization", "bf16", "bfloat16", "fp16", "torch_autocast", "gradient_clipping",
+              "gradient_accumulation_steps", "wall_clock_breakdown", "communication_data_type", "fused_comm",
+              "activation_checkpoint_keep", "activation_keep_memory_fraction", "activation_checkpoint_cpu_offload",
+              "train_micro_batch_size_per_gpu", "train_batch_size", "sequence_parallel_size"}
+_ACTED_ZERO = {"stage", "offload_optimizer", "offload_param", "stage3_param_persistence_threshold"}
+# defaults that the recipe loader itself writes into the section (so that the section reads like the reference's):
+# not worth a message
+_QUIET = {"steps_per_print", "zero_optimization.stage3_max_live_parameters",
+          "zero_optimization.stage3_prefetch_bucket_size", "zero_optimization.reduce_bucket_size"}
+_reported: set = set()
+
+
+def keys_without_effect(d: Dict[str, Any]) -> list:
+    """Dotted names of the entries of an engine section that this engine does not act on.  ``prescale_gradients`` and
+    ``seq_parallel_communication_data_type`` count only when they ask for something else than what the engine does
+    (no pre-scaling; exchanges in the activation dtype, bf16)."""
+    out = []
+    for k, v in d.items():
+        if k in _ACTED_TOP:
+            continue
+        if k == "prescale_gradients" and not v:
+            continue
+        if k == "seq_parallel_communication_data_type" and str(v).replace("torch.", "") in ("None", "bf16", "bfloat16"):
+            continue
+        out.append(k)
+    zo = d.get("zero_optimization") or {}
+    out += [f"zero_optimization.{k}" for k in zo if k not in _ACTED_ZERO]
+    return sorted(k for k in out if k not in _QUIET)
+
+
 def _parse_keep(v: Any) -> Any:
     if isinstance(v, str):
         if v.strip().lower() == "auto":
@@ -73,6 +105,13 @@ class EngineConfig:
     @classmethod
     def from_dict(cls, d: Optional[Dict[str, Any]]) -> "EngineConfig":
         d = dict(d or {})
+        unused = tuple(keys_without_effect(d))
+        if unused and unused not in _reported:
+            _reported.add(unused)
+            from ..logging import logger
+
+            logger.info("engine section: these keys tune the engine the recipe was written for and have no effect here: "
+                        + ", ".join(unused))
         zo = d.get("zero_optimization", {}) or {}
         bf = d.get("bfloat16", d.get("bf16", {})) or {}
         fp = d.get("fp16", {}) or {}

@@ -448,3 +448,21 @@ def test_library_model_checkpoints_with_host_offload():
     for n in want:
         torch.testing.assert_close(got[n], want[n], msg=lambda m, n=n: f"{n}: {m}")
     assert mp.enable_host_offload_on_hf_model(torch.nn.Linear(2, 2)) is False
+
+
+def test_engine_section_keys_without_effect_are_named():
+    from arctictraining_b200.engine.config import EngineConfig
+    from arctictraining_b200.engine.config import keys_without_effect
+
+    quiet = {"zero_optimization": {"stage": 3, "stage3_param_persistence_threshold": 10, "reduce_bucket_size": 5,
+                                   "stage3_max_live_parameters": 7, "offload_optimizer": {"device": "cpu"}},
+             "steps_per_print": 10, "prescale_gradients": False, "gradient_clipping": 1.0,
+             "seq_parallel_communication_data_type": "bf16", "bf16": {"enabled": True}}
+    assert keys_without_effect(quiet) == []
+    noisy = dict(quiet, prescale_gradients=True, zero_allow_untested_optimizer=True,
+                 seq_parallel_communication_data_type="fp32")
+    noisy["zero_optimization"] = dict(quiet["zero_optimization"], overlap_comm=True, memory_efficient_linear=True)
+    assert keys_without_effect(noisy) == ["prescale_gradients", "seq_parallel_communication_data_type",
+                                          "zero_allow_untested_optimizer", "zero_optimization.memory_efficient_linear",
+                                          "zero_optimization.overlap_comm"]
+    assert EngineConfig.from_dict(noisy).zero_stage == 3  # reported, not refused
