@@ -358,6 +358,7 @@ def _build_modules() -> Dict[str, types.ModuleType]:
     from ..ops.tiled import TiledFusedLogitsLoss
     from ..ops.tiled import TiledMLP
     from ..parallel.ulysses import UlyssesDataLoaderAdapter
+    from ..parallel.ulysses_hf import UlyssesSPAttentionHF
 
     comm = _module("deepspeed.comm", init_distributed=_init_distributed, get_local_rank=_get_local_rank)
     zero = _module("deepspeed.runtime.zero", GatheredParameters=GatheredParameters, ZeroParamStatus=ZeroParamStatus)
@@ -366,7 +367,8 @@ def _build_modules() -> Dict[str, types.ModuleType]:
     zero.partition_parameters = partition
     engine = _module("deepspeed.runtime.engine", DeepSpeedEngine=TrainingEngine)
     ulysses = _module("deepspeed.runtime.sequence_parallel.ulysses_sp", TiledMLP=TiledMLP,
-                      TiledFusedLogitsLoss=TiledFusedLogitsLoss, UlyssesSPDataLoaderAdapter=UlyssesDataLoaderAdapter)
+                      TiledFusedLogitsLoss=TiledFusedLogitsLoss, UlyssesSPDataLoaderAdapter=UlyssesDataLoaderAdapter,
+                      UlyssesSPAttentionHF=UlyssesSPAttentionHF)
     seqpar = _module("deepspeed.runtime.sequence_parallel", ulysses_sp=ulysses)
     runtime = _module("deepspeed.runtime", zero=zero, engine=engine, sequence_parallel=seqpar)
     adam = _module("deepspeed.ops.adam", FusedAdam=_fused_adam, DeepSpeedCPUAdam=_cpu_adam)

@@ -57,6 +57,8 @@ class SFTTrainer(Trainer):
                 raise ValueError("under sequence parallelism the batch must carry `shift_labels`, not `labels`")
             if "shift_labels" not in batch:
                 raise ValueError("`shift_labels` is missing from the batch (is the dataloader wrapped for sequence parallelism?)")
+        if sp > 1 and getattr(self, "hf_ulysses", None) is not None:
+            return self._library_model_sp_loss(batch)
         outputs = self.model(**batch, use_cache=False)
         if sp == 1:
             return outputs.loss
@@ -66,6 +68,23 @@ class SFTTrainer(Trainer):
         if getattr(outputs, "aux_loss", None) is not None:
             loss = loss + outputs.aux_loss
         return loss
+
+
+    def _library_model_sp_loss(self, batch: Dict[str, Any]) -> torch.Tensor:
+        """A ``transformers`` model under sequence parallelism: hidden states of this rank's slice from the model body,
+        output projection and cross-entropy chunk by chunk, then the token-weighted mean over the group."""
+        from ..parallel.ulysses_hf import chunked_causal_lm_loss_sum
+
+        model = self.model_unwrapped
+        body = getattr(model, getattr(model, "base_model_prefix", "model"), None)
+        head = model.get_output_embeddings() if hasattr(model, "get_output_embeddings") else None
+        if body is None or head is None:
+            raise ValueError(f"{type(model).__name__} does not expose a model body and an output projection")
+        shift_labels = batch.pop("shift_labels")
+        with self.model._timed("forward"), self.model.autocast():
+            hidden = body(**batch, use_cache=False).last_hidden_state
+            loss_sum, num_tokens = chunked_causal_lm_loss_sum(head, hidden, shift_labels)
+        return self.sp_context.aggregate_loss(loss_sum, num_tokens)
 
 
 class CausalTrainer(SFTTrainer):

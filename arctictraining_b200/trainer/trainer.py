@@ -191,6 +191,12 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
         """Hand run-time switches of the recipe to a native model."""
         if hasattr(model, "sp_context"):
             model.sp_context = self.sp_context
+        elif self.config.sequence_parallel_size > 1:
+            # a model of the transformers library: its attention calls go through a registered function that does the
+            # sequence <-> head exchange around the core attention
+            from ..parallel.ulysses_hf import enable_ulysses_for_hf_model
+
+            self.hf_ulysses = enable_ulysses_for_hf_model(model, self.sp_context, self.config.model.attn_implementation)
         if hasattr(model, "tiled_mlp"):
             model.tiled_mlp = self.config.tiled_mlp_compute
         elif self.config.tiled_mlp_compute:

@@ -106,6 +106,60 @@ def scenario_rank_failure(out_dir):
     time.sleep(60)
 
 
+def scenario_ulysses_hf(out_dir):
+    """A model of the transformers library under sequence parallelism: every rank holds a slice of a packed sequence;
+    loss and summed gradients must match the same model run on the whole sequence in one process."""
+    from transformers import LlamaConfig
+    from transformers import LlamaForCausalLM
+
+    from arctictraining_b200.parallel.ulysses import UlyssesContext
+    from arctictraining_b200.parallel.ulysses import shard_batch_for_rank
+    from arctictraining_b200.parallel.ulysses_hf import chunked_causal_lm_loss_sum
+    from arctictraining_b200.parallel.ulysses_hf import enable_ulysses_for_hf_model
+
+    rank, world = dist.get_rank(), dist.get_world_size()
+    cfg = LlamaConfig(vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=1, max_position_embeddings=128, attn_implementation="sdpa")
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg)
+    S = 48
+    g = torch.Generator().manual_seed(1)
+    ids = torch.randint(0, 160, (1, S), generator=g)
+    position_ids = torch.cat([torch.arange(20), torch.arange(S - 20)])[None]  # two packed samples
+    labels = ids.clone()
+    labels[0, :4] = -100
+    labels[0, 20] = -100  # the first token of a sample is no target of the sample before it
+    batch = {"input_ids": ids, "position_ids": position_ids, "labels": labels}
+
+    # in this process: the two packed samples run one by one, so neither can attend to the other (the library's own
+    # attention functions do not all isolate packed samples; the registered function must)
+    logits = torch.cat([model(input_ids=ids[:, :20]).logits, model(input_ids=ids[:, 20:]).logits], dim=1).float()
+    shift = torch.nn.functional.pad(labels[:, 1:], (0, 1), value=-100)
+    shift[0, 19] = -100
+    ref_sum = torch.nn.functional.cross_entropy(logits[0], shift[0], ignore_index=-100, reduction="sum")
+    ref_loss = ref_sum / (shift != -100).sum()
+    ref_loss.backward()
+    ref_grads = {n: p.grad.clone() for n, p in model.named_parameters()}
+    model.zero_grad()
+
+    ctx = UlyssesContext(dist.group.WORLD, world, rank)
+    fn = enable_ulysses_for_hf_model(model, ctx, "sdpa")
+    local = shard_batch_for_rank(dict(batch), rank, world)
+    sl = shift[:, rank * (S // world):(rank + 1) * (S // world)]
+    hidden = model.model(input_ids=local["input_ids"], position_ids=local["position_ids"], use_cache=False).last_hidden_state
+    loss_sum, n = chunked_causal_lm_loss_sum(model.lm_head, hidden, sl, logits_bytes_per_chunk=4 * 160 * 7)
+    loss = ctx.aggregate_loss(loss_sum, n)
+    loss.backward()
+    grads = {}
+    for name, p in model.named_parameters():
+        gsum = p.grad.clone()
+        dist.all_reduce(gsum)
+        grads[name] = gsum
+    if rank == 0:
+        torch.save({"ref_loss": ref_loss.detach(), "loss": loss.detach(), "ref_grads": ref_grads, "grads": grads,
+                    "calls": fn.calls}, Path(out_dir) / "ulysses_hf.pt")
+
+
 def scenario_shim(out_dir):
     """User code written against the upstream engine package: its imports resolve to the stand-in modules.  Rank 0
     overwrites a stage-3 parameter inside ``GatheredParameters(modifier_rank=0)``; every rank then sees the new value,
@@ -155,6 +209,8 @@ def main():
         scenario_rank_failure(out_dir)
     elif scenario == "shim":
         scenario_shim(out_dir)
+    elif scenario == "ulysses_hf":
+        scenario_ulysses_hf(out_dir)
     else:
         raise SystemExit(f"unknown scenario {scenario}")
     dist.barrier()

@@ -183,3 +183,36 @@ def test_gathered_parameters_of_the_stand_in_engine_package_two_ranks(tmp_path):
         # the value rank 0 wrote, not from the initial weights
         assert (r["after"] - 0.125).abs().max() < 0.03
     torch.testing.assert_close(r0["after"], r1["after"])
+
+
+@pytest.mark.parametrize("world", [2, 4])
+def test_library_model_attention_under_sequence_parallelism(tmp_path, world):
+    """Ulysses through the attention registry of the transformers library (one key/value head, so it is replicated
+    over the ranks; two packed samples): loss and summed gradients equal the single-process run."""
+    launch(world, "ulysses_hf", tmp_path)
+    r = torch.load(tmp_path / "ulysses_hf.pt", weights_only=True)
+    assert r["calls"] >= 2
+    torch.testing.assert_close(r["loss"], r["ref_loss"], rtol=1e-5, atol=1e-6)
+    for name, want in r["ref_grads"].items():
+        torch.testing.assert_close(r["grads"][name], want, rtol=2e-4, atol=2e-6, msg=lambda m, n=name: f"{n}: {m}")
+
+
+def test_library_model_trains_under_sequence_parallelism_like_data_parallel(tmp_path):
+    """An architecture without an own implementation (OLMo-2 from the transformers library, random weights): DP=2 vs
+    SP=2 with GAS=2 through the trainer - the same two samples feed every optimizer step, so the losses agree."""
+    from transformers import Olmo2Config
+
+    arch = tmp_path / "tiny-olmo2"
+    Olmo2Config(vocab_size=1024, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=2, max_position_embeddings=256).save_pretrained(arch)
+    model = {"name_or_path": str(arch), "dtype": "fp32", "attn_implementation": "sdpa",
+             "hf_config_kwargs": {"num_hidden_layers": 2}}  # a changed depth means random initialisation
+    common = dict(model=model, tokenizer={"type": "fake", "name_or_path": "tiny-llama"})
+    dp = _recipe(tmp_path, "lib_dp", **common)
+    sp = _recipe(tmp_path, "lib_sp", sequence_parallel_size=2, gradient_accumulation_steps=2, exit_iteration=2, **common)
+    launch(2, "trainer", tmp_path, dp)
+    launch(2, "trainer", tmp_path, sp)
+    l_dp, l_sp = _losses(tmp_path / "lib_dp.jsonl"), _losses(tmp_path / "lib_sp.jsonl")
+    assert len(l_dp) >= 2 and len(l_sp) >= 2
+    assert l_sp[0] == pytest.approx(l_dp[0], rel=1e-5, abs=1e-6)
+    assert l_sp[1] == pytest.approx(l_dp[1], rel=2e-3)
