@@ -466,3 +466,34 @@ def test_engine_section_keys_without_effect_are_named():
                                           "zero_allow_untested_optimizer", "zero_optimization.memory_efficient_linear",
                                           "zero_optimization.overlap_comm"]
     assert EngineConfig.from_dict(noisy).zero_stage == 3  # reported, not refused
+
+
+def test_tiled_mlp_patch_on_a_library_model_keeps_outputs_and_gradients():
+    """``tiled_mlp_compute`` on a transformers model: every ``*MLP`` module runs over sequence tiles (tokens / hidden
+    tiles, here 4), recomputing each tile in backward; loss and gradients are those of the plain model."""
+    from transformers import LlamaConfig
+    from transformers import LlamaForCausalLM
+
+    from arctictraining_b200.ops.tiled import enable_tiled_mlp_compute
+    from arctictraining_b200.ops.tiled import num_mlp_tiles
+
+    cfg = LlamaConfig(vocab_size=128, hidden_size=32, intermediate_size=64, num_hidden_layers=2, num_attention_heads=4,
+                      num_key_value_heads=2, max_position_embeddings=128)
+    torch.manual_seed(0)
+    model = LlamaForCausalLM(cfg)
+    ids = torch.randint(0, 128, (1, 100), generator=torch.Generator().manual_seed(3))
+    assert num_mlp_tiles(torch.empty(1, 100, 32)) == 4
+
+    def run():
+        model.zero_grad()
+        out = model(input_ids=ids, labels=ids)
+        out.loss.backward()
+        return out.loss.detach().clone(), {n: p.grad.clone() for n, p in model.named_parameters()}
+
+    want_loss, want = run()
+    assert enable_tiled_mlp_compute(model) == 2
+    assert enable_tiled_mlp_compute(model) == 0  # already patched
+    got_loss, got = run()
+    torch.testing.assert_close(got_loss, want_loss)
+    for n in want:
+        torch.testing.assert_close(got[n], want[n], rtol=1e-4, atol=1e-6, msg=lambda m, n=n: f"{n}: {m}")
