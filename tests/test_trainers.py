@@ -279,3 +279,54 @@ def test_eval_loss_is_reported_or_kept_according_to_the_log_interval(tiny_recipe
     assert t.metrics.summary_dict["loss/eval"] > 0 and "loss/eval" not in t.metrics.values
     t = run(exit_iteration=3, eval_log_iter_interval=2)
     assert "loss/eval" in t.metrics.values and "loss/eval" not in t.metrics.summary_dict
+
+
+def test_train_iters_sets_the_horizon_and_runs_over_epoch_boundaries(tiny_recipe):
+    """``train_iters`` replaces ``epochs``: 32 samples at batch 2 are 16 steps per epoch; 20 steps need a second epoch."""
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    r = tiny_recipe(train_iters=20, exit_iteration=0, epochs=1)
+    trainer = get_registered_trainer("sft")(get_config(r))
+    assert trainer.training_horizon == 20 and len(trainer.train_dataloader) == 16
+    trainer.train()
+    assert trainer.global_step == 20 and trainer.epoch_idx >= 1
+
+
+def test_loss_log_interval_and_epoch_checkpoints(tiny_recipe, tmp_path):
+    """``loss_log_interval: 2`` logs the loss of every second step; ``save_every_n_epochs: 1`` writes one export at the
+    end of each epoch (the directory is named after the global step)."""
+    from loguru import logger as loguru_logger
+
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    r = tiny_recipe(exit_iteration=0, epochs=2, loss_log_interval=2,
+                    checkpoint=[{"type": "huggingface", "output_dir": str(tmp_path / "hf"), "save_every_n_epochs": 1}])
+    r["data"]["sources"][0]["num_samples"] = 8  # 4 steps per epoch
+    lines = []
+    sink = loguru_logger.add(lambda m: lines.append(str(m)), level="INFO")
+    try:
+        trainer = get_registered_trainer("sft")(get_config(r))
+        trainer.train()
+    finally:
+        loguru_logger.remove(sink)
+    assert trainer.global_step == 8
+    logged = sorted(int(ln.split("Global Step: ")[1].split("/")[0]) for ln in lines if "Global Step:" in ln)
+    assert logged and all(step % 2 == 0 for step in logged)
+    assert sorted(p.name for p in (tmp_path / "hf").iterdir() if p.is_dir()) == ["global_step_4", "global_step_8"]
+
+
+def test_entrypoint_profile_option_prints_a_profile_and_trains(tiny_recipe, tmp_path, capsys, monkeypatch):
+    import yaml
+
+    from arctictraining_b200 import entrypoint
+
+    r = tiny_recipe(exit_iteration=2)
+    path = tmp_path / "r.yaml"
+    path.write_text(yaml.safe_dump(r))
+    monkeypatch.setenv("LOCAL_RANK", "0")
+    entrypoint.launch(["--config", str(path), "--python_profile", "tottime"])
+    out = capsys.readouterr().out
+    assert "function calls" in out and "tottime" in out
+    assert (tmp_path / "metrics.jsonl").read_text().count("\n") >= 2
