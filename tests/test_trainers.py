@@ -330,3 +330,37 @@ def test_entrypoint_profile_option_prints_a_profile_and_trains(tiny_recipe, tmp_
     out = capsys.readouterr().out
     assert "function calls" in out and "tottime" in out
     assert (tmp_path / "metrics.jsonl").read_text().count("\n") >= 2
+
+
+def test_library_architecture_trains_checkpoints_and_reloads(tiny_recipe, tmp_path):
+    """An architecture this package has no own implementation of (OLMo-2 through the transformers library): ZeRO-3
+    training with tiled MLP and LoRA off, Hugging Face export, and the export loads back into the library's class with
+    the trained weights."""
+    from transformers import AutoModelForCausalLM
+    from transformers import Olmo2Config
+
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    arch = tmp_path / "tiny-olmo2"
+    Olmo2Config(vocab_size=1024, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=2, max_position_embeddings=256).save_pretrained(arch)
+    r = tiny_recipe(
+        exit_iteration=3, tiled_mlp_compute=True,
+        model={"name_or_path": str(arch), "dtype": "fp32", "attn_implementation": "sdpa",
+               "hf_config_kwargs": {"num_hidden_layers": 2}},
+        tokenizer={"type": "fake", "name_or_path": "tiny-llama"},
+        checkpoint=[{"type": "huggingface", "output_dir": str(tmp_path / "hf"), "save_end_of_training": True}])
+    r["deepspeed"] = {"zero_optimization": {"stage": 3}}
+    trainer = get_registered_trainer("sft")(get_config(r))
+    assert type(trainer.model_unwrapped).__name__ == "Olmo2ForCausalLM"
+    before = {n: t.clone() for n, t in trainer.model.iter_full_named_parameters()}
+    trainer.train()
+    after = {n: t.clone() for n, t in trainer.model.iter_full_named_parameters()}
+    assert any(not torch.equal(before[n], after[n]) for n in before)
+    out = next((tmp_path / "hf").iterdir())
+    reloaded = AutoModelForCausalLM.from_pretrained(out)
+    assert reloaded.config.num_hidden_layers == 2
+    state = reloaded.state_dict()
+    for n, t in after.items():
+        torch.testing.assert_close(state[n].float(), t.float(), msg=lambda m, n=n: f"{n}: {m}")
