@@ -165,12 +165,9 @@ class HFModelFactory(ModelFactory):
             logger.info(f"Applied PEFT config: total params {total}, trainable {trainable} ({100 * trainable / total:.2f}%)")
         model.activation_checkpointing = not self.config.disable_activation_checkpoint
         if hasattr(model, "gradient_checkpointing_enable") and not self.config.disable_activation_checkpoint:
+            # kept for parity of the model's flags; the engine checkpoints (and, when asked, offloads) the inputs of
+            # the decoder layers itself, and a layer is computed twice per step, not three times (tested)
             model.gradient_checkpointing_enable()
-            if getattr(self.trainer.config, "activation_checkpoint_cpu_offload", False):
-                # a library model checkpoints through torch.utils.checkpoint: keep each layer's input in host memory
-                from ..monkey_patches import enable_host_offload_on_hf_model
-
-                enable_host_offload_on_hf_model(model)
         return model
 
 

@@ -3,8 +3,10 @@
 modules): the tensors a checkpointed region keeps for its backward pass - its inputs, i.e. the hidden state that enters
 a layer - wait in pinned host memory instead of on the device.
 
-The models of this package do not need this: the engine checkpoints their layers itself and offloads through the same
-:class:`~arctictraining_b200.engine.activation.ActivationStore` (``activation_checkpoint_cpu_offload: true``).
+Models that run under this package's engine do not need this - own architectures and transformers models alike: the
+engine checkpoints their decoder layers itself and offloads the layer inputs through the same
+:class:`~arctictraining_b200.engine.activation.ActivationStore` (``activation_checkpoint_cpu_offload: true``).  This
+module is for code that calls ``torch.utils.checkpoint`` on its own, outside those layers.
 
 How: ``torch.utils.checkpoint.checkpoint`` is wrapped so that the call runs in its re-entrant form under a pair of
 saved-tensor hooks.  The re-entrant form saves exactly its tensor arguments; the pack hook hands every large floating

@@ -364,3 +364,30 @@ def test_library_architecture_trains_checkpoints_and_reloads(tiny_recipe, tmp_pa
     state = reloaded.state_dict()
     for n, t in after.items():
         torch.testing.assert_close(state[n].float(), t.float(), msg=lambda m, n=n: f"{n}: {m}")
+
+
+def test_library_model_layers_are_computed_twice_per_step_and_inputs_go_through_the_store(tiny_recipe, tmp_path):
+    """The engine checkpoints the decoder layers of a transformers model itself: one forward and one recomputation per
+    step (the library's own checkpointing flag must not add a third), and with the offload switch the layer inputs are
+    handed to the activation store."""
+    from transformers import Olmo2Config
+
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    arch = tmp_path / "tiny-olmo2"
+    Olmo2Config(vocab_size=1024, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=2, max_position_embeddings=256).save_pretrained(arch)
+    r = tiny_recipe(exit_iteration=2, activation_checkpoint_cpu_offload=True,
+                    model={"name_or_path": str(arch), "dtype": "fp32", "attn_implementation": "sdpa",
+                           "hf_config_kwargs": {"num_hidden_layers": 2}},
+                    tokenizer={"type": "fake", "name_or_path": "tiny-llama"})
+    trainer = get_registered_trainer("sft")(get_config(r))
+    calls, saved = [0], [0]
+    trainer.model_unwrapped.model.layers[0].mlp.register_forward_hook(lambda *a: calls.__setitem__(0, calls[0] + 1))
+    store = trainer.model.act_store
+    original_save = store.save
+    store.save = lambda x: (saved.__setitem__(0, saved[0] + 1), original_save(x))[1]
+    trainer.train()
+    assert calls[0] == 2 * trainer.global_step
+    assert saved[0] >= 2 * trainer.global_step  # two layers per step
