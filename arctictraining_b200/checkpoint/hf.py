@@ -12,7 +12,9 @@ engine), as in the reference.
 
 from __future__ import annotations
 
+from pathlib import Path
 from typing import Any
+from typing import Optional
 
 import torch
 
@@ -30,6 +32,18 @@ class HFCheckpointEngine(CheckpointEngine):
     @property
     def latest_checkpoint_exists(self) -> bool:
         return False
+
+    def model_file(self, file_name: Optional[str] = None) -> Path:
+        """Path of a file inside the current step's export directory (``model.pt`` when no name is given)."""
+        return self.checkpoint_dir / (file_name or "model.pt")
+
+    @property
+    def config_file(self) -> Path:
+        return self.checkpoint_dir / "config.json"
+
+    @property
+    def generation_config_file(self) -> Path:
+        return self.checkpoint_dir / "generation_config.json"
 
     def _export_filter(self, model_module: torch.nn.Module):
         if getattr(self.trainer.config.model, "peft_config", None):

@@ -54,6 +54,22 @@ class ModelConfig(BaseConfig):
     def factory(self) -> Type["ModelFactory"]:
         return get_registered_model_factory(name=self.type)
 
+    @property
+    def peft_config_obj(self) -> Any:
+        """The adapter settings as a config object of the ``peft`` package (needs that package); without the package,
+        a plain namespace with the same fields, which is what the built-in LoRA of the native models reads."""
+        if self.peft_config is None:
+            raise ValueError("No PEFT config specified.")
+        conf = dict(self.peft_config)
+        conf["peft_type"] = str(conf["peft_type"]).upper()
+        try:
+            import peft
+        except ImportError:
+            from types import SimpleNamespace
+
+            return SimpleNamespace(**conf)
+        return peft.get_peft_config(conf)
+
     @field_validator("peft_config", mode="before")
     @classmethod
     def _check_peft(cls, value: Optional[Dict]) -> Optional[Dict]:
