@@ -49,6 +49,18 @@ def pool(hidden: Tensor, attention_mask: Tensor, how: str) -> Tensor:
     raise ValueError(f"unknown pooling {how!r}")
 
 
+def first_token_pool(hidden: Tensor, attention_mask: Tensor) -> Tensor:
+    return pool(hidden, attention_mask, "first")
+
+
+def last_token_pool(hidden: Tensor, attention_mask: Tensor) -> Tensor:
+    return pool(hidden, attention_mask, "last")
+
+
+def average_pool(hidden: Tensor, attention_mask: Tensor) -> Tensor:
+    return pool(hidden, attention_mask, "mean")
+
+
 class Biencoder(nn.Module):
     def __init__(self, encoder: nn.Module, config: BiencoderConfig) -> None:
         super().__init__()
