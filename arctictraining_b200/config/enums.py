@@ -32,3 +32,30 @@ class DType(Enum):
 
     def __repr__(self) -> str:
         return f"DType.{self.name}"
+
+    # A member compares equal to its torch dtype and to every alias string, so ``config.dtype == torch.bfloat16`` and
+    # ``config.dtype == "bf16"`` both hold; the hash is that of the torch dtype.
+    def __eq__(self, other) -> bool:
+        if isinstance(other, DType):
+            return self is other
+        if isinstance(other, str):
+            return other.strip().lower() in _ALIASES[self.value]
+        return other == self.value
+
+    def __hash__(self) -> int:
+        return hash(self.value)
+
+    # Config fields keep the member itself (``config.dtype.value`` is the torch dtype), whatever the model's
+    # ``use_enum_values`` setting says; serialisation writes the torch name.
+    @classmethod
+    def __get_pydantic_core_schema__(cls, source_type, handler):
+        from pydantic_core import core_schema
+
+        return core_schema.no_info_after_validator_function(
+            cls, core_schema.any_schema(),
+            serialization=core_schema.plain_serializer_function_ser_schema(lambda member: str(member.value)),
+        )
+
+    @classmethod
+    def __get_pydantic_json_schema__(cls, schema, handler):
+        return {"type": "string", "title": "Torch Dtype", "examples": ["float32", "bfloat16"]}

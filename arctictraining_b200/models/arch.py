@@ -41,6 +41,14 @@ class ArchConfig(dict):
     def to_json_dict(self) -> Dict[str, Any]:
         return {k: v for k, v in self.items() if not k.startswith("_")}
 
+    def to_hf(self) -> Any:
+        """The same architecture as a config object of the transformers library, e.g. for a custom model factory that
+        builds its model with ``AutoModelForCausalLM.from_config(model_config.to_hf())``."""
+        from transformers import AutoConfig
+
+        fields = {k: v for k, v in self.to_json_dict().items() if k not in ("model_type", "transformers_version")}
+        return AutoConfig.for_model(self["model_type"], **fields)
+
 
 def _llama(hidden, layers, heads, kv_heads, inter, vocab, theta, max_pos, **extra) -> Dict[str, Any]:
     cfg = dict(

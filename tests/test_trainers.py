@@ -391,3 +391,40 @@ def test_library_model_layers_are_computed_twice_per_step_and_inputs_go_through_
     trainer.train()
     assert calls[0] == 2 * trainer.global_step
     assert saved[0] >= 2 * trainer.global_step  # two layers per step
+
+
+def test_custom_model_factory_builds_a_library_model_from_the_architecture_config(tiny_recipe, tmp_path):
+    """Pattern of the reference's test helper (tests/helpers.py: a model factory that overrides ``create_model`` and
+    builds a random-weight model through the transformers library): the architecture config converts with ``to_hf()``,
+    and the resulting Llama model of the library trains on this package's engine."""
+    from transformers import AutoModelForCausalLM
+
+    from arctictraining_b200 import HFModelFactory
+    from arctictraining_b200 import SFTTrainer
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import RegistryMeta
+    from arctictraining_b200.registry import get_registered_trainer
+
+    class RandomWeightHFModelFactory(HFModelFactory):
+        name = "random-weight-hf-test"
+
+        def create_model(self, model_config):
+            torch.manual_seed(11)
+            assert self.config.dtype == torch.float32 and self.config.dtype == "fp32"
+            return AutoModelForCausalLM.from_config(model_config.to_hf(), attn_implementation="sdpa",
+                                                    dtype=self.config.dtype.value)
+
+    class LibraryLlamaTrainer(SFTTrainer):
+        name = "sft-library-llama-test"
+        model_factory: RandomWeightHFModelFactory
+
+    try:
+        r = tiny_recipe(type="sft-library-llama-test", exit_iteration=3, model={"type": "random-weight-hf-test"})
+        trainer = get_registered_trainer("sft-library-llama-test")(get_config(r))
+        assert type(trainer.model_unwrapped).__module__.startswith("transformers.")
+        assert trainer.model_unwrapped.config.num_hidden_layers == trainer.model_unwrapped.config.num_hidden_layers > 0
+        trainer.train()
+        assert trainer.global_step == 3
+    finally:
+        RegistryMeta._registry["ModelFactory"].pop("random-weight-hf-test", None)
+        RegistryMeta._registry["Trainer"].pop("sft-library-llama-test", None)
