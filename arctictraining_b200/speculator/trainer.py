@@ -166,6 +166,7 @@ def speculator_loss(module: torch.nn.Module, hidden: torch.Tensor, input_ids: to
 
 
 class ArcticLSTMSpeculatorTrainer(SFTTrainer):
+    supports_sequence_parallel = False  # the heads predict from whole hidden-state sequences
     name = "arctic-lstm-speculator"
     data_factory: SFTDataFactory
     model_factory: ArcticLSTMSpeculatorModelFactory

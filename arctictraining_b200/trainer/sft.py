@@ -38,6 +38,7 @@ from .utils import to_device
 
 class SFTTrainer(Trainer):
     name = "sft"
+    supports_sequence_parallel = True
     config: TrainerConfig
     data_factory: SFTDataFactory
     model_factory: Union[HFModelFactory, LigerModelFactory]

@@ -55,6 +55,9 @@ from ..utils.misc import append_json_file
 
 
 class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
+    supports_sequence_parallel = False
+    """ Whether ``loss`` works on a rank's slice of the sequence (``shift_labels``, group-wide loss aggregation). """
+
     name: str
     """ Name under which the trainer is selected in a recipe (``type``). """
 
@@ -135,6 +138,12 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
             if eng.name == "deepspeed" and eng.config.auto_resume and eng.latest_checkpoint_exists:
                 self.is_resume = True
 
+        if config.sequence_parallel_size > 1 and not self.supports_sequence_parallel:
+            raise ValueError(
+                f"trainer '{self.name}' computes its loss over whole sequences and does not support "
+                f"sequence_parallel_size={config.sequence_parallel_size}; sequence parallelism is available for the "
+                "sft / causal trainers and those derived from them that handle `shift_labels` (swiftkv, moba)"
+            )
         self.groups = ParallelGroups(config.sequence_parallel_size, config.expert_parallel_size)
         if config.sequence_parallel_size > 1:
             self.sp_group = self.groups.sp_group

@@ -428,3 +428,19 @@ def test_custom_model_factory_builds_a_library_model_from_the_architecture_confi
     finally:
         RegistryMeta._registry["ModelFactory"].pop("random-weight-hf-test", None)
         RegistryMeta._registry["Trainer"].pop("sft-library-llama-test", None)
+
+
+def test_trainers_without_sequence_parallel_support_refuse_the_setting(tiny_recipe, tmp_path):
+    """A trainer whose loss needs whole sequences (DPO, speculators, biencoder) says so instead of training on slices."""
+    r = tiny_recipe(type="dpo", micro_batch_size=1, ref_model={"name_or_path": "tiny-llama", "dtype": "fp32"},
+                    data={"sources": [{"type": "synthetic_dpo", "num_samples": 16, "words_per_message": 6}],
+                          "cache_dir": str(tmp_path / "c"), "max_length": 64, "dl_num_workers": 0},
+                    sequence_parallel_size=2)
+    with pytest.raises(ValueError, match="does not support sequence_parallel_size=2"):
+        build(r)
+    from arctictraining_b200 import CausalTrainer
+    from arctictraining_b200 import DPOTrainer
+    from arctictraining_b200 import SFTTrainer
+
+    assert SFTTrainer.supports_sequence_parallel and CausalTrainer.supports_sequence_parallel
+    assert not DPOTrainer.supports_sequence_parallel
