@@ -156,6 +156,11 @@ class Trainer(ABC, CallbackMixin, metaclass=RegistryMeta):
         self.original_model_params = self._count_params(self.model)
 
         self.use_arctic_moe = self._resolve_arctic_moe()
+        if config.expert_parallel_size > 1 and not self.use_arctic_moe:
+            raise ValueError(
+                f"expert_parallel_size={config.expert_parallel_size} needs a mixture-of-experts model run as ArcticMoE "
+                "(`arctic_moe: true` or `auto`); this model has no experts to distribute"
+            )
         if self.use_arctic_moe:
             from ..moe.convert import convert_hf_blocks_to_arctic_moe
             from ..moe.convert import convert_to_arctic_moe
