@@ -155,9 +155,25 @@ def scenario_ulysses_hf(out_dir):
         gsum = p.grad.clone()
         dist.all_reduce(gsum)
         grads[name] = gsum
+    # the call shape of the upstream helper: registered by name before the model exists, the function takes the place
+    # of the core implementation, so a model created with that implementation afterwards attends through it
+    from arctictraining_b200.parallel.ulysses_hf import UlyssesSPAttentionHF
+
+    mpu = UlyssesSPAttentionHF.register_with_transformers("some/model", "sdpa", world, 1, S)
+    assert mpu.get_sequence_parallel_world_size() == world and mpu.get_sequence_parallel_rank() == rank
+    cfg2 = LlamaConfig(vocab_size=160, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=4,
+                       num_key_value_heads=1, max_position_embeddings=128, attn_implementation="sdpa")
+    torch.manual_seed(0)
+    model2 = LlamaForCausalLM(cfg2)
+    assert model2.config._attn_implementation == "sdpa"
+    with torch.no_grad():
+        hidden2 = model2.model(input_ids=local["input_ids"], position_ids=local["position_ids"], use_cache=False).last_hidden_state
+    same = bool(torch.allclose(hidden2, hidden.detach(), rtol=1e-5, atol=1e-6)) and mpu.attention.calls >= 2
+    flag = torch.tensor([1.0 if same else 0.0])
+    dist.all_reduce(flag, op=dist.ReduceOp.MIN)
     if rank == 0:
         torch.save({"ref_loss": ref_loss.detach(), "loss": loss.detach(), "ref_grads": ref_grads, "grads": grads,
-                    "calls": fn.calls}, Path(out_dir) / "ulysses_hf.pt")
+                    "calls": fn.calls, "registered_by_name_matches": bool(flag.item())}, Path(out_dir) / "ulysses_hf.pt")
 
 
 def scenario_shim(out_dir):
