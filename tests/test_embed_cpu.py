@@ -2,7 +2,6 @@
 from pathlib import Path
 
 import numpy as np
-import pytest
 import torch
 import torch.nn.functional as F
 import yaml

@@ -2,9 +2,6 @@
 """Speculator data generation: prompt cutting, sharding, job scripts, the GPU-queue runner (with `echo` jobs on CPU),
 merging, and training on the merged dataset with ``process: false``."""
 import importlib.util
-import json
-import os
-import sys
 from pathlib import Path
 
 import pytest
