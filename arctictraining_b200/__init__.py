@@ -29,6 +29,7 @@ from .data.snowflake import SnowflakeDataSource
 from .data.source import DataSource
 from .data.synthetic import SyntheticDataSource
 from .logging import logger
+from .logging import setup_init_logger
 from .models.factory import HFModelFactory
 from .models.factory import LigerModelFactory
 from .models.factory import ModelFactory

@@ -55,6 +55,12 @@ def _default_setup() -> None:
 _default_setup()
 
 
+def setup_init_logger() -> None:
+    """(Re-)install the sink that is active before a recipe's ``logger:`` section has been read: standard error, level
+    from ``AT_LOG_LEVEL`` (INFO on rank 0, WARNING elsewhere)."""
+    _default_setup()
+
+
 def setup_logger(config: "LoggerConfig") -> None:
     """Install console and file sinks as the ``logger:`` section of a recipe asks.  Idempotent."""
     global _configured
