@@ -11,6 +11,8 @@ other architectures.  ``liger`` is kept as a recipe-compatible alias: the fused 
 
 from __future__ import annotations
 
+import os
+
 from abc import ABC
 from abc import abstractmethod
 from pathlib import Path
@@ -66,15 +68,18 @@ class ModelFactory(ABC, CallbackMixin, metaclass=RegistryMeta):
 
     @property
     def device(self):
-        return self.trainer.device
+        device = getattr(self.trainer, "device", None)
+        if device is None:  # a stand-in trainer object (tests, scripts that only build a model)
+            device = torch.device("cuda", torch.cuda.current_device()) if torch.cuda.is_available() else torch.device("cpu")
+        return device
 
     @property
     def world_size(self) -> int:
-        return self.trainer.world_size
+        return getattr(self.trainer, "world_size", int(os.getenv("WORLD_SIZE", 1)))
 
     @property
     def global_rank(self) -> int:
-        return self.trainer.global_rank
+        return getattr(self.trainer, "global_rank", int(os.getenv("RANK", 0)))
 
     @abstractmethod
     @callback_wrapper("create-config")

@@ -153,3 +153,20 @@ def test_every_shipped_recipe_validates(tmp_path, monkeypatch):
         cfg = get_config(path)
         assert cfg.type, path
         assert cfg.deepspeed["train_micro_batch_size_per_gpu"] == cfg.micro_batch_size, path
+
+
+def test_model_factory_works_with_a_stand_in_trainer():
+    """Pattern of the reference's tests/model/test_hf_factory.py: the factory is built around a plain namespace that
+    only carries the model config, and still creates the (LoRA-wrapped) model."""
+    from types import SimpleNamespace
+
+    from arctictraining_b200.config.model import ModelConfig
+
+    config = ModelConfig(type="huggingface", name_or_path="tiny-llama", dtype="fp32",
+                         peft_config={"peft_type": "Lora", "r": 4, "target_modules": ["q_proj", "k_proj", "v_proj", "o_proj"]})
+    assert config.peft_config_obj.r == 4
+    model = config.factory(SimpleNamespace(config=SimpleNamespace(model=config)))()
+    trainable = [n for n, p in model.named_parameters() if p.requires_grad]
+    assert trainable and all("lora_" in n for n in trainable)
+    with pytest.raises(ValueError):
+        ModelConfig(type="huggingface", name_or_path="tiny-llama", peft_config={"peft_type": "invalid"})
