@@ -12,7 +12,6 @@ other architectures.  ``liger`` is kept as a recipe-compatible alias: the fused 
 from __future__ import annotations
 
 import os
-
 from abc import ABC
 from abc import abstractmethod
 from pathlib import Path
