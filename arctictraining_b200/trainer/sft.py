@@ -77,6 +77,8 @@ class SFTTrainer(Trainer):
         from ..parallel.ulysses_hf import chunked_causal_lm_loss_sum
 
         model = self.model_unwrapped
+        if hasattr(model, "get_base_model"):  # an adapter wrapper of the peft package around the causal-LM model
+            model = model.get_base_model()
         body = getattr(model, getattr(model, "base_model_prefix", "model"), None)
         head = model.get_output_embeddings() if hasattr(model, "get_output_embeddings") else None
         if body is None or head is None:
