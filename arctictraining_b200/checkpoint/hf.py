@@ -102,6 +102,21 @@ class HFCheckpointEngine(CheckpointEngine):
             named = model.iter_full_named_parameters()  # every rank takes part in the gathers
         else:
             named = ((n, p.data) for n, p in module.named_parameters())
+        if type(module).__module__.split(".")[0] == "peft" and hasattr(module, "save_pretrained"):
+            # a transformers model wrapped by the peft package: that package writes its own layout, from the gathered
+            # trainable tensors (under ZeRO-3 the module's own state dict holds released, empty parameters)
+            trainable = {n for n, p in module.named_parameters() if p.requires_grad}
+            gathered = {n: t.detach().to("cpu").clone() for n, t in named if n in trainable}
+            if is_main:
+                module.save_pretrained(str(out_dir), state_dict=gathered, safe_serialization=True)
+                tok = getattr(self.trainer, "tokenizer", None)
+                if tok is not None and hasattr(tok, "save_pretrained"):
+                    tok.save_pretrained(out_dir)
+                logger.info(f"saved {len(gathered)} adapter tensors to {out_dir}")
+            from ..comm import dist as cdist
+
+            cdist.barrier()
+            return
         pairs = [(n, t.detach().to("cpu").clone()) for n, t in named if ".lora_A." in n or ".lora_B." in n]
         if is_main:
             n = save_adapter(out_dir, pairs, module, str(self.trainer.config.model.name_or_path))
