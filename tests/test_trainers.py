@@ -444,3 +444,34 @@ def test_trainers_without_sequence_parallel_support_refuse_the_setting(tiny_reci
 
     assert SFTTrainer.supports_sequence_parallel and CausalTrainer.supports_sequence_parallel
     assert not DPOTrainer.supports_sequence_parallel
+
+
+def test_export_of_a_package_wrapped_adapter_model_hands_gathered_tensors_to_its_writer(tmp_path):
+    """A transformers model wrapped by the adapter package is exported by that package's ``save_pretrained``; it gets
+    the trainable tensors as gathered by the engine, not the module's own (possibly released) parameters."""
+    from types import SimpleNamespace
+
+    from arctictraining_b200.checkpoint.hf import HFCheckpointEngine
+
+    calls = {}
+
+    class Wrapped(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.base = torch.nn.Linear(4, 4)
+            self.lora_A = torch.nn.Parameter(torch.ones(2, 4))
+            self.base.weight.requires_grad_(False)
+            self.base.bias.requires_grad_(False)
+
+        def save_pretrained(self, out_dir, state_dict=None, safe_serialization=True):
+            calls.update(out_dir=out_dir, names=sorted(state_dict), safe=safe_serialization,
+                         value=state_dict["lora_A"].clone())
+
+    Wrapped.__module__ = "peft.peft_model"
+    module = Wrapped()
+    engine_view = SimpleNamespace(module=module, iter_full_named_parameters=lambda: iter(
+        [("base.weight", module.base.weight.data), ("base.bias", module.base.bias.data), ("lora_A", torch.full((2, 4), 7.0))]))
+    fake_self = SimpleNamespace(trainer=SimpleNamespace(tokenizer=None, config=SimpleNamespace(model=SimpleNamespace(name_or_path="x"))))
+    HFCheckpointEngine._save_adapter(fake_self, engine_view, module, tmp_path / "out", True)
+    assert calls["names"] == ["lora_A"] and calls["safe"] is True and calls["out_dir"] == str(tmp_path / "out")
+    assert torch.all(calls["value"] == 7.0)  # the gathered tensor, not the module's parameter
