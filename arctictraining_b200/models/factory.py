@@ -176,4 +176,17 @@ class HFModelFactory(ModelFactory):
 
 
 class LigerModelFactory(HFModelFactory):
+    """Recipe name of the reference for "use the fused kernels".  Own architectures always do; a model of the
+    transformers library gets this package's RMSNorm kernel and the fused output-projection + cross-entropy loss."""
+
     name = "liger"
+
+    def create_model(self, model_config) -> torch.nn.Module:
+        model = super().create_model(model_config)
+        if type(model).__module__.startswith("transformers."):
+            from .hf_kernels import apply_kernels_to_hf_model
+
+            counts = apply_kernels_to_hf_model(model)
+            logger.info(f"library model: {counts['rms_norm']} RMSNorm modules on the own kernel, fused loss "
+                        f"{'on' if model._atb_fused_loss else 'off'}")
+        return model

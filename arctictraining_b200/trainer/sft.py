@@ -60,6 +60,8 @@ class SFTTrainer(Trainer):
                 raise ValueError("`shift_labels` is missing from the batch (is the dataloader wrapped for sequence parallelism?)")
         if sp > 1 and getattr(self, "hf_ulysses", None) is not None:
             return self._library_model_sp_loss(batch)
+        if sp == 1 and "labels" in batch and getattr(self.model_unwrapped, "_atb_fused_loss", False):
+            return self._library_model_fused_loss(batch)
         outputs = self.model(**batch, use_cache=False)
         if sp == 1:
             return outputs.loss
@@ -70,6 +72,20 @@ class SFTTrainer(Trainer):
             loss = loss + outputs.aux_loss
         return loss
 
+
+    def _library_model_fused_loss(self, batch: Dict[str, Any]) -> torch.Tensor:
+        """A ``transformers`` model created with ``model.type: liger``: hidden states from the model body, then the tiled
+        fused output projection + cross-entropy of this package (mean over target tokens, as the library computes)."""
+        from .. import ops
+
+        model = self.model_unwrapped
+        body = getattr(model, getattr(model, "base_model_prefix", "model"))
+        labels = batch.pop("labels")
+        shift_labels = torch.nn.functional.pad(labels[..., 1:], (0, 1), value=-100)
+        with self.model._timed("forward"), self.model.autocast():
+            hidden = body(**batch, use_cache=False).last_hidden_state
+            loss_sum, num_tokens = ops.fused_linear_cross_entropy(hidden, model.get_output_embeddings().weight, shift_labels)
+        return loss_sum / num_tokens.clamp(min=1)
 
     def _library_model_sp_loss(self, batch: Dict[str, Any]) -> torch.Tensor:
         """A ``transformers`` model under sequence parallelism: hidden states of this rank's slice from the model body,

@@ -475,3 +475,37 @@ def test_export_of_a_package_wrapped_adapter_model_hands_gathered_tensors_to_its
     HFCheckpointEngine._save_adapter(fake_self, engine_view, module, tmp_path / "out", True)
     assert calls["names"] == ["lora_A"] and calls["safe"] is True and calls["out_dir"] == str(tmp_path / "out")
     assert torch.all(calls["value"] == 7.0)  # the gathered tensor, not the module's parameter
+
+
+def test_liger_type_puts_own_ops_into_a_library_model_without_changing_the_numbers(tiny_recipe, tmp_path):
+    """``model.type: liger`` on a transformers architecture: RMSNorm modules call this package's op and the loss comes
+    from the fused output projection + cross-entropy; losses and updated weights equal the plain ``huggingface`` run."""
+    from transformers import Olmo2Config
+
+    from arctictraining_b200.config.trainer import get_config
+    from arctictraining_b200.registry import get_registered_trainer
+
+    arch = tmp_path / "tiny-olmo2"
+    Olmo2Config(vocab_size=1024, hidden_size=64, intermediate_size=128, num_hidden_layers=3, num_attention_heads=4,
+                num_key_value_heads=2, max_position_embeddings=256).save_pretrained(arch)
+
+    def run(kind):
+        r = tiny_recipe(exit_iteration=3,
+                        model={"type": kind, "name_or_path": str(arch), "dtype": "fp32", "attn_implementation": "sdpa",
+                               "hf_config_kwargs": {"num_hidden_layers": 2}},
+                        tokenizer={"type": "fake", "name_or_path": "tiny-llama"})
+        r["data"]["cache_dir"] = str(tmp_path / "cache")
+        r["train_log_metrics_path"] = str(tmp_path / f"{kind}.jsonl")
+        trainer = get_registered_trainer("sft")(get_config(r))
+        trainer.train()
+        losses = [json.loads(line)["loss"] for line in (tmp_path / f"{kind}.jsonl").read_text().splitlines() if line.strip()]
+        return trainer, losses, {n: t.clone() for n, t in trainer.model.iter_full_named_parameters()}
+
+    plain, plain_losses, plain_params = run("huggingface")
+    fused, fused_losses, fused_params = run("liger")
+    assert not getattr(plain.model_unwrapped, "_atb_fused_loss", False) and fused.model_unwrapped._atb_fused_loss
+    patched = [m for m in fused.model_unwrapped.modules() if getattr(m, "_atb_eps", None) is not None]
+    assert len(patched) >= 5  # two per layer and the final norm
+    assert fused_losses == pytest.approx(plain_losses, rel=1e-5)
+    for n, t in plain_params.items():
+        torch.testing.assert_close(fused_params[n], t, rtol=1e-4, atol=1e-6, msg=lambda m, n=n: f"{n}: {m}")
