@@ -93,6 +93,7 @@ class ModelFactory(ABC, CallbackMixin, metaclass=RegistryMeta):
 
 class HFModelFactory(ModelFactory):
     name = "huggingface"
+    library_kernels = False  # put this package's ops into a model that is built through the transformers library
     model_cls = None  # set lazily to CausalLM; subclasses override
 
     def create_config(self) -> ArchConfig:
@@ -148,7 +149,14 @@ class HFModelFactory(ModelFactory):
             model = AutoModelForCausalLM.from_pretrained(
                 self.config.name_or_path, config=hf_cfg, attn_implementation=attn, dtype=dtype
             )
-        return model.to(self.device)
+        model = model.to(self.device)
+        if self.library_kernels:
+            from .hf_kernels import apply_kernels_to_hf_model
+
+            counts = apply_kernels_to_hf_model(model)
+            logger.info(f"library model: {counts['rms_norm']} RMSNorm modules on the own kernel, fused loss "
+                        f"{'on' if model._atb_fused_loss else 'off'}")
+        return model
 
     def post_create_model_callback(self, model):
         if self.config.peft_config is not None:
@@ -180,13 +188,4 @@ class LigerModelFactory(HFModelFactory):
     transformers library gets this package's RMSNorm kernel and the fused output-projection + cross-entropy loss."""
 
     name = "liger"
-
-    def create_model(self, model_config) -> torch.nn.Module:
-        model = super().create_model(model_config)
-        if type(model).__module__.startswith("transformers."):
-            from .hf_kernels import apply_kernels_to_hf_model
-
-            counts = apply_kernels_to_hf_model(model)
-            logger.info(f"library model: {counts['rms_norm']} RMSNorm modules on the own kernel, fused loss "
-                        f"{'on' if model._atb_fused_loss else 'off'}")
-        return model
+    library_kernels = True

@@ -79,6 +79,8 @@ class SFTTrainer(Trainer):
         from .. import ops
 
         model = self.model_unwrapped
+        if hasattr(model, "get_base_model"):  # an adapter wrapper of the peft package around the causal-LM model
+            model = model.get_base_model()
         body = getattr(model, getattr(model, "base_model_prefix", "model"))
         labels = batch.pop("labels")
         shift_labels = torch.nn.functional.pad(labels[..., 1:], (0, 1), value=-100)
