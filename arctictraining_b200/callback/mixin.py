@@ -37,9 +37,19 @@ def callback_wrapper(name: str) -> Callable[[Callable], Callable]:
 
         @functools.wraps(method)
         def wrapper(self, *args, **kwargs):
-            args, kwargs = self._run_callbacks(f"pre-{name}", args, kwargs)
-            result = method(self, *args, **kwargs)
-            result, _ = self._run_callbacks(f"post-{name}", result, {})
+            # an override that calls ``super().<method>()`` enters the parent's wrapper while its own is running:
+            # the callbacks of the event belong to the outermost call only (otherwise a post-create-model callback
+            # such as the adapter wrapping would be applied twice)
+            running = self.__dict__.setdefault("_callback_events_running", set())
+            if name in running:
+                return method(self, *args, **kwargs)
+            running.add(name)
+            try:
+                args, kwargs = self._run_callbacks(f"pre-{name}", args, kwargs)
+                result = method(self, *args, **kwargs)
+                result, _ = self._run_callbacks(f"post-{name}", result, {})
+            finally:
+                running.discard(name)
             return result
 
         setattr(wrapper, WRAPPER_NAME_ATTR, name)

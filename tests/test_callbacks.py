@@ -148,3 +148,28 @@ def test_init_is_an_event():
 
     Thing(5)
     assert seen == [5]
+
+
+def test_callbacks_run_once_when_an_override_calls_super():
+    from arctictraining_b200.callback.mixin import CallbackMixin
+    from arctictraining_b200.callback.mixin import callback_wrapper
+
+    seen = []
+
+    class Base(CallbackMixin):
+        @callback_wrapper("make")
+        def make(self, x):
+            return x + 1
+
+        def post_make_callback(self, result):
+            seen.append(result)
+            return result * 10
+
+    class Child(Base):
+        def make(self, x):
+            return super().make(x) + 100  # the parent's wrapper must not run the callbacks a second time
+
+    assert Child().make(1) == 1020 and seen == [102]
+    assert Base().make(1) == 20
+    obj = Child()
+    assert obj.make(2) == 1030 and obj.make(2) == 1030  # the running-set is cleared after each call
